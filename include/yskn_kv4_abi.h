@@ -1,0 +1,131 @@
+/*
+ * C ABI of the B200 (sm_100a) KV4 attention path: quantize-and-append codec, split-K GQA
+ * flash-decode, split merge, multi-row verify, causal prefill, shard-triple merge.
+ *
+ * Conventions follow the reference's ABI (include/yskn_abi.h:19-20,31 and src/c_api.cpp:17-49):
+ * every entry returns int, 0 on success, -1 for a rejected argument (message via
+ * yskn_kv4_last_error(), thread-local), or a positive cudaError_t.  No C++ exception and no
+ * torch type crosses this boundary.  Entries taking `void* cuda_stream` only enqueue work:
+ * they never synchronise, allocate or read device memory on the host, so a caller may capture
+ * them into a CUDA graph exactly as the reference engine captures its passes
+ * (src/engine35.cpp:1973-1989).  All buffers are caller-owned device memory unless the entry
+ * name ends in `_host`.
+ *
+ * Argument structs are member-for-member the reference's launcher structs, so the engine can
+ * pass its own objects through a reinterpret_cast (file:line given at each struct).
+ */
+#ifndef YSKN_KV4_ABI_H
+#define YSKN_KV4_ABI_H
+#include <stddef.h>
+#include <stdint.h>
+#if defined(_WIN32)
+#  define YSKN_KV4_API __declspec(dllexport)
+#else
+#  define YSKN_KV4_API __attribute__((visibility("default")))
+#endif
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* yskn::KvLayer, src/post_kernels.hpp:7-15.  One layer's packed cache:
+ *   kq      u8  [Hkv][max_ctx/32][32][HD/2]   byte = channel 2j (low nibble) | channel 2j+1 (high)
+ *   kscale  f16 [Hkv][max_ctx/32][HD]          per channel, per 32-token group
+ *   kzero   f16 [Hkv][max_ctx/32][HD]
+ *   kshadow f16 [Hkv][max_ctx][HD]             every K row, un-rotated
+ *   vq      u8  [Hkv][max_ctx][HD/2]
+ *   vscale  f16 [Hkv][max_ctx]                 per token
+ *   vzero   f16 [Hkv][max_ctx]
+ * max_ctx is a multiple of 64 (src/loader.cpp:79).  Every array must be 16-byte aligned. */
+typedef struct yskn_kv_layer {
+  uint8_t*  kq;
+  uint16_t* kscale;
+  uint16_t* kzero;
+  uint16_t* kshadow;
+  uint8_t*  vq;
+  uint16_t* vscale;
+  uint16_t* vzero;
+} yskn_kv_layer;
+
+/* yskn::KvQuantArgs, src/post_kernels.hpp:26 */
+typedef struct yskn_kv_quant_args { yskn_kv_layer kv; const int* d_pos; int M; int max_ctx; } yskn_kv_quant_args;
+
+/* yskn::AttnGArgs, src/args.hpp:14-15.  q16 [M][nh][HD] already rotated; pm, pl [M][splits][nh];
+ * pacc [M][splits][nh][HD]; rope = (cos,sin) float pairs [max_ctx][rd/2]; *d_pos = position of
+ * row 0 (device scalar, so the launch does not depend on it). */
+typedef struct yskn_attn_g_args {
+  const uint16_t* q16; yskn_kv_layer kv; int max_ctx; int M; const int* d_pos; int splits;
+  float* pm; float* pl; float* pacc; const float* rope; int kvh; int nh; float qscale;
+} yskn_attn_g_args;
+
+/* yskn::AttnGCombineArgs, src/args.hpp:16-17.  bv [Hkv][HD] and gate [M][nh][HD] may be NULL. */
+typedef struct yskn_attn_g_combine_args {
+  const float* pm; const float* pl; const float* pacc; int splits; int M; const uint16_t* bv; uint16_t* o16;
+  const uint16_t* gate; int nh; int g;
+} yskn_attn_g_combine_args;
+
+/* Element type of activations handed in or out (q16, gate, o16, append rows). */
+enum { YSKN_KV4_F16 = 0, YSKN_KV4_BF16 = 1, YSKN_KV4_F32 = 2 };
+
+/* Input of the append step: the K and V branches of the reference's QKV epilogue
+ * (qkv_post_kernel, src/post_kernels.cu:48-82) with the GEMV un-mixing left to the caller.
+ * k_in, v_in: [M][kvh][hd] rows of `in_dtype`; K must be post-norm, PRE-RoPE. */
+typedef struct yskn_kv_append_args {
+  const void* k_in; const void* v_in; int in_dtype;
+  yskn_kv_layer kv; const int* d_pos; int M; int max_ctx; int kvh; int hd;
+} yskn_kv_append_args;
+
+YSKN_KV4_API const char* yskn_kv4_last_error(void);   /* yskn_last_error, include/yskn_abi.h:31 */
+YSKN_KV4_API const char* yskn_kv4_build_info(void);   /* yskn_build_info, src/c_api.cpp:55 */
+
+/* Kernel choice of yskn_kv4_attention / yskn_kv4_prefill: 0 = automatic (tensor-core kernels where they cover the
+ * shape, else the CUDA-core kernel), 1 = CUDA-core kernel only, 2 = tensor-core kernels only (unsupported shapes are
+ * rejected).  Process-wide; the counterpart of the reference's YSKN_ATTN_GENERIC switch (src/engine.cpp:189-193). */
+YSKN_KV4_API int yskn_kv4_set_algo(int algo);
+
+/* launch_rope_table_g, src/attention_gqa.cu:158-167. */
+YSKN_KV4_API int yskn_kv4_rope_table(float* d_out, int max_ctx, float theta, int rd, void* cuda_stream);
+
+/* K shadow store + per-token V int4 (src/post_kernels.cu:48-82) followed by the group quant of every
+ * 32-token K group completed by rows [*d_pos, *d_pos+M) (launch_kv_group_quant_g, src/attention_gqa.cu:182-187). */
+YSKN_KV4_API int yskn_kv4_append(const yskn_kv_append_args* a, void* cuda_stream);
+
+/* launch_kv_group_quant_g, src/attention_gqa.cu:182-187 (and launch_kv_group_quant, src/post_kernels.cu:86-96). */
+YSKN_KV4_API int yskn_kv4_group_quant(const yskn_kv_quant_args* a, int kvh, int hd, void* cuda_stream);
+
+/* launch_attention_gqa, src/attention_gqa.cu:168-175 (and launch_attention, src/attention_kv4q.cu:461-468):
+ * split-K partials (pm, pl, pacc) for rows 0..M-1, row r at position *d_pos + r seeing keys 0..*d_pos+r.
+ * act_dtype = element type of q16 (YSKN_KV4_F16 as in the reference, or YSKN_KV4_BF16).
+ * Every one of the `splits` partial slots of every (row, head) is written; unused ones carry pm = -1e30. */
+YSKN_KV4_API int yskn_kv4_attention(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, void* cuda_stream);
+
+/* launch_attn_combine_gqa_xform, src/attention_gqa.cu:123-134,176-181, up to and including the o16 store
+ * (the sign/FWHT/int8 preparation of the next GEMV input is the caller's). act_dtype applies to o16 and gate. */
+YSKN_KV4_API int yskn_kv4_combine(const yskn_attn_g_combine_args* a, int hd, int act_dtype, void* cuda_stream);
+
+/* launch_attention_prefill, src/attention_kv4q.cu:381-453: attention of M new rows whose K/V are already
+ * appended, merged in one call to o16 (+ optional bias bv).  `a->pm/pl/pacc` must hold `splits` slots per
+ * (row, head) as for yskn_kv4_attention. */
+YSKN_KV4_API int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype,
+                                  const uint16_t* bv, uint16_t* o16, void* cuda_stream);
+
+/* Sequence-sharded decode (no reference counterpart: the reference is single-GPU, README.md:37).
+ * yskn_kv4_local_triple folds the `splits` partials of each (row, head) into one un-normalised
+ * (m, l, O[HD]) triple, float [M][nh][HD+2]; yskn_kv4_merge_triples merges `ranks` gathered triples
+ * [ranks][M][nh][HD+2] into o16 with the same arithmetic as yskn_kv4_combine. */
+YSKN_KV4_API int yskn_kv4_local_triple(const yskn_attn_g_combine_args* a, int hd, float* d_triple, void* cuda_stream);
+YSKN_KV4_API int yskn_kv4_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd,
+                                        const uint16_t* bv, const uint16_t* gate, uint16_t* o16, int act_dtype,
+                                        void* cuda_stream);
+
+/* Host-pointer probe in the style of the reference's kernel probes (yskn_atxpk_bench, src/kvx_probe.cu:190-330):
+ * uploads a packed cache and M query rows, runs attention + combine `reps` times on the current device,
+ * downloads o16 and, if ms_out != NULL, the per-repetition device times in milliseconds (ms_out[reps]).
+ * Returns 0, -1 (bad argument) or a cudaError_t.  Allocates and frees its own device memory. */
+YSKN_KV4_API int yskn_kv4_attention_host(const uint16_t* h_q16, const yskn_kv_layer* h_kv, int max_ctx, int M, int pos0,
+                                         int splits, const float* h_rope, int kvh, int nh, int hd, int rd, float qscale,
+                                         int act_dtype, uint16_t* h_o16, int reps, float* ms_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

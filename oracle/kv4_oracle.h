@@ -1,0 +1,86 @@
+/*
+ * CPU oracle for the KV4 attention path -- TEST INFRASTRUCTURE, NOT PRODUCT.
+ *
+ * A scalar C restatement of the reference's Family-A ("KV4") algorithm: the
+ * quantize-and-append codec, the packed-cache layout, the dequantisation rule,
+ * RoPE-on-read, split-K online softmax and the split merge.  Only tests, the
+ * smoke check and the bench's CPU-baseline leg may call into this library; the
+ * product library never links or loads it.
+ *
+ * Pinning: the reference ships no golden vectors or known-answer tests for this
+ * path, so the restatement is pinned against the reference's own CUDA kernels
+ * compiled from its sources (oracle/_ref, run on a GPU box) and against the
+ * committed known-answer files under tests/golden/ that this oracle produced.
+ *
+ * Citations are file:line inside the reference project.
+ */
+#ifndef YSKN_KV4_ORACLE_H
+#define YSKN_KV4_ORACLE_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Packed cache of one layer; same member order as the reference's KvLayer
+ * (src/post_kernels.hpp:7-15).  Shapes (src/attention_gqa.cu:40-49,153):
+ *   kq      u8   [Hkv][max_ctx/32][32][HD/2]  byte = ch 2j low nibble, 2j+1 high
+ *   kscale  f16  [Hkv][max_ctx/32][HD]
+ *   kzero   f16  [Hkv][max_ctx/32][HD]
+ *   kshadow f16  [Hkv][max_ctx][HD]           every token, un-rotated
+ *   vq      u8   [Hkv][max_ctx][HD/2]
+ *   vscale  f16  [Hkv][max_ctx]
+ *   vzero   f16  [Hkv][max_ctx]                                              */
+typedef struct ysko_kv_layer {
+  uint8_t* kq; uint16_t* kscale; uint16_t* kzero; uint16_t* kshadow;
+  uint8_t* vq; uint16_t* vscale; uint16_t* vzero;
+} ysko_kv_layer;
+
+/* scalar conversions (IEEE, round-to-nearest-even) */
+uint16_t ysko_f32_to_f16(float f);
+float    ysko_f16_to_f32(uint16_t h);
+uint16_t ysko_f32_to_bf16(float f);
+float    ysko_bf16_to_f32(uint16_t h);
+void     ysko_bf16_to_f16_array(const uint16_t* in, uint16_t* out, size_t n);
+
+/* (cos,sin) table [max_ctx][rd/2][2], angle = float(t) * theta^(-2i/rd)
+ * (src/attention_gqa.cu:158-162). */
+void ysko_rope_table(float* out, int max_ctx, float theta, int rd);
+
+/* Append M rows at positions [pos0, pos0+M): K row -> fp16 shadow
+ * (src/post_kernels.cu:52-54), V row -> per-token int4 (src/post_kernels.cu:64-82),
+ * then quantise every 32-token K group whose last token lies in the pass
+ * (src/attention_gqa.cu:143-154).  k16/v16 are fp16 [M][Hkv][HD]. */
+void ysko_append(const ysko_kv_layer* kv, int hkv, int hd, int max_ctx, int pos0, int M,
+                 const uint16_t* k16, const uint16_t* v16);
+/* Only the group-quant step (src/attention_gqa.cu:143-154). */
+void ysko_group_quant(const ysko_kv_layer* kv, int hkv, int hd, int max_ctx, int pos0, int M);
+
+/* Reference-literal split-K partials (src/attention_gqa.cu:17-118): row r has
+ * pos = pos0 + r, len = pos + 1, per = ceil(len/S), keys [s*per, min(len,(s+1)*per)).
+ * pm, pl: [M][S][Hq]; pacc: [M][S][Hq][HD].  rope may be NULL when rd == 0. */
+void ysko_attention_partials(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
+                             int S, float* pm, float* pl, float* pacc, const float* rope,
+                             int hkv, int hq, int hd, int rd, float qscale, int threads);
+/* Split merge -> fp16 (src/attention_gqa.cu:127-134): optional V bias bv [Hkv][HD]
+ * and sigmoid gate [M][Hq][HD], both fp16. */
+void ysko_combine(const float* pm, const float* pl, const float* pacc, int S, int M, int hq, int g, int hd,
+                  const uint16_t* bv, const uint16_t* gate, uint16_t* o16);
+
+/* Tolerance oracle: softmax over the dequantised cache with double accumulators,
+ * no splits; row r sees keys 0..pos0+r with the own-group-from-shadow rule
+ * (src/attention_gqa.cu:24,38-43,55-70).  out: float [M][Hq][HD] (no bias/gate).
+ * row_begin/row_end select a subset of rows (others left untouched). */
+void ysko_attention_exact(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
+                          const float* rope, int hkv, int hq, int hd, int rd, float qscale,
+                          float* out, int row_begin, int row_end, int threads);
+
+/* Merge of R (m, l, O) triples per head, as exchanged between sequence shards:
+ * parts [R][Hq][HD+2] = {m, l, O[HD]} un-normalised; out float [Hq][HD]. */
+void ysko_merge_triples(const float* parts, int R, int hq, int hd, float* out);
+
+int ysko_max_threads(void);
+#ifdef __cplusplus
+}
+#endif
+#endif

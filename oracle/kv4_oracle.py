@@ -1,0 +1,148 @@
+"""ctypes binding of the CPU oracle (oracle/kv4_oracle.c) over numpy arrays.
+
+TEST INFRASTRUCTURE, NOT PRODUCT: only tests/, the smoke check and the bench's
+CPU-baseline leg import this module.  The product package never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle (and, if the reference tree is mounted, oracle/_ref)."""
+    so = os.path.join(_HERE, "libkv4_oracle.so")
+    src = os.path.join(_HERE, "kv4_oracle.c")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "libkv4_oracle.so"], check=True, capture_output=True)
+    return so
+
+
+class _Layer(C.Structure):
+    _fields_ = [("kq", C.c_void_p), ("kscale", C.c_void_p), ("kzero", C.c_void_p), ("kshadow", C.c_void_p),
+                ("vq", C.c_void_p), ("vscale", C.c_void_p), ("vzero", C.c_void_p)]
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        L = C.CDLL(build())
+        L.ysko_f32_to_f16.restype = C.c_uint16
+        L.ysko_f32_to_f16.argtypes = [C.c_float]
+        L.ysko_f16_to_f32.restype = C.c_float
+        L.ysko_f16_to_f32.argtypes = [C.c_uint16]
+        L.ysko_max_threads.restype = C.c_int
+        _LIB = L
+    return _LIB
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class KvCache:
+    """Packed KV4 cache of one layer in the reference's layout (numpy, host)."""
+
+    def __init__(self, hkv: int, hd: int, max_ctx: int):
+        assert max_ctx % 64 == 0 and hd % 32 == 0
+        self.hkv, self.hd, self.max_ctx = hkv, hd, max_ctx
+        ng = max_ctx // 32
+        self.kq = np.zeros((hkv, ng, 32, hd // 2), np.uint8)
+        self.kscale = np.zeros((hkv, ng, hd), np.uint16)
+        self.kzero = np.zeros((hkv, ng, hd), np.uint16)
+        self.kshadow = np.zeros((hkv, max_ctx, hd), np.uint16)
+        self.vq = np.zeros((hkv, max_ctx, hd // 2), np.uint8)
+        self.vscale = np.zeros((hkv, max_ctx), np.uint16)
+        self.vzero = np.zeros((hkv, max_ctx), np.uint16)
+
+    NAMES = ("kq", "kscale", "kzero", "kshadow", "vq", "vscale", "vzero")
+
+    def arrays(self):
+        return {n: getattr(self, n) for n in self.NAMES}
+
+    def struct(self):
+        return _Layer(*[_p(getattr(self, n)) for n in self.NAMES])
+
+
+def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:
+    return np.asarray(x, np.float32).astype(np.float16).view(np.uint16)
+
+
+def bf16_bits_to_f16_bits(b: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(b, np.uint16)
+    out = np.empty_like(b)
+    lib().ysko_bf16_to_f16_array(_p(b), _p(out), C.c_size_t(b.size))
+    return out
+
+
+def rope_table(max_ctx: int, theta: float, rd: int) -> np.ndarray:
+    out = np.zeros((max_ctx, rd // 2, 2), np.float32)
+    lib().ysko_rope_table(_p(out), max_ctx, C.c_float(theta), rd)
+    return out
+
+
+def append(kv: KvCache, pos0: int, k16: np.ndarray, v16: np.ndarray) -> None:
+    """k16, v16: uint16 fp16 bits [M][Hkv][HD]."""
+    k16 = np.ascontiguousarray(k16, np.uint16)
+    v16 = np.ascontiguousarray(v16, np.uint16)
+    M = k16.shape[0]
+    assert k16.shape == (M, kv.hkv, kv.hd) and v16.shape == k16.shape and pos0 + M <= kv.max_ctx
+    s = kv.struct()
+    lib().ysko_append(C.byref(s), kv.hkv, kv.hd, kv.max_ctx, pos0, M, _p(k16), _p(v16))
+
+
+def group_quant(kv: KvCache, pos0: int, M: int) -> None:
+    s = kv.struct()
+    lib().ysko_group_quant(C.byref(s), kv.hkv, kv.hd, kv.max_ctx, pos0, M)
+
+
+def attention_partials(q16, kv: KvCache, pos0: int, S: int, rope, hq: int, rd: int, qscale: float, threads: int = 0):
+    q16 = np.ascontiguousarray(q16, np.uint16)
+    M = q16.shape[0]
+    pm = np.zeros((M, S, hq), np.float32)
+    pl = np.zeros((M, S, hq), np.float32)
+    pacc = np.zeros((M, S, hq, kv.hd), np.float32)
+    s = kv.struct()
+    lib().ysko_attention_partials(_p(q16), C.byref(s), kv.max_ctx, M, pos0, S, _p(pm), _p(pl), _p(pacc), _p(rope),
+                                  kv.hkv, hq, kv.hd, rd, C.c_float(qscale), threads or lib().ysko_max_threads())
+    return pm, pl, pacc
+
+
+def combine(pm, pl, pacc, g: int, bv=None, gate=None) -> np.ndarray:
+    M, S, hq = pm.shape
+    hd = pacc.shape[-1]
+    o16 = np.zeros((M, hq, hd), np.uint16)
+    lib().ysko_combine(_p(np.ascontiguousarray(pm)), _p(np.ascontiguousarray(pl)), _p(np.ascontiguousarray(pacc)),
+                       S, M, hq, g, hd, _p(bv), _p(gate), _p(o16))
+    return o16
+
+
+def attention_exact(q16, kv: KvCache, pos0: int, rope, hq: int, rd: int, qscale: float,
+                    rows=None, threads: int = 0) -> np.ndarray:
+    """float32 [M][Hq][HD]; rows=(begin,end) restricts the computed rows (others stay 0)."""
+    q16 = np.ascontiguousarray(q16, np.uint16)
+    M = q16.shape[0]
+    out = np.zeros((M, hq, kv.hd), np.float32)
+    b, e = rows if rows is not None else (0, M)
+    s = kv.struct()
+    lib().ysko_attention_exact(_p(q16), C.byref(s), kv.max_ctx, M, pos0, _p(rope), kv.hkv, hq, kv.hd, rd,
+                               C.c_float(qscale), _p(out), b, e, threads or lib().ysko_max_threads())
+    return out
+
+
+def merge_triples(parts: np.ndarray) -> np.ndarray:
+    parts = np.ascontiguousarray(parts, np.float32)
+    R, hq, w = parts.shape
+    out = np.zeros((hq, w - 2), np.float32)
+    lib().ysko_merge_triples(_p(parts), R, hq, w - 2, _p(out))
+    return out
+
+
+def max_threads() -> int:
+    return int(lib().ysko_max_threads())

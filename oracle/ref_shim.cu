@@ -1,0 +1,60 @@
+// TEST INFRASTRUCTURE, NOT PRODUCT.
+// C entry points around the reference's own Family-A launchers, compiled together with
+// the reference's source files where they lie (see oracle/Makefile target `ref`).  The
+// resulting library pins the CPU oracle against the reference itself on a GPU and gives
+// the reference kernels' timings on the same inputs.  It contains no product code and the
+// product never loads it.
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <stdexcept>
+#include "args.hpp"          // reference: src/args.hpp (AttnGArgs, AttnGCombineArgs)
+#include "post_kernels.hpp"  // reference: src/post_kernels.hpp (KvLayer, KvQuantArgs)
+
+namespace yskn {
+// The reference defines this in engine.cpp (not compiled here); plain launches are enough.
+bool pdl_enabled() { return false; }
+}
+
+namespace {
+yskn::KvLayer mk(uint8_t* kq, uint16_t* ks, uint16_t* kz, uint16_t* ksh, uint8_t* vq, uint16_t* vs, uint16_t* vz) {
+  yskn::KvLayer L; L.kq = kq; L.kscale = ks; L.kzero = kz; L.kshadow = ksh; L.vq = vq; L.vscale = vs; L.vzero = vz; return L;
+}
+int finish() { return (int)cudaGetLastError(); }
+}
+
+extern "C" {
+
+int yref_rope_table_g(float* out, int max_ctx, float theta, int rd, void* st) {
+  yskn::launch_rope_table_g(reinterpret_cast<float2*>(out), max_ctx, theta, rd, (cudaStream_t)st); return finish();
+}
+
+// src/attention_gqa.cu:182-187 (hd 128 or 256)
+int yref_kv_group_quant_g(uint8_t* kq, uint16_t* ks, uint16_t* kz, uint16_t* ksh, uint8_t* vq, uint16_t* vs, uint16_t* vz,
+                          const int* d_pos, int M, int max_ctx, int kvh, int hd, void* st) {
+  yskn::KvQuantArgs A; A.kv = mk(kq, ks, kz, ksh, vq, vs, vz); A.d_pos = d_pos; A.M = M; A.max_ctx = max_ctx;
+  try { yskn::launch_kv_group_quant_g(A, kvh, hd, (cudaStream_t)st); } catch (const std::exception&) { return -1; }
+  return finish();
+}
+
+// src/attention_gqa.cu:168-175; only (g7,hd128,rd128) and (g6,hd256,rd64) exist there.
+int yref_attention_gqa(const uint16_t* q16, uint8_t* kq, uint16_t* ks, uint16_t* kz, uint16_t* ksh, uint8_t* vq, uint16_t* vs,
+                       uint16_t* vz, int max_ctx, int M, const int* d_pos, int splits, float* pm, float* pl, float* pacc,
+                       const float* rope, int kvh, int nh, float qscale, int g, int hd, int rd, void* st) {
+  yskn::AttnGArgs A; A.q16 = q16; A.kv = mk(kq, ks, kz, ksh, vq, vs, vz); A.max_ctx = max_ctx; A.M = M; A.d_pos = d_pos;
+  A.splits = splits; A.pm = pm; A.pl = pl; A.pacc = pacc; A.rope = reinterpret_cast<const float2*>(rope);
+  A.kvh = kvh; A.nh = nh; A.qscale = qscale;
+  try { yskn::launch_attention_gqa(A, g, hd, rd, (cudaStream_t)st); } catch (const std::exception&) { return -1; }
+  return finish();
+}
+
+// src/attention_gqa.cu:176-181; signs/qx/alpha feed the next GEMV and are required by the kernel.
+int yref_attn_combine_gqa_xform(const float* pm, const float* pl, const float* pacc, int splits, int M, const uint16_t* bv,
+                                uint16_t* o16, const uint16_t* gate, int nh, int g, int hd, const int8_t* signs, int8_t* qx,
+                                float* alpha, void* st) {
+  yskn::AttnGCombineArgs A; A.pm = pm; A.pl = pl; A.pacc = pacc; A.splits = splits; A.M = M; A.bv = bv; A.o16 = o16;
+  A.gate = gate; A.nh = nh; A.g = g;
+  try { yskn::launch_attn_combine_gqa_xform(A, hd, signs, qx, alpha, (cudaStream_t)st); } catch (const std::exception&) { return -1; }
+  return finish();
+}
+
+}  // extern "C"

@@ -1,0 +1,89 @@
+"""ctypes view of libyskn_kv4.so: the structs and prototypes of include/yskn_kv4_abi.h.
+
+There is no fallback: if the library is missing or an entry fails, callers get an exception.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+F16, BF16, F32 = 0, 1, 2
+ALGO_AUTO, ALGO_SCALAR, ALGO_MMA = 0, 1, 2
+
+
+class KvLayerC(C.Structure):          # yskn_kv_layer
+    _fields_ = [("kq", C.c_void_p), ("kscale", C.c_void_p), ("kzero", C.c_void_p), ("kshadow", C.c_void_p),
+                ("vq", C.c_void_p), ("vscale", C.c_void_p), ("vzero", C.c_void_p)]
+
+
+class KvQuantArgsC(C.Structure):      # yskn_kv_quant_args
+    _fields_ = [("kv", KvLayerC), ("d_pos", C.c_void_p), ("M", C.c_int), ("max_ctx", C.c_int)]
+
+
+class AttnGArgsC(C.Structure):        # yskn_attn_g_args
+    _fields_ = [("q16", C.c_void_p), ("kv", KvLayerC), ("max_ctx", C.c_int), ("M", C.c_int), ("d_pos", C.c_void_p),
+                ("splits", C.c_int), ("pm", C.c_void_p), ("pl", C.c_void_p), ("pacc", C.c_void_p), ("rope", C.c_void_p),
+                ("kvh", C.c_int), ("nh", C.c_int), ("qscale", C.c_float)]
+
+
+class AttnGCombineArgsC(C.Structure):  # yskn_attn_g_combine_args
+    _fields_ = [("pm", C.c_void_p), ("pl", C.c_void_p), ("pacc", C.c_void_p), ("splits", C.c_int), ("M", C.c_int),
+                ("bv", C.c_void_p), ("o16", C.c_void_p), ("gate", C.c_void_p), ("nh", C.c_int), ("g", C.c_int)]
+
+
+class KvAppendArgsC(C.Structure):     # yskn_kv_append_args
+    _fields_ = [("k_in", C.c_void_p), ("v_in", C.c_void_p), ("in_dtype", C.c_int), ("kv", KvLayerC),
+                ("d_pos", C.c_void_p), ("M", C.c_int), ("max_ctx", C.c_int), ("kvh", C.c_int), ("hd", C.c_int)]
+
+
+# name -> (restype, argtypes); every symbol include/yskn_kv4_abi.h declares
+PROTOTYPES = {
+    "yskn_kv4_last_error": (C.c_char_p, []),
+    "yskn_kv4_build_info": (C.c_char_p, []),
+    "yskn_kv4_set_algo": (C.c_int, [C.c_int]),
+    "yskn_kv4_rope_table": (C.c_int, [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "yskn_kv4_append": (C.c_int, [C.POINTER(KvAppendArgsC), C.c_void_p]),
+    "yskn_kv4_group_quant": (C.c_int, [C.POINTER(KvQuantArgsC), C.c_int, C.c_int, C.c_void_p]),
+    "yskn_kv4_attention": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "yskn_kv4_combine": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_int, C.c_void_p]),
+    "yskn_kv4_prefill": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "yskn_kv4_local_triple": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_void_p, C.c_void_p]),
+    "yskn_kv4_merge_triples": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.c_int, C.c_void_p]),
+    "yskn_kv4_attention_host": (C.c_int, [C.c_void_p, C.POINTER(KvLayerC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                          C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_int,
+                                          C.c_void_p]),
+}
+
+_LIB = None
+
+
+class Kv4Error(RuntimeError):
+    pass
+
+
+def lib_path() -> str:
+    return _build.LIB
+
+
+def load():
+    """Load the CUDA library (building it first if sources are newer). Raises if that is impossible."""
+    global _LIB
+    if _LIB is None:
+        path = _build.LIB
+        if not os.path.exists(path) or os.environ.get("YSKN_KV4_REBUILD"):
+            path = _build.build()
+        L = C.CDLL(path)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(L, name)          # AttributeError here = header and library disagree
+            fn.restype, fn.argtypes = res, args
+        _LIB = L
+    return _LIB
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load().yskn_kv4_last_error().decode(errors="replace")
+        raise Kv4Error(f"{what} failed (code {rc}): {msg}")

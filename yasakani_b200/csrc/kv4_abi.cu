@@ -1,0 +1,148 @@
+// extern "C" surface of the KV4 attention library: argument checks, kernel selection, error text.
+// Entry points mirror the reference's launcher set (see include/yskn_kv4_abi.h for file:line of each).
+#include "kv4_common.cuh"
+#include <cstdarg>
+#include <cstring>
+#include <vector>
+
+#define KV4_STR2(x) #x
+#define KV4_STR(x) KV4_STR2(x)
+
+namespace kv4 {
+
+static thread_local char g_err[512] = "";
+static int g_algo = ALGO_AUTO;
+
+void set_error(const char* fmt, ...) {
+  va_list ap; va_start(ap, fmt); vsnprintf(g_err, sizeof(g_err), fmt, ap); va_end(ap);
+}
+
+static int check_attn(const yskn_attn_g_args* a, int g, int hd, const char* who) {
+  if (!a) KV4_REJECT("%s: null argument struct", who);
+  if (!a->q16 || !a->d_pos || !a->pm || !a->pl || !a->pacc) KV4_REJECT("%s: null buffer", who);
+  if (!a->kv.kq || !a->kv.kscale || !a->kv.kzero || !a->kv.kshadow || !a->kv.vq || !a->kv.vscale || !a->kv.vzero)
+    KV4_REJECT("%s: null cache array", who);
+  if (a->M <= 0 || a->splits <= 0 || a->kvh <= 0 || g <= 0 || a->nh != a->kvh * g)
+    KV4_REJECT("%s: bad shape (M %d, splits %d, kvh %d, nh %d, g %d)", who, a->M, a->splits, a->kvh, a->nh, g);
+  if (a->max_ctx <= 0 || a->max_ctx % 64) KV4_REJECT("%s: max_ctx %d is not a positive multiple of 64", who, a->max_ctx);
+  if (a->splits > 65535 || a->M > 65535) KV4_REJECT("%s: splits %d / M %d exceed the grid limit", who, a->splits, a->M);
+  (void)hd; return 0;
+}
+
+static int attention_dispatch(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, cudaStream_t st) {
+  if (act_dtype != YSKN_KV4_F16 && act_dtype != YSKN_KV4_BF16) KV4_REJECT("yskn_kv4_attention: act_dtype must be F16 or BF16");
+  if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_attention: rotary width %d needs a rope table", rd);
+  const bool mma_ok = decode_mma_supports(g, hd, rd, a->M);
+  if (g_algo == ALGO_MMA && !mma_ok) KV4_REJECT("yskn_kv4_attention: tensor-core path does not cover (g %d, hd %d, rd %d, M %d)", g, hd, rd, a->M);
+  if (mma_ok && g_algo != ALGO_SCALAR) return launch_decode_mma(*a, g, hd, rd, act_dtype, st);
+  return launch_attention_scalar(*a, g, hd, rd, act_dtype, st);
+}
+
+}  // namespace kv4
+
+using namespace kv4;
+
+extern "C" {
+
+const char* yskn_kv4_last_error(void) { return g_err; }
+
+const char* yskn_kv4_build_info(void) {
+  return "yskn-kv4 b200 (sm_100a) cudart " KV4_STR(CUDART_VERSION);
+}
+
+int yskn_kv4_set_algo(int algo) {
+  if (algo < ALGO_AUTO || algo > ALGO_MMA) KV4_REJECT("yskn_kv4_set_algo: unknown algorithm %d", algo);
+  g_algo = algo; return 0;
+}
+
+int yskn_kv4_rope_table(float* d_out, int max_ctx, float theta, int rd, void* cuda_stream) {
+  return launch_rope_table(d_out, max_ctx, theta, rd, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_append(const yskn_kv_append_args* a, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_kv4_append: null argument struct");
+  if (!a->kv.kshadow || !a->kv.vq || !a->kv.vscale || !a->kv.vzero || !a->kv.kq || !a->kv.kscale || !a->kv.kzero)
+    KV4_REJECT("yskn_kv4_append: null cache array");
+  return launch_append(*a, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_group_quant(const yskn_kv_quant_args* a, int kvh, int hd, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_kv4_group_quant: null argument struct");
+  if (!a->kv.kshadow || !a->kv.kq || !a->kv.kscale || !a->kv.kzero) KV4_REJECT("yskn_kv4_group_quant: null cache array");
+  return launch_group_quant(*a, kvh, hd, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_attention(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, void* cuda_stream) {
+  if (int rc = check_attn(a, g, hd, "yskn_kv4_attention")) return rc;
+  return attention_dispatch(a, g, hd, rd, act_dtype, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_combine(const yskn_attn_g_combine_args* a, int hd, int act_dtype, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_kv4_combine: null argument struct");
+  return launch_combine(*a, hd, act_dtype, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, const uint16_t* bv, uint16_t* o16,
+                     void* cuda_stream) {
+  if (int rc = check_attn(a, g, hd, "yskn_kv4_prefill")) return rc;
+  if (!o16) KV4_REJECT("yskn_kv4_prefill: null output");
+  if (int rc = attention_dispatch(a, g, hd, rd, act_dtype, (cudaStream_t)cuda_stream)) return rc;
+  yskn_attn_g_combine_args c{a->pm, a->pl, a->pacc, a->splits, a->M, bv, o16, nullptr, a->nh, g};
+  return launch_combine(c, hd, act_dtype, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_local_triple(const yskn_attn_g_combine_args* a, int hd, float* d_triple, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_kv4_local_triple: null argument struct");
+  return launch_local_triple(*a, hd, d_triple, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd, const uint16_t* bv,
+                           const uint16_t* gate, uint16_t* o16, int act_dtype, void* cuda_stream) {
+  return launch_merge_triples(d_triples, ranks, M, nh, g, hd, bv, gate, o16, act_dtype, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_attention_host(const uint16_t* h_q16, const yskn_kv_layer* h_kv, int max_ctx, int M, int pos0, int splits,
+                            const float* h_rope, int kvh, int nh, int hd, int rd, float qscale, int act_dtype,
+                            uint16_t* h_o16, int reps, float* ms_out) {
+  if (!h_q16 || !h_kv || !h_o16) KV4_REJECT("yskn_kv4_attention_host: null buffer");
+  if (max_ctx <= 0 || max_ctx % 64 || M <= 0 || pos0 < 0 || pos0 + M > max_ctx || kvh <= 0 || nh % kvh || hd % 32 || reps <= 0 || splits <= 0)
+    KV4_REJECT("yskn_kv4_attention_host: bad shape");
+  if (rd > 0 && !h_rope) KV4_REJECT("yskn_kv4_attention_host: rotary width %d needs a rope table", rd);
+  const int g = nh / kvh; const size_t ng = (size_t)max_ctx / 32;
+  const size_t bytes[7] = {(size_t)kvh * ng * 32 * (hd / 2), (size_t)kvh * ng * hd * 2, (size_t)kvh * ng * hd * 2,
+                           (size_t)kvh * max_ctx * hd * 2, (size_t)kvh * max_ctx * (hd / 2), (size_t)kvh * max_ctx * 2,
+                           (size_t)kvh * max_ctx * 2};
+  const void* src[7] = {h_kv->kq, h_kv->kscale, h_kv->kzero, h_kv->kshadow, h_kv->vq, h_kv->vscale, h_kv->vzero};
+  std::vector<void*> dev;
+  auto cleanup = [&]() { for (void* p : dev) cudaFree(p); };
+  auto dalloc = [&](size_t n, const void* h) -> void* {
+    void* p = nullptr; if (cudaMalloc(&p, n ? n : 16) != cudaSuccess) return nullptr; dev.push_back(p);
+    if (h && cudaMemcpy(p, h, n, cudaMemcpyHostToDevice) != cudaSuccess) return nullptr; return p; };
+  void* d[7];
+  for (int i = 0; i < 7; ++i) { d[i] = dalloc(bytes[i], src[i]); if (!d[i]) { int e = (int)cudaGetLastError(); cleanup(); set_error("yskn_kv4_attention_host: device allocation or upload failed"); return e ? e : (int)cudaErrorMemoryAllocation; } }
+  const size_t nq = (size_t)M * nh * hd, np = (size_t)M * splits * nh;
+  void* dq = dalloc(nq * 2, h_q16); void* dpos = dalloc(4, &pos0);
+  void* drope = rd > 0 ? dalloc((size_t)max_ctx * (rd / 2) * 8, h_rope) : nullptr;
+  void* dpm = dalloc(np * 4, nullptr); void* dpl = dalloc(np * 4, nullptr); void* dpa = dalloc(np * hd * 4, nullptr);
+  void* dout = dalloc(nq * 2, nullptr);
+  if (!dq || !dpos || (rd > 0 && !drope) || !dpm || !dpl || !dpa || !dout) { cleanup(); set_error("yskn_kv4_attention_host: device allocation or upload failed"); return (int)cudaErrorMemoryAllocation; }
+  yskn_attn_g_args A{(const uint16_t*)dq, {(uint8_t*)d[0], (uint16_t*)d[1], (uint16_t*)d[2], (uint16_t*)d[3], (uint8_t*)d[4], (uint16_t*)d[5], (uint16_t*)d[6]},
+                     max_ctx, M, (const int*)dpos, splits, (float*)dpm, (float*)dpl, (float*)dpa, (const float*)drope, kvh, nh, qscale};
+  yskn_attn_g_combine_args Cb{(float*)dpm, (float*)dpl, (float*)dpa, splits, M, nullptr, (uint16_t*)dout, nullptr, nh, g};
+  cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
+  int rc = 0;
+  for (int i = 0; i < reps && !rc; ++i) {
+    cudaEventRecord(e0, 0);
+    rc = yskn_kv4_attention(&A, g, hd, rd, act_dtype, nullptr);
+    if (!rc) rc = yskn_kv4_combine(&Cb, hd, act_dtype, nullptr);
+    cudaEventRecord(e1, 0);
+    cudaError_t se = cudaEventSynchronize(e1);
+    if (!rc && se != cudaSuccess) { set_error("yskn_kv4_attention_host: %s", cudaGetErrorString(se)); rc = (int)se; }
+    if (!rc && ms_out) cudaEventElapsedTime(&ms_out[i], e0, e1);
+  }
+  if (!rc) { cudaError_t ce = cudaMemcpy(h_o16, dout, nq * 2, cudaMemcpyDeviceToHost); if (ce != cudaSuccess) { set_error("yskn_kv4_attention_host: download: %s", cudaGetErrorString(ce)); rc = (int)ce; } }
+  cudaEventDestroy(e0); cudaEventDestroy(e1); cleanup();
+  return rc;
+}
+
+}  // extern "C"

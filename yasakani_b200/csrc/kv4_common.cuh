@@ -1,0 +1,59 @@
+// Shared declarations of the KV4 attention library (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstdio>
+#include "../../include/yskn_kv4_abi.h"
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "this library is written for sm_100a (B200) only"
+#endif
+
+namespace kv4 {
+
+// ---- host-side error plumbing (thread-local message, like src/c_api.cpp:17) ----
+void set_error(const char* fmt, ...);
+#define KV4_REJECT(...) do { ::kv4::set_error(__VA_ARGS__); return -1; } while (0)
+#define KV4_CUDA(expr) do { cudaError_t e__ = (expr); if (e__ != cudaSuccess) { \
+    ::kv4::set_error("%s: %s", #expr, cudaGetErrorString(e__)); return (int)e__; } } while (0)
+inline int launch_status(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("%s: %s", what, cudaGetErrorString(e)); return (int)e; }
+  return 0;
+}
+
+// ---- device scalar helpers ----
+__device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+__device__ __forceinline__ uint16_t f2h(float f) { return __half_as_ushort(__float2half_rn(f)); }
+__device__ __forceinline__ float bf2f(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+__device__ __forceinline__ uint16_t f2bf(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+__device__ __forceinline__ float round_f16(float f) { return __half2float(__float2half_rn(f)); }
+
+// activation element (q16, gate, o16, append rows) -> float and back
+template <int DT> __device__ __forceinline__ float act_load(const void* p, size_t i) {
+  if (DT == YSKN_KV4_F16) return h2f(static_cast<const uint16_t*>(p)[i]);
+  if (DT == YSKN_KV4_BF16) return bf2f(static_cast<const uint16_t*>(p)[i]);
+  return static_cast<const float*>(p)[i];
+}
+template <int DT> __device__ __forceinline__ uint16_t act_store16(float v) {
+  return DT == YSKN_KV4_BF16 ? f2bf(v) : f2h(v);
+}
+
+// ---- launchers implemented in the .cu files (all enqueue-only) ----
+int launch_rope_table(float* d_out, int max_ctx, float theta, int rd, cudaStream_t st);
+int launch_append(const yskn_kv_append_args& a, cudaStream_t st);
+int launch_group_quant(const yskn_kv_quant_args& a, int kvh, int hd, cudaStream_t st);
+int launch_attention_scalar(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, cudaStream_t st);
+int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, cudaStream_t st);
+bool decode_mma_supports(int g, int hd, int rd, int M);
+int launch_combine(const yskn_attn_g_combine_args& a, int hd, int act_dtype, cudaStream_t st);
+int launch_local_triple(const yskn_attn_g_combine_args& a, int hd, float* d_triple, cudaStream_t st);
+int launch_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd, const uint16_t* bv,
+                         const uint16_t* gate, uint16_t* o16, int act_dtype, cudaStream_t st);
+
+// Which attention kernel yskn_kv4_attention picks; set through yskn_kv4_set_algo (tests compare paths).
+enum Algo { ALGO_AUTO = 0, ALGO_SCALAR = 1, ALGO_MMA = 2 };
+
+}  // namespace kv4

@@ -1,0 +1,167 @@
+"""Host-side mirror of the reference's Family-A operator interface over the C ABI.
+
+Function names and argument meaning follow the reference's launchers (src/args.hpp:14-21,
+src/post_kernels.hpp:26,39-41); tensors are torch CUDA tensors used purely as device memory, and
+every call is enqueue-only on torch's current stream.  All arithmetic happens in libyskn_kv4.so;
+there is no torch or CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+from ._lib import F16, BF16, F32, KvLayerC, KvQuantArgsC, AttnGArgsC, AttnGCombineArgsC, KvAppendArgsC, check
+
+_NAMES = ("kq", "kscale", "kzero", "kshadow", "vq", "vscale", "vzero")
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "device buffers must be contiguous CUDA tensors"
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream(stream):
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def _dtype_code(t) -> int:
+    if t.dtype in (torch.float16,):
+        return F16
+    if t.dtype == torch.bfloat16:
+        return BF16
+    if t.dtype == torch.float32:
+        return F32
+    raise TypeError(f"unsupported activation dtype {t.dtype}")
+
+
+class KvLayer:
+    """One layer's packed KV4 cache in the reference's layout (src/post_kernels.hpp:7-15), on one GPU."""
+
+    def __init__(self, hkv: int, hd: int, max_ctx: int, device="cuda"):
+        if max_ctx % 64 or hd not in (64, 128, 256):
+            raise ValueError("max_ctx must be a multiple of 64 and head_dim one of 64/128/256")
+        self.hkv, self.hd, self.max_ctx, self.device = hkv, hd, max_ctx, torch.device(device)
+        ng = max_ctx // 32
+        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=self.device)
+        self.kq = z((hkv, ng, 32, hd // 2), torch.uint8)
+        self.kscale = z((hkv, ng, hd), torch.float16)
+        self.kzero = z((hkv, ng, hd), torch.float16)
+        self.kshadow = z((hkv, max_ctx, hd), torch.float16)
+        self.vq = z((hkv, max_ctx, hd // 2), torch.uint8)
+        self.vscale = z((hkv, max_ctx), torch.float16)
+        self.vzero = z((hkv, max_ctx), torch.float16)
+
+    def struct(self) -> KvLayerC:
+        return KvLayerC(*[t.data_ptr() for t in self.tensors()])
+
+    def tensors(self):
+        return [getattr(self, n) for n in _NAMES]
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.tensors())
+
+    def to_numpy(self) -> dict:
+        """Raw bytes of each array (fp16 arrays as uint16 bit patterns), for bit-exact comparison."""
+        out = {}
+        for n in _NAMES:
+            t = getattr(self, n).cpu()
+            out[n] = t.view(torch.int16).numpy().view("uint16") if t.dtype == torch.float16 else t.numpy()
+        return out
+
+    def load_numpy(self, arrays: dict) -> "KvLayer":
+        import numpy as np
+        for n in _NAMES:
+            dst = getattr(self, n)
+            a = np.ascontiguousarray(arrays[n])
+            src = torch.from_numpy(a.view(np.int16)).view(torch.float16) if dst.dtype == torch.float16 else torch.from_numpy(a)
+            dst.copy_(src.reshape(dst.shape))
+        return self
+
+
+def build_info() -> str:
+    return _lib.load().yskn_kv4_build_info().decode()
+
+
+def set_algo(algo: int) -> None:
+    check(_lib.load().yskn_kv4_set_algo(int(algo)), "yskn_kv4_set_algo")
+
+
+def launch_rope_table_g(out: torch.Tensor, max_ctx: int, theta: float, rd: int, stream=None) -> None:
+    """(cos,sin) float pairs [max_ctx][rd/2]; reference: launch_rope_table_g (src/attention_gqa.cu:166)."""
+    assert out.dtype == torch.float32 and out.numel() >= max_ctx * rd
+    check(_lib.load().yskn_kv4_rope_table(_ptr(out), max_ctx, C.c_float(theta), rd, _stream(stream)), "yskn_kv4_rope_table")
+
+
+def launch_kv_append(kv: KvLayer, k_in: torch.Tensor, v_in: torch.Tensor, d_pos: torch.Tensor, M: int, stream=None) -> None:
+    """K/V branches of launch_qkv_post (src/post_kernels.cu:48-82) + launch_kv_group_quant_g."""
+    assert k_in.shape == v_in.shape and k_in.dtype == v_in.dtype and k_in.numel() == M * kv.hkv * kv.hd
+    a = KvAppendArgsC(k_in.data_ptr(), v_in.data_ptr(), _dtype_code(k_in), kv.struct(), d_pos.data_ptr(), M, kv.max_ctx, kv.hkv, kv.hd)
+    assert k_in.is_cuda and k_in.is_contiguous() and v_in.is_contiguous() and d_pos.dtype == torch.int32
+    check(_lib.load().yskn_kv4_append(C.byref(a), _stream(stream)), "yskn_kv4_append")
+
+
+def launch_kv_group_quant_g(kv: KvLayer, d_pos: torch.Tensor, M: int, stream=None) -> None:
+    """launch_kv_group_quant_g (src/attention_gqa.cu:182-187)."""
+    a = KvQuantArgsC(kv.struct(), d_pos.data_ptr(), M, kv.max_ctx)
+    check(_lib.load().yskn_kv4_group_quant(C.byref(a), kv.hkv, kv.hd, _stream(stream)), "yskn_kv4_group_quant")
+
+
+def attn_scratch(M: int, splits: int, nh: int, hd: int, device="cuda"):
+    """pm, pl [M][splits][nh] and pacc [M][splits][nh][hd], sized as the reference sizes them (src/engine.cpp:560-561)."""
+    pm = torch.empty((M, splits, nh), dtype=torch.float32, device=device)
+    pl = torch.empty((M, splits, nh), dtype=torch.float32, device=device)
+    pacc = torch.empty((M, splits, nh, hd), dtype=torch.float32, device=device)
+    return pm, pl, pacc
+
+
+def _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale) -> AttnGArgsC:
+    assert q16.is_cuda and q16.is_contiguous() and q16.numel() == M * nh * kv.hd
+    assert pm.numel() >= M * splits * nh and pacc.numel() >= M * splits * nh * kv.hd and d_pos.dtype == torch.int32
+    return AttnGArgsC(q16.data_ptr(), kv.struct(), kv.max_ctx, M, d_pos.data_ptr(), splits, pm.data_ptr(), pl.data_ptr(),
+                      pacc.data_ptr(), rope.data_ptr() if rope is not None else None, kv.hkv, nh, qscale)
+
+
+def launch_attention_gqa(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float,
+                         rd: int, stream=None) -> None:
+    """launch_attention_gqa (src/attention_gqa.cu:168-175): split-K partials for M rows."""
+    a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
+    check(_lib.load().yskn_kv4_attention(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), _stream(stream)), "yskn_kv4_attention")
+
+
+def launch_attn_combine_gqa(pm, pl, pacc, splits: int, M: int, o16, nh: int, g: int, bv=None, gate=None, stream=None) -> None:
+    """Merge half of launch_attn_combine_gqa_xform (src/attention_gqa.cu:123-134,176-181), up to the o16 store."""
+    hd = o16.numel() // (M * nh)
+    a = AttnGCombineArgsC(pm.data_ptr(), pl.data_ptr(), pacc.data_ptr(), splits, M, bv.data_ptr() if bv is not None else None,
+                          o16.data_ptr(), gate.data_ptr() if gate is not None else None, nh, g)
+    check(_lib.load().yskn_kv4_combine(C.byref(a), hd, _dtype_code(o16), _stream(stream)), "yskn_kv4_combine")
+
+
+def launch_attention_prefill(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float,
+                             rd: int, o16, bv=None, stream=None) -> None:
+    """launch_attention_prefill (src/attention_kv4q.cu:449-453): attention of M appended rows, merged to o16."""
+    a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
+    check(_lib.load().yskn_kv4_prefill(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), bv.data_ptr() if bv is not None else None,
+                                      _ptr(o16), _stream(stream)), "yskn_kv4_prefill")
+
+
+def launch_local_triple(pm, pl, pacc, splits: int, M: int, nh: int, hd: int, triple, stream=None) -> None:
+    """Fold one shard's partials into (m, l, O) per (row, head): float [M][nh][hd+2]."""
+    a = AttnGCombineArgsC(pm.data_ptr(), pl.data_ptr(), pacc.data_ptr(), splits, M, None, None, None, nh, 1)
+    check(_lib.load().yskn_kv4_local_triple(C.byref(a), hd, _ptr(triple), _stream(stream)), "yskn_kv4_local_triple")
+
+
+def launch_merge_triples(triples, ranks: int, M: int, nh: int, g: int, hd: int, o16, bv=None, gate=None, stream=None) -> None:
+    """Merge triples gathered from all shards, [ranks][M][nh][hd+2], into o16."""
+    check(_lib.load().yskn_kv4_merge_triples(_ptr(triples), ranks, M, nh, g, hd, bv.data_ptr() if bv is not None else None,
+                                            gate.data_ptr() if gate is not None else None, _ptr(o16), _dtype_code(o16),
+                                            _stream(stream)), "yskn_kv4_merge_triples")
+
+
+def default_qscale(hd: int) -> float:
+    return 1.0 / math.sqrt(hd)
