@@ -1,0 +1,335 @@
+#!/usr/bin/env python
+"""Benchmark of the KV4 decode-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--ctx 262144]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one decode step of one full-attention layer for one sequence: split-K attention of one query token
+(Hq 24 / Hkv 4 / head_dim 256) over a KV4 cache of `ctx` tokens, then the split merge to o16.  With N > 1
+the cache is sequence-sharded over the ranks and the step adds the one (m, l, O) all-gather (strong scaling:
+the total work is fixed).  Inputs are seeded synthetic rows (yasakani_b200/synth.py), quantised by the
+library's own codec.  Rank 0 prints one JSON line.
+
+--impl reference times the CPU restatement of the reference's algorithm (oracle/, test infrastructure) on the
+host cores: the reference has no CPU implementation of this path and its CUDA kernels are not a CPU arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from yasakani_b200 import synth  # noqa: E402
+
+CONFIG_INDEX = 3                    # BASELINE.json configs[3]: long-context single-sequence decode, 262,144 tokens
+CHUNK = 8192                        # rows generated, uploaded and appended per pass
+METRIC, UNIT = "kv4_decode_attn_tokens_per_s", "tokens/s"
+
+
+def chunk_rows(shape, c):
+    """Rows of global tokens [c*CHUNK, (c+1)*CHUNK): the same on every rank and in the CPU arm."""
+    return synth.make_kv(shape, CHUNK, synth.seed_for(CONFIG_INDEX, c))
+
+
+def workload_name(shape, ctx):
+    return f"C4 long-context decode: 1 query token, Hq{shape.hq}/Hkv{shape.hkv}/hd{shape.hd}, KV4 cache of {ctx} tokens"
+
+
+# ------------------------------------------------------------------------------------------ clocks
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True); self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+
+def cpu_decode_rate(shape, ctx, sample_ctx, steps, warmup, threads):
+    """Times the oracle's reference-literal decode (split-K partials + merge) over a cache of `sample_ctx` tokens and
+    scales the step time by ctx/sample_ctx (the work is linear in the number of keys)."""
+    from oracle import kv4_oracle as o
+    bits = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16)
+    max_ctx = ((sample_ctx + 63) // 64) * 64
+    kv = o.KvCache(shape.hkv, shape.hd, max_ctx)
+    for c in range((sample_ctx + CHUNK - 1) // CHUNK):
+        k, v = chunk_rows(shape, c)
+        n = min(CHUNK, sample_ctx - c * CHUNK)
+        o.append(kv, c * CHUNK, bits(k[:n]), bits(v[:n]))
+    rope = o.rope_table(max_ctx, shape.theta, shape.rd)
+    q16 = bits(synth.make_q(shape, 1, synth.seed_for(CONFIG_INDEX)))
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        pm, pl, pacc = o.attention_partials(q16, kv, sample_ctx - 1, 32, rope, shape.hq, shape.rd, shape.qscale, threads=threads)
+        o16 = o.combine(pm, pl, pacc, shape.g)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    step_s = float(np.mean(times)) * (ctx / sample_ctx)
+    return step_s, o16, (kv, rope, q16)
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the CPU restatement on all host threads; rank 0 only."""
+    if rank != 0:
+        return
+    from oracle import kv4_oracle as o
+    shape, ctx = synth.C2, args.ctx
+    threads = o.max_threads()
+    budget = max(0.05, min(2.0, 100.0 / (args.steps + args.warmup)))          # seconds of CPU work per step
+    probe_s, _, _ = cpu_decode_rate(shape, 4096, 4096, 1, 1, threads)         # seconds per step at 4,096 keys
+    sample_ctx = int(min(ctx, max(4096, (budget / probe_s * 4096) // 4096 * 4096)))
+    step_s, _, _ = cpu_decode_rate(shape, ctx, sample_ctx, args.steps, args.warmup, threads)
+    value = 1.0 / step_s
+    sample = f"each step = reference-literal decode over the first {sample_ctx} of {ctx} keys, time scaled by {ctx / sample_ctx:.1f}"
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "impl": "reference", "config": {"workload": workload_name(shape, ctx)},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------ our arm
+
+def peak_hbm():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from yasakani_b200 import kv4
+    from yasakani_b200.sharded import ShardedDecoder, gather_triples, plan_shards
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path for the product arm"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    shape, ctx, K, W = synth.C2, args.ctx, args.steps, args.warmup
+    max_ctx = ctx + 64
+    plan = plan_shards(ctx, world, rank, max_ctx)
+    splits = args.splits
+
+    rope = torch.empty((max_ctx, shape.rd // 2, 2), dtype=torch.float32, device=dev)
+    kv4.launch_rope_table_g(rope, max_ctx, shape.theta, shape.rd)
+
+    # ---- build this rank's shard with the library's own codec, then clone it so timed loops miss L2
+    first = ShardedDecoder(shape, plan, splits, rope)
+    lo, hi = plan.local_rows(0, ctx)
+    for c in range(lo // CHUNK, (hi + CHUNK - 1) // CHUNK if hi > lo else 0):
+        k, v = chunk_rows(shape, c)
+        first.append(k.to(dev), v.to(dev), c * CHUNK)
+    torch.cuda.synchronize()
+    shard_tokens = hi - lo
+    shard_bytes = shape.decode_bytes(shard_tokens)                 # algorithmic bytes one launch of the decode kernel reads
+    n_copies = max(2, int(math.ceil(256e6 / max(shard_bytes, 1))) + 1)
+    decs = [first]
+    for _ in range(n_copies - 1):
+        d = ShardedDecoder(shape, plan, splits, rope)
+        for a, b in zip(d.layer.tensors(), first.layer.tensors()):
+            a.copy_(b)
+        decs.append(d)
+    for d in decs:
+        d.d_pos.fill_(ctx - 1)                                      # the query is the last cached token: ctx keys visible
+    q_host = synth.make_q(shape, 1, synth.seed_for(CONFIG_INDEX)).pin_memory()
+    q_dev = q_host.to(dev)
+    o_host = torch.empty((1, shape.hq, shape.hd), dtype=torch.float16).pin_memory()
+
+    def step(d):
+        d.local_step(q_dev)
+        if world > 1:
+            gather_triples(d.mine, d.gathered)
+            d.merge()
+        else:
+            kv4.launch_attn_combine_gqa(d.pm, d.pl, d.pacc, splits, 1, d.o16, shape.hq, shape.g)
+
+    launches_per_step = 3 if world > 1 else 2
+
+    # one CUDA graph per cache copy: the step is launch-bound otherwise (a few 10 us of kernels)
+    side = torch.cuda.Stream(device=dev)
+    graphs = []
+    with torch.cuda.stream(side):
+        for d in decs:
+            step(d)                                                # warm up outside capture (module load, NCCL setup)
+        torch.cuda.synchronize()
+        for d in decs:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                step(d)
+            graphs.append(g)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(n):
+            fn(i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    sampler = ClockSampler(local_rank)
+    with sampler:
+        # ---- value: inputs resident in HBM, whole step (attention + merge [+ exchange])
+        timed(lambda i: graphs[i % n_copies].replay(), W)
+        ms_total = timed(lambda i: graphs[i % n_copies].replay(), K)
+        # ---- roofline: the decode-attention kernel alone, same stream, same copies
+        def attn_only(i):
+            d = decs[i % n_copies]
+            kv4.launch_attention_shard(q_dev, d.layer, 1, d.d_pos, splits, d.pm, d.pl, d.pacc, rope, shape.hq, shape.qscale, shape.rd,
+                                       plan.start, plan.capacity)
+        timed(attn_only, W)
+        ms_attn = timed(attn_only, K)
+        # ---- e2e: host buffers in, host buffer out, every step (q, and the new token's k/v on the owning rank)
+        k_new, v_new = chunk_rows(shape, (ctx - 1) // CHUNK)
+        kn_host = k_new[(ctx - 1) % CHUNK:(ctx - 1) % CHUNK + 1].contiguous().pin_memory()
+        vn_host = v_new[(ctx - 1) % CHUNK:(ctx - 1) % CHUNK + 1].contiguous().pin_memory()
+        kn_dev, vn_dev = kn_host.to(dev), vn_host.to(dev)
+
+        def e2e_step(i):
+            d = decs[i % n_copies]
+            q_dev.copy_(q_host, non_blocking=True)
+            if plan.is_last:
+                kn_dev.copy_(kn_host, non_blocking=True); vn_dev.copy_(vn_host, non_blocking=True)
+                d.append(kn_dev, vn_dev, ctx - 1)
+            graphs[i % n_copies].replay()
+            if rank == 0:
+                o_host.copy_(d.o16, non_blocking=True)
+            torch.cuda.current_stream().synchronize()               # the caller consumes o16 on the host
+
+        with torch.cuda.stream(side):
+            timed(e2e_step, W)
+            ms_e2e = timed(e2e_step, K)
+    clocks = sampler.summary()
+
+    peak, peak_kind = peak_hbm()
+    t_attn = ms_attn / K * 1e-3
+    achieved = shard_bytes / t_attn / 1e9
+    value = K / (ms_total * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": workload_name(shape, ctx), "splits": splits, "parallelism": f"sequence-sharded x{world}",
+                   "l2": f"{n_copies} distinct cache copies cycled; {shard_bytes / 1e6:.1f} MB read per launch (L2 is 126 MB)",
+                   "kv_tokens_scanned_per_s": ctx * value},
+        "clocks": clocks,
+        "e2e": {"value": K / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(q_host.numel() * 2 + (kn_host.numel() + vn_host.numel()) * 2),
+                "d2h_bytes_per_step": int(o_host.numel() * 2), "ms_per_step": ms_e2e / K},
+        "gpu_launches": launches_per_step * K,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": args.traffic,
+                     "kernel": "decode attention (split-K partials)", "us_per_launch": t_attn * 1e6, "bytes_per_launch": shard_bytes,
+                     "peak_kind": f"of {peak_kind}"},
+    }
+
+    # ---- CPU baseline beside it (rank 0, N = 1): the oracle on the host cores, bounded sample; doubles as a result check
+    if world == 1 and not args.no_cpu_baseline:
+        from oracle import kv4_oracle as o
+        threads = o.max_threads()
+        sample_ctx = min(ctx, args.cpu_sample_ctx)
+        step_s, o16_cpu, (okv, rope_np, q16) = cpu_decode_rate(shape, ctx, sample_ctx, 3, 1, threads)
+        line["cpu_baseline"] = {"value": 1.0 / step_s, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"3 reference-literal decode steps over the first {sample_ctx} of {ctx} keys, time scaled by {ctx / sample_ctx:.1f}"}
+        # check: the GPU path over the same sample prefix against the exact oracle
+        d = decs[0]
+        d.d_pos.fill_(sample_ctx - 1)
+        step(d)
+        torch.cuda.synchronize()
+        want = o.attention_exact(q16, okv, sample_ctx - 1, rope_np, shape.hq, shape.rd, shape.qscale)
+        err = np.abs(d.o16.float().cpu().numpy() - want)
+        line["check"] = {"max_abs_err_vs_oracle": float(err.max()), "ok": bool((err <= 2e-3 + 1e-2 * np.abs(want)).all())}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ctx", type=int, default=262144)
+    ap.add_argument("--splits", type=int, default=74)
+    ap.add_argument("--cpu-sample-ctx", type=int, default=32768)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch from an ncu capture, if known")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

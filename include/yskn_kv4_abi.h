@@ -109,9 +109,15 @@ YSKN_KV4_API int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int 
                                   const uint16_t* bv, uint16_t* o16, void* cuda_stream);
 
 /* Sequence-sharded decode (no reference counterpart: the reference is single-GPU, README.md:37).
+ * yskn_kv4_attention_shard is yskn_kv4_attention over a cache that holds only the global tokens
+ * [shard_start, shard_start + shard_len) (shard_start a multiple of 32; local token t = global t + shard_start):
+ * *d_pos stays the GLOBAL position of row 0, `a->rope` the full table, `a->max_ctx` the local capacity.  Keys outside
+ * the shard contribute nothing; a shard with no visible key writes pm = -1e30 in every slot.
  * yskn_kv4_local_triple folds the `splits` partials of each (row, head) into one un-normalised
  * (m, l, O[HD]) triple, float [M][nh][HD+2]; yskn_kv4_merge_triples merges `ranks` gathered triples
  * [ranks][M][nh][HD+2] into o16 with the same arithmetic as yskn_kv4_combine. */
+YSKN_KV4_API int yskn_kv4_attention_shard(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype,
+                                          int shard_start, int shard_len, void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_local_triple(const yskn_attn_g_combine_args* a, int hd, float* d_triple, void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd,
                                         const uint16_t* bv, const uint16_t* gate, uint16_t* o16, int act_dtype,

@@ -176,12 +176,25 @@ static void load_token(const ysko_kv_layer* kv, int max_ctx, int kvh, int hd, in
 void ysko_attention_partials(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
                              int S, float* pm, float* pl, float* pacc, const float* rope,
                              int hkv, int hq, int hd, int rd, float qscale, int threads) {
+  ysko_attention_partials_shard(q16, kv, max_ctx, M, pos0, S, pm, pl, pacc, rope, hkv, hq, hd, rd, qscale, threads, 0, max_ctx);
+}
+
+/* The same over a cache that holds only global tokens [shard_start, shard_start+shard_len): local token t is
+ * global token t + shard_start; pos0 stays global; rope is the full table.  No reference counterpart (the
+ * reference is single-GPU); with shard_start 0 and shard_len max_ctx it is the function above. */
+void ysko_attention_partials_shard(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
+                                   int S, float* pm, float* pl, float* pacc, const float* rope,
+                                   int hkv, int hq, int hd, int rd, float qscale, int threads,
+                                   int shard_start, int shard_len) {
   const int g = hq / hkv, jobs = M * hkv * S;
+  if (rope) rope += (size_t)shard_start * (rd / 2) * 2;
   if (threads < 1) threads = 1;
   #pragma omp parallel for schedule(dynamic, 1) num_threads(threads)
   for (int job = 0; job < jobs; ++job) {
     const int r = job / (hkv * S), kvh = (job / S) % hkv, split = job % S;
-    const int pos = pos0 + r, len = pos + 1, per = (len + S - 1) / S;
+    const int pos = pos0 + r - shard_start;
+    int len = pos + 1; if (len > shard_len) len = shard_len; if (len < 0) len = 0;
+    const int per = (len + S - 1) / S;
     const int t0 = split * per, t1 = (t0 + per < len) ? t0 + per : len;
     const int cur_group = pos / 32;
     float* kd = (float*)malloc(sizeof(float) * hd * 2); float* vd = kd + hd;

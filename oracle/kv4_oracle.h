@@ -62,6 +62,10 @@ void ysko_group_quant(const ysko_kv_layer* kv, int hkv, int hd, int max_ctx, int
 void ysko_attention_partials(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
                              int S, float* pm, float* pl, float* pacc, const float* rope,
                              int hkv, int hq, int hd, int rd, float qscale, int threads);
+void ysko_attention_partials_shard(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
+                                   int S, float* pm, float* pl, float* pacc, const float* rope,
+                                   int hkv, int hq, int hd, int rd, float qscale, int threads,
+                                   int shard_start, int shard_len);
 /* Split merge -> fp16 (src/attention_gqa.cu:127-134): optional V bias bv [Hkv][HD]
  * and sigmoid gate [M][Hq][HD], both fp16. */
 void ysko_combine(const float* pm, const float* pl, const float* pacc, int S, int M, int hq, int g, int hd,

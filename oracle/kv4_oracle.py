@@ -102,15 +102,17 @@ def group_quant(kv: KvCache, pos0: int, M: int) -> None:
     lib().ysko_group_quant(C.byref(s), kv.hkv, kv.hd, kv.max_ctx, pos0, M)
 
 
-def attention_partials(q16, kv: KvCache, pos0: int, S: int, rope, hq: int, rd: int, qscale: float, threads: int = 0):
+def attention_partials(q16, kv: KvCache, pos0: int, S: int, rope, hq: int, rd: int, qscale: float, threads: int = 0,
+                       shard_start: int = 0, shard_len: int | None = None):
     q16 = np.ascontiguousarray(q16, np.uint16)
     M = q16.shape[0]
     pm = np.zeros((M, S, hq), np.float32)
     pl = np.zeros((M, S, hq), np.float32)
     pacc = np.zeros((M, S, hq, kv.hd), np.float32)
     s = kv.struct()
-    lib().ysko_attention_partials(_p(q16), C.byref(s), kv.max_ctx, M, pos0, S, _p(pm), _p(pl), _p(pacc), _p(rope),
-                                  kv.hkv, hq, kv.hd, rd, C.c_float(qscale), threads or lib().ysko_max_threads())
+    lib().ysko_attention_partials_shard(_p(q16), C.byref(s), kv.max_ctx, M, pos0, S, _p(pm), _p(pl), _p(pacc), _p(rope),
+                                        kv.hkv, hq, kv.hd, rd, C.c_float(qscale), threads or lib().ysko_max_threads(),
+                                        shard_start, kv.max_ctx if shard_len is None else shard_len)
     return pm, pl, pacc
 
 

@@ -35,3 +35,32 @@ def assert_close(got: np.ndarray, want: np.ndarray, what: str, atol: float = ATO
     bad = err > (atol + rtol * np.abs(want))
     assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.size} outside atol {atol} rtol {rtol}; max abs err {err.max():.3e}"
     return float(err.max())
+
+
+# ---- GPU side (only used by -m gpu tests) ----
+
+def gpu_append_all(kv4, layer, k: torch.Tensor, v: torch.Tensor, passes, pos0: int = 0):
+    """Append host rows k, v [n][hkv][hd] to a device KvLayer in passes of the given sizes."""
+    dk, dv = k.cuda(), v.cuda()
+    d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    p = 0
+    for n in passes:
+        d_pos.fill_(pos0 + p)
+        kv4.launch_kv_append(layer, dk[p:p + n].contiguous(), dv[p:p + n].contiguous(), d_pos, int(n))
+        p += int(n)
+    torch.cuda.synchronize()
+    return p
+
+
+def gpu_attention(kv4, layer, q: torch.Tensor, pos0: int, splits: int, rope, shape, bv=None, gate=None):
+    """attention + combine through the C ABI; returns o16 as float32 numpy [M][hq][hd] and the raw partials."""
+    M = q.shape[0]
+    dq = q.cuda().contiguous()
+    d_pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    pm, pl, pacc = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
+    pm.fill_(float("nan")); pl.fill_(float("nan")); pacc.fill_(float("nan"))      # every slot must be written
+    kv4.launch_attention_gqa(dq, layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd)
+    o16 = torch.empty((M, shape.hq, shape.hd), dtype=q.dtype, device="cuda")
+    kv4.launch_attn_combine_gqa(pm, pl, pacc, splits, M, o16, shape.hq, shape.g, bv=bv, gate=gate)
+    torch.cuda.synchronize()
+    return o16.float().cpu().numpy(), (pm.cpu().numpy(), pl.cpu().numpy(), pacc.cpu().numpy())

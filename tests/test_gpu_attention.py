@@ -1,0 +1,158 @@
+"""GPU parity of KV4 attention (split-K partials + merge) through the C ABI against the CPU oracle.
+
+Bar: |got - want| <= 2e-3 + 1e-2*|want| against a double-accumulated softmax over the dequantised cache.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import ATOL, RTOL, assert_close, bits_f16, build_oracle_cache, f16_bits, gpu_append_all, gpu_attention
+from yasakani_b200 import synth, ALGO_AUTO, ALGO_SCALAR, ALGO_MMA
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _setup(oracle, shape, ctx, M, seed, chunk=None):
+    from yasakani_b200 import kv4
+    okv, k16, v16 = build_oracle_cache(oracle, shape, ctx + M, seed=seed, chunk=chunk)
+    layer = kv4.KvLayer(shape.hkv, shape.hd, okv.max_ctx).load_numpy(okv.arrays())
+    q = synth.make_q(shape, M, seed=seed)
+    rope_np = oracle.rope_table(okv.max_ctx, shape.theta, shape.rd) if shape.rd else None
+    rope = torch.from_numpy(rope_np).cuda() if shape.rd else None
+    return kv4, okv, layer, q, rope_np, rope
+
+
+@pytest.fixture(autouse=True)
+def _reset_algo():
+    yield
+    from yasakani_b200 import kv4
+    kv4.set_algo(ALGO_AUTO)
+
+
+CASES = [
+    # shape, cached ctx, M rows, splits
+    (synth.C1, 4095, 1, 32),                                     # config 1: pos 4095 -> 4,096 keys
+    (synth.C1, 33, 1, 32),                                       # more splits than keys per split
+    (synth.C1, 0, 1, 4),                                         # first token: one key, from the shadow
+    (synth.C2, 8191, 1, 37),                                     # config 2, smallest context
+    (synth.C2, 1000, 3, 16),
+    (synth.C2, 31, 2, 8),                                        # only shadow keys
+    (synth.Shape(8, 1, 64, 64, 1e4), 777, 2, 9),
+    (synth.Shape(7, 1, 128, 128, 1e6), 500, 1, 32),              # G = 7 as in the reference's 7B instantiation
+]
+
+
+@pytest.mark.parametrize("algo", [ALGO_SCALAR, ALGO_AUTO])
+@pytest.mark.parametrize("shape,ctx,M,splits", CASES)
+def test_attention_matches_exact_oracle(oracle, shape, ctx, M, splits, algo):
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, M, seed=31, chunk=61)
+    kv4.set_algo(algo)
+    got, (pm, pl, pacc) = gpu_attention(kv4, layer, q, ctx, splits, rope, shape)
+    assert np.isfinite(pm).all() and np.isfinite(pl).all() and np.isfinite(pacc).all(), "a partial slot was not written"
+    want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    err = assert_close(got, want, f"attention {shape} ctx {ctx} M {M}")
+    assert err < 1e-3, f"max abs err {err} is inside the bar but larger than fp16 output rounding explains"
+
+
+def test_combine_matches_literal_merge_with_bias_and_gate(oracle):
+    shape, ctx, M, S = synth.C2, 300, 2, 11
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, M, seed=32)
+    pm, pl, pacc = oracle.attention_partials(f16_bits(q), okv, ctx, S, rope_np, shape.hq, shape.rd, shape.qscale)
+    g = torch.Generator().manual_seed(1)
+    bv = torch.randn((shape.hkv, shape.hd), generator=g).half(); gate = torch.randn((M, shape.hq, shape.hd), generator=g).half()
+    want = bits_f16(oracle.combine(pm, pl, pacc, shape.g, bv=f16_bits(bv), gate=f16_bits(gate)))
+    o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+    kv4.launch_attn_combine_gqa(torch.from_numpy(pm).cuda(), torch.from_numpy(pl).cuda(), torch.from_numpy(pacc).cuda(), S, M, o16,
+                                shape.hq, shape.g, bv=bv.cuda(), gate=gate.cuda())
+    got = o16.float().cpu().numpy()
+    # same formula and summation order; expf and FMA contraction may move a result by one fp16 ulp
+    assert np.max(np.abs(got - want)) <= 2 ** -10 * max(1.0, float(np.abs(want).max()))
+    assert np.mean(got == want) > 0.98
+
+
+def test_triples_merge_like_combine(oracle):
+    """local_triple + merge_triples (the multi-GPU exchange) equals combining all partials at once."""
+    shape, ctx, M, S = synth.C2, 700, 1, 12
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, M, seed=33)
+    pm, pl, pacc = [torch.from_numpy(a).cuda() for a in
+                    oracle.attention_partials(f16_bits(q), okv, ctx, S, rope_np, shape.hq, shape.rd, shape.qscale)]
+    o_all = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+    kv4.launch_attn_combine_gqa(pm, pl, pacc, S, M, o_all, shape.hq, shape.g)
+    R = 3                                                        # three "ranks", 4 splits each
+    triples = torch.empty((R, M, shape.hq, shape.hd + 2), dtype=torch.float32, device="cuda")
+    for r in range(R):
+        sl = slice(4 * r, 4 * r + 4)
+        kv4.launch_local_triple(pm[:, sl].contiguous(), pl[:, sl].contiguous(), pacc[:, sl].contiguous(), 4, M, shape.hq, shape.hd, triples[r])
+    o_merged = torch.empty_like(o_all)
+    kv4.launch_merge_triples(triples, R, M, shape.hq, shape.g, shape.hd, o_merged)
+    torch.cuda.synchronize()
+    a, b = o_all.float().cpu().numpy(), o_merged.float().cpu().numpy()
+    assert np.max(np.abs(a - b)) <= 2 ** -10 * max(1.0, float(np.abs(a).max()))
+    assert_close(oracle.merge_triples(triples[:, 0].cpu().numpy()), oracle.attention_exact(
+        f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)[0], "gpu triples vs exact", atol=1e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "kv4_kat_*.npz"))))
+def test_attention_reproduces_golden_outputs(path):
+    from yasakani_b200 import kv4
+    z = np.load(path)
+    hq, hkv, hd, rd, ctx, M, max_ctx = [int(x) for x in z["meta"]]
+    shape = synth.Shape(hq, hkv, hd, rd, float(z["theta"]))
+    layer = kv4.KvLayer(hkv, hd, max_ctx).load_numpy({n: z[n] for n in ("kq", "kscale", "kzero", "kshadow", "vq", "vscale", "vzero")})
+    q = torch.from_numpy(z["q16"].view(np.int16)).view(torch.float16)
+    got, _ = gpu_attention(kv4, layer, q, ctx, 8, torch.from_numpy(z["rope"]).cuda(), shape)
+    assert_close(got, z["out"], os.path.basename(path))
+
+
+def test_bf16_activations(oracle):
+    shape, ctx = synth.C2, 515
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, 1, seed=34)
+    qb = q.to(torch.bfloat16)                                    # values are bf16-representable by construction
+    got, _ = gpu_attention(kv4, layer, qb, ctx, 16, rope, shape)
+    want = oracle.attention_exact(f16_bits(qb.to(torch.float16)), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    assert_close(got, want, "bf16 activations", atol=4e-3)       # bf16 output rounding: 2^-9 relative
+
+
+def test_rows_of_a_wider_pass_equal_the_narrower_pass(oracle):
+    """Shared rows are bitwise identical whether verified 16, 32 or 64 wide (same base position).
+
+    Rows 0-31 sit in group ctx/32 and read it from the fp16 shadow; rows 32-63 of the 64-wide pass see that
+    group already quantised by the same pass (src/attention_gqa.cu:145-146)."""
+    from yasakani_b200 import kv4
+    shape, ctx = synth.C2, 1024
+    k, v = synth.make_kv(shape, ctx + 64, seed=35)
+    q = synth.make_q(shape, 64, seed=35)
+    k16, v16 = f16_bits(k), f16_bits(v)
+    base = oracle.KvCache(shape.hkv, shape.hd, 1152)
+    oracle.append(base, 0, k16[:ctx], v16[:ctx])
+    rope_np = oracle.rope_table(base.max_ctx, shape.theta, shape.rd)
+    rope = torch.from_numpy(rope_np).cuda()
+    outs = {}
+    for M in (16, 32, 64):
+        lay = kv4.KvLayer(shape.hkv, shape.hd, base.max_ctx).load_numpy(base.arrays())
+        gpu_append_all(kv4, lay, k[ctx:ctx + M], v[ctx:ctx + M], [M], pos0=ctx)      # the pass appends exactly its own rows
+        outs[M], _ = gpu_attention(kv4, lay, q[:M], ctx, 13, rope, shape)
+    assert np.array_equal(outs[16], outs[32][:16]) and np.array_equal(outs[32], outs[64][:32])
+    oracle.append(base, ctx, k16[ctx:], v16[ctx:])
+    want = oracle.attention_exact(f16_bits(q), base, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    assert_close(outs[64], want, "verify M=64")
+
+
+def test_host_probe_runs_and_times(oracle):
+    import ctypes as C
+    from yasakani_b200 import _lib
+    shape, ctx = synth.C1, 600
+    okv, _, _ = build_oracle_cache(oracle, shape, ctx + 1, seed=36)
+    q16 = f16_bits(synth.make_q(shape, 1, seed=36))
+    rope = oracle.rope_table(okv.max_ctx, shape.theta, shape.rd)
+    hk = _lib.KvLayerC(*[a.ctypes.data for a in (okv.kq, okv.kscale, okv.kzero, okv.kshadow, okv.vq, okv.vscale, okv.vzero)])
+    out = np.zeros((1, shape.hq, shape.hd), np.uint16); ms = np.zeros(3, np.float32)
+    rc = _lib.load().yskn_kv4_attention_host(q16.ctypes.data, C.byref(hk), okv.max_ctx, 1, ctx, 8, rope.ctypes.data, shape.hkv, shape.hq,
+                                             shape.hd, shape.rd, C.c_float(shape.qscale), 0, out.ctypes.data, 3, ms.ctypes.data)
+    assert rc == 0, _lib.load().yskn_kv4_last_error()
+    assert (ms > 0).all()
+    assert_close(bits_f16(out), oracle.attention_exact(q16, okv, ctx, rope, shape.hq, shape.rd, shape.qscale), "host probe")

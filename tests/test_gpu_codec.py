@@ -1,0 +1,119 @@
+"""GPU parity of the KV4 codec through the C ABI: packed cache bit-exact against the CPU oracle."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import build_oracle_cache, f16_bits, gpu_append_all
+from yasakani_b200 import synth
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _compare(layer, okv):
+    got = layer.to_numpy()
+    for name, want in okv.arrays().items():
+        assert np.array_equal(got[name].reshape(want.shape), want), f"{name} differs"
+
+
+@pytest.mark.parametrize("shape,ctx,passes", [
+    (synth.C1, 200, [1] * 40 + [31, 33, 64, 32]),               # single-token decode appends, then ragged chunks
+    (synth.C2, 291, [97, 1, 1, 30, 2, 160]),
+    (synth.Shape(4, 1, 64, 64, 1e4), 96, [96]),
+    (synth.C2, 8192, [8192]),                                   # one prefill-sized pass (C5's prompt length)
+])
+def test_append_is_bit_exact(oracle, shape, ctx, passes):
+    from yasakani_b200 import kv4
+    assert sum(passes) == ctx
+    k, v = synth.make_kv(shape, ctx, seed=21)
+    okv = oracle.KvCache(shape.hkv, shape.hd, ((ctx + 127) // 64) * 64)
+    k16, v16 = f16_bits(k), f16_bits(v)
+    p = 0
+    for n in passes:
+        oracle.append(okv, p, k16[p:p + n], v16[p:p + n]); p += n
+    layer = kv4.KvLayer(shape.hkv, shape.hd, okv.max_ctx)
+    gpu_append_all(kv4, layer, k, v, passes)
+    _compare(layer, okv)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_append_converts_bf16_and_f32_rows_like_the_oracle(oracle, dtype):
+    from yasakani_b200 import kv4
+    shape, ctx = synth.C2, 96
+    k, v = synth.make_kv(shape, ctx, seed=22, dtype=torch.bfloat16)
+    if dtype == torch.float32:                                  # values that do not fit fp16 exactly
+        k, v = k.float() * 1.0003, v.float() * 0.9997
+    okv = oracle.KvCache(shape.hkv, shape.hd, 128)
+    oracle.append(okv, 0, f16_bits(k.to(torch.float16)), f16_bits(v.to(torch.float16)))      # RNE to fp16 first
+    layer = kv4.KvLayer(shape.hkv, shape.hd, 128)
+    gpu_append_all(kv4, layer, k, v, [ctx])
+    _compare(layer, okv)
+
+
+def test_edge_rows_constant_and_extreme(oracle):
+    from yasakani_b200 import kv4
+    shape = synth.Shape(8, 2, 128, 0, 1.0)
+    k, v = synth.make_kv(shape, 64, seed=23)
+    k[0:32, 0] = 1.5; v[3] = -2.25                               # hi == lo: scale 0, codes 0
+    k[40, 1, 5] = 60000.0; v[41, 0, 7] = -60000.0                # near the fp16 limit
+    k[50, 0, 9] = 6e-8; v[51, 1, 11] = 6e-8                      # fp16 subnormal
+    okv = oracle.KvCache(shape.hkv, shape.hd, 64)
+    oracle.append(okv, 0, f16_bits(k), f16_bits(v))
+    layer = kv4.KvLayer(shape.hkv, shape.hd, 64)
+    gpu_append_all(kv4, layer, k, v, [64])
+    _compare(layer, okv)
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "kv4_kat_*.npz"))))
+def test_append_reproduces_golden_cache(path):
+    from yasakani_b200 import kv4
+    z = np.load(path)
+    hq, hkv, hd, rd, ctx, M, max_ctx = [int(x) for x in z["meta"]]
+    layer = kv4.KvLayer(hkv, hd, max_ctx)
+    k = torch.from_numpy(z["k16"].view(np.int16)).view(torch.float16); v = torch.from_numpy(z["v16"].view(np.int16)).view(torch.float16)
+    gpu_append_all(kv4, layer, k, v, [int(n) for n in z["passes"]])
+    got = layer.to_numpy()
+    for name in ("kq", "kscale", "kzero", "kshadow", "vq", "vscale", "vzero"):
+        assert np.array_equal(got[name].reshape(z[name].shape), z[name]), name
+
+
+def test_group_quant_entry_alone_and_idempotent(oracle):
+    """Writing shadow rows and calling only the group-quant entry gives the same groups; a second call changes nothing."""
+    from yasakani_b200 import kv4
+    shape, ctx = synth.C2, 128
+    okv, k16, v16 = build_oracle_cache(oracle, shape, ctx, seed=24, max_ctx=128)
+    layer = kv4.KvLayer(shape.hkv, shape.hd, 128)
+    layer.kshadow.copy_(torch.from_numpy(okv.kshadow.view(np.int16)).view(torch.float16))
+    d_pos = torch.tensor([0], dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        kv4.launch_kv_group_quant_g(layer, d_pos, ctx)
+        torch.cuda.synchronize()
+        got = layer.to_numpy()
+        for name in ("kq", "kscale", "kzero"):
+            assert np.array_equal(got[name].reshape(getattr(okv, name).shape), getattr(okv, name)), name
+
+
+def test_rope_table_matches_oracle(oracle):
+    from yasakani_b200 import kv4
+    for max_ctx, theta, rd in [(4096, 1e6, 128), (8192, 1e7, 64)]:
+        out = torch.empty((max_ctx, rd // 2, 2), dtype=torch.float32, device="cuda")
+        kv4.launch_rope_table_g(out, max_ctx, theta, rd)
+        torch.cuda.synchronize()
+        want = oracle.rope_table(max_ctx, theta, rd)
+        got = out.cpu().numpy()
+        # identical angle (fp32 product), double-precision cos/sin rounded once: equal up to one fp32 ulp
+        assert np.max(np.abs(got - want)) <= 1.2e-7
+        assert np.mean(got == want) > 0.99
+
+
+def test_bad_arguments_are_rejected_with_a_message():
+    from yasakani_b200 import kv4, Kv4Error
+    layer = kv4.KvLayer(2, 128, 64)
+    d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rows = torch.zeros((1, 2, 128), dtype=torch.float16, device="cuda")
+    layer.hd = 96                                                 # unsupported head_dim
+    with pytest.raises(Kv4Error, match="unsupported head_dim"):
+        kv4.launch_kv_append(layer, rows[:, :, :96].contiguous(), rows[:, :, :96].contiguous(), d_pos, 1)

@@ -1,0 +1,84 @@
+"""Pins the CPU oracle (and our kernels) against the reference's own CUDA kernels.
+
+oracle/_ref/libyskn_ref_kv4.so is compiled from the reference's source files where they lie
+(oracle/Makefile, target `ref`) and travels to the GPU box as a built file.  It covers the K group codec
+(kv_group_quant_g_kernel), the generic GQA decode kernel and its merge kernel.  The per-token V codec lives
+inside the reference's fused QKV epilogue, which cannot be driven without its GEMV inputs; it shares the
+K codec's formula line for line (src/post_kernels.cu:76-77 vs src/attention_gqa.cu:149-152).
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import assert_close, bits_f16, build_oracle_cache, f16_bits, gpu_attention
+from yasakani_b200 import synth
+
+pytestmark = pytest.mark.gpu
+REF = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libyskn_ref_kv4.so")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not os.path.exists(REF):
+        pytest.skip("oracle/_ref not built (reference tree was not mounted at build time)")
+    return C.CDLL(REF)
+
+
+def _ptrs(layer):
+    return [C.c_void_p(t.data_ptr()) for t in layer.tensors()]
+
+
+@pytest.mark.parametrize("shape", [synth.C2, synth.C1])
+def test_oracle_group_codec_equals_reference_kernel_bit_for_bit(oracle, ref, shape):
+    from yasakani_b200 import kv4
+    ctx = 160
+    okv, k16, v16 = build_oracle_cache(oracle, shape, ctx, seed=41, max_ctx=192)
+    ours = kv4.KvLayer(shape.hkv, shape.hd, 192)
+    ours.kshadow.copy_(torch.from_numpy(okv.kshadow.view(np.int16)).view(torch.float16))
+    d_pos = torch.tensor([0], dtype=torch.int32, device="cuda")
+    rc = ref.yref_kv_group_quant_g(*_ptrs(ours), C.c_void_p(d_pos.data_ptr()), ctx, 192, shape.hkv, shape.hd, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    got = ours.to_numpy()
+    for name in ("kq", "kscale", "kzero"):
+        assert np.array_equal(got[name].reshape(getattr(okv, name).shape), getattr(okv, name)), name
+
+
+@pytest.mark.parametrize("shape,ctx,M", [(synth.C2, 2100, 1), (synth.C2, 700, 3), (synth.Shape(28, 4, 128, 128, 1e6), 1500, 2)])
+def test_reference_attention_kernel_agrees_with_oracle_and_with_ours(oracle, ref, shape, ctx, M):
+    from yasakani_b200 import kv4
+    S = 32
+    okv, _, _ = build_oracle_cache(oracle, shape, ctx + M, seed=42, chunk=50)
+    layer = kv4.KvLayer(shape.hkv, shape.hd, okv.max_ctx).load_numpy(okv.arrays())
+    q = synth.make_q(shape, M, seed=42)
+    rope_np = oracle.rope_table(okv.max_ctx, shape.theta, shape.rd)
+    rope = torch.from_numpy(rope_np).cuda()
+    dq = q.cuda(); d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    pm, pl, pacc = kv4.attn_scratch(M, S, shape.hq, shape.hd)
+    rc = ref.yref_attention_gqa(C.c_void_p(dq.data_ptr()), *_ptrs(layer), okv.max_ctx, M, C.c_void_p(d_pos.data_ptr()), S,
+                                C.c_void_p(pm.data_ptr()), C.c_void_p(pl.data_ptr()), C.c_void_p(pacc.data_ptr()),
+                                C.c_void_p(rope.data_ptr()), shape.hkv, shape.hq, C.c_float(shape.qscale), shape.g, shape.hd, shape.rd, None)
+    assert rc == 0
+    n = shape.hq * shape.hd
+    signs = torch.ones(n, dtype=torch.int8, device="cuda"); qx = torch.empty((M, n), dtype=torch.int8, device="cuda")
+    alpha = torch.empty((M, n // 512), dtype=torch.float32, device="cuda")
+    o_ref = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+    rc = ref.yref_attn_combine_gqa_xform(C.c_void_p(pm.data_ptr()), C.c_void_p(pl.data_ptr()), C.c_void_p(pacc.data_ptr()), S, M, None,
+                                         C.c_void_p(o_ref.data_ptr()), None, shape.hq, shape.g, shape.hd, C.c_void_p(signs.data_ptr()),
+                                         C.c_void_p(qx.data_ptr()), C.c_void_p(alpha.data_ptr()), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    o_ref = o_ref.float().cpu().numpy()
+    # (1) the reference's partials against the oracle's literal restatement of the same kernel
+    opm, opl, opacc = oracle.attention_partials(f16_bits(q), okv, ctx, S, rope_np, shape.hq, shape.rd, shape.qscale)
+    assert_close(pm.cpu().numpy(), opm, "pm", atol=1e-4, rtol=1e-5)
+    assert_close(pl.cpu().numpy(), opl, "pl", atol=1e-4, rtol=1e-4)
+    assert_close(pacc.cpu().numpy(), opacc, "pacc", atol=1e-3, rtol=1e-3)
+    # (2) the reference's final output against the tolerance oracle, and (3) against our kernels
+    exact = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    assert_close(o_ref, exact, "reference vs exact oracle", atol=1e-3, rtol=2e-3)
+    ours, _ = gpu_attention(kv4, layer, q, ctx, S, rope, shape)
+    assert_close(ours, o_ref, "ours vs reference kernels")

@@ -29,13 +29,13 @@ static int check_attn(const yskn_attn_g_args* a, int g, int hd, const char* who)
   (void)hd; return 0;
 }
 
-static int attention_dispatch(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, cudaStream_t st) {
+static int attention_dispatch(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st) {
   if (act_dtype != YSKN_KV4_F16 && act_dtype != YSKN_KV4_BF16) KV4_REJECT("yskn_kv4_attention: act_dtype must be F16 or BF16");
   if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_attention: rotary width %d needs a rope table", rd);
   const bool mma_ok = decode_mma_supports(g, hd, rd, a->M);
   if (g_algo == ALGO_MMA && !mma_ok) KV4_REJECT("yskn_kv4_attention: tensor-core path does not cover (g %d, hd %d, rd %d, M %d)", g, hd, rd, a->M);
-  if (mma_ok && g_algo != ALGO_SCALAR) return launch_decode_mma(*a, g, hd, rd, act_dtype, st);
-  return launch_attention_scalar(*a, g, hd, rd, act_dtype, st);
+  if (mma_ok && g_algo != ALGO_SCALAR) return launch_decode_mma(*a, g, hd, rd, act_dtype, sh, st);
+  return launch_attention_scalar(*a, g, hd, rd, act_dtype, sh, st);
 }
 
 }  // namespace kv4
@@ -74,7 +74,15 @@ int yskn_kv4_group_quant(const yskn_kv_quant_args* a, int kvh, int hd, void* cud
 
 int yskn_kv4_attention(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, void* cuda_stream) {
   if (int rc = check_attn(a, g, hd, "yskn_kv4_attention")) return rc;
-  return attention_dispatch(a, g, hd, rd, act_dtype, (cudaStream_t)cuda_stream);
+  return attention_dispatch(a, g, hd, rd, act_dtype, Shard{0, a->max_ctx}, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_attention_shard(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, int shard_start, int shard_len,
+                             void* cuda_stream) {
+  if (int rc = check_attn(a, g, hd, "yskn_kv4_attention_shard")) return rc;
+  if (shard_start < 0 || shard_start % 32 || shard_len < 0 || shard_len > a->max_ctx)
+    KV4_REJECT("yskn_kv4_attention_shard: shard [%d, +%d) must start on a multiple of 32 and fit max_ctx %d", shard_start, shard_len, a->max_ctx);
+  return attention_dispatch(a, g, hd, rd, act_dtype, Shard{shard_start, shard_len}, (cudaStream_t)cuda_stream);
 }
 
 int yskn_kv4_combine(const yskn_attn_g_combine_args* a, int hd, int act_dtype, void* cuda_stream) {
@@ -86,7 +94,7 @@ int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int rd, int act_d
                      void* cuda_stream) {
   if (int rc = check_attn(a, g, hd, "yskn_kv4_prefill")) return rc;
   if (!o16) KV4_REJECT("yskn_kv4_prefill: null output");
-  if (int rc = attention_dispatch(a, g, hd, rd, act_dtype, (cudaStream_t)cuda_stream)) return rc;
+  if (int rc = attention_dispatch(a, g, hd, rd, act_dtype, Shard{0, a->max_ctx}, (cudaStream_t)cuda_stream)) return rc;
   yskn_attn_g_combine_args c{a->pm, a->pl, a->pacc, a->splits, a->M, bv, o16, nullptr, a->nh, g};
   return launch_combine(c, hd, act_dtype, (cudaStream_t)cuda_stream);
 }

@@ -16,12 +16,13 @@ namespace kv4 {
 namespace {
 
 template <int G, int HD, int DT>
-__global__ void __launch_bounds__(128) kv4_attn_scalar_kernel(yskn_attn_g_args A, int rd) {
+__global__ void __launch_bounds__(128) kv4_attn_scalar_kernel(yskn_attn_g_args A, int rd, Shard sh) {
   constexpr int CPL = HD / 32;
   __shared__ float s_m[4][G], s_l[4][G];
   __shared__ float s_acc[4][G][HD];
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pos = *A.d_pos + r, len = pos + 1, per = (len + A.splits - 1) / A.splits;
+  // pos/len/cur_group are LOCAL to this shard: local token t is global token t + sh.start (1 GPU: start 0)
+  const int pos = *A.d_pos + r - sh.start, len = max(0, min(pos + 1, sh.len)), per = (len + A.splits - 1) / A.splits;
   const int t0 = split * per, t1 = min(len, t0 + per), cur_group = pos / 32;
   const int c0 = lane * CPL;                          // first channel of this lane
   const int half = rd / 2, lanes_off = half / CPL;    // rotary partner distance in lanes
@@ -64,7 +65,7 @@ __global__ void __launch_bounds__(128) kv4_attn_scalar_kernel(yskn_attn_g_args A
       for (int e = 0; e < CPL; ++e) {
         const float other = __shfl_xor_sync(0xffffffffu, kd[e], lanes_off);
         if (rot) {
-          const float2 cs = *reinterpret_cast<const float2*>(A.rope + ((size_t)t * half + ((c0 + e) % half)) * 2);
+          const float2 cs = *reinterpret_cast<const float2*>(A.rope + ((size_t)(t + sh.start) * half + ((c0 + e) % half)) * 2);
           kd[e] = lower ? (kd[e] * cs.x - other * cs.y) : (other * cs.y + kd[e] * cs.x);
         }
       }
@@ -119,33 +120,33 @@ __global__ void __launch_bounds__(128) kv4_attn_scalar_kernel(yskn_attn_g_args A
   }
 }
 
-template <int G, int HD> int launch_gd(const yskn_attn_g_args& a, int rd, int dt, cudaStream_t st) {
+template <int G, int HD> int launch_gd(const yskn_attn_g_args& a, int rd, int dt, Shard sh, cudaStream_t st) {
   const dim3 grid(a.splits, a.kvh, a.M);
-  if (dt == YSKN_KV4_F16) kv4_attn_scalar_kernel<G, HD, YSKN_KV4_F16><<<grid, 128, 0, st>>>(a, rd);
-  else kv4_attn_scalar_kernel<G, HD, YSKN_KV4_BF16><<<grid, 128, 0, st>>>(a, rd);
+  if (dt == YSKN_KV4_F16) kv4_attn_scalar_kernel<G, HD, YSKN_KV4_F16><<<grid, 128, 0, st>>>(a, rd, sh);
+  else kv4_attn_scalar_kernel<G, HD, YSKN_KV4_BF16><<<grid, 128, 0, st>>>(a, rd, sh);
   return launch_status("kv4_attn_scalar_kernel");
 }
-template <int HD> int launch_d(const yskn_attn_g_args& a, int g, int rd, int dt, cudaStream_t st) {
+template <int HD> int launch_d(const yskn_attn_g_args& a, int g, int rd, int dt, Shard sh, cudaStream_t st) {
   switch (g) {
-    case 1: return launch_gd<1, HD>(a, rd, dt, st);
-    case 2: return launch_gd<2, HD>(a, rd, dt, st);
-    case 4: return launch_gd<4, HD>(a, rd, dt, st);
-    case 6: return launch_gd<6, HD>(a, rd, dt, st);
-    case 7: return launch_gd<7, HD>(a, rd, dt, st);
-    case 8: return launch_gd<8, HD>(a, rd, dt, st);
+    case 1: return launch_gd<1, HD>(a, rd, dt, sh, st);
+    case 2: return launch_gd<2, HD>(a, rd, dt, sh, st);
+    case 4: return launch_gd<4, HD>(a, rd, dt, sh, st);
+    case 6: return launch_gd<6, HD>(a, rd, dt, sh, st);
+    case 7: return launch_gd<7, HD>(a, rd, dt, sh, st);
+    case 8: return launch_gd<8, HD>(a, rd, dt, sh, st);
   }
   KV4_REJECT("yskn_kv4_attention: unsupported group size %d (1, 2, 4, 6, 7, 8)", g);
 }
 
 }  // namespace
 
-int launch_attention_scalar(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, cudaStream_t st) {
+int launch_attention_scalar(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st) {
   const int cpl = hd / 32;
   if (rd < 0 || rd > hd || (rd & 1) || (rd > 0 && ((rd / 2) % cpl || ((rd / 2 / cpl) & (rd / 2 / cpl - 1)))))
     KV4_REJECT("yskn_kv4_attention: unsupported rotary width %d for head_dim %d", rd, hd);   // src/attention_gqa.cu:174
-  if (hd == 256) return launch_d<256>(a, g, rd, act_dtype, st);
-  if (hd == 128) return launch_d<128>(a, g, rd, act_dtype, st);
-  if (hd == 64) return launch_d<64>(a, g, rd, act_dtype, st);
+  if (hd == 256) return launch_d<256>(a, g, rd, act_dtype, sh, st);
+  if (hd == 128) return launch_d<128>(a, g, rd, act_dtype, sh, st);
+  if (hd == 64) return launch_d<64>(a, g, rd, act_dtype, sh, st);
   KV4_REJECT("yskn_kv4_attention: unsupported head_dim %d (64, 128, 256)", hd);
 }
 

@@ -41,12 +41,16 @@ template <int DT> __device__ __forceinline__ uint16_t act_store16(float v) {
   return DT == YSKN_KV4_BF16 ? f2bf(v) : f2h(v);
 }
 
+// A sequence shard: the local cache arrays hold global tokens [start, start+len); start is a multiple of 32.
+// One GPU: {0, max_ctx}.
+struct Shard { int start; int len; };
+
 // ---- launchers implemented in the .cu files (all enqueue-only) ----
 int launch_rope_table(float* d_out, int max_ctx, float theta, int rd, cudaStream_t st);
 int launch_append(const yskn_kv_append_args& a, cudaStream_t st);
 int launch_group_quant(const yskn_kv_quant_args& a, int kvh, int hd, cudaStream_t st);
-int launch_attention_scalar(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, cudaStream_t st);
-int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, cudaStream_t st);
+int launch_attention_scalar(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st);
+int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st);
 bool decode_mma_supports(int g, int hd, int rd, int M);
 int launch_combine(const yskn_attn_g_combine_args& a, int hd, int act_dtype, cudaStream_t st);
 int launch_local_triple(const yskn_attn_g_combine_args& a, int hd, float* d_triple, cudaStream_t st);

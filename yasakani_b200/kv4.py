@@ -134,6 +134,14 @@ def launch_attention_gqa(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, p
     check(_lib.load().yskn_kv4_attention(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), _stream(stream)), "yskn_kv4_attention")
 
 
+def launch_attention_shard(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float,
+                           rd: int, shard_start: int, shard_len: int, stream=None) -> None:
+    """Partials over a cache holding only global tokens [shard_start, shard_start+shard_len); d_pos stays global."""
+    a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
+    check(_lib.load().yskn_kv4_attention_shard(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), shard_start, shard_len,
+                                              _stream(stream)), "yskn_kv4_attention_shard")
+
+
 def launch_attn_combine_gqa(pm, pl, pacc, splits: int, M: int, o16, nh: int, g: int, bv=None, gate=None, stream=None) -> None:
     """Merge half of launch_attn_combine_gqa_xform (src/attention_gqa.cu:123-134,176-181), up to the o16 store."""
     hd = o16.numel() // (M * nh)
