@@ -82,6 +82,12 @@ YSKN_KV4_API const char* yskn_kv4_build_info(void);   /* yskn_build_info, src/c_
  * rejected).  Process-wide; the counterpart of the reference's YSKN_ATTN_GENERIC switch (src/engine.cpp:189-193). */
 YSKN_KV4_API int yskn_kv4_set_algo(int algo);
 
+/* Reads and clears the device status word of the tensor-core decode kernel on the current device (synchronises):
+ * 0 = ok, 1/2 = a bounded wait on the staging ring ran out (consumer/producer), 3 = misaligned shared memory.
+ * A non-zero status means the partials of that launch are invalid.  The kernels never trap; compare the reference's
+ * device-side __trap() on bad input (src/kvq_gpu.cuh:91). */
+YSKN_KV4_API int yskn_kv4_device_status(int* status);
+
 /* launch_rope_table_g, src/attention_gqa.cu:158-167. */
 YSKN_KV4_API int yskn_kv4_rope_table(float* d_out, int max_ctx, float theta, int rd, void* cuda_stream);
 

@@ -55,7 +55,7 @@ def test_attention_matches_exact_oracle(oracle, shape, ctx, M, splits, algo):
     assert np.isfinite(pm).all() and np.isfinite(pl).all() and np.isfinite(pacc).all(), "a partial slot was not written"
     want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
     err = assert_close(got, want, f"attention {shape} ctx {ctx} M {M}")
-    assert err < 1e-3, f"max abs err {err} is inside the bar but larger than fp16 output rounding explains"
+    assert err < 1.8e-3, f"max abs err {err} is inside the bar but larger than fp16 operand rounding explains"
 
 
 def test_combine_matches_literal_merge_with_bias_and_gate(oracle):
@@ -156,3 +156,60 @@ def test_host_probe_runs_and_times(oracle):
     assert rc == 0, _lib.load().yskn_kv4_last_error()
     assert (ms > 0).all()
     assert_close(bits_f16(out), oracle.attention_exact(q16, okv, ctx, rope, shape.hq, shape.rd, shape.qscale), "host probe")
+
+
+MMA_CASES = [
+    (synth.C2, 32767, 1, 74),                                    # config 2 at 32,768 keys
+    (synth.C2, 4096 + 5, 1, 37),                                 # open group of 6 tokens
+    (synth.C2, 4096 + 31, 1, 148),                               # full open group, more splits than groups per split
+    (synth.C2, 40, 2, 4),                                        # one int4 group + open group, two rows
+    (synth.C2, 15, 1, 3),                                        # open group only, less than one tile
+    (synth.C1, 4095, 1, 32),
+    (synth.C1, 1234, 3, 16),
+    (synth.Shape(24, 4, 256, 0, 1.0), 999, 1, 8),                # no rotary channels
+    (synth.Shape(5, 1, 128, 0, 1.0), 700, 1, 8),                 # odd group size, padded heads
+]
+
+
+@pytest.mark.parametrize("shape,ctx,M,splits", MMA_CASES)
+def test_tensor_core_decode_matches_exact_oracle(oracle, shape, ctx, M, splits):
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, M, seed=37, chunk=97)
+    kv4.set_algo(ALGO_MMA)
+    got, (pm, pl, pacc) = gpu_attention(kv4, layer, q, ctx, splits, rope, shape)
+    assert kv4.device_status() == 0
+    assert np.isfinite(pm).all() and np.isfinite(pl).all() and np.isfinite(pacc).all(), "a partial slot was not written"
+    want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    err = assert_close(got, want, f"mma decode {shape} ctx {ctx} M {M}")
+    assert err < 1.8e-3
+    kv4.set_algo(ALGO_SCALAR)
+    ref, _ = gpu_attention(kv4, layer, q, ctx, splits, rope, shape)
+    assert_close(got, ref, "mma vs cuda-core kernel", atol=1.5e-3, rtol=1e-2)
+
+
+@pytest.mark.parametrize("algo", [ALGO_SCALAR, ALGO_MMA])
+@pytest.mark.parametrize("world", [2, 4])
+def test_shards_merge_to_the_unsharded_result(oracle, algo, world):
+    """Sequence shards on ONE GPU (separate launches, no waiting on one another): shard partials -> triples -> merge."""
+    from yasakani_b200.sharded import plan_shards
+    shape, ctx = synth.C2, 3000
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, 1, seed=38)
+    kv4.set_algo(algo)
+    k, v = synth.make_kv(shape, ctx + 1, seed=38)
+    triples = torch.empty((world, 1, shape.hq, shape.hd + 2), dtype=torch.float32, device="cuda")
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    dq = q.cuda()
+    for rnk in range(world):
+        plan = plan_shards(ctx, world, rnk, okv.max_ctx)
+        lay = kv4.KvLayer(shape.hkv, shape.hd, plan.capacity)
+        a, b = plan.local_rows(0, ctx + 1)
+        if b > a:
+            gpu_append_all(kv4, lay, k[a:b], v[a:b], [b - a], pos0=a - plan.start)
+        pm, pl, pacc = kv4.attn_scratch(1, 9, shape.hq, shape.hd)
+        kv4.launch_attention_shard(dq, lay, 1, d_pos, 9, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, plan.start, plan.capacity)
+        kv4.launch_local_triple(pm, pl, pacc, 9, 1, shape.hq, shape.hd, triples[rnk])
+    o16 = torch.empty((1, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+    kv4.launch_merge_triples(triples, world, 1, shape.hq, shape.g, shape.hd, o16)
+    torch.cuda.synchronize()
+    assert kv4.device_status() == 0
+    want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    assert_close(o16.float().cpu().numpy(), want, f"{world} shards")

@@ -43,6 +43,7 @@ PROTOTYPES = {
     "yskn_kv4_last_error": (C.c_char_p, []),
     "yskn_kv4_build_info": (C.c_char_p, []),
     "yskn_kv4_set_algo": (C.c_int, [C.c_int]),
+    "yskn_kv4_device_status": (C.c_int, [C.POINTER(C.c_int)]),
     "yskn_kv4_rope_table": (C.c_int, [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_void_p]),
     "yskn_kv4_append": (C.c_int, [C.POINTER(KvAppendArgsC), C.c_void_p]),
     "yskn_kv4_group_quant": (C.c_int, [C.POINTER(KvQuantArgsC), C.c_int, C.c_int, C.c_void_p]),
@@ -73,7 +74,7 @@ def load():
     """Load the CUDA library (building it first if sources are newer). Raises if that is impossible."""
     global _LIB
     if _LIB is None:
-        path = _build.LIB
+        path = os.environ.get("YSKN_KV4_LIB") or _build.LIB          # an explicit library (e.g. a diagnostic build) wins
         if not os.path.exists(path) or os.environ.get("YSKN_KV4_REBUILD"):
             path = _build.build()
         L = C.CDLL(path)

@@ -55,6 +55,11 @@ int yskn_kv4_set_algo(int algo) {
   g_algo = algo; return 0;
 }
 
+int yskn_kv4_device_status(int* status) {
+  if (!status) KV4_REJECT("yskn_kv4_device_status: null output");
+  return decode_status_fetch(status);
+}
+
 int yskn_kv4_rope_table(float* d_out, int max_ctx, float theta, int rd, void* cuda_stream) {
   return launch_rope_table(d_out, max_ctx, theta, rd, (cudaStream_t)cuda_stream);
 }

@@ -130,12 +130,14 @@ template <int HD> int launch_d(const yskn_attn_g_args& a, int g, int rd, int dt,
   switch (g) {
     case 1: return launch_gd<1, HD>(a, rd, dt, sh, st);
     case 2: return launch_gd<2, HD>(a, rd, dt, sh, st);
+    case 3: return launch_gd<3, HD>(a, rd, dt, sh, st);
     case 4: return launch_gd<4, HD>(a, rd, dt, sh, st);
+    case 5: return launch_gd<5, HD>(a, rd, dt, sh, st);
     case 6: return launch_gd<6, HD>(a, rd, dt, sh, st);
     case 7: return launch_gd<7, HD>(a, rd, dt, sh, st);
     case 8: return launch_gd<8, HD>(a, rd, dt, sh, st);
   }
-  KV4_REJECT("yskn_kv4_attention: unsupported group size %d (1, 2, 4, 6, 7, 8)", g);
+  KV4_REJECT("yskn_kv4_attention: unsupported group size %d (1..8)", g);
 }
 
 }  // namespace

@@ -92,6 +92,13 @@ def set_algo(algo: int) -> None:
     check(_lib.load().yskn_kv4_set_algo(int(algo)), "yskn_kv4_set_algo")
 
 
+def device_status() -> int:
+    """Status word of the tensor-core decode kernel (0 = ok); reading it synchronises and clears it."""
+    v = C.c_int(0)
+    check(_lib.load().yskn_kv4_device_status(C.byref(v)), "yskn_kv4_device_status")
+    return v.value
+
+
 def launch_rope_table_g(out: torch.Tensor, max_ctx: int, theta: float, rd: int, stream=None) -> None:
     """(cos,sin) float pairs [max_ctx][rd/2]; reference: launch_rope_table_g (src/attention_gqa.cu:166)."""
     assert out.dtype == torch.float32 and out.numel() >= max_ctx * rd
