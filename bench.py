@@ -308,7 +308,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=262144)
-    ap.add_argument("--splits", type=int, default=74)
+    ap.add_argument("--splits", type=int, default=37, help="split-K factor; splits*Hkv = 148 = one CTA per SM")
     ap.add_argument("--cpu-sample-ctx", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch from an ncu capture, if known")
