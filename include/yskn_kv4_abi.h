@@ -83,7 +83,8 @@ YSKN_KV4_API const char* yskn_kv4_build_info(void);   /* yskn_build_info, src/c_
 YSKN_KV4_API int yskn_kv4_set_algo(int algo);
 
 /* Reads and clears the device status word of the tensor-core decode kernel on the current device (synchronises):
- * 0 = ok, 1/2 = a bounded wait on the staging ring ran out (consumer/producer), 3 = misaligned shared memory.
+ * 0 = ok, 1/2 = a bounded wait on the decode staging ring ran out (consumer/producer), 3 = misaligned shared memory,
+ * 4/5/6 = a bounded wait ran out in the tcgen05 kernel (softmax warps / MMA issuer / producer).
  * A non-zero status means the partials of that launch are invalid.  The kernels never trap; compare the reference's
  * device-side __trap() on bad input (src/kvq_gpu.cuh:91). */
 YSKN_KV4_API int yskn_kv4_device_status(int* status);
@@ -113,6 +114,20 @@ YSKN_KV4_API int yskn_kv4_combine(const yskn_attn_g_combine_args* a, int hd, int
  * (row, head) as for yskn_kv4_attention. */
 YSKN_KV4_API int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype,
                                   const uint16_t* bv, uint16_t* o16, void* cuda_stream);
+
+/* Tensor-core (tcgen05) attention for many rows: the verify pass and causal prefill.  The counterpart of the reference's
+ * dequantise-once path for wide passes, launch_kv_dequant + launch_attention_f32 / launch_attention_prefill_f32
+ * (src/attention_kv4q.cu:198-323, src/args.hpp:37-40), whose caller-owned KvF32 arrays become one caller-owned fp16
+ * workspace of yskn_kv4_tc_workspace_bytes(kvh, hd, max_ctx, M) bytes (16-byte aligned).  Each call first brings the
+ * workspace up to date for tokens [valid_tokens, *d_pos + M): pass 0 unless the same workspace already holds the
+ * dequantised tokens [0, valid_tokens) of this cache from an earlier call.  q16 must be fp16.  Semantics, partial
+ * layout and `splits` are those of yskn_kv4_attention; yskn_kv4_prefill_tc also merges to o16 (+ optional bias). */
+YSKN_KV4_API size_t yskn_kv4_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M);
+YSKN_KV4_API int yskn_kv4_attention_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, void* d_workspace,
+                                       size_t workspace_bytes, int valid_tokens, void* cuda_stream);
+YSKN_KV4_API int yskn_kv4_prefill_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, const uint16_t* bv,
+                                     uint16_t* o16, void* d_workspace, size_t workspace_bytes, int valid_tokens,
+                                     void* cuda_stream);
 
 /* Sequence-sharded decode (no reference counterpart: the reference is single-GPU, README.md:37).
  * yskn_kv4_attention_shard is yskn_kv4_attention over a cache that holds only the global tokens

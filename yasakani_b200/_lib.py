@@ -51,6 +51,10 @@ PROTOTYPES = {
     "yskn_kv4_attention_shard": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_combine": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_prefill": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "yskn_kv4_tc_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "yskn_kv4_attention_tc": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
+    "yskn_kv4_prefill_tc": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                      C.c_size_t, C.c_int, C.c_void_p]),
     "yskn_kv4_local_triple": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_void_p, C.c_void_p]),
     "yskn_kv4_merge_triples": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_int, C.c_void_p]),

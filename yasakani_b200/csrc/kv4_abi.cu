@@ -57,7 +57,30 @@ int yskn_kv4_set_algo(int algo) {
 
 int yskn_kv4_device_status(int* status) {
   if (!status) KV4_REJECT("yskn_kv4_device_status: null output");
-  return decode_status_fetch(status);
+  int a = 0, b = 0;
+  if (int rc = decode_status_fetch(&a)) return rc;
+  if (int rc = tc_status_fetch(&b)) return rc;
+  *status = a ? a : b; return 0;
+}
+
+size_t yskn_kv4_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M) {
+  if (kvh <= 0 || (hd != 128 && hd != 256) || max_ctx <= 0 || M <= 0) return 0;
+  return attention_tc_workspace_bytes(kvh, hd, max_ctx, M);
+}
+
+int yskn_kv4_attention_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, void* d_workspace, size_t workspace_bytes,
+                          int valid_tokens, void* cuda_stream) {
+  if (int rc = check_attn(a, g, hd, "yskn_kv4_attention_tc")) return rc;
+  if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_attention_tc: rotary width %d needs a rope table", rd);
+  return launch_attention_tc(*a, g, hd, rd, act_dtype, d_workspace, workspace_bytes, valid_tokens, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_prefill_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, const uint16_t* bv, uint16_t* o16,
+                        void* d_workspace, size_t workspace_bytes, int valid_tokens, void* cuda_stream) {
+  if (!o16) KV4_REJECT("yskn_kv4_prefill_tc: null output");
+  if (int rc = yskn_kv4_attention_tc(a, g, hd, rd, act_dtype, d_workspace, workspace_bytes, valid_tokens, cuda_stream)) return rc;
+  yskn_attn_g_combine_args c{a->pm, a->pl, a->pacc, a->splits, a->M, bv, o16, nullptr, a->nh, g};
+  return launch_combine(c, hd, act_dtype, (cudaStream_t)cuda_stream);
 }
 
 int yskn_kv4_rope_table(float* d_out, int max_ctx, float theta, int rd, void* cuda_stream) {

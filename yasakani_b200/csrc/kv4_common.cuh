@@ -52,7 +52,12 @@ int launch_group_quant(const yskn_kv_quant_args& a, int kvh, int hd, cudaStream_
 int launch_attention_scalar(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st);
 int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st);
 bool decode_mma_supports(int g, int hd, int rd, int M);
-int decode_status_fetch(int* out);   // reads and clears the device status word of the tensor-core decode kernel
+int decode_status_fetch(int* out);
+int tc_status_fetch(int* out);       // same for the tcgen05 multi-row kernel
+bool attention_tc_supports(int g, int hd, int rd, int act_dtype);
+size_t attention_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M);
+int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, void* workspace, size_t workspace_bytes,
+                        int valid_tokens, cudaStream_t st);   // reads and clears the device status word of the tensor-core decode kernel
 int launch_combine(const yskn_attn_g_combine_args& a, int hd, int act_dtype, cudaStream_t st);
 int launch_local_triple(const yskn_attn_g_combine_args& a, int hd, float* d_triple, cudaStream_t st);
 int launch_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd, const uint16_t* bv,

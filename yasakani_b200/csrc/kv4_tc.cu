@@ -1,0 +1,559 @@
+// Multi-row KV4 attention on the 5th-generation tensor cores (tcgen05 + TMEM) for sm_100a: the verify pass
+// (up to 64 query rows against a long cache) and causal prefill (thousands of rows).
+//
+// Semantics: the reference's Family-A attention for M rows (src/attention_gqa.cu:17-118, src/attention_kv4q.cu:381-448):
+// row r sits at pos = *d_pos + r, sees keys 0..pos, reads 32-token groups before its own group as int4 and its own
+// group from the fp16 shadow, K rotated at read time, V int4 per token.  Tile shapes and the split of the key range
+// follow the reference's tensor-core verify kernels in spirit (rows = (token, head) pairs packed into MMA tiles per
+// kv-head, split-K partials in the same [M][splits][Hq] layout; src/q35_fa.cu:48-303, src/q35_atx.cu:92-793).
+//
+// Two kernels.
+//  1. kv4_tc_prep_kernel dequantises the cache once per pass into a caller-owned fp16 workspace, as the reference's
+//     kv_dequant_kernel does into fp32 (src/attention_kv4q.cu:198-243): Kd = rotated int4 keys of every complete
+//     group, Vd = int4 values of every token, Ks = rotated fp16-shadow keys of the groups the new rows live in.
+//     fp32 arithmetic, one rounding to fp16.  HBM-bound byte mover: one warp per (token, kv-head).
+//  2. kv4_tc_attn_kernel: one CTA = 128 query rows ((token, head) pairs of one kv-head) x one split of the keys.
+//       warp 4      TMA producer: Q tile once, then K/V tiles of 64 keys into a 2-stage mbarrier ring
+//       warp 5      issues tcgen05.mma: S = Q.K^T (M128 N64 K16 steps, both operands K-major, 128-byte swizzle) into one
+//                   of two TMEM buffers, and O += P.V (M128 N=HD, V as MN-major operand) into TMEM; commits to mbarriers
+//       warps 0-3   one query row per thread: tcgen05.ld of the S row, masks, online softmax in the log2 domain with a
+//                   lazy rescale of O, P -> fp16 -> shared memory in the operand layout; final (m, l, O) store
+//     S of tile j+1 is issued before P.V of tile j, so the tensor pipe works while the softmax warps run.
+//     Tiles that contain a row's own group ("edge" tiles, at most two per CTA) get S twice, from Kd and from Ks, and
+//     each row picks per 32-key half: int4 keys for groups before its own, shadow keys (causally masked) for its own.
+//
+// Rows are independent of one another inside every step (an MMA output row depends on its own A row only, the lazy
+// rescale multiplies other rows by exactly 1), tiles start at multiples of 64 keys and split boundaries depend on
+// *d_pos and `splits` only, so a row's result does not depend on how many rows the pass holds.
+//
+// Every wait is bounded; a wait that runs out sets the device status word (4/5/6 = softmax / MMA / producer) and the CTA
+// frees its TMEM and returns.
+#include "kv4_common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace kv4 {
+
+__device__ int g_tc_status = 0;              // 0 ok; 4/5/6 = a bounded wait ran out in the softmax warps / MMA warp / producer
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------ prep kernel
+struct PrepP {
+  yskn_kv_layer kv; const int* d_pos; int M; int max_ctx; int kvh; const float* rope; int rd;
+  uint16_t* kd; uint16_t* vd; uint16_t* ks; int ks_rows; int valid_tokens;
+};
+
+// One warp per (token t, kv-head); lane owns HD/32 contiguous channels.
+template <int HD>
+__global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
+  constexpr int CPL = HD / 32;
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int t = (int)(w / P.kvh), head = (int)(w % P.kvh);
+  const int pos0 = *P.d_pos, end = pos0 + P.M;                      // tokens [0, end) exist
+  const int end64 = min(P.max_ctx, (end + 63) / 64 * 64);           // tiles read whole 64-key rows: keep V finite there
+  if (t >= end64) return;
+  const int c0 = lane * CPL, half = P.rd / 2, lanes_off = half > 0 ? half / CPL : 1;
+  const bool rot = c0 < P.rd, lower = c0 < half;
+  const size_t row = (size_t)head * P.max_ctx + t;
+  auto store = [&](uint16_t* dst, const float (&v)[CPL]) {
+    #pragma unroll
+    for (int e = 0; e < CPL; e += 2) *reinterpret_cast<uint32_t*>(dst + e) = (uint32_t)f2h(v[e]) | ((uint32_t)f2h(v[e + 1]) << 16);
+  };
+  auto rotate = [&](float (&k)[CPL]) {
+    if (P.rd <= 0) return;
+    #pragma unroll
+    for (int e = 0; e < CPL; ++e) {
+      const float other = __shfl_xor_sync(0xffffffffu, k[e], lanes_off);
+      if (rot) {
+        const float2 cs = *reinterpret_cast<const float2*>(P.rope + ((size_t)t * half + ((c0 + e) % half)) * 2);
+        k[e] = lower ? (k[e] * cs.x - other * cs.y) : (other * cs.y + k[e] * cs.x);
+      }
+    }
+  };
+  // ---- V: every token below `end`, zero rows up to the tile boundary
+  if (t >= P.valid_tokens) {
+    float v[CPL];
+    if (t < end) {
+      const float vs = h2f(P.kv.vscale[row]), vz = h2f(P.kv.vzero[row]);
+      const uint8_t* vb = P.kv.vq + row * (HD / 2) + c0 / 2;
+      #pragma unroll
+      for (int e = 0; e < CPL; e += 2) { const uint8_t b = vb[e / 2]; v[e] = (float)(b & 15) * vs + vz; v[e + 1] = (float)(b >> 4) * vs + vz; }
+    } else {
+      #pragma unroll
+      for (int e = 0; e < CPL; ++e) v[e] = 0.f;
+    }
+    store(P.vd + row * HD + c0, v);
+  }
+  // ---- Kd: tokens of complete groups (32g+31 < end), rotated
+  const int gi = t / 32;
+  if (gi * 32 + 31 < end && t >= (P.valid_tokens / 32) * 32) {       // a group completed since the last pass is (re)written whole
+    const size_t gb = (size_t)head * (P.max_ctx / 32) + gi;
+    const uint8_t* kb = P.kv.kq + (gb * 32 + (t & 31)) * (HD / 2) + c0 / 2;
+    float k[CPL];
+    #pragma unroll
+    for (int e = 0; e < CPL; e += 2) {
+      const uint8_t b = kb[e / 2];
+      const uint32_t s2 = *reinterpret_cast<const uint32_t*>(P.kv.kscale + gb * HD + c0 + e);
+      const uint32_t z2 = *reinterpret_cast<const uint32_t*>(P.kv.kzero + gb * HD + c0 + e);
+      k[e] = __fadd_rn(__fmul_rn((float)(b & 15), h2f((uint16_t)s2)), h2f((uint16_t)z2));
+      k[e + 1] = __fadd_rn(__fmul_rn((float)(b >> 4), h2f((uint16_t)(s2 >> 16))), h2f((uint16_t)(z2 >> 16)));
+    }
+    rotate(k);
+    store(P.kd + row * HD + c0, k);
+  }
+  // ---- Ks: rotated shadow keys from the 64-key tile that holds *d_pos onwards (row index relative to that tile)
+  const int ks0 = (pos0 / 64) * 64;
+  if (t >= ks0 && t - ks0 < P.ks_rows) {
+    float k[CPL];
+    if (t < end) {
+      const uint16_t* sh = P.kv.kshadow + row * HD + c0;
+      #pragma unroll
+      for (int e = 0; e < CPL; e += 2) { const uint32_t u = *reinterpret_cast<const uint32_t*>(sh + e); k[e] = h2f((uint16_t)u); k[e + 1] = h2f((uint16_t)(u >> 16)); }
+      rotate(k);
+    } else {
+      #pragma unroll
+      for (int e = 0; e < CPL; ++e) k[e] = 0.f;
+      rotate(k);                                                     // keeps the shuffles convergent
+    }
+    store(P.ks + ((size_t)head * P.ks_rows + (t - ks0)) * HD + c0, k);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------------ PTX helpers
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
+constexpr float TC_LOG2E = 1.4426950408889634f, TC_LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {          // bounded; false = gave up
+  for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) if (bar_try(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(m), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, int x, int y, int z, int w, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+               ::"r"(dst), "l"(m), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar) : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100): start address, leading and stride byte offsets
+// in 16-byte units.  K-major operands: 8-row x 128-byte atoms, SBO = 1024 between atoms along M/N, LBO unused.
+// MN-major operands: 128-byte rows hold 64 M/N-elements of one k; SBO = 1024 between groups of 8 k; LBO = distance
+// between 64-element blocks along M/N.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: fp16 A and B, fp32 accumulator, A K-major, B K-major or MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool b_mn_major) {
+  return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                 "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+                 "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  #pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])),
+                 "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])),
+                 "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+                 "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+                 "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])),
+                 "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+                 "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31])) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float tc_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ uint32_t tc_pack(float lo, float hi) { uint32_t d; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo)); return d; }
+
+// ------------------------------------------------------------------------------------------------ attention kernel
+constexpr int TC_BN = 64;                                  // keys per tile
+constexpr int TC_THREADS = 192;                            // warps 0-3 softmax, 4 producer, 5 MMA issuer
+
+template <int HD> struct TcLay {
+  static constexpr int KBLK = HD / 64;                     // 64-channel (128-byte) operand blocks
+  static constexpr int Q_BLOCK = 128 * 128;                // 128 rows x 128 bytes
+  static constexpr int Q_BYTES = KBLK * Q_BLOCK;
+  static constexpr int KV_BLOCK = TC_BN * 128;             // 64 keys x 128 bytes
+  static constexpr int KV_TILE = KBLK * KV_BLOCK;
+  static constexpr int STAGE = 2 * KV_TILE;                // K then V
+  static constexpr int P_BYTES = 128 * TC_BN * 2;
+  static constexpr int OFF_Q = 0, OFF_ST = Q_BYTES, OFF_P = OFF_ST + 2 * STAGE, OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256;
+  static constexpr uint32_t TM_S0 = 0, TM_S1 = TC_BN, TM_O = 2 * TC_BN;   // TMEM columns
+  static_assert(TOTAL <= 227 * 1024, "shared memory budget");
+  static constexpr int TM_COLS = 2 * TC_BN + HD <= 256 ? 256 : 512;  // allocation must be a power of two
+  static_assert(2 * TC_BN + HD <= 512, "TMEM columns");
+};
+
+struct TcP {
+  const int* d_pos; int M, splits, G, nh, max_ctx, ks_rows; float qscale;
+  float* pm; float* pl; float* pacc;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapKd,
+                   const __grid_constant__ CUtensorMap mapVd, const __grid_constant__ CUtensorMap mapKs, const TcP P) {
+  using L = TcLay<HD>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sb = s_u32(smem);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // barriers (8 bytes each): full[2] empty[2] qfull sready[2] sfree[2] pready pvdone | tmem slot | abort flag
+  const uint32_t B0 = sb + L::OFF_BAR;
+  const uint32_t b_full = B0, b_empty = B0 + 16, b_q = B0 + 32, b_sready = B0 + 40, b_sfree = B0 + 56, b_pready = B0 + 72, b_pvdone = B0 + 80;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 96);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 100);
+
+  // ---- geometry (uniform over the CTA)
+  const int G = P.G, TOK = 128 / G, kvh = blockIdx.z, S = P.splits, split = blockIdx.y;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;               // heaviest query tiles first
+  const int tok0 = qt * TOK, ntok = min(TOK, P.M - tok0);
+  const int pos0 = *P.d_pos;
+  const int pmax = pos0 + tok0 + ntok - 1;                           // last key any row of this tile sees
+  const int nt_all = pmax / TC_BN + 1;
+  const int per = (pos0 / TC_BN + 1 + S - 1) / S;                    // split width in tiles: a function of *d_pos and S only
+  const int j0 = min(split * per, nt_all), j1 = split == S - 1 ? nt_all : min((split + 1) * per, nt_all);
+  const int n = j1 - j0;
+  const int jb = ((pos0 + tok0) / 32) / 2;                           // tiles below jb hold only groups before every row's own group
+  const int nbulk = max(0, min(n, jb - j0));
+  const int ks0 = (pos0 / TC_BN) * TC_BN;
+
+  if (sb & 1023u) { if (threadIdx.x == 0) atomicExch(&g_tc_status, 3); return; }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) { bar_init(b_full + 8 * i, 1); bar_init(b_empty + 8 * i, 1); bar_init(b_sready + 8 * i, 1); bar_init(b_sfree + 8 * i, 4); }
+    bar_init(b_q, 1); bar_init(b_pready, 4); bar_init(b_pvdone, 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 96), "n"(L::TM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    // ======================================================================= TMA producer
+    if (lane == 0 && n > 0) {
+      bar_expect_tx(b_q, L::KBLK * G * TOK * 128);
+      for (int kb = 0; kb < L::KBLK; ++kb) tma_load_4d(sb + L::OFF_Q + kb * L::Q_BLOCK, &mapQ, 64 * kb, 0, kvh, tok0, b_q);
+      int it = 0; bool ok = true;
+      for (int i = 0; i < n && ok; ++i) {
+        const int j = j0 + i;
+        for (int half = 0; half < (i >= nbulk ? 2 : 1) && ok; ++half, ++it) {       // item A: Kd+Vd; item B (edge tiles): Ks
+          const int st = it & 1;
+          if (it >= 2 && !bar_wait(b_empty + 8 * st, ((it >> 1) - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
+          if (*s_abort) { ok = false; break; }
+          const uint32_t dst = sb + L::OFF_ST + st * L::STAGE, bar = b_full + 8 * st;
+          if (half == 0) {
+            bar_expect_tx(bar, 2 * L::KV_TILE);
+            const int row = kvh * P.max_ctx + j * TC_BN;
+            for (int kb = 0; kb < L::KBLK; ++kb) {
+              tma_load_2d(dst + kb * L::KV_BLOCK, &mapKd, 64 * kb, row, bar);
+              tma_load_2d(dst + L::KV_TILE + kb * L::KV_BLOCK, &mapVd, 64 * kb, row, bar);
+            }
+          } else {
+            bar_expect_tx(bar, L::KV_TILE);
+            const int row = kvh * P.ks_rows + j * TC_BN - ks0;
+            for (int kb = 0; kb < L::KBLK; ++kb) tma_load_2d(dst + kb * L::KV_BLOCK, &mapKs, 64 * kb, row, bar);
+          }
+        }
+      }
+      if (*s_abort)                                                  // let the last copies land before the CTA ends
+        for (int k = max(0, it - 2); k < it; ++k) bar_wait(b_full + 8 * (k & 1), (k >> 1) & 1);
+    }
+  } else if (warp == 5) {
+    // ======================================================================= MMA issuer (one thread)
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t ID_S = instr_desc(128, TC_BN, false), ID_PV = instr_desc(128, HD, true);
+      bool ok = true;
+      int it = 0;                                                    // load item counter (same order as the producer's)
+      int swr[2] = {0, 0};                                           // how often each S buffer has been written
+      auto fail = [&]() { atomicExch(&g_tc_status, 5); *s_abort = 1; ok = false; };
+      auto issue_s = [&](int item, int buf) {                        // S[buf] = Q . K(item)^T
+        const int st = item & 1;
+        if (!bar_wait(b_full + 8 * st, (item >> 1) & 1)) { fail(); return; }
+        if (swr[buf] > 0 && !bar_wait(b_sfree + 8 * buf, (swr[buf] - 1) & 1)) { fail(); return; }
+        tc_fence_after();
+        const uint32_t kaddr = sb + L::OFF_ST + st * L::STAGE;
+        #pragma unroll
+        for (int kb = 0; kb < L::KBLK; ++kb)
+          #pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma(tmem + (buf ? L::TM_S1 : L::TM_S0), smem_desc(sb + L::OFF_Q + kb * L::Q_BLOCK + ks * 32, 16, 1024),
+                 smem_desc(kaddr + kb * L::KV_BLOCK + ks * 32, 16, 1024), ID_S, (kb | ks) ? 1u : 0u);
+        umma_commit(b_sready + 8 * buf);
+        ++swr[buf];
+      };
+      auto issue_pv = [&](int tile_i, int item_v) {                  // O (+)= P . V(item_v)
+        if (!bar_wait(b_pready, tile_i & 1)) { fail(); return; }
+        tc_fence_after();
+        const uint32_t vaddr = sb + L::OFF_ST + (item_v & 1) * L::STAGE + L::KV_TILE;
+        #pragma unroll
+        for (int ks = 0; ks < TC_BN / 16; ++ks)
+          umma(tmem + L::TM_O, smem_desc(sb + L::OFF_P + ks * 32, 16, 1024), smem_desc(vaddr + ks * 2048, L::KV_BLOCK, 1024), ID_PV,
+               (tile_i | ks) ? 1u : 0u);
+      };
+      if (!bar_wait(b_q, 0)) fail();
+      // bulk tiles: S of the next tile is in flight while the softmax warps work on this one
+      if (ok && nbulk > 0) issue_s(0, 0);
+      for (int i = 0; i < nbulk && ok; ++i) {
+        if (i + 1 < nbulk) issue_s(i + 1, (i + 1) & 1);
+        if (!ok) break;
+        issue_pv(i, i);
+        if (!ok) break;
+        umma_commit(b_empty + 8 * (i & 1));                          // K and V of item i are free once these MMAs are done
+        umma_commit(b_pvdone);
+      }
+      it = nbulk;
+      // edge tiles: S from the int4 keys and from the shadow keys, one after the other
+      for (int i = nbulk; i < n && ok; ++i, it += 2) {
+        issue_s(it, 0); if (!ok) break;
+        issue_s(it + 1, 1); if (!ok) break;
+        issue_pv(i, it); if (!ok) break;
+        umma_commit(b_empty + 8 * (it & 1));
+        umma_commit(b_empty + 8 * ((it + 1) & 1));
+        umma_commit(b_pvdone);
+      }
+    }
+  } else {
+    // ======================================================================= softmax warps: one query row per thread
+    const int rho = warp * 32 + lane;                                // row of the tile = TMEM lane
+    const int tok = tok0 + rho / G, head = rho % G;
+    const bool valid = rho < TOK * G && tok < P.M;
+    const int pr = pos0 + tok, cr = pr / 32;                         // row position and its own group
+    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+    const float cs = P.qscale * TC_LOG2E;
+    float m = -1e30f, l = 0.f;
+    int srd[2] = {0, 0};                                             // how often each S buffer has been read
+    bool ok = true;
+    for (int i = 0; i < n && ok; ++i) {
+      const int j = j0 + i;
+      const bool edge = i >= nbulk;
+      const int buf = edge ? 0 : (i & 1);
+      float x[TC_BN];
+      if (!bar_wait(b_sready + 8 * buf, srd[buf] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
+      tc_fence_after();
+      {
+        float a[32], b[32];
+        tmem_ld32(trow + (buf ? L::TM_S1 : L::TM_S0), a); tmem_ld32(trow + (buf ? L::TM_S1 : L::TM_S0) + 32, b);
+        #pragma unroll
+        for (int k = 0; k < 32; ++k) { x[k] = a[k] * cs; x[32 + k] = b[k] * cs; }
+      }
+      ++srd[buf];
+      if (edge) {
+        if (!bar_wait(b_sready + 8, srd[1] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
+        tc_fence_after();
+        float a[32], b[32];
+        tmem_ld32(trow + L::TM_S1, a); tmem_ld32(trow + L::TM_S1 + 32, b);
+        ++srd[1];
+        // per 32-key half: group before the row's own -> int4 keys; own group -> shadow keys up to the row; later -> nothing
+        const int g0 = 2 * j, g1 = 2 * j + 1, tb = j * TC_BN;
+        #pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          x[k] = !valid ? -INFINITY : g0 < cr ? x[k] : (g0 == cr && tb + k <= pr) ? a[k] * cs : -INFINITY;
+          x[32 + k] = !valid ? -INFINITY : g1 < cr ? x[32 + k] : (g1 == cr && tb + 32 + k <= pr) ? b[k] * cs : -INFINITY;
+        }
+      } else if (!valid) {
+        #pragma unroll
+        for (int k = 0; k < TC_BN; ++k) x[k] = -INFINITY;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { bar_arrive(b_sfree + 8 * buf); if (edge) bar_arrive(b_sfree + 8); }
+      // ---- online softmax, log2 domain, lazy rescale (the running max may lag the true one by up to 2^8)
+      float tmax = x[0];
+      #pragma unroll
+      for (int k = 1; k < TC_BN; ++k) tmax = fmaxf(tmax, x[k]);
+      const bool bump = tmax > m + 8.f;
+      const float mn = bump ? tmax : m, alpha = bump ? tc_ex2(m - mn) : 1.f;
+      m = mn; l *= alpha;
+      uint32_t pk[TC_BN / 2];
+      float ls = 0.f;
+      #pragma unroll
+      for (int k = 0; k < TC_BN; k += 2) {
+        const float p0 = tc_ex2(x[k] - m), p1 = tc_ex2(x[k + 1] - m);      // exp2(-inf) = 0 for masked keys
+        ls += p0 + p1; pk[k / 2] = tc_pack(p0, p1);
+      }
+      l += ls;
+      // ---- O and the P buffer are free once P.V of the previous tile is done
+      if (i > 0 && !bar_wait(b_pvdone, (i - 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
+      tc_fence_after();
+      if (i > 0 && __any_sync(0xffffffffu, bump)) {                  // rows that did not bump multiply by exactly 1
+        #pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          float o[32];
+          tmem_ld32(trow + L::TM_O + 32 * c, o);
+          #pragma unroll
+          for (int k = 0; k < 32; ++k) o[k] *= alpha;
+          tmem_st32(trow + L::TM_O + 32 * c, o);
+        }
+        tmem_st_wait();
+      }
+      {
+        const uint32_t prow = sb + L::OFF_P + rho * 128;
+        #pragma unroll
+        for (int c = 0; c < 8; ++c)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + ((c ^ (rho & 7)) << 4)), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
+                       "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) bar_arrive(b_pready);
+    }
+    // ---- this split's partial: (m, l, O) per (row, head); m back in natural-log units
+    if (ok && n > 0 && !bar_wait(b_pvdone, (n - 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; }
+    tc_fence_after();
+    if (ok && !*s_abort) {
+      const size_t pidx = ((size_t)tok * S + split) * P.nh + kvh * G + head;
+      if (valid) { P.pm[pidx] = (n > 0 && m > -1e29f) ? m * TC_LN2 : -1e30f; P.pl[pidx] = n > 0 ? l : 0.f; }
+      #pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        float o[32];
+        if (n > 0) tmem_ld32(trow + L::TM_O + 32 * c, o);
+        else {
+          #pragma unroll
+          for (int k = 0; k < 32; ++k) o[k] = 0.f;
+        }
+        if (valid) {
+          float4* dst = reinterpret_cast<float4*>(P.pacc + pidx * HD + 32 * c);
+          #pragma unroll
+          for (int k = 0; k < 8; ++k) dst[k] = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(L::TM_COLS) : "memory");
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn tc_encode_fn() {
+  static EncodeFn fn = [] {
+    void* p = nullptr; cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// fp16 array viewed as [rows][hd]; box = 64 channels x 64 rows, 128-byte swizzle.
+bool tc_map_rows(CUtensorMap* out, const void* base, uint64_t rows, int hd) {
+  EncodeFn fn = tc_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)hd, rows}, strides[1] = {(cuuint64_t)hd * 2};
+  const cuuint32_t box[2] = {64, 64}, es[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// q16 [M][kvh][G][hd] viewed as 4-D; box = 64 channels x G heads x 1 kv-head x TOK tokens: rows land as (token, head).
+bool tc_map_q(CUtensorMap* out, const void* q16, int M, int kvh, int G, int hd) {
+  EncodeFn fn = tc_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)G, (cuuint64_t)kvh, (cuuint64_t)M};
+  const cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)G * hd * 2, (cuuint64_t)kvh * G * hd * 2};
+  const cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)(128 / G)}, es[4] = {1, 1, 1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(q16), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct TcWs { uint16_t* kd; uint16_t* vd; uint16_t* ks; int ks_rows; size_t bytes; };
+TcWs carve(void* ws, int kvh, int hd, int max_ctx, int M) {
+  TcWs w; const size_t plane = (size_t)kvh * max_ctx * hd * 2;
+  w.ks_rows = 64 * ((M + 63) / 64 + 1);
+  w.kd = static_cast<uint16_t*>(ws);
+  w.vd = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(ws) + plane);
+  w.ks = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(ws) + 2 * plane);
+  w.bytes = 2 * plane + (size_t)kvh * w.ks_rows * hd * 2;
+  return w;
+}
+
+template <int HD>
+int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int valid_tokens, cudaStream_t st) {
+  using L = TcLay<HD>;
+  PrepP pp{a.kv, a.d_pos, a.M, a.max_ctx, a.kvh, a.rope, rd, w.kd, w.vd, w.ks, w.ks_rows, valid_tokens};
+  const long long warps = (long long)a.max_ctx * a.kvh;
+  kv4_tc_prep_kernel<HD><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(pp);
+  if (int rc = launch_status("kv4_tc_prep_kernel")) return rc;
+  CUtensorMap mq, mkd, mvd, mks;
+  const uint64_t rows = (uint64_t)a.kvh * a.max_ctx;
+  if (!tc_map_q(&mq, a.q16, a.M, a.kvh, g, HD) || !tc_map_rows(&mkd, w.kd, rows, HD) || !tc_map_rows(&mvd, w.vd, rows, HD) ||
+      !tc_map_rows(&mks, w.ks, (uint64_t)a.kvh * w.ks_rows, HD))
+    KV4_REJECT("yskn_kv4_attention_tc: cuTensorMapEncodeTiled failed or is unavailable");
+  auto kern = kv4_tc_attn_kernel<HD>;
+  static bool attr = false;
+  if (!attr) { KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL)); attr = true; }
+  const int tok = 128 / g, qtiles = (a.M + tok - 1) / tok;
+  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc};
+  kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mq, mkd, mvd, mks, P);
+  return launch_status("kv4_tc_attn_kernel");
+}
+
+}  // namespace
+
+bool attention_tc_supports(int g, int hd, int rd, int act_dtype) {
+  return g >= 1 && g <= 8 && (hd == 256 || hd == 128) && rd >= 0 && rd <= hd && rd % 2 == 0 && act_dtype == YSKN_KV4_F16 &&
+         (rd == 0 || ((rd / 2) % (hd / 32) == 0 && (((rd / 2) / (hd / 32)) & ((rd / 2) / (hd / 32) - 1)) == 0));
+}
+
+size_t attention_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M) { return carve(nullptr, kvh, hd, max_ctx, M).bytes; }
+
+int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, void* workspace, size_t workspace_bytes,
+                        int valid_tokens, cudaStream_t st) {
+  if (!attention_tc_supports(g, hd, rd, act_dtype))
+    KV4_REJECT("yskn_kv4_attention_tc: unsupported (g %d, hd %d, rd %d, act_dtype %d): fp16 activations, hd 128/256", g, hd, rd, act_dtype);
+  const TcWs w = carve(workspace, a.kvh, hd, a.max_ctx, a.M);
+  if (!workspace || workspace_bytes < w.bytes) KV4_REJECT("yskn_kv4_attention_tc: workspace of %zu bytes needed, %zu given", w.bytes, workspace_bytes);
+  if (((uintptr_t)workspace | (uintptr_t)a.q16) & 15) KV4_REJECT("yskn_kv4_attention_tc: workspace and q16 must be 16-byte aligned");
+  if (valid_tokens < 0) valid_tokens = 0;
+  return hd == 256 ? launch_tc_hd<256>(a, g, rd, w, valid_tokens, st) : launch_tc_hd<128>(a, g, rd, w, valid_tokens, st);
+}
+
+int tc_status_fetch(int* out) {
+  int v = 0;
+  KV4_CUDA(cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)));
+  const int zero = 0;
+  KV4_CUDA(cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int)));
+  *out = v; return 0;
+}
+
+}  // namespace kv4

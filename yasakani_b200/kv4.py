@@ -165,6 +165,30 @@ def launch_attention_prefill(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, p
                                       _ptr(o16), _stream(stream)), "yskn_kv4_prefill")
 
 
+def tc_workspace(kv: KvLayer, M: int) -> torch.Tensor:
+    """Caller-owned fp16 workspace of the tensor-core multi-row path (the reference's KvF32 arrays, src/args.hpp:37)."""
+    n = _lib.load().yskn_kv4_tc_workspace_bytes(kv.hkv, kv.hd, kv.max_ctx, M)
+    if n == 0:
+        raise ValueError("unsupported shape for the tensor-core path")
+    return torch.empty(n, dtype=torch.uint8, device=kv.device)
+
+
+def launch_attention_tc(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float, rd: int,
+                        workspace: torch.Tensor, valid_tokens: int = 0, stream=None) -> None:
+    """launch_kv_dequant + launch_attention_f32 (src/attention_kv4q.cu:198-285) on tcgen05: partials for M rows."""
+    a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
+    check(_lib.load().yskn_kv4_attention_tc(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), _ptr(workspace),
+                                           workspace.numel(), valid_tokens, _stream(stream)), "yskn_kv4_attention_tc")
+
+
+def launch_attention_prefill_tc(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float, rd: int,
+                                o16, workspace: torch.Tensor, bv=None, valid_tokens: int = 0, stream=None) -> None:
+    """launch_attention_prefill_f32 (src/attention_kv4q.cu:287-323) on tcgen05: M appended rows, merged to o16."""
+    a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
+    check(_lib.load().yskn_kv4_prefill_tc(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), bv.data_ptr() if bv is not None else None,
+                                         _ptr(o16), _ptr(workspace), workspace.numel(), valid_tokens, _stream(stream)), "yskn_kv4_prefill_tc")
+
+
 def launch_local_triple(pm, pl, pacc, splits: int, M: int, nh: int, hd: int, triple, stream=None) -> None:
     """Fold one shard's partials into (m, l, O) per (row, head): float [M][nh][hd+2]."""
     a = AttnGCombineArgsC(pm.data_ptr(), pl.data_ptr(), pacc.data_ptr(), splits, M, None, None, None, nh, 1)
