@@ -144,6 +144,21 @@ YSKN_KV4_API int yskn_kv4_merge_triples(const float* d_triples, int ranks, int M
                                         const uint16_t* bv, const uint16_t* gate, uint16_t* o16, int act_dtype,
                                         void* cuda_stream);
 
+/* No counterpart in the reference (its launchers always take caller scratch, src/engine.cpp:560-561).
+ * One decode step -- split-K attention of ONE query row plus the merge to o16 -- for callers that cannot get device
+ * memory for the pm/pl/pacc partials: a plugin host without an allocator, or a serving loop where cudaMalloc is off
+ * limits because it stalls the whole GPU.  The partials live in a fixed array inside the library (2,113,536 bytes per
+ * GPU that loads it, held until exit), so the call allocates nothing, on the host side of CUDA or through any library.
+ * Limit: splits * nh * (hd + 2) <= 528,384 floats (for instance 64 splits x 32 heads x head_dim 256); anything
+ * larger is rejected with -1 and a message.  The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current) and should therefore be made before any stream capture; later
+ * calls only enqueue.  All calls on a device share the array: calls that overlap on the GPU race, run them in order.
+ * Nothing needs clearing between calls, every partial slot is rewritten before it is read.  Arguments as for
+ * yskn_kv4_attention / yskn_kv4_combine with M = 1, no bias, no gate. */
+YSKN_KV4_API int yskn_kv4_decode_noalloc(const uint16_t* q16, const yskn_kv_layer* kv, int max_ctx, const int* d_pos, int splits,
+                                         const float* rope, int kvh, int nh, int hd, int rd, float qscale, int act_dtype,
+                                         uint16_t* o16, void* cuda_stream);
+
 /* Host-pointer probe in the style of the reference's kernel probes (yskn_atxpk_bench, src/kvx_probe.cu:190-330):
  * uploads a packed cache and M query rows, runs attention + combine `reps` times on the current device,
  * downloads o16 and, if ms_out != NULL, the per-repetition device times in milliseconds (ms_out[reps]).

@@ -58,6 +58,8 @@ PROTOTYPES = {
     "yskn_kv4_local_triple": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_void_p, C.c_void_p]),
     "yskn_kv4_merge_triples": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_int, C.c_void_p]),
+    "yskn_kv4_decode_noalloc": (C.c_int, [C.c_void_p, C.POINTER(KvLayerC), C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int,
+                                          C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_void_p]),
     "yskn_kv4_attention_host": (C.c_int, [C.c_void_p, C.POINTER(KvLayerC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                           C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_int,
                                           C.c_void_p]),

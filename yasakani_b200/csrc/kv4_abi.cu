@@ -137,6 +137,11 @@ int yskn_kv4_merge_triples(const float* d_triples, int ranks, int M, int nh, int
   return launch_merge_triples(d_triples, ranks, M, nh, g, hd, bv, gate, o16, act_dtype, (cudaStream_t)cuda_stream);
 }
 
+int yskn_kv4_decode_noalloc(const uint16_t* q16, const yskn_kv_layer* kv, int max_ctx, const int* d_pos, int splits, const float* rope,
+                            int kvh, int nh, int hd, int rd, float qscale, int act_dtype, uint16_t* o16, void* cuda_stream) {
+  return decode_noalloc(q16, kv, max_ctx, d_pos, splits, rope, kvh, nh, hd, rd, qscale, act_dtype, o16, (cudaStream_t)cuda_stream);
+}
+
 int yskn_kv4_attention_host(const uint16_t* h_q16, const yskn_kv_layer* h_kv, int max_ctx, int M, int pos0, int splits,
                             const float* h_rope, int kvh, int nh, int hd, int rd, float qscale, int act_dtype,
                             uint16_t* h_o16, int reps, float* ms_out) {

@@ -63,6 +63,9 @@ int launch_local_triple(const yskn_attn_g_combine_args& a, int hd, float* d_trip
 int launch_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd, const uint16_t* bv,
                          const uint16_t* gate, uint16_t* o16, int act_dtype, cudaStream_t st);
 
+int decode_noalloc(const uint16_t* q16, const yskn_kv_layer* kv, int max_ctx, const int* d_pos, int splits, const float* rope,
+                   int kvh, int nh, int hd, int rd, float qscale, int act_dtype, uint16_t* o16, cudaStream_t st);
+
 // Which attention kernel yskn_kv4_attention picks; set through yskn_kv4_set_algo (tests compare paths).
 enum Algo { ALGO_AUTO = 0, ALGO_SCALAR = 1, ALGO_MMA = 2 };
 

@@ -202,5 +202,14 @@ def launch_merge_triples(triples, ranks: int, M: int, nh: int, g: int, hd: int, 
                                             _stream(stream)), "yskn_kv4_merge_triples")
 
 
+def decode_noalloc(q16, kv: KvLayer, d_pos, splits: int, rope, nh: int, qscale: float, rd: int, o16, stream=None) -> None:
+    """One decode step with the split-K scratch held inside the library (no buffer to allocate); M = 1 and
+    splits * nh * (hd + 2) <= 528,384 floats.  Calls on one GPU share that scratch and must not overlap."""
+    s = kv.struct()
+    check(_lib.load().yskn_kv4_decode_noalloc(_ptr(q16), C.byref(s), kv.max_ctx, _ptr(d_pos), splits, rope.data_ptr() if rope is not None else None,
+                                             kv.hkv, nh, kv.hd, rd, C.c_float(qscale), _dtype_code(q16), _ptr(o16), _stream(stream)),
+          "yskn_kv4_decode_noalloc")
+
+
 def default_qscale(hd: int) -> float:
     return 1.0 / math.sqrt(hd)
