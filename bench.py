@@ -187,14 +187,14 @@ def run_ours(args, rank, world, local_rank):
     o_host = torch.empty((1, shape.hq, shape.hd), dtype=torch.float16).pin_memory()
 
     def step(d):
-        d.local_step(q_dev)
         if world > 1:
+            d.local_step(q_dev)
             gather_triples(d.mine, d.gathered)
             d.merge()
         else:
-            kv4.launch_attn_combine_gqa(d.pm, d.pl, d.pacc, splits, 1, d.o16, shape.hq, shape.g)
+            kv4.launch_decode(q_dev, d.layer, 1, d.d_pos, splits, d.pm, d.pl, d.pacc, rope, shape.hq, shape.qscale, shape.rd, d.o16)
 
-    launches_per_step = 3 if world > 1 else 2
+    launches_per_step = 3 if world > 1 else 2          # attention, merge (N=1); attention, triple, merge of triples (N>1)
 
     # one CUDA graph per cache copy: the step is launch-bound otherwise (a few 10 us of kernels)
     side = torch.cuda.Stream(device=dev)

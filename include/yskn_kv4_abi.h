@@ -109,6 +109,12 @@ YSKN_KV4_API int yskn_kv4_attention(const yskn_attn_g_args* a, int g, int hd, in
  * (the sign/FWHT/int8 preparation of the next GEMV input is the caller's). act_dtype applies to o16 and gate. */
 YSKN_KV4_API int yskn_kv4_combine(const yskn_attn_g_combine_args* a, int hd, int act_dtype, void* cuda_stream);
 
+/* yskn_kv4_attention followed by yskn_kv4_combine in one call: the merge kernel is launched with programmatic stream
+ * serialization (the reference's PDL launches, src/pdl.cuh:23-30), so its launch latency hides behind the attention
+ * kernel.  `c->pm/pl/pacc/splits/M/nh/g` must describe the same scratch as `a`. */
+YSKN_KV4_API int yskn_kv4_decode(const yskn_attn_g_args* a, const yskn_attn_g_combine_args* c, int g, int hd, int rd, int act_dtype,
+                                 void* cuda_stream);
+
 /* launch_attention_prefill, src/attention_kv4q.cu:381-453: attention of M new rows whose K/V are already
  * appended, merged in one call to o16 (+ optional bias bv).  `a->pm/pl/pacc` must hold `splits` slots per
  * (row, head) as for yskn_kv4_attention. */
@@ -139,6 +145,9 @@ YSKN_KV4_API int yskn_kv4_prefill_tc(const yskn_attn_g_args* a, int g, int hd, i
  * [ranks][M][nh][HD+2] into o16 with the same arithmetic as yskn_kv4_combine. */
 YSKN_KV4_API int yskn_kv4_attention_shard(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype,
                                           int shard_start, int shard_len, void* cuda_stream);
+/* yskn_kv4_attention_shard + yskn_kv4_local_triple in one call (same launch form as yskn_kv4_decode). */
+YSKN_KV4_API int yskn_kv4_decode_shard_triple(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, int shard_start,
+                                              int shard_len, float* d_triple, void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_local_triple(const yskn_attn_g_combine_args* a, int hd, float* d_triple, void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd,
                                         const uint16_t* bv, const uint16_t* gate, uint16_t* o16, int act_dtype,

@@ -211,3 +211,21 @@ def test_shards_merge_to_the_unsharded_result(oracle, algo, world):
     assert kv4.device_status() == 0
     want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
     assert_close(o16.float().cpu().numpy(), want, f"{world} shards")
+
+
+@pytest.mark.parametrize("shape,ctx,M,splits", [(synth.C2, 9000, 1, 37), (synth.C2, 300, 2, 5), (synth.C1, 2000, 1, 16), (synth.Shape(8, 1, 64, 64, 1e4), 500, 1, 6)])
+def test_fused_decode_equals_attention_plus_merge(oracle, shape, ctx, M, splits):
+    """yskn_kv4_decode (one launch where covered) against the two-launch sequence, twice in a row (the arrival counters reset themselves)."""
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, M, seed=39)
+    g = torch.Generator().manual_seed(2)
+    bv = torch.randn((shape.hkv, shape.hd), generator=g).half().cuda(); gate = torch.randn((M, shape.hq, shape.hd), generator=g).half().cuda()
+    want, _ = gpu_attention(kv4, layer, q, ctx, splits, rope, shape, bv=bv, gate=gate)
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    pm, pl, pacc = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
+    for _ in range(2):
+        o16 = torch.full((M, shape.hq, shape.hd), float("nan"), dtype=torch.float16, device="cuda")
+        kv4.launch_decode(q.cuda(), layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, bv=bv, gate=gate)
+        torch.cuda.synchronize()
+        assert kv4.device_status() == 0
+        got = o16.float().cpu().numpy()
+        assert np.max(np.abs(got - want)) <= 2 ** -10 * max(1.0, float(np.abs(want).max()))      # same formula; expf/FMA may move one fp16 ulp

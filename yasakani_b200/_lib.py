@@ -49,6 +49,8 @@ PROTOTYPES = {
     "yskn_kv4_group_quant": (C.c_int, [C.POINTER(KvQuantArgsC), C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_attention": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_attention_shard": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "yskn_kv4_decode": (C.c_int, [C.POINTER(AttnGArgsC), C.POINTER(AttnGCombineArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "yskn_kv4_decode_shard_triple": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "yskn_kv4_combine": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_prefill": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "yskn_kv4_tc_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),

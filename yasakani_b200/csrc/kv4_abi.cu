@@ -113,6 +113,31 @@ int yskn_kv4_attention_shard(const yskn_attn_g_args* a, int g, int hd, int rd, i
   return attention_dispatch(a, g, hd, rd, act_dtype, Shard{shard_start, shard_len}, (cudaStream_t)cuda_stream);
 }
 
+int yskn_kv4_decode(const yskn_attn_g_args* a, const yskn_attn_g_combine_args* c, int g, int hd, int rd, int act_dtype, void* cuda_stream) {
+  if (int rc = check_attn(a, g, hd, "yskn_kv4_decode")) return rc;
+  if (!c || !c->o16 || c->pm != a->pm || c->pl != a->pl || c->pacc != a->pacc || c->splits != a->splits || c->M != a->M || c->nh != a->nh || c->g != g)
+    KV4_REJECT("yskn_kv4_decode: the merge arguments must describe the attention call's scratch and shape");
+  if (act_dtype != YSKN_KV4_F16 && act_dtype != YSKN_KV4_BF16) KV4_REJECT("yskn_kv4_decode: act_dtype must be F16 or BF16");
+  if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_decode: rotary width %d needs a rope table", rd);
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  if (int rc = attention_dispatch(a, g, hd, rd, act_dtype, Shard{0, a->max_ctx}, st)) return rc;
+  return launch_combine(*c, hd, act_dtype, st);
+}
+
+int yskn_kv4_decode_shard_triple(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, int shard_start, int shard_len,
+                                 float* d_triple, void* cuda_stream) {
+  if (int rc = check_attn(a, g, hd, "yskn_kv4_decode_shard_triple")) return rc;
+  if (!d_triple) KV4_REJECT("yskn_kv4_decode_shard_triple: null output");
+  if (shard_start < 0 || shard_start % 32 || shard_len < 0 || shard_len > a->max_ctx)
+    KV4_REJECT("yskn_kv4_decode_shard_triple: shard [%d, +%d) must start on a multiple of 32 and fit max_ctx %d", shard_start, shard_len, a->max_ctx);
+  if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_decode_shard_triple: rotary width %d needs a rope table", rd);
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  const Shard sh{shard_start, shard_len};
+  if (int rc = attention_dispatch(a, g, hd, rd, act_dtype, sh, st)) return rc;
+  yskn_attn_g_combine_args c{a->pm, a->pl, a->pacc, a->splits, a->M, nullptr, nullptr, nullptr, a->nh, g};
+  return launch_local_triple(c, hd, d_triple, st);
+}
+
 int yskn_kv4_combine(const yskn_attn_g_combine_args* a, int hd, int act_dtype, void* cuda_stream) {
   if (!a) KV4_REJECT("yskn_kv4_combine: null argument struct");
   return launch_combine(*a, hd, act_dtype, (cudaStream_t)cuda_stream);

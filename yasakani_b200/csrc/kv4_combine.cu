@@ -1,13 +1,17 @@
 // Log-sum-exp merge of split-K partials (sm_100a).
 //
 // Restates the merge half of the reference's attn_combine_gqa_xform_kernel (src/attention_gqa.cu:123-134):
-//   M2 = max_s pm;  w_s = pm > -1e29 ? exp(pm - M2) : 0;  L = sum w_s*pl;  o = sum w_s*pacc (in split order);
+//   M2 = max_s pm;  w_s = pm > -1e29 ? exp(pm - M2) : 0;  L = sum w_s*pl;  o = sum w_s*pacc;
 //   y = round_f16(o / L);  y += bv[kvh][d];  y *= sigmoid(gate);  store 16-bit.
-// The same kernel, with other index maps, folds one shard's partials into an un-normalised (m, l, O) triple
-// and merges the triples gathered from all shards of a sequence-sharded decode.
+// The same kernel, with other index maps, folds one shard's partials into an un-normalised (m, l, O) triple and
+// merges the triples gathered from all shards of a sequence-sharded decode.
 //
-// One block per (head, row), one thread per channel: the pacc reads of a block are `splits` contiguous
-// HD*4-byte rows, the weights are computed once per block into shared memory.
+// The kernel is pure latency: a few hundred KB read once.  One block per (head, row) with 4*HD threads: thread
+// (q, d) owns channel d and a quarter of the splits, issues its pacc loads before anything else so that they and the
+// pm/pl loads are one round trip to L2, then the quarters are added in fixed order (0,1,2,3).  The sum over splits is
+// therefore grouped in four runs rather than strictly sequential as in the reference; the result is deterministic.
+// The launch carries the programmatic-stream-serialization attribute (the reference's PDL launches,
+// src/pdl.cuh:23-30): the grid may be scheduled while the attention kernel drains and waits in griddepcontrol.wait.
 #include "kv4_common.cuh"
 
 namespace kv4 {
@@ -20,29 +24,47 @@ struct CombineP {
   const void* bv; const void* gate; uint16_t* o16; float* triple_out;
 };
 
+constexpr int CQ = 4;                                    // split quarters per block
+constexpr int CB = 8;                                    // loads in flight per thread and batch
+
 template <int HD, int DT, bool TRIPLE_IN, bool TRIPLE_OUT>
-__global__ void __launch_bounds__(HD) kv4_combine_kernel(CombineP P) {
-  extern __shared__ float sm[];                          // [S] m, [S] l, [S] w
-  float* s_m = sm; float* s_l = sm + P.S; float* s_w = sm + 2 * P.S;
-  const int head = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
+__global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
+  extern __shared__ float sm[];                          // [S] m, [S] l, [S] w, [CQ][HD] partial sums
+  float* s_m = sm; float* s_l = sm + P.S; float* s_w = sm + 2 * P.S; float* s_part = sm + 3 * P.S;
+  const int head = blockIdx.x, r = blockIdx.y, tid = threadIdx.x, q = tid / HD, d = tid % HD;
+  const int per = (P.S + CQ - 1) / CQ, s0 = min(P.S, q * per), s1 = min(P.S, s0 + per);
   auto slot = [&](int s) -> size_t { return TRIPLE_IN ? (((size_t)s * P.M + r) * P.nh + head) * (HD + 2)
                                                       : ((size_t)r * P.S + s) * P.nh + head; };
-  for (int s = d; s < P.S; s += HD) {
-    if (TRIPLE_IN) { s_m[s] = P.triples[slot(s)]; s_l[s] = P.triples[slot(s) + 1]; }
-    else { s_m[s] = P.pm[slot(s)]; s_l[s] = P.pl[slot(s)]; }
+  auto ld_acc = [&](int s) -> float { return TRIPLE_IN ? __ldcg(P.triples + slot(s) + 2 + d) : __ldcg(P.pacc + slot(s) * HD + d); };
+  asm volatile("griddepcontrol.wait;" ::: "memory");     // the producer grid's writes are visible from here on
+
+  float v[CB];                                           // first batch of this thread's values: in flight with pm/pl
+  #pragma unroll
+  for (int k = 0; k < CB; ++k) v[k] = s0 + k < s1 ? ld_acc(s0 + k) : 0.f;
+  for (int s = tid; s < P.S; s += CQ * HD) {
+    if (TRIPLE_IN) { s_m[s] = __ldcg(P.triples + slot(s)); s_l[s] = __ldcg(P.triples + slot(s) + 1); }
+    else { s_m[s] = __ldcg(P.pm + slot(s)); s_l[s] = __ldcg(P.pl + slot(s)); }
   }
   __syncthreads();
   float M2 = -1e30f;
   for (int s = 0; s < P.S; ++s) M2 = fmaxf(M2, s_m[s]);
-  for (int s = d; s < P.S; s += HD) s_w[s] = (s_m[s] > -1e29f) ? expf(s_m[s] - M2) : 0.f;
+  for (int s = tid; s < P.S; s += CQ * HD) s_w[s] = (s_m[s] > -1e29f) ? expf(s_m[s] - M2) : 0.f;
   __syncthreads();
-  float L2 = 0.f, o = 0.f;
-  #pragma unroll 4
-  for (int s = 0; s < P.S; ++s) {
-    const float w = s_w[s];
-    const float a = TRIPLE_IN ? P.triples[slot(s) + 2 + d] : P.pacc[slot(s) * HD + d];
-    L2 += w * s_l[s]; o += w * a;
+  float o = 0.f;
+  #pragma unroll
+  for (int k = 0; k < CB; ++k) if (s0 + k < s1) o += s_w[s0 + k] * v[k];
+  for (int sb = s0 + CB; sb < s1; sb += CB) {            // more than 4*CB splits: further batches
+    #pragma unroll
+    for (int k = 0; k < CB; ++k) v[k] = sb + k < s1 ? ld_acc(sb + k) : 0.f;
+    #pragma unroll
+    for (int k = 0; k < CB; ++k) if (sb + k < s1) o += s_w[sb + k] * v[k];
   }
+  s_part[q * HD + d] = o;
+  __syncthreads();
+  if (q != 0) return;
+  o = (s_part[d] + s_part[HD + d]) + (s_part[2 * HD + d] + s_part[3 * HD + d]);
+  float L2 = 0.f;
+  for (int s = 0; s < P.S; ++s) L2 += s_w[s] * s_l[s];
   if (TRIPLE_OUT) {
     float* t = P.triple_out + ((size_t)r * P.nh + head) * (HD + 2);
     if (d == 0) { t[0] = M2; t[1] = L2; }
@@ -56,18 +78,30 @@ __global__ void __launch_bounds__(HD) kv4_combine_kernel(CombineP P) {
   P.o16[e] = act_store16<DT>(y);
 }
 
+template <int HD, int DT, bool TI, bool TO>
+int launch_k(const CombineP& P, size_t smem, cudaStream_t st) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(P.nh, P.M); cfg.blockDim = dim3(CQ * HD); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  KV4_CUDA(cudaLaunchKernelEx(&cfg, kv4_combine_kernel<HD, DT, TI, TO>, P));
+  return 0;
+}
+
 template <bool TI, bool TO> int launch_p(const CombineP& P, int hd, int dt, cudaStream_t st, const char* who) {
   if (P.S <= 0 || P.M <= 0 || P.nh <= 0 || P.g <= 0) KV4_REJECT("%s: bad arguments (splits %d, M %d, nh %d, g %d)", who, P.S, P.M, P.nh, P.g);
-  const dim3 grid(P.nh, P.M); const size_t smem = (size_t)3 * P.S * sizeof(float);
+  if (P.M > 65535) KV4_REJECT("%s: M %d exceeds the grid limit", who, P.M);
+  const size_t smem = ((size_t)3 * P.S + (size_t)CQ * hd) * sizeof(float);
   if (smem > 48 * 1024) KV4_REJECT("%s: too many partials per row (%d)", who, P.S);
-#define KV4_GO(HD_, DT_) kv4_combine_kernel<HD_, DT_, TI, TO><<<grid, HD_, smem, st>>>(P)
   const bool bf = dt == YSKN_KV4_BF16;
   if (dt != YSKN_KV4_F16 && dt != YSKN_KV4_BF16) KV4_REJECT("%s: act_dtype must be F16 or BF16", who);
-  if (hd == 256) { if (bf) KV4_GO(256, YSKN_KV4_BF16); else KV4_GO(256, YSKN_KV4_F16); }
-  else if (hd == 128) { if (bf) KV4_GO(128, YSKN_KV4_BF16); else KV4_GO(128, YSKN_KV4_F16); }
-  else if (hd == 64) { if (bf) KV4_GO(64, YSKN_KV4_BF16); else KV4_GO(64, YSKN_KV4_F16); }
+  int rc;
+  if (hd == 256) rc = bf ? launch_k<256, YSKN_KV4_BF16, TI, TO>(P, smem, st) : launch_k<256, YSKN_KV4_F16, TI, TO>(P, smem, st);
+  else if (hd == 128) rc = bf ? launch_k<128, YSKN_KV4_BF16, TI, TO>(P, smem, st) : launch_k<128, YSKN_KV4_F16, TI, TO>(P, smem, st);
+  else if (hd == 64) rc = bf ? launch_k<64, YSKN_KV4_BF16, TI, TO>(P, smem, st) : launch_k<64, YSKN_KV4_F16, TI, TO>(P, smem, st);
   else KV4_REJECT("%s: unsupported head_dim %d (64, 128, 256)", who, hd);               // src/attention_gqa.cu:180
-#undef KV4_GO
+  if (rc) return rc;
   return launch_status(who);
 }
 

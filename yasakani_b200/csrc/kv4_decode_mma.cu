@@ -176,6 +176,9 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
   const int G = P.g;
+  // Let a dependent launch (the merge kernel, launched with programmatic stream serialization) be scheduled early; it
+  // still waits for this grid to finish before it reads the partials (src/pdl.cuh:15-21 is the reference's form of this).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ---- which groups this CTA owns (local token indices of this shard)
   const int pos = *A.d_pos + r - P.sh.start;

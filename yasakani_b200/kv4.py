@@ -149,6 +149,25 @@ def launch_attention_shard(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl,
                                               _stream(stream)), "yskn_kv4_attention_shard")
 
 
+def launch_decode(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float, rd: int, o16,
+                  bv=None, gate=None, stream=None) -> None:
+    """launch_attention_gqa + the merge of launch_attn_combine_gqa_xform as one launch where the shape allows
+    (src/attention_gqa.cu:168-181).  Calls on one device must not overlap."""
+    a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
+    g = nh // kv.hkv
+    c = AttnGCombineArgsC(pm.data_ptr(), pl.data_ptr(), pacc.data_ptr(), splits, M, bv.data_ptr() if bv is not None else None,
+                          o16.data_ptr(), gate.data_ptr() if gate is not None else None, nh, g)
+    check(_lib.load().yskn_kv4_decode(C.byref(a), C.byref(c), g, kv.hd, rd, _dtype_code(q16), _stream(stream)), "yskn_kv4_decode")
+
+
+def launch_decode_shard_triple(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float, rd: int,
+                               shard_start: int, shard_len: int, triple, stream=None) -> None:
+    """Shard partials and their fold into this shard's (m, l, O) triple [M][nh][hd+2], one launch where the shape allows."""
+    a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
+    check(_lib.load().yskn_kv4_decode_shard_triple(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), shard_start, shard_len,
+                                                  _ptr(triple), _stream(stream)), "yskn_kv4_decode_shard_triple")
+
+
 def launch_attn_combine_gqa(pm, pl, pacc, splits: int, M: int, o16, nh: int, g: int, bv=None, gate=None, stream=None) -> None:
     """Merge half of launch_attn_combine_gqa_xform (src/attention_gqa.cu:123-134,176-181), up to the o16 store."""
     hd = o16.numel() // (M * nh)

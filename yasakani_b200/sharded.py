@@ -91,9 +91,8 @@ class ShardedDecoder:
     def local_step(self, q16: torch.Tensor) -> None:
         """Shard partials -> this rank's triple (enqueue only)."""
         s = self.shape
-        self.kv4.launch_attention_shard(q16, self.layer, self.M, self.d_pos, self.splits, self.pm, self.pl, self.pacc, self.rope,
-                                        s.hq, s.qscale, s.rd, self.plan.start, self.plan.capacity)
-        self.kv4.launch_local_triple(self.pm, self.pl, self.pacc, self.splits, self.M, s.hq, s.hd, self.mine)
+        self.kv4.launch_decode_shard_triple(q16, self.layer, self.M, self.d_pos, self.splits, self.pm, self.pl, self.pacc, self.rope,
+                                            s.hq, s.qscale, s.rd, self.plan.start, self.plan.capacity, self.mine)
 
     def merge(self) -> torch.Tensor:
         s = self.shape
