@@ -165,7 +165,17 @@ def run_ours(args, rank, world, local_rank):
     kv4.launch_rope_table_g(rope, max_ctx, shape.theta, shape.rd)
 
     # ---- build this rank's shard with the library's own codec, then clone it so timed loops miss L2
-    first = ShardedDecoder(shape, plan, splits, rope)
+    exchange = args.exchange if world > 1 else "nccl"
+    xch = None
+    if exchange == "p2p":
+        from yasakani_b200.sharded import make_peer_exchange
+        try:
+            xkeep, xch = make_peer_exchange(kv4, world, rank, 1, shape.hq, shape.hd)
+        except Exception as e:                                      # symmetric memory unavailable: the NCCL form still works
+            if rank == 0:
+                print(f"[bench] peer exchange unavailable ({type(e).__name__}: {e}); using the NCCL all-gather", file=sys.stderr)
+            exchange = "nccl"
+    first = ShardedDecoder(shape, plan, splits, rope, exchange=exchange, peer_exchange=xch)
     lo, hi = plan.local_rows(0, ctx)
     for c in range(lo // CHUNK, (hi + CHUNK - 1) // CHUNK if hi > lo else 0):
         k, v = chunk_rows(shape, c)
@@ -176,7 +186,7 @@ def run_ours(args, rank, world, local_rank):
     n_copies = max(2, int(math.ceil(256e6 / max(shard_bytes, 1))) + 1)
     decs = [first]
     for _ in range(n_copies - 1):
-        d = ShardedDecoder(shape, plan, splits, rope)
+        d = ShardedDecoder(shape, plan, splits, rope, exchange=exchange, peer_exchange=xch)
         for a, b in zip(d.layer.tensors(), first.layer.tensors()):
             a.copy_(b)
         decs.append(d)
@@ -188,9 +198,7 @@ def run_ours(args, rank, world, local_rank):
 
     def step(d):
         if world > 1:
-            d.local_step(q_dev)
-            gather_triples(d.mine, d.gathered)
-            d.merge()
+            d.decode(q_dev)
         else:
             kv4.launch_decode(q_dev, d.layer, 1, d.d_pos, splits, d.pm, d.pl, d.pacc, rope, shape.hq, shape.qscale, shape.rd, d.o16)
 
@@ -269,7 +277,7 @@ def run_ours(args, rank, world, local_rank):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": workload_name(shape, ctx), "splits": splits, "parallelism": f"sequence-sharded x{world}",
+        "config": {"workload": workload_name(shape, ctx), "splits": splits, "parallelism": f"sequence-sharded x{world}" + (f", triples by {exchange}" if world > 1 else ""),
                    "l2": f"{n_copies} distinct cache copies cycled; {shard_bytes / 1e6:.1f} MB read per launch (L2 is 126 MB)",
                    "kv_tokens_scanned_per_s": ctx * value},
         "clocks": clocks,
@@ -311,6 +319,7 @@ def main():
     ap.add_argument("--splits", type=int, default=37, help="split-K factor; splits*Hkv = 148 = one CTA per SM")
     ap.add_argument("--cpu-sample-ctx", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="N > 1: how the shards' (m, l, O) triples travel")
     ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch from an ncu capture, if known")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

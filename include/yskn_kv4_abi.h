@@ -84,7 +84,8 @@ YSKN_KV4_API int yskn_kv4_set_algo(int algo);
 
 /* Reads and clears the device status word of the tensor-core decode kernel on the current device (synchronises):
  * 0 = ok, 1/2 = a bounded wait on the decode staging ring ran out (consumer/producer), 3 = misaligned shared memory,
- * 4/5/6 = a bounded wait ran out in the tcgen05 kernel (softmax warps / MMA issuer / producer).
+ * 4/5/6 = a bounded wait ran out in the tcgen05 kernel (softmax warps / MMA issuer / producer),
+ * 7 = the wait for another shard's triple ran out (yskn_kv4_merge_pushed).
  * A non-zero status means the partials of that launch are invalid.  The kernels never trap; compare the reference's
  * device-side __trap() on bad input (src/kvq_gpu.cuh:91). */
 YSKN_KV4_API int yskn_kv4_device_status(int* status);
@@ -148,6 +149,17 @@ YSKN_KV4_API int yskn_kv4_attention_shard(const yskn_attn_g_args* a, int g, int 
 /* yskn_kv4_attention_shard + yskn_kv4_local_triple in one call (same launch form as yskn_kv4_decode). */
 YSKN_KV4_API int yskn_kv4_decode_shard_triple(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, int shard_start,
                                               int shard_len, float* d_triple, void* cuda_stream);
+/* The same exchange without a library collective: every rank stores its triple straight into every rank's exchange
+ * buffer through NVLink peer mappings and raises a per-source arrival counter there; the merge kernel waits (bounded,
+ * about half a second, then device status 7) for all sources and merges.  buf[w] is rank w's exchange buffer as mapped
+ * into THIS process (buf[rank] is the local one), each of yskn_kv4_exchange_bytes(world, M, nh, hd) bytes, 16-byte
+ * aligned and zero-filled once before the first step.  Two halves are used alternately, so the ranks need no other
+ * synchronisation between steps; every rank must run push and merge exactly once per step, in this order. */
+typedef struct yskn_kv4_peer_exchange { float* buf[8]; int world; int rank; } yskn_kv4_peer_exchange;
+YSKN_KV4_API size_t yskn_kv4_exchange_bytes(int world, int M, int nh, int hd);
+YSKN_KV4_API int yskn_kv4_push_triple(const yskn_attn_g_combine_args* a, int hd, const yskn_kv4_peer_exchange* x, void* cuda_stream);
+YSKN_KV4_API int yskn_kv4_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, int hd, const uint16_t* bv,
+                                       const uint16_t* gate, uint16_t* o16, int act_dtype, void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_local_triple(const yskn_attn_g_combine_args* a, int hd, float* d_triple, void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd,
                                         const uint16_t* bv, const uint16_t* gate, uint16_t* o16, int act_dtype,

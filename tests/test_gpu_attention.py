@@ -229,3 +229,38 @@ def test_fused_decode_equals_attention_plus_merge(oracle, shape, ctx, M, splits)
         assert kv4.device_status() == 0
         got = o16.float().cpu().numpy()
         assert np.max(np.abs(got - want)) <= 2 ** -10 * max(1.0, float(np.abs(want).max()))      # same formula; expf/FMA may move one fp16 ulp
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_peer_exchange_on_one_gpu_matches_the_gathered_merge(oracle, world):
+    """push_triple / merge_pushed with all 'ranks' in one process on one GPU (every push is launched before any merge,
+    so no kernel waits for a later launch), three steps in a row to exercise both halves of the exchange buffers."""
+    from yasakani_b200.sharded import plan_shards
+    shape, ctx = synth.C2, 2500
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, 1, seed=40)
+    k, v = synth.make_kv(shape, ctx + 1, seed=40)
+    bufs = [torch.zeros((kv4.exchange_bytes(world, 1, shape.hq, shape.hd) + 3) // 4, dtype=torch.float32, device="cuda") for _ in range(world)]
+    xs = [kv4.peer_exchange([b.data_ptr() for b in bufs], rnk) for rnk in range(world)]
+    lays, plans = [], []
+    for rnk in range(world):
+        plan = plan_shards(ctx, world, rnk, okv.max_ctx)
+        lay = kv4.KvLayer(shape.hkv, shape.hd, plan.capacity)
+        a, b = plan.local_rows(0, ctx + 1)
+        if b > a:
+            gpu_append_all(kv4, lay, k[a:b], v[a:b], [b - a], pos0=a - plan.start)
+        lays.append(lay); plans.append(plan)
+    want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    dq = q.cuda()
+    for step in range(3):
+        scratch = [kv4.attn_scratch(1, 9, shape.hq, shape.hd) for _ in range(world)]
+        for rnk in range(world):
+            pm, pl, pacc = scratch[rnk]
+            kv4.launch_attention_shard(dq, lays[rnk], 1, d_pos, 9, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, plans[rnk].start, plans[rnk].capacity)
+            kv4.launch_push_triple(pm, pl, pacc, 9, 1, shape.hq, shape.hd, xs[rnk])
+        for rnk in range(world):
+            o16 = torch.full((1, shape.hq, shape.hd), float("nan"), dtype=torch.float16, device="cuda")
+            kv4.launch_merge_pushed(xs[rnk], 1, shape.hq, shape.g, shape.hd, o16)
+            torch.cuda.synchronize()
+            assert kv4.device_status() == 0
+            assert_close(o16.float().cpu().numpy(), want, f"step {step} rank {rnk} of {world}")

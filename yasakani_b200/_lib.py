@@ -38,6 +38,10 @@ class KvAppendArgsC(C.Structure):     # yskn_kv_append_args
                 ("d_pos", C.c_void_p), ("M", C.c_int), ("max_ctx", C.c_int), ("kvh", C.c_int), ("hd", C.c_int)]
 
 
+class PeerExchangeC(C.Structure):     # yskn_kv4_peer_exchange
+    _fields_ = [("buf", C.c_void_p * 8), ("world", C.c_int), ("rank", C.c_int)]
+
+
 # name -> (restype, argtypes); every symbol include/yskn_kv4_abi.h declares
 PROTOTYPES = {
     "yskn_kv4_last_error": (C.c_char_p, []),
@@ -57,6 +61,10 @@ PROTOTYPES = {
     "yskn_kv4_attention_tc": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
     "yskn_kv4_prefill_tc": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_size_t, C.c_int, C.c_void_p]),
+    "yskn_kv4_exchange_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "yskn_kv4_push_triple": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.POINTER(PeerExchangeC), C.c_void_p]),
+    "yskn_kv4_merge_pushed": (C.c_int, [C.POINTER(PeerExchangeC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_int, C.c_void_p]),
     "yskn_kv4_local_triple": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_void_p, C.c_void_p]),
     "yskn_kv4_merge_triples": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_int, C.c_void_p]),

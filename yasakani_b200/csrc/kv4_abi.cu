@@ -60,7 +60,24 @@ int yskn_kv4_device_status(int* status) {
   int a = 0, b = 0;
   if (int rc = decode_status_fetch(&a)) return rc;
   if (int rc = tc_status_fetch(&b)) return rc;
-  *status = a ? a : b; return 0;
+  int c = 0;
+  if (int rc = merge_status_fetch(&c)) return rc;
+  *status = a ? a : (b ? b : c); return 0;
+}
+
+size_t yskn_kv4_exchange_bytes(int world, int M, int nh, int hd) {
+  if (world < 1 || world > 8 || M <= 0 || nh <= 0 || hd <= 0) return 0;
+  return exchange_bytes(world, M, nh, hd);
+}
+
+int yskn_kv4_push_triple(const yskn_attn_g_combine_args* a, int hd, const yskn_kv4_peer_exchange* x, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_kv4_push_triple: null argument struct");
+  return launch_push_triple(*a, hd, x, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, int hd, const uint16_t* bv, const uint16_t* gate,
+                          uint16_t* o16, int act_dtype, void* cuda_stream) {
+  return launch_merge_pushed(x, M, nh, g, hd, bv, gate, o16, act_dtype, (cudaStream_t)cuda_stream);
 }
 
 size_t yskn_kv4_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M) {

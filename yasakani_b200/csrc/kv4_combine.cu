@@ -22,12 +22,23 @@ struct CombineP {
   const float* triples;                                  // triple layout   [S][M][nh][HD+2]
   int S, M, nh, g;
   const void* bv; const void* gate; uint16_t* o16; float* triple_out;
+  yskn_kv4_peer_exchange x;                              // PEER modes only
 };
+
+__device__ int g_merge_status = 0;                       // 7 = the wait for the other shards' triples ran out
+
+// Exchange buffer of one rank (yskn_kv4_peer_exchange): float data[2][world][M*nh*(HD+2)], then unsigned arrived[2][world],
+// then int step, unsigned ticket.  Buffer `step & 1` is the one in use; a rank is never more than one step ahead of another.
+__device__ __forceinline__ size_t xch_data_floats(int world, int M, int nh, int hd) { return (size_t)2 * world * M * nh * (hd + 2); }
+constexpr unsigned PEER_WAIT_POLLS = 1u << 22;           // x ~100 ns: about half a second
 
 constexpr int CQ = 4;                                    // split quarters per block
 constexpr int CB = 8;                                    // loads in flight per thread and batch
 
-template <int HD, int DT, bool TRIPLE_IN, bool TRIPLE_OUT>
+// PEER: with TRIPLE_OUT, the triple goes into every rank's exchange buffer (plain stores through NVLink peer mappings,
+// then one system-scope arrival per block and destination); with TRIPLE_IN, the block first waits (bounded) until every
+// rank's arrivals for this step are complete, and the last block of the grid opens the next step.
+template <int HD, int DT, bool TRIPLE_IN, bool TRIPLE_OUT, bool PEER>
 __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   extern __shared__ float sm[];                          // [S] m, [S] l, [S] w, [CQ][HD] partial sums
   float* s_m = sm; float* s_l = sm + P.S; float* s_w = sm + 2 * P.S; float* s_part = sm + 3 * P.S;
@@ -37,6 +48,30 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
                                                       : ((size_t)r * P.S + s) * P.nh + head; };
   auto ld_acc = [&](int s) -> float { return TRIPLE_IN ? __ldcg(P.triples + slot(s) + 2 + d) : __ldcg(P.pacc + slot(s) * HD + d); };
   asm volatile("griddepcontrol.wait;" ::: "memory");     // the producer grid's writes are visible from here on
+  __shared__ int s_bad;
+  int par = 0;                                           // which half of the exchange buffers this step uses
+  const size_t xdata = PEER ? xch_data_floats(P.x.world, P.M, P.nh, HD) : 0;
+  if (PEER) {
+    unsigned* mine_flags = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata);
+    par = *reinterpret_cast<volatile int*>(mine_flags + 2 * P.x.world) & 1;
+    if (TRIPLE_IN) {
+      if (tid == 0) {
+        int bad = 0;
+        const unsigned want = (unsigned)(P.M * P.nh);
+        for (int src = 0; src < P.x.world && !bad; ++src) {
+          volatile unsigned* f = mine_flags + par * P.x.world + src;
+          unsigned polls = 0;
+          while (*f < want) { __nanosleep(100); if (++polls > PEER_WAIT_POLLS) { bad = 1; break; } }
+        }
+        if (bad) atomicExch(&g_merge_status, 7);
+        __threadfence_system();
+        s_bad = bad;
+      }
+      __syncthreads();
+      if (s_bad) return;
+      P.triples = P.x.buf[P.x.rank] + (size_t)par * (xdata / 2);
+    }
+  }
 
   float v[CB];                                           // first batch of this thread's values: in flight with pm/pl
   #pragma unroll
@@ -65,6 +100,20 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   o = (s_part[d] + s_part[HD + d]) + (s_part[2 * HD + d] + s_part[3 * HD + d]);
   float L2 = 0.f;
   for (int s = 0; s < P.S; ++s) L2 += s_w[s] * s_l[s];
+  if (TRIPLE_OUT && PEER) {
+    const size_t off = (size_t)par * (xdata / 2) + (((size_t)P.x.rank * P.M + r) * P.nh + head) * (HD + 2);
+    for (int w = 0; w < P.x.world; ++w) {
+      float* t = P.x.buf[w] + off;
+      if (d == 0) { t[0] = M2; t[1] = L2; }
+      t[2 + d] = o;
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");     // the HD threads of quarter 0
+    if (d == 0)
+      for (int w = 0; w < P.x.world; ++w)
+        atomicAdd_system(reinterpret_cast<unsigned*>(P.x.buf[w] + xdata) + par * P.x.world + P.x.rank, 1u);
+    return;
+  }
   if (TRIPLE_OUT) {
     float* t = P.triple_out + ((size_t)r * P.nh + head) * (HD + 2);
     if (d == 0) { t[0] = M2; t[1] = L2; }
@@ -76,20 +125,35 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   if (P.bv) y = __fadd_rn(y, act_load<DT>(P.bv, (size_t)(head / P.g) * HD + d));
   if (P.gate) { const float gt = act_load<DT>(P.gate, e); y = __fmul_rn(y, __fdiv_rn(1.f, __fadd_rn(1.f, expf(-gt)))); }
   P.o16[e] = act_store16<DT>(y);
+  if (PEER && TRIPLE_IN) {                               // the last block of the grid closes this step
+    __threadfence();
+    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");
+    if (d == 0) {
+      unsigned* flags = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata);
+      unsigned* ticket = flags + 2 * P.x.world + 1;
+      if (atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1) {
+        for (int src = 0; src < P.x.world; ++src) flags[par * P.x.world + src] = 0u;
+        *ticket = 0u;
+        __threadfence();
+        volatile int* step = reinterpret_cast<volatile int*>(flags + 2 * P.x.world);
+        *step = *step + 1;                             // every block of this grid has read it already
+      }
+    }
+  }
 }
 
-template <int HD, int DT, bool TI, bool TO>
+template <int HD, int DT, bool TI, bool TO, bool PEER>
 int launch_k(const CombineP& P, size_t smem, cudaStream_t st) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(P.nh, P.M); cfg.blockDim = dim3(CQ * HD); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  KV4_CUDA(cudaLaunchKernelEx(&cfg, kv4_combine_kernel<HD, DT, TI, TO>, P));
+  KV4_CUDA(cudaLaunchKernelEx(&cfg, kv4_combine_kernel<HD, DT, TI, TO, PEER>, P));
   return 0;
 }
 
-template <bool TI, bool TO> int launch_p(const CombineP& P, int hd, int dt, cudaStream_t st, const char* who) {
+template <bool TI, bool TO, bool PEER = false> int launch_p(const CombineP& P, int hd, int dt, cudaStream_t st, const char* who) {
   if (P.S <= 0 || P.M <= 0 || P.nh <= 0 || P.g <= 0) KV4_REJECT("%s: bad arguments (splits %d, M %d, nh %d, g %d)", who, P.S, P.M, P.nh, P.g);
   if (P.M > 65535) KV4_REJECT("%s: M %d exceeds the grid limit", who, P.M);
   const size_t smem = ((size_t)3 * P.S + (size_t)CQ * hd) * sizeof(float);
@@ -97,9 +161,9 @@ template <bool TI, bool TO> int launch_p(const CombineP& P, int hd, int dt, cuda
   const bool bf = dt == YSKN_KV4_BF16;
   if (dt != YSKN_KV4_F16 && dt != YSKN_KV4_BF16) KV4_REJECT("%s: act_dtype must be F16 or BF16", who);
   int rc;
-  if (hd == 256) rc = bf ? launch_k<256, YSKN_KV4_BF16, TI, TO>(P, smem, st) : launch_k<256, YSKN_KV4_F16, TI, TO>(P, smem, st);
-  else if (hd == 128) rc = bf ? launch_k<128, YSKN_KV4_BF16, TI, TO>(P, smem, st) : launch_k<128, YSKN_KV4_F16, TI, TO>(P, smem, st);
-  else if (hd == 64) rc = bf ? launch_k<64, YSKN_KV4_BF16, TI, TO>(P, smem, st) : launch_k<64, YSKN_KV4_F16, TI, TO>(P, smem, st);
+  if (hd == 256) rc = bf ? launch_k<256, YSKN_KV4_BF16, TI, TO, PEER>(P, smem, st) : launch_k<256, YSKN_KV4_F16, TI, TO, PEER>(P, smem, st);
+  else if (hd == 128) rc = bf ? launch_k<128, YSKN_KV4_BF16, TI, TO, PEER>(P, smem, st) : launch_k<128, YSKN_KV4_F16, TI, TO, PEER>(P, smem, st);
+  else if (hd == 64) rc = bf ? launch_k<64, YSKN_KV4_BF16, TI, TO, PEER>(P, smem, st) : launch_k<64, YSKN_KV4_F16, TI, TO, PEER>(P, smem, st);
   else KV4_REJECT("%s: unsupported head_dim %d (64, 128, 256)", who, hd);               // src/attention_gqa.cu:180
   if (rc) return rc;
   return launch_status(who);
@@ -109,21 +173,54 @@ template <bool TI, bool TO> int launch_p(const CombineP& P, int hd, int dt, cuda
 
 int launch_combine(const yskn_attn_g_combine_args& a, int hd, int act_dtype, cudaStream_t st) {
   if (!a.pm || !a.pl || !a.pacc || !a.o16) KV4_REJECT("yskn_kv4_combine: null buffer");
-  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g, a.bv, a.gate, a.o16, nullptr};
+  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g, a.bv, a.gate, a.o16, nullptr, {}};
   return launch_p<false, false>(P, hd, act_dtype, st, "yskn_kv4_combine");
 }
 
 int launch_local_triple(const yskn_attn_g_combine_args& a, int hd, float* d_triple, cudaStream_t st) {
   if (!a.pm || !a.pl || !a.pacc || !d_triple) KV4_REJECT("yskn_kv4_local_triple: null buffer");
-  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g > 0 ? a.g : 1, nullptr, nullptr, nullptr, d_triple};
+  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g > 0 ? a.g : 1, nullptr, nullptr, nullptr, d_triple, {}};
   return launch_p<false, true>(P, hd, YSKN_KV4_F16, st, "yskn_kv4_local_triple");
 }
 
 int launch_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd, const uint16_t* bv,
                          const uint16_t* gate, uint16_t* o16, int act_dtype, cudaStream_t st) {
   if (!d_triples || !o16) KV4_REJECT("yskn_kv4_merge_triples: null buffer");
-  CombineP P{nullptr, nullptr, nullptr, d_triples, ranks, M, nh, g, bv, gate, o16, nullptr};
+  CombineP P{nullptr, nullptr, nullptr, d_triples, ranks, M, nh, g, bv, gate, o16, nullptr, {}};
   return launch_p<true, false>(P, hd, act_dtype, st, "yskn_kv4_merge_triples");
+}
+
+static int check_exchange(const yskn_kv4_peer_exchange* x, const char* who) {
+  if (!x || x->world < 1 || x->world > 8 || x->rank < 0 || x->rank >= x->world) KV4_REJECT("%s: bad exchange descriptor", who);
+  for (int w = 0; w < x->world; ++w) if (!x->buf[w] || ((uintptr_t)x->buf[w] & 15)) KV4_REJECT("%s: exchange buffer %d missing or misaligned", who, w);
+  return 0;
+}
+
+size_t exchange_bytes(int world, int M, int nh, int hd) {
+  return ((size_t)2 * world * M * nh * (hd + 2)) * 4 + ((size_t)2 * world + 2) * 4;
+}
+
+int launch_push_triple(const yskn_attn_g_combine_args& a, int hd, const yskn_kv4_peer_exchange* x, cudaStream_t st) {
+  if (int rc = check_exchange(x, "yskn_kv4_push_triple")) return rc;
+  if (!a.pm || !a.pl || !a.pacc) KV4_REJECT("yskn_kv4_push_triple: null buffer");
+  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g > 0 ? a.g : 1, nullptr, nullptr, nullptr, nullptr, *x};
+  return launch_p<false, true, true>(P, hd, YSKN_KV4_F16, st, "yskn_kv4_push_triple");
+}
+
+int launch_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, int hd, const uint16_t* bv, const uint16_t* gate,
+                        uint16_t* o16, int act_dtype, cudaStream_t st) {
+  if (int rc = check_exchange(x, "yskn_kv4_merge_pushed")) return rc;
+  if (!o16) KV4_REJECT("yskn_kv4_merge_pushed: null output");
+  CombineP P{nullptr, nullptr, nullptr, nullptr, x->world, M, nh, g, bv, gate, o16, nullptr, *x};
+  return launch_p<true, false, true>(P, hd, act_dtype, st, "yskn_kv4_merge_pushed");
+}
+
+int merge_status_fetch(int* out) {
+  int v = 0;
+  KV4_CUDA(cudaMemcpyFromSymbol(&v, g_merge_status, sizeof(int)));
+  const int zero = 0;
+  KV4_CUDA(cudaMemcpyToSymbol(g_merge_status, &zero, sizeof(int)));
+  *out = v; return 0;
 }
 
 }  // namespace kv4

@@ -66,6 +66,12 @@ int launch_merge_triples(const float* d_triples, int ranks, int M, int nh, int g
 int decode_noalloc(const uint16_t* q16, const yskn_kv_layer* kv, int max_ctx, const int* d_pos, int splits, const float* rope,
                    int kvh, int nh, int hd, int rd, float qscale, int act_dtype, uint16_t* o16, cudaStream_t st);
 
+size_t exchange_bytes(int world, int M, int nh, int hd);
+int launch_push_triple(const yskn_attn_g_combine_args& a, int hd, const yskn_kv4_peer_exchange* x, cudaStream_t st);
+int launch_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, int hd, const uint16_t* bv, const uint16_t* gate,
+                        uint16_t* o16, int act_dtype, cudaStream_t st);
+int merge_status_fetch(int* out);
+
 // Which attention kernel yskn_kv4_attention picks; set through yskn_kv4_set_algo (tests compare paths).
 enum Algo { ALGO_AUTO = 0, ALGO_SCALAR = 1, ALGO_MMA = 2 };
 

@@ -13,7 +13,7 @@ import math
 import torch
 
 from . import _lib
-from ._lib import F16, BF16, F32, KvLayerC, KvQuantArgsC, AttnGArgsC, AttnGCombineArgsC, KvAppendArgsC, check
+from ._lib import F16, BF16, F32, KvLayerC, KvQuantArgsC, AttnGArgsC, AttnGCombineArgsC, KvAppendArgsC, PeerExchangeC, check
 
 _NAMES = ("kq", "kscale", "kzero", "kshadow", "vq", "vscale", "vzero")
 
@@ -228,6 +228,32 @@ def decode_noalloc(q16, kv: KvLayer, d_pos, splits: int, rope, nh: int, qscale: 
     check(_lib.load().yskn_kv4_decode_noalloc(_ptr(q16), C.byref(s), kv.max_ctx, _ptr(d_pos), splits, rope.data_ptr() if rope is not None else None,
                                              kv.hkv, nh, kv.hd, rd, C.c_float(qscale), _dtype_code(q16), _ptr(o16), _stream(stream)),
           "yskn_kv4_decode_noalloc")
+
+
+def exchange_bytes(world: int, M: int, nh: int, hd: int) -> int:
+    return int(_lib.load().yskn_kv4_exchange_bytes(world, M, nh, hd))
+
+
+def peer_exchange(buffer_ptrs, rank: int) -> PeerExchangeC:
+    """Descriptor of the ranks' exchange buffers as mapped into this process (buffer_ptrs[rank] is the local one)."""
+    x = PeerExchangeC()
+    for w, p in enumerate(buffer_ptrs):
+        x.buf[w] = int(p)
+    x.world, x.rank = len(buffer_ptrs), rank
+    return x
+
+
+def launch_push_triple(pm, pl, pacc, splits: int, M: int, nh: int, hd: int, x: PeerExchangeC, stream=None) -> None:
+    """Fold this shard's partials into its (m, l, O) triple and store it into every rank's exchange buffer (peer stores)."""
+    a = AttnGCombineArgsC(pm.data_ptr(), pl.data_ptr(), pacc.data_ptr(), splits, M, None, None, None, nh, 1)
+    check(_lib.load().yskn_kv4_push_triple(C.byref(a), hd, C.byref(x), _stream(stream)), "yskn_kv4_push_triple")
+
+
+def launch_merge_pushed(x: PeerExchangeC, M: int, nh: int, g: int, hd: int, o16, bv=None, gate=None, stream=None) -> None:
+    """Wait (bounded) for every rank's pushed triple of this step and merge them into o16."""
+    check(_lib.load().yskn_kv4_merge_pushed(C.byref(x), M, nh, g, hd, bv.data_ptr() if bv is not None else None,
+                                           gate.data_ptr() if gate is not None else None, _ptr(o16), _dtype_code(o16), _stream(stream)),
+          "yskn_kv4_merge_pushed")
 
 
 def default_qscale(hd: int) -> float:

@@ -6,9 +6,15 @@ rank runs the same split-K decode on its range, folds its partials into one (m, 
 (Hq*(HD+2) floats), the triples are all-gathered (NCCL over NVLink on GPUs, gloo in CPU tests) and every
 rank merges them with the arithmetic of the single-GPU split merge.  The reference has no multi-GPU path
 (README.md:37); the 1-GPU result is the oracle.
+
+Two forms of the exchange: the NCCL all-gather (`exchange="nccl"`), and direct peer stores (`exchange="p2p"`): the
+kernel that folds a shard's partials writes the triple into every rank's exchange buffer over NVLink and raises an
+arrival counter there; the merge kernel waits for the counters.  The peer buffers are torch symmetric memory (plain
+peer mappings; NVLink multicast is switched off) and NCCL is used only to set them up.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -66,9 +72,13 @@ class ShardedDecoder:
 
     All arithmetic runs in the CUDA library (kv4.launch_*); this class only owns buffers and the exchange."""
 
-    def __init__(self, shape, plan: ShardPlan, splits: int, rope: torch.Tensor, M: int = 1, dtype=torch.float16, group=None):
+    def __init__(self, shape, plan: ShardPlan, splits: int, rope: torch.Tensor, M: int = 1, dtype=torch.float16, group=None,
+                 exchange: str = "nccl", peer_exchange=None):
         from . import kv4
         self.kv4, self.shape, self.plan, self.splits, self.rope, self.M, self.group = kv4, shape, plan, splits, rope, M, group
+        self.exchange, self.x = exchange, peer_exchange
+        if exchange == "p2p" and peer_exchange is None:
+            self._xbuf, self.x = make_peer_exchange(kv4, plan.world, plan.rank, M, shape.hq, shape.hd, group)
         self.layer = kv4.KvLayer(shape.hkv, shape.hd, plan.capacity)
         self.pm, self.pl, self.pacc = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
         self.mine = torch.empty((M, shape.hq, shape.hd + 2), dtype=torch.float32, device="cuda")
@@ -101,6 +111,26 @@ class ShardedDecoder:
 
     def decode(self, q16: torch.Tensor) -> torch.Tensor:
         """q16 [M][Hq][HD] on this GPU (replicated on all ranks); self.d_pos must hold the global position."""
+        s = self.shape
+        if self.exchange == "p2p":
+            self.kv4.launch_attention_shard(q16, self.layer, self.M, self.d_pos, self.splits, self.pm, self.pl, self.pacc, self.rope,
+                                            s.hq, s.qscale, s.rd, self.plan.start, self.plan.capacity)
+            self.kv4.launch_push_triple(self.pm, self.pl, self.pacc, self.splits, self.M, s.hq, s.hd, self.x)
+            self.kv4.launch_merge_pushed(self.x, self.M, s.hq, s.g, s.hd, self.o16)
+            return self.o16
         self.local_step(q16)
         gather_triples(self.mine, self.gathered, self.group)
         return self.merge()
+
+
+def make_peer_exchange(kv4, world: int, rank: int, M: int, nh: int, hd: int, group=None):
+    """Symmetric exchange buffer of every rank, zero-filled, and its descriptor.  Collective over `group`."""
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")     # plain peer mappings only
+    import torch.distributed._symmetric_memory as symm
+    n = kv4.exchange_bytes(world, M, nh, hd)
+    buf = symm.empty((n + 3) // 4, dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+    buf.zero_()
+    hdl = symm.rendezvous(buf, group=group if group is not None else dist.group.WORLD)
+    torch.cuda.synchronize()
+    dist.barrier(group=group)                                          # nobody pushes into a buffer that is not cleared yet
+    return (buf, hdl), kv4.peer_exchange(list(hdl.buffer_ptrs), rank)
