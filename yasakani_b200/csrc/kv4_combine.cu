@@ -28,7 +28,7 @@ struct CombineP {
 __device__ int g_merge_status = 0;                       // 7 = the wait for the other shards' triples ran out
 
 // Exchange buffer of one rank (yskn_kv4_peer_exchange): float data[2][world][M*nh*(HD+2)], then unsigned arrived[2][world],
-// then int step, unsigned ticket.  Buffer `step & 1` is the one in use; a rank is never more than one step ahead of another.
+// then int step, unsigned merge ticket, unsigned push ticket.  Buffer `step & 1` is the one in use; a rank is never more than one step ahead of another.
 __device__ __forceinline__ size_t xch_data_floats(int world, int M, int nh, int hd) { return (size_t)2 * world * M * nh * (hd + 2); }
 constexpr unsigned PEER_WAIT_POLLS = 1u << 22;           // x ~100 ns: about half a second
 
@@ -59,12 +59,16 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
         int bad = 0;
         const unsigned want = (unsigned)(P.M * P.nh);
         for (int src = 0; src < P.x.world && !bad; ++src) {
-          volatile unsigned* f = mine_flags + par * P.x.world + src;
-          unsigned polls = 0;
-          while (*f < want) { __nanosleep(100); if (++polls > PEER_WAIT_POLLS) { bad = 1; break; } }
+          const unsigned* f = mine_flags + par * P.x.world + src;
+          unsigned polls = 0, got = 0;
+          for (;;) {                                           // acquire at system scope: the triple stored before the arrival is visible
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(f) : "memory");
+            if (got >= want) break;
+            __nanosleep(100);
+            if (++polls > PEER_WAIT_POLLS) { bad = 1; break; }
+          }
         }
         if (bad) atomicExch(&g_merge_status, 7);
-        __threadfence_system();
         s_bad = bad;
       }
       __syncthreads();
@@ -107,11 +111,20 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
       if (d == 0) { t[0] = M2; t[1] = L2; }
       t[2 + d] = o;
     }
-    __threadfence_system();
-    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");     // the HD threads of quarter 0
-    if (d == 0)
-      for (int w = 0; w < P.x.world; ++w)
-        atomicAdd_system(reinterpret_cast<unsigned*>(P.x.buf[w] + xdata) + par * P.x.world + P.x.rank, 1u);
+    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");     // the HD threads of quarter 0 have stored
+    if (d == 0) {
+      // Blocks meet at a device-scope ticket; the last one publishes the whole grid's stores with ONE system-scope
+      // fence and one arrival per destination (a system fence per block cost several microseconds each).
+      unsigned* mine_flags = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata);
+      unsigned* ticket = mine_flags + 2 * P.x.world + 2;
+      __threadfence();
+      if (atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1) {
+        *ticket = 0u;
+        __threadfence_system();
+        for (int w = 0; w < P.x.world; ++w)
+          atomicAdd_system(reinterpret_cast<unsigned*>(P.x.buf[w] + xdata) + par * P.x.world + P.x.rank, (unsigned)(P.M * P.nh));
+      }
+    }
     return;
   }
   if (TRIPLE_OUT) {
@@ -126,8 +139,7 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   if (P.gate) { const float gt = act_load<DT>(P.gate, e); y = __fmul_rn(y, __fdiv_rn(1.f, __fadd_rn(1.f, expf(-gt)))); }
   P.o16[e] = act_store16<DT>(y);
   if (PEER && TRIPLE_IN) {                               // the last block of the grid closes this step
-    __threadfence();
-    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");      // every thread of the block has read its triples
     if (d == 0) {
       unsigned* flags = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata);
       unsigned* ticket = flags + 2 * P.x.world + 1;
@@ -197,7 +209,7 @@ static int check_exchange(const yskn_kv4_peer_exchange* x, const char* who) {
 }
 
 size_t exchange_bytes(int world, int M, int nh, int hd) {
-  return ((size_t)2 * world * M * nh * (hd + 2)) * 4 + ((size_t)2 * world + 2) * 4;
+  return ((size_t)2 * world * M * nh * (hd + 2)) * 4 + ((size_t)2 * world + 4) * 4;   // data, arrived[2][world], step, merge ticket, push ticket, pad
 }
 
 int launch_push_triple(const yskn_attn_g_combine_args& a, int hd, const yskn_kv4_peer_exchange* x, cudaStream_t st) {
