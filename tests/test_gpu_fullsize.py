@@ -1,0 +1,121 @@
+"""Benchmark-sized cases (BASELINE.json configs 2, 3 and 5) on the GPU: sampled rows against the CPU oracle, plus
+properties that need no oracle (bitwise width invariance, tensor-core kernel against the CUDA-core kernel)."""
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import assert_close, f16_bits
+from yasakani_b200 import synth, ALGO_AUTO, ALGO_SCALAR
+
+pytestmark = pytest.mark.gpu
+CHUNK = 8192
+
+
+def _build(kv4, oracle, shape, n_tokens, seed, want_oracle=True):
+    """GPU cache (library codec) and, optionally, the oracle's cache from the same seeded rows, chunk by chunk."""
+    max_ctx = ((n_tokens + 127) // 64) * 64
+    layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
+    okv = oracle.KvCache(shape.hkv, shape.hd, max_ctx) if want_oracle else None
+    d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for c in range((n_tokens + CHUNK - 1) // CHUNK):
+        n = min(CHUNK, n_tokens - c * CHUNK)
+        k, v = synth.make_kv(shape, CHUNK, seed=seed * 1000 + c)
+        d_pos.fill_(c * CHUNK)
+        kv4.launch_kv_append(layer, k[:n].cuda(), v[:n].cuda(), d_pos, n)
+        if want_oracle:
+            oracle.append(okv, c * CHUNK, f16_bits(k[:n]), f16_bits(v[:n]))
+    torch.cuda.synchronize()
+    return layer, okv, max_ctx
+
+
+def _rope(kv4, shape, max_ctx):
+    rope = torch.empty((max_ctx, shape.rd // 2, 2), dtype=torch.float32, device="cuda")
+    kv4.launch_rope_table_g(rope, max_ctx, shape.theta, shape.rd)
+    torch.cuda.synchronize()
+    return rope
+
+
+def test_config5_prefill_8192_rows_sampled_against_oracle(oracle):
+    from yasakani_b200 import kv4
+    shape, M = synth.C2, 8192
+    layer, okv, max_ctx = _build(kv4, oracle, shape, M, seed=71)
+    got_cache = layer.to_numpy()
+    for name, want in okv.arrays().items():                              # the prompt's K/V went through the codec: bit-exact
+        assert np.array_equal(got_cache[name].reshape(want.shape), want), name
+    rope = _rope(kv4, shape, max_ctx)
+    q = synth.make_q(shape, M, seed=71)
+    d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pm, pl, pacc = kv4.attn_scratch(M, 1, shape.hq, shape.hd)
+    o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+    kv4.launch_attention_prefill_tc(q.cuda(), layer, M, d_pos, 1, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, kv4.tc_workspace(layer, M))
+    torch.cuda.synchronize()
+    assert kv4.device_status() == 0
+    got = o16.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    rope_np = rope.cpu().numpy()
+    for lo, hi in ((0, 3), (31, 34), (4094, 4098), (8189, 8192)):        # group edges, middle, last rows
+        want = oracle.attention_exact(f16_bits(q), okv, 0, rope_np, shape.hq, shape.rd, shape.qscale, rows=(lo, hi))
+        assert_close(got[lo:hi], want[lo:hi], f"prefill rows {lo}..{hi}")
+
+
+def test_config5_decode_batch_at_mixed_contexts(oracle):
+    """Eight independent single-token decodes at 2k ... 128k; the oracle checks the small ones, the large ones compare the
+    tensor-core kernel with the CUDA-core kernel (itself oracle-checked on the small ones)."""
+    from yasakani_b200 import kv4
+    shape = synth.C2
+    for i, ctx in enumerate((2048, 4096, 8192, 16384, 32768, 65536, 98304, 131072)):
+        small = ctx <= 16384
+        layer, okv, max_ctx = _build(kv4, oracle, shape, ctx, seed=80 + i, want_oracle=small)
+        rope = _rope(kv4, shape, max_ctx)
+        q = synth.make_q(shape, 1, seed=80 + i)
+        d_pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda")
+        outs = {}
+        for algo in (ALGO_AUTO, ALGO_SCALAR):
+            kv4.set_algo(algo)
+            pm, pl, pacc = kv4.attn_scratch(1, 37, shape.hq, shape.hd)
+            o16 = torch.empty((1, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+            kv4.launch_decode(q.cuda(), layer, 1, d_pos, 37, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16)
+            torch.cuda.synchronize()
+            outs[algo] = o16.float().cpu().numpy()
+        kv4.set_algo(ALGO_AUTO)
+        assert kv4.device_status() == 0
+        assert_close(outs[ALGO_AUTO], outs[ALGO_SCALAR], f"ctx {ctx}: tensor-core vs CUDA-core")
+        if small:
+            want = oracle.attention_exact(f16_bits(q), okv, ctx - 1, rope.cpu().numpy(), shape.hq, shape.rd, shape.qscale)
+            assert_close(outs[ALGO_AUTO], want, f"ctx {ctx} vs oracle")
+        del layer, rope
+        torch.cuda.empty_cache()
+
+
+def test_config3_verify_widths_over_32768_tokens(oracle):
+    """16-, 32- and 64-row verify passes over a 32,768-token cache: shared rows bitwise identical; sampled rows vs oracle."""
+    from yasakani_b200 import kv4
+    shape, ctx = synth.C2, 32768
+    base, okv, max_ctx = _build(kv4, oracle, shape, ctx, seed=90)
+    max_ctx = base.max_ctx
+    rope = _rope(kv4, shape, max_ctx)
+    k_new, v_new = synth.make_kv(shape, 64, seed=91)
+    q = synth.make_q(shape, 64, seed=91)
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    outs = {}
+    for M, splits in ((16, 37), (32, 18), (64, 12)):
+        layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
+        for a, b in zip(layer.tensors(), base.tensors()):
+            a.copy_(b)
+        kv4.launch_kv_append(layer, k_new[:M].cuda(), v_new[:M].cuda(), d_pos, M)
+        pm, pl, pacc = kv4.attn_scratch(M, 7, shape.hq, shape.hd)          # same split count for every width
+        o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+        kv4.launch_attention_tc(q[:M].cuda(), layer, M, d_pos, 7, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, kv4.tc_workspace(layer, M))
+        kv4.launch_attn_combine_gqa(pm, pl, pacc, 7, M, o16, shape.hq, shape.g)
+        torch.cuda.synchronize()
+        assert kv4.device_status() == 0
+        outs[M] = o16.cpu()
+        del splits
+    b16, b32, b64 = (outs[m].view(torch.int16).numpy() for m in (16, 32, 64))
+    assert np.array_equal(b16, b32[:16]) and np.array_equal(b32, b64[:32])
+    oracle.append(okv, ctx, f16_bits(k_new), f16_bits(v_new))
+    rope_np = rope.cpu().numpy()
+    got = outs[64].float().numpy()
+    for lo, hi in ((0, 2), (31, 33), (62, 64)):
+        want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale, rows=(lo, hi))
+        assert_close(got[lo:hi], want[lo:hi], f"verify rows {lo}..{hi}")
