@@ -36,7 +36,8 @@ def _run_tc(kv4, oracle, shape, ctx, M, splits, seed, prefill=False):
         kv4.launch_attn_combine_gqa(pm, pl, pacc, splits, M, o16, shape.hq, shape.g)
     torch.cuda.synchronize()
     assert kv4.device_status() == 0
-    assert torch.isfinite(pm).all() and torch.isfinite(pl).all() and torch.isfinite(pacc).all(), "a partial slot was not written"
+    if not (prefill and splits == 1):                 # a one-split prefill finishes its rows in the kernel and writes no partials
+        assert torch.isfinite(pm).all() and torch.isfinite(pl).all() and torch.isfinite(pacc).all(), "a partial slot was not written"
     want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
     return o16.float().cpu().numpy(), want
 

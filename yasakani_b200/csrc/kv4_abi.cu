@@ -89,12 +89,17 @@ int yskn_kv4_attention_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int 
                           int valid_tokens, void* cuda_stream) {
   if (int rc = check_attn(a, g, hd, "yskn_kv4_attention_tc")) return rc;
   if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_attention_tc: rotary width %d needs a rope table", rd);
-  return launch_attention_tc(*a, g, hd, rd, act_dtype, d_workspace, workspace_bytes, valid_tokens, (cudaStream_t)cuda_stream);
+  return launch_attention_tc(*a, g, hd, rd, act_dtype, d_workspace, workspace_bytes, valid_tokens, nullptr, nullptr, (cudaStream_t)cuda_stream);
 }
 
 int yskn_kv4_prefill_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, const uint16_t* bv, uint16_t* o16,
                         void* d_workspace, size_t workspace_bytes, int valid_tokens, void* cuda_stream) {
   if (!o16) KV4_REJECT("yskn_kv4_prefill_tc: null output");
+  if (a && a->splits == 1) {                                 // one split: the attention kernel finishes the rows itself
+    if (int rc = check_attn(a, g, hd, "yskn_kv4_prefill_tc")) return rc;
+    if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_prefill_tc: rotary width %d needs a rope table", rd);
+    return launch_attention_tc(*a, g, hd, rd, act_dtype, d_workspace, workspace_bytes, valid_tokens, o16, bv, (cudaStream_t)cuda_stream);
+  }
   if (int rc = yskn_kv4_attention_tc(a, g, hd, rd, act_dtype, d_workspace, workspace_bytes, valid_tokens, cuda_stream)) return rc;
   yskn_attn_g_combine_args c{a->pm, a->pl, a->pacc, a->splits, a->M, bv, o16, nullptr, a->nh, g};
   return launch_combine(c, hd, act_dtype, (cudaStream_t)cuda_stream);

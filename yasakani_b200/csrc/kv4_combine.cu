@@ -32,13 +32,13 @@ __device__ int g_merge_status = 0;                       // 7 = the wait for the
 __device__ __forceinline__ size_t xch_data_floats(int world, int M, int nh, int hd) { return (size_t)2 * world * M * nh * (hd + 2); }
 constexpr unsigned PEER_WAIT_POLLS = 1u << 22;           // x ~100 ns: about half a second
 
-constexpr int CQ = 4;                                    // split quarters per block
 constexpr int CB = 8;                                    // loads in flight per thread and batch
 
 // PEER: with TRIPLE_OUT, the triple goes into every rank's exchange buffer (plain stores through NVLink peer mappings,
 // then one system-scope arrival per block and destination); with TRIPLE_IN, the block first waits (bounded) until every
 // rank's arrivals for this step are complete, and the last block of the grid opens the next step.
-template <int HD, int DT, bool TRIPLE_IN, bool TRIPLE_OUT, bool PEER>
+// CQ = split runs per block: 4 when there are many splits to fetch (latency), 1 for short sums (prefill: thousands of rows).
+template <int HD, int DT, bool TRIPLE_IN, bool TRIPLE_OUT, bool PEER, int CQ>
 __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   extern __shared__ float sm[];                          // [S] m, [S] l, [S] w, [CQ][HD] partial sums
   float* s_m = sm; float* s_l = sm + P.S; float* s_w = sm + 2 * P.S; float* s_part = sm + 3 * P.S;
@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   s_part[q * HD + d] = o;
   __syncthreads();
   if (q != 0) return;
-  o = (s_part[d] + s_part[HD + d]) + (s_part[2 * HD + d] + s_part[3 * HD + d]);
+  if (CQ == 4) o = (s_part[d] + s_part[HD + d]) + (s_part[2 * HD + d] + s_part[3 * HD + d]);
   float L2 = 0.f;
   for (int s = 0; s < P.S; ++s) L2 += s_w[s] * s_l[s];
   if (TRIPLE_OUT && PEER) {
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
       if (d == 0) { t[0] = M2; t[1] = L2; }
       t[2 + d] = o;
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");     // the HD threads of quarter 0 have stored
+    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");     // the HD threads of run 0 have stored
     if (d == 0) {
       // Blocks meet at a device-scope ticket; the last one publishes the whole grid's stores with ONE system-scope
       // fence and one arrival per destination (a system fence per block cost several microseconds each).
@@ -156,19 +156,21 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
 
 template <int HD, int DT, bool TI, bool TO, bool PEER>
 int launch_k(const CombineP& P, size_t smem, cudaStream_t st) {
+  const int CQ = P.S >= 8 ? 4 : 1;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(P.nh, P.M); cfg.blockDim = dim3(CQ * HD); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  KV4_CUDA(cudaLaunchKernelEx(&cfg, kv4_combine_kernel<HD, DT, TI, TO, PEER>, P));
+  if (CQ == 4) KV4_CUDA(cudaLaunchKernelEx(&cfg, kv4_combine_kernel<HD, DT, TI, TO, PEER, 4>, P));
+  else KV4_CUDA(cudaLaunchKernelEx(&cfg, kv4_combine_kernel<HD, DT, TI, TO, PEER, 1>, P));
   return 0;
 }
 
 template <bool TI, bool TO, bool PEER = false> int launch_p(const CombineP& P, int hd, int dt, cudaStream_t st, const char* who) {
   if (P.S <= 0 || P.M <= 0 || P.nh <= 0 || P.g <= 0) KV4_REJECT("%s: bad arguments (splits %d, M %d, nh %d, g %d)", who, P.S, P.M, P.nh, P.g);
   if (P.M > 65535) KV4_REJECT("%s: M %d exceeds the grid limit", who, P.M);
-  const size_t smem = ((size_t)3 * P.S + (size_t)CQ * hd) * sizeof(float);
+  const size_t smem = ((size_t)3 * P.S + (size_t)4 * hd) * sizeof(float);
   if (smem > 48 * 1024) KV4_REJECT("%s: too many partials per row (%d)", who, P.S);
   const bool bf = dt == YSKN_KV4_BF16;
   if (dt != YSKN_KV4_F16 && dt != YSKN_KV4_BF16) KV4_REJECT("%s: act_dtype must be F16 or BF16", who);

@@ -209,7 +209,7 @@ template <int HD> struct TcLay {
   static constexpr int KV_TILE = KBLK * KV_BLOCK;
   static constexpr int STAGE = 2 * KV_TILE;                // K then V
   static constexpr int P_BYTES = 128 * TC_BN * 2;
-  static constexpr int OFF_Q = 0, OFF_ST = Q_BYTES, OFF_P = OFF_ST + 2 * STAGE, OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_Q = 0, OFF_ST = Q_BYTES, OFF_P = OFF_ST + 2 * STAGE, OFF_BAR = OFF_P + 2 * P_BYTES;   // two P buffers
   static constexpr int TOTAL = OFF_BAR + 256;
   static constexpr uint32_t TM_S0 = 0, TM_S1 = TC_BN, TM_O = 2 * TC_BN;   // TMEM columns
   static_assert(TOTAL <= 227 * 1024, "shared memory budget");
@@ -220,6 +220,7 @@ template <int HD> struct TcLay {
 struct TcP {
   const int* d_pos; int M, splits, G, nh, max_ctx, ks_rows; float qscale;
   float* pm; float* pl; float* pacc;
+  uint16_t* o16; const uint16_t* bv;                       // splits == 1 and o16 set: store the finished rows, no partials
 };
 
 template <int HD>
@@ -230,11 +231,11 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = s_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // barriers (8 bytes each): full[2] empty[2] qfull sready[2] sfree[2] pready pvdone | tmem slot | abort flag
+  // barriers (8 bytes each): full[2] empty[2] qfull sready[2] sfree[2] pready[2] pvdone[2] | tmem slot | abort flag
   const uint32_t B0 = sb + L::OFF_BAR;
-  const uint32_t b_full = B0, b_empty = B0 + 16, b_q = B0 + 32, b_sready = B0 + 40, b_sfree = B0 + 56, b_pready = B0 + 72, b_pvdone = B0 + 80;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 96);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 100);
+  const uint32_t b_full = B0, b_empty = B0 + 16, b_q = B0 + 32, b_sready = B0 + 40, b_sfree = B0 + 56, b_pready = B0 + 72, b_pvdone = B0 + 88;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 104);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 108);
 
   // ---- geometry (uniform over the CTA)
   const int G = P.G, TOK = 128 / G, kvh = blockIdx.z, S = P.splits, split = blockIdx.y;
@@ -252,13 +253,16 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 
   if (sb & 1023u) { if (threadIdx.x == 0) atomicExch(&g_tc_status, 3); return; }
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) { bar_init(b_full + 8 * i, 1); bar_init(b_empty + 8 * i, 1); bar_init(b_sready + 8 * i, 1); bar_init(b_sfree + 8 * i, 4); }
-    bar_init(b_q, 1); bar_init(b_pready, 4); bar_init(b_pvdone, 1);
+    for (int i = 0; i < 2; ++i) {
+      bar_init(b_full + 8 * i, 1); bar_init(b_empty + 8 * i, 1); bar_init(b_sready + 8 * i, 1); bar_init(b_sfree + 8 * i, 4);
+      bar_init(b_pready + 8 * i, 4); bar_init(b_pvdone + 8 * i, 1);
+    }
+    bar_init(b_q, 1);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 5) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 96), "n"(L::TM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 104), "n"(L::TM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -319,13 +323,13 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         umma_commit(b_sready + 8 * buf);
         ++swr[buf];
       };
-      auto issue_pv = [&](int tile_i, int item_v) {                  // O (+)= P . V(item_v)
-        if (!bar_wait(b_pready, tile_i & 1)) { fail(); return; }
+      auto issue_pv = [&](int tile_i, int item_v) {                  // O (+)= P(tile_i & 1) . V(item_v)
+        if (!bar_wait(b_pready + 8 * (tile_i & 1), (tile_i >> 1) & 1)) { fail(); return; }
         tc_fence_after();
-        const uint32_t vaddr = sb + L::OFF_ST + (item_v & 1) * L::STAGE + L::KV_TILE;
+        const uint32_t vaddr = sb + L::OFF_ST + (item_v & 1) * L::STAGE + L::KV_TILE, paddr = sb + L::OFF_P + (tile_i & 1) * L::P_BYTES;
         #pragma unroll
         for (int ks = 0; ks < TC_BN / 16; ++ks)
-          umma(tmem + L::TM_O, smem_desc(sb + L::OFF_P + ks * 32, 16, 1024), smem_desc(vaddr + ks * 2048, L::KV_BLOCK, 1024), ID_PV,
+          umma(tmem + L::TM_O, smem_desc(paddr + ks * 32, 16, 1024), smem_desc(vaddr + ks * 2048, L::KV_BLOCK, 1024), ID_PV,
                (tile_i | ks) ? 1u : 0u);
       };
       if (!bar_wait(b_q, 0)) fail();
@@ -337,7 +341,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         issue_pv(i, i);
         if (!ok) break;
         umma_commit(b_empty + 8 * (i & 1));                          // K and V of item i are free once these MMAs are done
-        umma_commit(b_pvdone);
+        umma_commit(b_pvdone + 8 * (i & 1));
       }
       it = nbulk;
       // edge tiles: S from the int4 keys and from the shadow keys, one after the other
@@ -347,7 +351,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         issue_pv(i, it); if (!ok) break;
         umma_commit(b_empty + 8 * (it & 1));
         umma_commit(b_empty + 8 * ((it + 1) & 1));
-        umma_commit(b_pvdone);
+        umma_commit(b_pvdone + 8 * (i & 1));
       }
     }
   } else {
@@ -365,15 +369,10 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       const int j = j0 + i;
       const bool edge = i >= nbulk;
       const int buf = edge ? 0 : (i & 1);
-      float x[TC_BN];
+      float x0[32], x1[32];                                          // raw scores of the two 32-key halves
       if (!bar_wait(b_sready + 8 * buf, srd[buf] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
       tc_fence_after();
-      {
-        float a[32], b[32];
-        tmem_ld32(trow + (buf ? L::TM_S1 : L::TM_S0), a); tmem_ld32(trow + (buf ? L::TM_S1 : L::TM_S0) + 32, b);
-        #pragma unroll
-        for (int k = 0; k < 32; ++k) { x[k] = a[k] * cs; x[32 + k] = b[k] * cs; }
-      }
+      tmem_ld32(trow + (buf ? L::TM_S1 : L::TM_S0), x0); tmem_ld32(trow + (buf ? L::TM_S1 : L::TM_S0) + 32, x1);
       ++srd[buf];
       if (edge) {
         if (!bar_wait(b_sready + 8, srd[1] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
@@ -385,35 +384,44 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         const int g0 = 2 * j, g1 = 2 * j + 1, tb = j * TC_BN;
         #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          x[k] = !valid ? -INFINITY : g0 < cr ? x[k] : (g0 == cr && tb + k <= pr) ? a[k] * cs : -INFINITY;
-          x[32 + k] = !valid ? -INFINITY : g1 < cr ? x[32 + k] : (g1 == cr && tb + 32 + k <= pr) ? b[k] * cs : -INFINITY;
+          x0[k] = g0 < cr ? x0[k] : (g0 == cr && tb + k <= pr) ? a[k] : -INFINITY;
+          x1[k] = g1 < cr ? x1[k] : (g1 == cr && tb + 32 + k <= pr) ? b[k] : -INFINITY;
         }
-      } else if (!valid) {
-        #pragma unroll
-        for (int k = 0; k < TC_BN; ++k) x[k] = -INFINITY;
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) { bar_arrive(b_sfree + 8 * buf); if (edge) bar_arrive(b_sfree + 8); }
-      // ---- online softmax, log2 domain, lazy rescale (the running max may lag the true one by up to 2^8)
-      float tmax = x[0];
+      // ---- online softmax in the log2 domain on p = 2^(x*cs - m); lazy rescale (the running max may lag by up to 2^8)
+      float tmax = fmaxf(x0[0], x1[0]);
       #pragma unroll
-      for (int k = 1; k < TC_BN; ++k) tmax = fmaxf(tmax, x[k]);
-      const bool bump = tmax > m + 8.f;
+      for (int k = 1; k < 32; ++k) tmax = fmaxf(tmax, fmaxf(x0[k], x1[k]));
+      tmax *= cs;
+      const bool bump = valid && tmax > m + 8.f;
       const float mn = bump ? tmax : m, alpha = bump ? tc_ex2(m - mn) : 1.f;
       m = mn; l *= alpha;
       uint32_t pk[TC_BN / 2];
-      float ls = 0.f;
-      #pragma unroll
-      for (int k = 0; k < TC_BN; k += 2) {
-        const float p0 = tc_ex2(x[k] - m), p1 = tc_ex2(x[k + 1] - m);      // exp2(-inf) = 0 for masked keys
-        ls += p0 + p1; pk[k / 2] = tc_pack(p0, p1);
+      {
+        const float nm = -m;
+        float ls0 = 0.f, ls1 = 0.f;
+        #pragma unroll
+        for (int k = 0; k < 32; k += 2) {
+          const float p0 = tc_ex2(fmaf(x0[k], cs, nm)), p1 = tc_ex2(fmaf(x0[k + 1], cs, nm));      // exp2(-inf) = 0 for masked keys
+          const float p2 = tc_ex2(fmaf(x1[k], cs, nm)), p3 = tc_ex2(fmaf(x1[k + 1], cs, nm));
+          ls0 += p0 + p1; ls1 += p2 + p3; pk[k / 2] = tc_pack(p0, p1); pk[16 + k / 2] = tc_pack(p2, p3);
+        }
+        l += ls0 + ls1;
       }
-      l += ls;
-      // ---- O and the P buffer are free once P.V of the previous tile is done
-      if (i > 0 && !bar_wait(b_pvdone, (i - 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
-      tc_fence_after();
+      if (__any_sync(0xffffffffu, !valid) && !valid) {               // rows of the tile that hold no query: P = 0, state untouched
+        #pragma unroll
+        for (int k = 0; k < TC_BN / 2; ++k) pk[k] = 0u;
+        l = 0.f;
+      }
+      // ---- this tile's P buffer is free once P.V of tile i-2 is done; O may be rescaled once P.V of tile i-1 is done
+      const int pb = i & 1;
+      if (i >= 2 && !bar_wait(b_pvdone + 8 * pb, ((i >> 1) - 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
       if (i > 0 && __any_sync(0xffffffffu, bump)) {                  // rows that did not bump multiply by exactly 1
+        if (!bar_wait(b_pvdone + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
+        tc_fence_after();
         #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
           float o[32];
@@ -425,7 +433,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         tmem_st_wait();
       }
       {
-        const uint32_t prow = sb + L::OFF_P + rho * 128;
+        const uint32_t prow = sb + L::OFF_P + pb * L::P_BYTES + rho * 128;
         #pragma unroll
         for (int c = 0; c < 8; ++c)
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + ((c ^ (rho & 7)) << 4)), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
@@ -434,14 +442,15 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) bar_arrive(b_pready);
+      if (lane == 0) bar_arrive(b_pready + 8 * pb);
     }
     // ---- this split's partial: (m, l, O) per (row, head); m back in natural-log units
-    if (ok && n > 0 && !bar_wait(b_pvdone, (n - 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; }
+    if (ok && n > 0 && !bar_wait(b_pvdone + 8 * ((n - 1) & 1), ((n - 1) >> 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; }
     tc_fence_after();
     if (ok && !*s_abort) {
       const size_t pidx = ((size_t)tok * S + split) * P.nh + kvh * G + head;
-      if (valid) { P.pm[pidx] = (n > 0 && m > -1e29f) ? m * TC_LN2 : -1e30f; P.pl[pidx] = n > 0 ? l : 0.f; }
+      const bool direct = P.o16 != nullptr && S == 1;                // one split: this CTA holds the whole row, finish it here
+      if (valid && !direct) { P.pm[pidx] = (n > 0 && m > -1e29f) ? m * TC_LN2 : -1e30f; P.pl[pidx] = n > 0 ? l : 0.f; }
       #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         float o[32];
@@ -450,7 +459,19 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           #pragma unroll
           for (int k = 0; k < 32; ++k) o[k] = 0.f;
         }
-        if (valid) {
+        if (valid && direct) {                                       // y = round_f16(o / l) (+ V bias), as the merge kernel
+          const size_t oi = ((size_t)tok * P.nh + kvh * G + head) * HD + 32 * c;
+          uint32_t w[16];
+          #pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            float y0 = round_f16(o[k] / l), y1 = round_f16(o[k + 1] / l);
+            if (P.bv) { y0 = __fadd_rn(y0, h2f(P.bv[kvh * HD + 32 * c + k])); y1 = __fadd_rn(y1, h2f(P.bv[kvh * HD + 32 * c + k + 1])); }
+            w[k / 2] = (uint32_t)f2h(y0) | ((uint32_t)f2h(y1) << 16);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(P.o16 + oi);
+          #pragma unroll
+          for (int k = 0; k < 4; ++k) dst[k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+        } else if (valid) {
           float4* dst = reinterpret_cast<float4*>(P.pacc + pidx * HD + 32 * c);
           #pragma unroll
           for (int k = 0; k < 8; ++k) dst[k] = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
@@ -508,7 +529,7 @@ TcWs carve(void* ws, int kvh, int hd, int max_ctx, int M) {
 }
 
 template <int HD>
-int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int valid_tokens, cudaStream_t st) {
+int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int valid_tokens, uint16_t* o16, const uint16_t* bv, cudaStream_t st) {
   using L = TcLay<HD>;
   PrepP pp{a.kv, a.d_pos, a.M, a.max_ctx, a.kvh, a.rope, rd, w.kd, w.vd, w.ks, w.ks_rows, valid_tokens};
   const long long warps = (long long)a.max_ctx * a.kvh;
@@ -523,7 +544,7 @@ int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int va
   static bool attr = false;
   if (!attr) { KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL)); attr = true; }
   const int tok = 128 / g, qtiles = (a.M + tok - 1) / tok;
-  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc};
+  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv};
   kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mq, mkd, mvd, mks, P);
   return launch_status("kv4_tc_attn_kernel");
 }
@@ -538,14 +559,15 @@ bool attention_tc_supports(int g, int hd, int rd, int act_dtype) {
 size_t attention_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M) { return carve(nullptr, kvh, hd, max_ctx, M).bytes; }
 
 int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, void* workspace, size_t workspace_bytes,
-                        int valid_tokens, cudaStream_t st) {
+                        int valid_tokens, uint16_t* o16_direct, const uint16_t* bv, cudaStream_t st) {
   if (!attention_tc_supports(g, hd, rd, act_dtype))
     KV4_REJECT("yskn_kv4_attention_tc: unsupported (g %d, hd %d, rd %d, act_dtype %d): fp16 activations, hd 128/256", g, hd, rd, act_dtype);
   const TcWs w = carve(workspace, a.kvh, hd, a.max_ctx, a.M);
   if (!workspace || workspace_bytes < w.bytes) KV4_REJECT("yskn_kv4_attention_tc: workspace of %zu bytes needed, %zu given", w.bytes, workspace_bytes);
   if (((uintptr_t)workspace | (uintptr_t)a.q16) & 15) KV4_REJECT("yskn_kv4_attention_tc: workspace and q16 must be 16-byte aligned");
   if (valid_tokens < 0) valid_tokens = 0;
-  return hd == 256 ? launch_tc_hd<256>(a, g, rd, w, valid_tokens, st) : launch_tc_hd<128>(a, g, rd, w, valid_tokens, st);
+  if (o16_direct && ((uintptr_t)o16_direct & 15)) KV4_REJECT("yskn_kv4_prefill_tc: o16 must be 16-byte aligned");
+  return hd == 256 ? launch_tc_hd<256>(a, g, rd, w, valid_tokens, o16_direct, bv, st) : launch_tc_hd<128>(a, g, rd, w, valid_tokens, o16_direct, bv, st);
 }
 
 int tc_status_fetch(int* out) {
