@@ -13,11 +13,12 @@
 //     group, Vd = int4 values of every token, Ks = rotated fp16-shadow keys of the groups the new rows live in.
 //     fp32 arithmetic, one rounding to fp16.  HBM-bound byte mover: one warp per (token, kv-head).
 //  2. kv4_tc_attn_kernel: one CTA = 128 query rows ((token, head) pairs of one kv-head) x one split of the keys.
-//       warp 4      TMA producer: Q tile once, then K/V tiles of 64 keys into a 2-stage mbarrier ring
-//       warp 5      issues tcgen05.mma: S = Q.K^T (M128 N64 K16 steps, both operands K-major, 128-byte swizzle) into one
+//       warp 8      TMA producer: Q tile once, then K/V tiles of 64 keys into a 2-stage mbarrier ring
+//       warp 9      issues tcgen05.mma: S = Q.K^T (M128 N64 K16 steps, both operands K-major, 128-byte swizzle) into one
 //                   of two TMEM buffers, and O += P.V (M128 N=HD, V as MN-major operand) into TMEM; commits to mbarriers
-//       warps 0-3   one query row per thread: tcgen05.ld of the S row, masks, online softmax in the log2 domain with a
-//                   lazy rescale of O, P -> fp16 -> shared memory in the operand layout; final (m, l, O) store
+//       warps 0-7   two threads per query row (32 of the tile's 64 keys each): tcgen05.ld of the S row, masks, online
+//                   softmax in the log2 domain with a lazy rescale of O, P -> fp16 -> shared memory (two buffers) in the
+//                   operand layout; final (m, l, O) store, or the finished fp16 row when there is a single split
 //     S of tile j+1 is issued before P.V of tile j, so the tensor pipe works while the softmax warps run.
 //     Tiles that contain a row's own group ("edge" tiles, at most two per CTA) get S twice, from Kd and from Ks, and
 //     each row picks per 32-key half: int4 keys for groups before its own, shadow keys (causally masked) for its own.
@@ -36,6 +37,14 @@
 namespace kv4 {
 
 __device__ int g_tc_status = 0;              // 0 ok; 4/5/6 = a bounded wait ran out in the softmax warps / MMA warp / producer
+
+#ifdef KV4_TC_TIMING
+// Diagnostic build only: cycles summed over softmax threads' lane 0 {wait S, TMEM load, math, wait PV/P buffer, P store+signal, tiles}.
+__device__ unsigned long long g_tc_cycles[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define TC_T(x) x
+#else
+#define TC_T(x)
+#endif
 
 namespace {
 
@@ -199,7 +208,8 @@ __device__ __forceinline__ uint32_t tc_pack(float lo, float hi) { uint32_t d; as
 
 // ------------------------------------------------------------------------------------------------ attention kernel
 constexpr int TC_BN = 64;                                  // keys per tile
-constexpr int TC_THREADS = 192;                            // warps 0-3 softmax, 4 producer, 5 MMA issuer
+constexpr int TC_SW = 8;                                   // softmax warps: warp w owns rows 32*(w%4).., key columns 32*(w/4)..
+constexpr int TC_THREADS = (TC_SW + 2) * 32;               // + producer warp, + MMA issuer warp
 
 template <int HD> struct TcLay {
   static constexpr int KBLK = HD / 64;                     // 64-channel (128-byte) operand blocks
@@ -207,10 +217,10 @@ template <int HD> struct TcLay {
   static constexpr int Q_BYTES = KBLK * Q_BLOCK;
   static constexpr int KV_BLOCK = TC_BN * 128;             // 64 keys x 128 bytes
   static constexpr int KV_TILE = KBLK * KV_BLOCK;
-  static constexpr int STAGE = 2 * KV_TILE;                // K then V
   static constexpr int P_BYTES = 128 * TC_BN * 2;
-  static constexpr int OFF_Q = 0, OFF_ST = Q_BYTES, OFF_P = OFF_ST + 2 * STAGE, OFF_BAR = OFF_P + 2 * P_BYTES;   // two P buffers
-  static constexpr int TOTAL = OFF_BAR + 256;
+  static constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_TILE, OFF_P = OFF_V + 2 * KV_TILE, OFF_BAR = OFF_P + 2 * P_BYTES;   // two K, V, P buffers each
+  static constexpr int OFF_XCH = OFF_BAR + 128;            // float val[2 tile parities][2 column halves][128 rows], u16 seq[2][128]
+  static constexpr int TOTAL = OFF_XCH + 2 * 2 * 128 * 4 + 2 * 128 * 2;
   static constexpr uint32_t TM_S0 = 0, TM_S1 = TC_BN, TM_O = 2 * TC_BN;   // TMEM columns
   static_assert(TOTAL <= 227 * 1024, "shared memory budget");
   static constexpr int TM_COLS = 2 * TC_BN + HD <= 256 ? 256 : 512;  // allocation must be a power of two
@@ -231,11 +241,12 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = s_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // barriers (8 bytes each): full[2] empty[2] qfull sready[2] sfree[2] pready[2] pvdone[2] | tmem slot | abort flag
+  // barriers (8 bytes each): kfull[2] kempty[2] qfull sready[2] sfree[2] pready[2] pvdone[2] vfull[2] | tmem slot | abort flag
   const uint32_t B0 = sb + L::OFF_BAR;
-  const uint32_t b_full = B0, b_empty = B0 + 16, b_q = B0 + 32, b_sready = B0 + 40, b_sfree = B0 + 56, b_pready = B0 + 72, b_pvdone = B0 + 88;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 104);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 108);
+  const uint32_t b_kfull = B0, b_kempty = B0 + 16, b_q = B0 + 32, b_sready = B0 + 40, b_sfree = B0 + 56, b_pready = B0 + 72, b_pvdone = B0 + 88,
+                 b_vfull = B0 + 104;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 120);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 124);
 
   // ---- geometry (uniform over the CTA)
   const int G = P.G, TOK = 128 / G, kvh = blockIdx.z, S = P.splits, split = blockIdx.y;
@@ -254,15 +265,16 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   if (sb & 1023u) { if (threadIdx.x == 0) atomicExch(&g_tc_status, 3); return; }
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
-      bar_init(b_full + 8 * i, 1); bar_init(b_empty + 8 * i, 1); bar_init(b_sready + 8 * i, 1); bar_init(b_sfree + 8 * i, 4);
-      bar_init(b_pready + 8 * i, 4); bar_init(b_pvdone + 8 * i, 1);
+      bar_init(b_kfull + 8 * i, 1); bar_init(b_kempty + 8 * i, 1); bar_init(b_sready + 8 * i, 1); bar_init(b_sfree + 8 * i, TC_SW);
+      bar_init(b_pready + 8 * i, TC_SW); bar_init(b_pvdone + 8 * i, 1); bar_init(b_vfull + 8 * i, 1);
     }
     bar_init(b_q, 1);
     *s_abort = 0;
+    for (int i = 0; i < 128; ++i) reinterpret_cast<volatile uint32_t*>(smem + L::OFF_XCH + 2 * 2 * 128 * 4)[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 104), "n"(L::TM_COLS) : "memory");
+  if (warp == TC_SW + 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 120), "n"(L::TM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -270,50 +282,47 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == TC_SW) {
     // ======================================================================= TMA producer
+    // Two rings of two tiles each: K tiles are free again as soon as their S MMAs are done, V tiles only after P.V,
+    // so the next K load starts a whole tile earlier than it would in a joint stage.
     if (lane == 0 && n > 0) {
       bar_expect_tx(b_q, L::KBLK * G * TOK * 128);
       for (int kb = 0; kb < L::KBLK; ++kb) tma_load_4d(sb + L::OFF_Q + kb * L::Q_BLOCK, &mapQ, 64 * kb, 0, kvh, tok0, b_q);
-      int it = 0; bool ok = true;
+      int kit = 0; bool ok = true;
       for (int i = 0; i < n && ok; ++i) {
         const int j = j0 + i;
-        for (int half = 0; half < (i >= nbulk ? 2 : 1) && ok; ++half, ++it) {       // item A: Kd+Vd; item B (edge tiles): Ks
-          const int st = it & 1;
-          if (it >= 2 && !bar_wait(b_empty + 8 * st, ((it >> 1) - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
+        for (int half = 0; half < (i >= nbulk ? 2 : 1) && ok; ++half, ++kit) {      // Kd; edge tiles: then Ks
+          const int st = kit & 1;
+          if (kit >= 2 && !bar_wait(b_kempty + 8 * st, ((kit >> 1) - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
           if (*s_abort) { ok = false; break; }
-          const uint32_t dst = sb + L::OFF_ST + st * L::STAGE, bar = b_full + 8 * st;
-          if (half == 0) {
-            bar_expect_tx(bar, 2 * L::KV_TILE);
-            const int row = kvh * P.max_ctx + j * TC_BN;
-            for (int kb = 0; kb < L::KBLK; ++kb) {
-              tma_load_2d(dst + kb * L::KV_BLOCK, &mapKd, 64 * kb, row, bar);
-              tma_load_2d(dst + L::KV_TILE + kb * L::KV_BLOCK, &mapVd, 64 * kb, row, bar);
-            }
-          } else {
-            bar_expect_tx(bar, L::KV_TILE);
-            const int row = kvh * P.ks_rows + j * TC_BN - ks0;
-            for (int kb = 0; kb < L::KBLK; ++kb) tma_load_2d(dst + kb * L::KV_BLOCK, &mapKs, 64 * kb, row, bar);
-          }
+          const uint32_t dst = sb + L::OFF_K + st * L::KV_TILE, bar = b_kfull + 8 * st;
+          bar_expect_tx(bar, L::KV_TILE);
+          const int row = half == 0 ? kvh * P.max_ctx + j * TC_BN : kvh * P.ks_rows + j * TC_BN - ks0;
+          for (int kb = 0; kb < L::KBLK; ++kb) tma_load_2d(dst + kb * L::KV_BLOCK, half == 0 ? &mapKd : &mapKs, 64 * kb, row, bar);
         }
+        if (!ok) break;
+        const int st = i & 1;                                        // V of tile i; its buffer was last read by P.V of tile i-2
+        if (i >= 2 && !bar_wait(b_pvdone + 8 * st, ((i >> 1) - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
+        bar_expect_tx(b_vfull + 8 * st, L::KV_TILE);
+        for (int kb = 0; kb < L::KBLK; ++kb)
+          tma_load_2d(sb + L::OFF_V + st * L::KV_TILE + kb * L::KV_BLOCK, &mapVd, 64 * kb, kvh * P.max_ctx + j * TC_BN, b_vfull + 8 * st);
       }
-      if (*s_abort)                                                  // let the last copies land before the CTA ends
-        for (int k = max(0, it - 2); k < it; ++k) bar_wait(b_full + 8 * (k & 1), (k >> 1) & 1);
     }
-  } else if (warp == 5) {
+  } else if (warp == TC_SW + 1) {
     // ======================================================================= MMA issuer (one thread)
     if (lane == 0 && n > 0) {
       constexpr uint32_t ID_S = instr_desc(128, TC_BN, false), ID_PV = instr_desc(128, HD, true);
       bool ok = true;
-      int it = 0;                                                    // load item counter (same order as the producer's)
+      int kit = 0;                                                   // K tile counter (same order as the producer's)
       int swr[2] = {0, 0};                                           // how often each S buffer has been written
       auto fail = [&]() { atomicExch(&g_tc_status, 5); *s_abort = 1; ok = false; };
       auto issue_s = [&](int item, int buf) {                        // S[buf] = Q . K(item)^T
         const int st = item & 1;
-        if (!bar_wait(b_full + 8 * st, (item >> 1) & 1)) { fail(); return; }
+        if (!bar_wait(b_kfull + 8 * st, (item >> 1) & 1)) { fail(); return; }
         if (swr[buf] > 0 && !bar_wait(b_sfree + 8 * buf, (swr[buf] - 1) & 1)) { fail(); return; }
         tc_fence_after();
-        const uint32_t kaddr = sb + L::OFF_ST + st * L::STAGE;
+        const uint32_t kaddr = sb + L::OFF_K + st * L::KV_TILE;
         #pragma unroll
         for (int kb = 0; kb < L::KBLK; ++kb)
           #pragma unroll
@@ -321,16 +330,20 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             umma(tmem + (buf ? L::TM_S1 : L::TM_S0), smem_desc(sb + L::OFF_Q + kb * L::Q_BLOCK + ks * 32, 16, 1024),
                  smem_desc(kaddr + kb * L::KV_BLOCK + ks * 32, 16, 1024), ID_S, (kb | ks) ? 1u : 0u);
         umma_commit(b_sready + 8 * buf);
+        umma_commit(b_kempty + 8 * st);                              // the K tile may be overwritten once these MMAs are done
         ++swr[buf];
       };
-      auto issue_pv = [&](int tile_i, int item_v) {                  // O (+)= P(tile_i & 1) . V(item_v)
-        if (!bar_wait(b_pready + 8 * (tile_i & 1), (tile_i >> 1) & 1)) { fail(); return; }
+      auto issue_pv = [&](int tile_i) {                              // O (+)= P(tile_i & 1) . V(tile_i & 1)
+        const int st = tile_i & 1;
+        if (!bar_wait(b_pready + 8 * st, (tile_i >> 1) & 1)) { fail(); return; }
+        if (!bar_wait(b_vfull + 8 * st, (tile_i >> 1) & 1)) { fail(); return; }
         tc_fence_after();
-        const uint32_t vaddr = sb + L::OFF_ST + (item_v & 1) * L::STAGE + L::KV_TILE, paddr = sb + L::OFF_P + (tile_i & 1) * L::P_BYTES;
+        const uint32_t vaddr = sb + L::OFF_V + st * L::KV_TILE, paddr = sb + L::OFF_P + st * L::P_BYTES;
         #pragma unroll
         for (int ks = 0; ks < TC_BN / 16; ++ks)
           umma(tmem + L::TM_O, smem_desc(paddr + ks * 32, 16, 1024), smem_desc(vaddr + ks * 2048, L::KV_BLOCK, 1024), ID_PV,
                (tile_i | ks) ? 1u : 0u);
+        umma_commit(b_pvdone + 8 * st);                              // frees P and V of this parity, and O for a rescale
       };
       if (!bar_wait(b_q, 0)) fail();
       // bulk tiles: S of the next tile is in flight while the softmax warps work on this one
@@ -338,84 +351,94 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       for (int i = 0; i < nbulk && ok; ++i) {
         if (i + 1 < nbulk) issue_s(i + 1, (i + 1) & 1);
         if (!ok) break;
-        issue_pv(i, i);
-        if (!ok) break;
-        umma_commit(b_empty + 8 * (i & 1));                          // K and V of item i are free once these MMAs are done
-        umma_commit(b_pvdone + 8 * (i & 1));
+        issue_pv(i);
       }
-      it = nbulk;
+      kit = nbulk;
       // edge tiles: S from the int4 keys and from the shadow keys, one after the other
-      for (int i = nbulk; i < n && ok; ++i, it += 2) {
-        issue_s(it, 0); if (!ok) break;
-        issue_s(it + 1, 1); if (!ok) break;
-        issue_pv(i, it); if (!ok) break;
-        umma_commit(b_empty + 8 * (it & 1));
-        umma_commit(b_empty + 8 * ((it + 1) & 1));
-        umma_commit(b_pvdone + 8 * (i & 1));
+      for (int i = nbulk; i < n && ok; ++i, kit += 2) {
+        issue_s(kit, 0); if (!ok) break;
+        issue_s(kit + 1, 1); if (!ok) break;
+        issue_pv(i);
       }
     }
   } else {
-    // ======================================================================= softmax warps: one query row per thread
-    const int rho = warp * 32 + lane;                                // row of the tile = TMEM lane
+    // ======================================================================= softmax warps: two threads per query row
+    const int quad = warp & 3, hf = warp >> 2;                       // TMEM lane quadrant; which 32 of the tile's 64 key columns
+    const int rho = quad * 32 + lane;                                // row of the tile = TMEM lane
     const int tok = tok0 + rho / G, head = rho % G;
     const bool valid = rho < TOK * G && tok < P.M;
     const int pr = pos0 + tok, cr = pr / 32;                         // row position and its own group
-    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
     const float cs = P.qscale * TC_LOG2E;
-    float m = -1e30f, l = 0.f;
+    // The row's two threads swap one float per tile through shared memory: value first, then a sequence number the
+    // partner polls (bounded, like every wait here; a named barrier could not give up).
+    volatile float* xval = reinterpret_cast<volatile float*>(smem + L::OFF_XCH);
+    volatile uint16_t* xseq = reinterpret_cast<volatile uint16_t*>(smem + L::OFF_XCH + 2 * 2 * 128 * 4);   // tags modulo 2^16
+    auto swap_with_partner = [&](float v, int tag) -> float {       // tag = 1, 2, 3, ... in program order
+      xval[((tag & 1) * 2 + hf) * 128 + rho] = v;
+      __threadfence_block();
+      xseq[hf * 128 + rho] = (uint16_t)tag;
+      for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {             // until the partner is at this tag (or one ahead)
+        if ((uint16_t)(xseq[(hf ^ 1) * 128 + rho] - (uint16_t)tag) < 0x8000u) { __threadfence_block(); return xval[((tag & 1) * 2 + (hf ^ 1)) * 128 + rho]; }
+      }
+      atomicExch(&g_tc_status, 4); *s_abort = 1;
+      return v;
+    };
+    float m = -1e30f, l = 0.f;                                       // m is common to the row's two threads, l is this half's sum
     int srd[2] = {0, 0};                                             // how often each S buffer has been read
     bool ok = true;
     for (int i = 0; i < n && ok; ++i) {
       const int j = j0 + i;
       const bool edge = i >= nbulk;
       const int buf = edge ? 0 : (i & 1);
-      float x0[32], x1[32];                                          // raw scores of the two 32-key halves
+      float x[32];                                                   // raw scores of this thread's 32 keys
+      TC_T(long long c0 = clock64();)
       if (!bar_wait(b_sready + 8 * buf, srd[buf] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
       tc_fence_after();
-      tmem_ld32(trow + (buf ? L::TM_S1 : L::TM_S0), x0); tmem_ld32(trow + (buf ? L::TM_S1 : L::TM_S0) + 32, x1);
+      TC_T(long long c1 = clock64();)
+      tmem_ld32(trow + (buf ? L::TM_S1 : L::TM_S0) + 32 * hf, x);
       ++srd[buf];
       if (edge) {
         if (!bar_wait(b_sready + 8, srd[1] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
         tc_fence_after();
-        float a[32], b[32];
-        tmem_ld32(trow + L::TM_S1, a); tmem_ld32(trow + L::TM_S1 + 32, b);
+        float a[32];
+        tmem_ld32(trow + L::TM_S1 + 32 * hf, a);
         ++srd[1];
-        // per 32-key half: group before the row's own -> int4 keys; own group -> shadow keys up to the row; later -> nothing
-        const int g0 = 2 * j, g1 = 2 * j + 1, tb = j * TC_BN;
+        // this 32-key half is one group: before the row's own -> int4 keys; own group -> shadow keys up to the row; later -> nothing
+        const int gk = 2 * j + hf, tb = j * TC_BN + 32 * hf;
         #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          x0[k] = g0 < cr ? x0[k] : (g0 == cr && tb + k <= pr) ? a[k] : -INFINITY;
-          x1[k] = g1 < cr ? x1[k] : (g1 == cr && tb + 32 + k <= pr) ? b[k] : -INFINITY;
-        }
+        for (int k = 0; k < 32; ++k) x[k] = gk < cr ? x[k] : (gk == cr && tb + k <= pr) ? a[k] : -INFINITY;
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) { bar_arrive(b_sfree + 8 * buf); if (edge) bar_arrive(b_sfree + 8); }
+      TC_T(long long c2 = clock64();)
       // ---- online softmax in the log2 domain on p = 2^(x*cs - m); lazy rescale (the running max may lag by up to 2^8)
-      float tmax = fmaxf(x0[0], x1[0]);
+      float tmax = x[0];
       #pragma unroll
-      for (int k = 1; k < 32; ++k) tmax = fmaxf(tmax, fmaxf(x0[k], x1[k]));
-      tmax *= cs;
+      for (int k = 1; k < 32; ++k) tmax = fmaxf(tmax, x[k]);
+      tmax = fmaxf(tmax, swap_with_partner(tmax, i + 1)) * cs;        // the row's two threads swap their maxima
       const bool bump = valid && tmax > m + 8.f;
       const float mn = bump ? tmax : m, alpha = bump ? tc_ex2(m - mn) : 1.f;
       m = mn; l *= alpha;
-      uint32_t pk[TC_BN / 2];
+      uint32_t pk[16];
       {
         const float nm = -m;
         float ls0 = 0.f, ls1 = 0.f;
         #pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          const float p0 = tc_ex2(fmaf(x0[k], cs, nm)), p1 = tc_ex2(fmaf(x0[k + 1], cs, nm));      // exp2(-inf) = 0 for masked keys
-          const float p2 = tc_ex2(fmaf(x1[k], cs, nm)), p3 = tc_ex2(fmaf(x1[k + 1], cs, nm));
-          ls0 += p0 + p1; ls1 += p2 + p3; pk[k / 2] = tc_pack(p0, p1); pk[16 + k / 2] = tc_pack(p2, p3);
+        for (int k = 0; k < 32; k += 4) {
+          const float p0 = tc_ex2(fmaf(x[k], cs, nm)), p1 = tc_ex2(fmaf(x[k + 1], cs, nm));        // exp2(-inf) = 0 for masked keys
+          const float p2 = tc_ex2(fmaf(x[k + 2], cs, nm)), p3 = tc_ex2(fmaf(x[k + 3], cs, nm));
+          ls0 += p0 + p1; ls1 += p2 + p3; pk[k / 2] = tc_pack(p0, p1); pk[k / 2 + 1] = tc_pack(p2, p3);
         }
         l += ls0 + ls1;
       }
       if (__any_sync(0xffffffffu, !valid) && !valid) {               // rows of the tile that hold no query: P = 0, state untouched
         #pragma unroll
-        for (int k = 0; k < TC_BN / 2; ++k) pk[k] = 0u;
+        for (int k = 0; k < 16; ++k) pk[k] = 0u;
         l = 0.f;
       }
+      TC_T(long long c3 = clock64();)
       // ---- this tile's P buffer is free once P.V of tile i-2 is done; O may be rescaled once P.V of tile i-1 is done
       const int pb = i & 1;
       if (i >= 2 && !bar_wait(b_pvdone + 8 * pb, ((i >> 1) - 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
@@ -423,7 +446,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         if (!bar_wait(b_pvdone + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
         tc_fence_after();
         #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = hf; c < HD / 32; c += 2) {                      // the row's two threads take alternate 32-column chunks of O
           float o[32];
           tmem_ld32(trow + L::TM_O + 32 * c, o);
           #pragma unroll
@@ -432,27 +455,32 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         }
         tmem_st_wait();
       }
+      TC_T(long long c4 = clock64();)
       {
         const uint32_t prow = sb + L::OFF_P + pb * L::P_BYTES + rho * 128;
         #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + ((c ^ (rho & 7)) << 4)), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
+        for (int c = 0; c < 4; ++c)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (((4 * hf + c) ^ (rho & 7)) << 4)), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
                        "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
       tc_fence_before();
       __syncwarp();
       if (lane == 0) bar_arrive(b_pready + 8 * pb);
+      TC_T(if (lane == 0 && warp == 0) { long long c5 = clock64(); atomicAdd(&g_tc_cycles[0], (unsigned long long)(c1 - c0)); atomicAdd(&g_tc_cycles[1], (unsigned long long)(c2 - c1));
+             atomicAdd(&g_tc_cycles[2], (unsigned long long)(c3 - c2)); atomicAdd(&g_tc_cycles[3], (unsigned long long)(c4 - c3)); atomicAdd(&g_tc_cycles[4], (unsigned long long)(c5 - c4));
+             atomicAdd(&g_tc_cycles[5], 1ull); })
     }
-    // ---- this split's partial: (m, l, O) per (row, head); m back in natural-log units
+    // ---- this split's result per (row, head): (m, l, O) partial, or the finished row when there is one split
     if (ok && n > 0 && !bar_wait(b_pvdone + 8 * ((n - 1) & 1), ((n - 1) >> 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; }
     tc_fence_after();
+    if (ok) l += swap_with_partner(l, n + 1);                        // the row's sum = the two halves' sums
     if (ok && !*s_abort) {
       const size_t pidx = ((size_t)tok * S + split) * P.nh + kvh * G + head;
       const bool direct = P.o16 != nullptr && S == 1;                // one split: this CTA holds the whole row, finish it here
-      if (valid && !direct) { P.pm[pidx] = (n > 0 && m > -1e29f) ? m * TC_LN2 : -1e30f; P.pl[pidx] = n > 0 ? l : 0.f; }
+      if (valid && !direct && hf == 0) { P.pm[pidx] = (n > 0 && m > -1e29f) ? m * TC_LN2 : -1e30f; P.pl[pidx] = n > 0 ? l : 0.f; }
       #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = hf; c < HD / 32; c += 2) {
         float o[32];
         if (n > 0) tmem_ld32(trow + L::TM_O + 32 * c, o);
         else {
@@ -481,7 +509,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(L::TM_COLS) : "memory");
+  if (warp == TC_SW + 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(L::TM_COLS) : "memory");
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -569,6 +597,14 @@ int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int ac
   if (o16_direct && ((uintptr_t)o16_direct & 15)) KV4_REJECT("yskn_kv4_prefill_tc: o16 must be 16-byte aligned");
   return hd == 256 ? launch_tc_hd<256>(a, g, rd, w, valid_tokens, o16_direct, bv, st) : launch_tc_hd<128>(a, g, rd, w, valid_tokens, o16_direct, bv, st);
 }
+
+#ifdef KV4_TC_TIMING
+extern "C" __attribute__((visibility("default"))) int yskn_kv4_tc_debug_cycles(unsigned long long* out8) {
+  if (cudaMemcpyFromSymbol(out8, g_tc_cycles, 64) != cudaSuccess) return 1;
+  unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  return cudaMemcpyToSymbol(g_tc_cycles, z, 64) != cudaSuccess;
+}
+#endif
 
 int tc_status_fetch(int* out) {
   int v = 0;
