@@ -13,7 +13,7 @@
 //     group, Vd = int4 values of every token, Ks = rotated fp16-shadow keys of the groups the new rows live in.
 //     fp32 arithmetic, one rounding to fp16.  HBM-bound byte mover: one warp per (token, kv-head).
 //  2. kv4_tc_attn_kernel: one CTA = 128 query rows ((token, head) pairs of one kv-head) x one split of the keys.
-//       warp 8      TMA producer: Q tile once, then K/V tiles of 64 keys into a 2-stage mbarrier ring
+//       warp 8      TMA producer: Q tile once, then K and V tiles of 64 keys into two 2-stage mbarrier rings
 //       warp 9      issues tcgen05.mma: S = Q.K^T (M128 N64 K16 steps, both operands K-major, 128-byte swizzle) into one
 //                   of two TMEM buffers, and O += P.V (M128 N=HD, V as MN-major operand) into TMEM; commits to mbarriers
 //       warps 0-7   two threads per query row (32 of the tile's 64 keys each): tcgen05.ld of the S row, masks, online
@@ -176,6 +176,11 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t b
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// A operand (128 rows x 16 k, fp16 pairs in 8 columns) from tensor memory, B from shared memory.
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -202,6 +207,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
                  "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
                  "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31])) : "memory");
 }
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
+                 "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                 "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_st16u(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
+                 "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float tc_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ uint32_t tc_pack(float lo, float hi) { uint32_t d; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo)); return d; }
@@ -211,23 +227,26 @@ constexpr int TC_BN = 64;                                  // keys per tile
 constexpr int TC_SW = 8;                                   // softmax warps: warp w owns rows 32*(w%4).., key columns 32*(w/4)..
 constexpr int TC_THREADS = (TC_SW + 2) * 32;               // + producer warp, + MMA issuer warp
 
+// Shared memory holds only the K and V rings: Q, S, P and O live in tensor memory, so every MMA reads one operand
+// from shared memory, not two (the S MMAs with Q in shared memory alone moved 96 KB per tile through the 128 B/clk port).
 template <int HD> struct TcLay {
   static constexpr int KBLK = HD / 64;                     // 64-channel (128-byte) operand blocks
-  static constexpr int Q_BLOCK = 128 * 128;                // 128 rows x 128 bytes
-  static constexpr int Q_BYTES = KBLK * Q_BLOCK;
   static constexpr int KV_BLOCK = TC_BN * 128;             // 64 keys x 128 bytes
   static constexpr int KV_TILE = KBLK * KV_BLOCK;
-  static constexpr int P_BYTES = 128 * TC_BN * 2;
-  static constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_TILE, OFF_P = OFF_V + 2 * KV_TILE, OFF_BAR = OFF_P + 2 * P_BYTES;   // two K, V, P buffers each
-  static constexpr int OFF_XCH = OFF_BAR + 128;            // float val[2 tile parities][2 column halves][128 rows], u16 seq[2][128]
+  static constexpr int NK = HD == 256 ? 3 : 4, NV = 4;     // ring depths
+  static constexpr int OFF_K = 0, OFF_V = NK * KV_TILE, OFF_BAR = OFF_V + NV * KV_TILE;
+  static constexpr int OFF_XCH = OFF_BAR + 192;            // float val[2 tile parities][2 column halves][128 rows], u16 seq[2][128]
   static constexpr int TOTAL = OFF_XCH + 2 * 2 * 128 * 4 + 2 * 128 * 2;
-  static constexpr uint32_t TM_S0 = 0, TM_S1 = TC_BN, TM_O = 2 * TC_BN;   // TMEM columns
+  // TMEM columns (32-bit): two S buffers of 64 fp32 columns (P, fp16 pairs, is written over the S columns its
+  // thread has read: 16 columns at +0 for keys 0-31, 16 at +32 for keys 32-63), O, and Q as fp16 pairs.
+  static constexpr uint32_t TM_S0 = 0, TM_S1 = TC_BN, TM_O = 2 * TC_BN, TM_Q = 2 * TC_BN + HD;
+  static constexpr int TM_COLS = 512;
   static_assert(TOTAL <= 227 * 1024, "shared memory budget");
-  static constexpr int TM_COLS = 2 * TC_BN + HD <= 256 ? 256 : 512;  // allocation must be a power of two
-  static_assert(2 * TC_BN + HD <= 512, "TMEM columns");
+  static_assert(2 * TC_BN + HD + HD / 2 <= 512, "TMEM columns");
 };
 
 struct TcP {
+  const uint16_t* q16;                                     // [M][nh][HD]
   const int* d_pos; int M, splits, G, nh, max_ctx, ks_rows; float qscale;
   float* pm; float* pl; float* pacc;
   uint16_t* o16; const uint16_t* bv;                       // splits == 1 and o16 set: store the finished rows, no partials
@@ -235,18 +254,18 @@ struct TcP {
 
 template <int HD>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapKd,
-                   const __grid_constant__ CUtensorMap mapVd, const __grid_constant__ CUtensorMap mapKs, const TcP P) {
+kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_constant__ CUtensorMap mapVd,
+                   const __grid_constant__ CUtensorMap mapKs, const TcP P) {
   using L = TcLay<HD>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = s_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // barriers (8 bytes each): kfull[2] kempty[2] qfull sready[2] sfree[2] pready[2] pvdone[2] vfull[2] | tmem slot | abort flag
+  // barriers (8 bytes each): kfull[4] kempty[4] vfull[4] vempty[4] sready[2] pready[2] pvdone[2] qready | tmem slot | abort flag
   const uint32_t B0 = sb + L::OFF_BAR;
-  const uint32_t b_kfull = B0, b_kempty = B0 + 16, b_q = B0 + 32, b_sready = B0 + 40, b_sfree = B0 + 56, b_pready = B0 + 72, b_pvdone = B0 + 88,
-                 b_vfull = B0 + 104;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 120);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 124);
+  const uint32_t b_kfull = B0, b_kempty = B0 + 32, b_vfull = B0 + 64, b_vempty = B0 + 96, b_sready = B0 + 128, b_pready = B0 + 144,
+                 b_pvdone = B0 + 160, b_q = B0 + 176;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 184);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 188);
 
   // ---- geometry (uniform over the CTA)
   const int G = P.G, TOK = 128 / G, kvh = blockIdx.z, S = P.splits, split = blockIdx.y;
@@ -264,17 +283,15 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 
   if (sb & 1023u) { if (threadIdx.x == 0) atomicExch(&g_tc_status, 3); return; }
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      bar_init(b_kfull + 8 * i, 1); bar_init(b_kempty + 8 * i, 1); bar_init(b_sready + 8 * i, 1); bar_init(b_sfree + 8 * i, TC_SW);
-      bar_init(b_pready + 8 * i, TC_SW); bar_init(b_pvdone + 8 * i, 1); bar_init(b_vfull + 8 * i, 1);
-    }
-    bar_init(b_q, 1);
+    for (int i = 0; i < 4; ++i) { bar_init(b_kfull + 8 * i, 1); bar_init(b_kempty + 8 * i, 1); bar_init(b_vfull + 8 * i, 1); bar_init(b_vempty + 8 * i, 1); }
+    for (int i = 0; i < 2; ++i) { bar_init(b_sready + 8 * i, 1); bar_init(b_pready + 8 * i, TC_SW); bar_init(b_pvdone + 8 * i, 1); }
+    bar_init(b_q, TC_SW);
     *s_abort = 0;
     for (int i = 0; i < 128; ++i) reinterpret_cast<volatile uint32_t*>(smem + L::OFF_XCH + 2 * 2 * 128 * 4)[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == TC_SW + 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 120), "n"(L::TM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 184), "n"(L::TM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -284,17 +301,14 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 
   if (warp == TC_SW) {
     // ======================================================================= TMA producer
-    // Two rings of two tiles each: K tiles are free again as soon as their S MMAs are done, V tiles only after P.V,
-    // so the next K load starts a whole tile earlier than it would in a joint stage.
+    // Two rings: K tiles are free again as soon as their S MMAs are done, V tiles only after P.V.
     if (lane == 0 && n > 0) {
-      bar_expect_tx(b_q, L::KBLK * G * TOK * 128);
-      for (int kb = 0; kb < L::KBLK; ++kb) tma_load_4d(sb + L::OFF_Q + kb * L::Q_BLOCK, &mapQ, 64 * kb, 0, kvh, tok0, b_q);
       int kit = 0; bool ok = true;
       for (int i = 0; i < n && ok; ++i) {
         const int j = j0 + i;
         for (int half = 0; half < (i >= nbulk ? 2 : 1) && ok; ++half, ++kit) {      // Kd; edge tiles: then Ks
-          const int st = kit & 1;
-          if (kit >= 2 && !bar_wait(b_kempty + 8 * st, ((kit >> 1) - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
+          const int st = kit % L::NK;
+          if (kit >= L::NK && !bar_wait(b_kempty + 8 * st, (kit / L::NK - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
           if (*s_abort) { ok = false; break; }
           const uint32_t dst = sb + L::OFF_K + st * L::KV_TILE, bar = b_kfull + 8 * st;
           bar_expect_tx(bar, L::KV_TILE);
@@ -302,8 +316,8 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           for (int kb = 0; kb < L::KBLK; ++kb) tma_load_2d(dst + kb * L::KV_BLOCK, half == 0 ? &mapKd : &mapKs, 64 * kb, row, bar);
         }
         if (!ok) break;
-        const int st = i & 1;                                        // V of tile i; its buffer was last read by P.V of tile i-2
-        if (i >= 2 && !bar_wait(b_pvdone + 8 * st, ((i >> 1) - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
+        const int st = i % L::NV;                                    // V of tile i; its buffer was last read by P.V of tile i-NV
+        if (i >= L::NV && !bar_wait(b_vempty + 8 * st, (i / L::NV - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
         bar_expect_tx(b_vfull + 8 * st, L::KV_TILE);
         for (int kb = 0; kb < L::KBLK; ++kb)
           tma_load_2d(sb + L::OFF_V + st * L::KV_TILE + kb * L::KV_BLOCK, &mapVd, 64 * kb, kvh * P.max_ctx + j * TC_BN, b_vfull + 8 * st);
@@ -311,54 +325,53 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     }
   } else if (warp == TC_SW + 1) {
     // ======================================================================= MMA issuer (one thread)
+    // The tensor pipe runs this thread's MMAs in issue order, so S of tile i+2, issued after P.V of tile i, may
+    // overwrite the TMEM buffer that P.V reads P from without a barrier in between.
     if (lane == 0 && n > 0) {
       constexpr uint32_t ID_S = instr_desc(128, TC_BN, false), ID_PV = instr_desc(128, HD, true);
       bool ok = true;
-      int kit = 0;                                                   // K tile counter (same order as the producer's)
-      int swr[2] = {0, 0};                                           // how often each S buffer has been written
       auto fail = [&]() { atomicExch(&g_tc_status, 5); *s_abort = 1; ok = false; };
-      auto issue_s = [&](int item, int buf) {                        // S[buf] = Q . K(item)^T
-        const int st = item & 1;
-        if (!bar_wait(b_kfull + 8 * st, (item >> 1) & 1)) { fail(); return; }
-        if (swr[buf] > 0 && !bar_wait(b_sfree + 8 * buf, (swr[buf] - 1) & 1)) { fail(); return; }
+      auto issue_s = [&](int item, int buf) {                        // S[buf] = Q . K(item)^T, Q from TMEM
+        const int st = item % L::NK;
+        if (!bar_wait(b_kfull + 8 * st, (item / L::NK) & 1)) { fail(); return; }
         tc_fence_after();
         const uint32_t kaddr = sb + L::OFF_K + st * L::KV_TILE;
         #pragma unroll
         for (int kb = 0; kb < L::KBLK; ++kb)
           #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            umma(tmem + (buf ? L::TM_S1 : L::TM_S0), smem_desc(sb + L::OFF_Q + kb * L::Q_BLOCK + ks * 32, 16, 1024),
-                 smem_desc(kaddr + kb * L::KV_BLOCK + ks * 32, 16, 1024), ID_S, (kb | ks) ? 1u : 0u);
+            umma_ts(tmem + (buf ? L::TM_S1 : L::TM_S0), tmem + L::TM_Q + 32 * kb + 8 * ks,
+                    smem_desc(kaddr + kb * L::KV_BLOCK + ks * 32, 16, 1024), ID_S, (kb | ks) ? 1u : 0u);
         umma_commit(b_sready + 8 * buf);
         umma_commit(b_kempty + 8 * st);                              // the K tile may be overwritten once these MMAs are done
-        ++swr[buf];
       };
-      auto issue_pv = [&](int tile_i) {                              // O (+)= P(tile_i & 1) . V(tile_i & 1)
-        const int st = tile_i & 1;
-        if (!bar_wait(b_pready + 8 * st, (tile_i >> 1) & 1)) { fail(); return; }
-        if (!bar_wait(b_vfull + 8 * st, (tile_i >> 1) & 1)) { fail(); return; }
+      auto issue_pv = [&](int tile_i, int buf) {                     // O (+)= P . V(tile_i), P from TMEM (over S[buf])
+        const int st = tile_i % L::NV;
+        if (!bar_wait(b_pready + 8 * (tile_i & 1), (tile_i >> 1) & 1)) { fail(); return; }
+        if (!bar_wait(b_vfull + 8 * st, (tile_i / L::NV) & 1)) { fail(); return; }
         tc_fence_after();
-        const uint32_t vaddr = sb + L::OFF_V + st * L::KV_TILE, paddr = sb + L::OFF_P + st * L::P_BYTES;
+        const uint32_t vaddr = sb + L::OFF_V + st * L::KV_TILE, pcol = tmem + (buf ? L::TM_S1 : L::TM_S0);
         #pragma unroll
         for (int ks = 0; ks < TC_BN / 16; ++ks)
-          umma(tmem + L::TM_O, smem_desc(paddr + ks * 32, 16, 1024), smem_desc(vaddr + ks * 2048, L::KV_BLOCK, 1024), ID_PV,
-               (tile_i | ks) ? 1u : 0u);
-        umma_commit(b_pvdone + 8 * st);                              // frees P and V of this parity, and O for a rescale
+          umma_ts(tmem + L::TM_O, pcol + 32 * (ks >> 1) + 8 * (ks & 1), smem_desc(vaddr + ks * 2048, L::KV_BLOCK, 1024), ID_PV,
+                  (tile_i | ks) ? 1u : 0u);
+        umma_commit(b_pvdone + 8 * (tile_i & 1));                    // O may be rescaled
+        umma_commit(b_vempty + 8 * st);                              // the V tile may be overwritten
       };
       if (!bar_wait(b_q, 0)) fail();
-      // bulk tiles: S of the next tile is in flight while the softmax warps work on this one
+      tc_fence_after();
+      // bulk tiles: S of the next two tiles is done or in flight while the softmax warps work on this one
       if (ok && nbulk > 0) issue_s(0, 0);
+      if (ok && nbulk > 1) issue_s(1, 1);
       for (int i = 0; i < nbulk && ok; ++i) {
-        if (i + 1 < nbulk) issue_s(i + 1, (i + 1) & 1);
-        if (!ok) break;
-        issue_pv(i);
+        issue_pv(i, i & 1);
+        if (ok && i + 2 < nbulk) issue_s(i + 2, i & 1);
       }
-      kit = nbulk;
       // edge tiles: S from the int4 keys and from the shadow keys, one after the other
-      for (int i = nbulk; i < n && ok; ++i, kit += 2) {
+      for (int i = nbulk, kit = nbulk; i < n && ok; ++i, kit += 2) {
         issue_s(kit, 0); if (!ok) break;
         issue_s(kit + 1, 1); if (!ok) break;
-        issue_pv(i);
+        issue_pv(i, 0);
       }
     }
   } else {
@@ -370,6 +383,25 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     const int pr = pos0 + tok, cr = pr / 32;                         // row position and its own group
     const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
     const float cs = P.qscale * TC_LOG2E;
+    // ---- the row's Q into TMEM as the A operand of the S MMAs: column c = channels 2c, 2c+1; the row's two threads
+    //      take alternate 64-channel chunks
+    if (n > 0) {
+      const uint4* qrow = reinterpret_cast<const uint4*>(P.q16 + ((size_t)(valid ? tok : 0) * P.nh + kvh * G + head % G) * HD);
+      #pragma unroll 1
+      for (int c = hf; c < HD / 64; c += 2) {
+        uint32_t w[32];
+        #pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint4 u = valid ? __ldg(qrow + 8 * c + k) : make_uint4(0u, 0u, 0u, 0u);
+          w[4 * k] = u.x; w[4 * k + 1] = u.y; w[4 * k + 2] = u.z; w[4 * k + 3] = u.w;
+        }
+        tmem_st32u(trow + L::TM_Q + 32 * c, w);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) bar_arrive(b_q);
+    }
     // The row's two threads swap one float per tile through shared memory: value first, then a sequence number the
     // partner polls (bounded, like every wait here; a named barrier could not give up).
     volatile float* xval = reinterpret_cast<volatile float*>(smem + L::OFF_XCH);
@@ -391,12 +423,13 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       const int j = j0 + i;
       const bool edge = i >= nbulk;
       const int buf = edge ? 0 : (i & 1);
+      const uint32_t scol = trow + (buf ? L::TM_S1 : L::TM_S0) + 32 * hf;   // this thread's 32 S columns; P goes over the first 16
       float x[32];                                                   // raw scores of this thread's 32 keys
       TC_T(long long c0 = clock64();)
       if (!bar_wait(b_sready + 8 * buf, srd[buf] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
       tc_fence_after();
       TC_T(long long c1 = clock64();)
-      tmem_ld32(trow + (buf ? L::TM_S1 : L::TM_S0) + 32 * hf, x);
+      tmem_ld32(scol, x);
       ++srd[buf];
       if (edge) {
         if (!bar_wait(b_sready + 8, srd[1] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
@@ -409,9 +442,6 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         #pragma unroll
         for (int k = 0; k < 32; ++k) x[k] = gk < cr ? x[k] : (gk == cr && tb + k <= pr) ? a[k] : -INFINITY;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) { bar_arrive(b_sfree + 8 * buf); if (edge) bar_arrive(b_sfree + 8); }
       TC_T(long long c2 = clock64();)
       // ---- online softmax in the log2 domain on p = 2^(x*cs - m); lazy rescale (the running max may lag by up to 2^8)
       float tmax = x[0];
@@ -439,9 +469,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         l = 0.f;
       }
       TC_T(long long c3 = clock64();)
-      // ---- this tile's P buffer is free once P.V of tile i-2 is done; O may be rescaled once P.V of tile i-1 is done
-      const int pb = i & 1;
-      if (i >= 2 && !bar_wait(b_pvdone + 8 * pb, ((i >> 1) - 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
+      // ---- O may be rescaled once P.V of tile i-1 is done (P.V of this tile waits for the signal below)
       if (i > 0 && __any_sync(0xffffffffu, bump)) {                  // rows that did not bump multiply by exactly 1
         if (!bar_wait(b_pvdone + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
         tc_fence_after();
@@ -453,20 +481,13 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           for (int k = 0; k < 32; ++k) o[k] *= alpha;
           tmem_st32(trow + L::TM_O + 32 * c, o);
         }
-        tmem_st_wait();
       }
       TC_T(long long c4 = clock64();)
-      {
-        const uint32_t prow = sb + L::OFF_P + pb * L::P_BYTES + rho * 128;
-        #pragma unroll
-        for (int c = 0; c < 4; ++c)
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (((4 * hf + c) ^ (rho & 7)) << 4)), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
-                       "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
+      tmem_st16u(scol, pk);                                          // P as the A operand of P.V, over S columns this thread has read
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) bar_arrive(b_pready + 8 * pb);
+      if (lane == 0) bar_arrive(b_pready + 8 * (i & 1));
       TC_T(if (lane == 0 && warp == 0) { long long c5 = clock64(); atomicAdd(&g_tc_cycles[0], (unsigned long long)(c1 - c0)); atomicAdd(&g_tc_cycles[1], (unsigned long long)(c2 - c1));
              atomicAdd(&g_tc_cycles[2], (unsigned long long)(c3 - c2)); atomicAdd(&g_tc_cycles[3], (unsigned long long)(c4 - c3)); atomicAdd(&g_tc_cycles[4], (unsigned long long)(c5 - c4));
              atomicAdd(&g_tc_cycles[5], 1ull); })
@@ -534,17 +555,6 @@ bool tc_map_rows(CUtensorMap* out, const void* base, uint64_t rows, int hd) {
   return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-// q16 [M][kvh][G][hd] viewed as 4-D; box = 64 channels x G heads x 1 kv-head x TOK tokens: rows land as (token, head).
-bool tc_map_q(CUtensorMap* out, const void* q16, int M, int kvh, int G, int hd) {
-  EncodeFn fn = tc_encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)G, (cuuint64_t)kvh, (cuuint64_t)M};
-  const cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)G * hd * 2, (cuuint64_t)kvh * G * hd * 2};
-  const cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)(128 / G)}, es[4] = {1, 1, 1, 1};
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(q16), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 struct TcWs { uint16_t* kd; uint16_t* vd; uint16_t* ks; int ks_rows; size_t bytes; };
 TcWs carve(void* ws, int kvh, int hd, int max_ctx, int M) {
   TcWs w; const size_t plane = (size_t)kvh * max_ctx * hd * 2;
@@ -563,17 +573,17 @@ int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int va
   const long long warps = (long long)a.max_ctx * a.kvh;
   kv4_tc_prep_kernel<HD><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(pp);
   if (int rc = launch_status("kv4_tc_prep_kernel")) return rc;
-  CUtensorMap mq, mkd, mvd, mks;
+  CUtensorMap mkd, mvd, mks;
   const uint64_t rows = (uint64_t)a.kvh * a.max_ctx;
-  if (!tc_map_q(&mq, a.q16, a.M, a.kvh, g, HD) || !tc_map_rows(&mkd, w.kd, rows, HD) || !tc_map_rows(&mvd, w.vd, rows, HD) ||
+  if (!tc_map_rows(&mkd, w.kd, rows, HD) || !tc_map_rows(&mvd, w.vd, rows, HD) ||
       !tc_map_rows(&mks, w.ks, (uint64_t)a.kvh * w.ks_rows, HD))
     KV4_REJECT("yskn_kv4_attention_tc: cuTensorMapEncodeTiled failed or is unavailable");
   auto kern = kv4_tc_attn_kernel<HD>;
   static bool attr = false;
   if (!attr) { KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL)); attr = true; }
   const int tok = 128 / g, qtiles = (a.M + tok - 1) / tok;
-  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv};
-  kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mq, mkd, mvd, mks, P);
+  TcP P{a.q16, a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv};
+  kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mkd, mvd, mks, P);
   return launch_status("kv4_tc_attn_kernel");
 }
 
