@@ -40,7 +40,8 @@ __device__ int g_tc_status = 0;              // 0 ok; 4/5/6 = a bounded wait ran
 
 #ifdef KV4_TC_TIMING
 // Diagnostic build only: cycles summed over softmax threads' lane 0 {wait S, TMEM load, math, wait PV/P buffer, P store+signal, tiles}.
-__device__ unsigned long long g_tc_cycles[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+__device__ unsigned long long g_tc_cycles[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};   // [6..9]: issuer waits for K, P, V; issuer tiles
+__device__ long long g_tc_trace[256][8];   // leader CTA of block (0,0,0): per tile {P seen, V seen, PV issued, K seen, S(i+2) issued, softmax start, S seen, P signalled}
 #define TC_T(x) x
 #else
 #define TC_T(x)
@@ -152,13 +153,21 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {       
   for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) if (bar_try(bar, parity)) return true;
   return false;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, int x, int y, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(m), "r"(x), "r"(y), "r"(bar) : "memory");
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+// Address of the leader CTA's copy (rank 0 of the pair) of a shared-memory location, in the cluster window.
+__device__ __forceinline__ uint32_t leader_addr(uint32_t local) { uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(r) : "r"(local)); return r; }
+// What the arrival publishes lives in tensor memory and is ordered by the tcgen05 fences around it, so the default
+// (CTA-scope) release is enough; a cluster-scope release costs several hundred cycles per call.
+__device__ __forceinline__ void bar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, int x, int y, int z, int w, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-               ::"r"(dst), "l"(m), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar) : "memory");
+__device__ __forceinline__ void cluster_sync_all() {                 // every thread of both CTAs
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// One tiled copy into this CTA's shared memory that reports its bytes to a barrier of the pair's leader.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, int x, int y, int z, uint32_t cluster_bar) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(m), "r"(x), "r"(y), "r"(z), "r"(cluster_bar) : "memory");
 }
 // Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100): start address, leading and stride byte offsets
 // in 16-byte units.  K-major operands: 8-row x 128-byte atoms, SBO = 1024 between atoms along M/N, LBO unused.
@@ -172,17 +181,15 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 __host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool b_mn_major) {
   return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
 // A operand (128 rows x 16 k, fp16 pairs in 8 columns) from tensor memory, B from shared memory.
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+// One instruction drives the tensor cores of both SMs of the pair (M = 256: 128 rows in each CTA's tensor memory).
+__device__ __forceinline__ void umma2_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}"
                ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+// Arrives on the barrier at this offset in BOTH CTAs once all MMAs issued so far are done.
+__device__ __forceinline__ void umma2_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -227,15 +234,19 @@ constexpr int TC_BN = 64;                                  // keys per tile
 constexpr int TC_SW = 8;                                   // softmax warps: warp w owns rows 32*(w%4).., key columns 32*(w/4)..
 constexpr int TC_THREADS = (TC_SW + 2) * 32;               // + producer warp, + MMA issuer warp
 
-// Shared memory holds only the K and V rings: Q, S, P and O live in tensor memory, so every MMA reads one operand
-// from shared memory, not two (the S MMAs with Q in shared memory alone moved 96 KB per tile through the 128 B/clk port).
+// A pair of CTAs (a cluster of two, tcgen05 cta_group::2) works on 256 query rows with MMAs of M = 256: each CTA keeps
+// its 128 rows of Q, S, P and O in its own tensor memory and stages HALF of every K tile (32 of the 64 keys) and half
+// of every V tile (HD/2 of the channels) in its shared memory; the tensor cores of both SMs read both halves.  An SM
+// takes in about 40-50 bytes per clock from L2, so bytes staged per SM and tile, not MMA rate, bound a one-CTA design.
 template <int HD> struct TcLay {
   static constexpr int KBLK = HD / 64;                     // 64-channel (128-byte) operand blocks
-  static constexpr int KV_BLOCK = TC_BN * 128;             // 64 keys x 128 bytes
-  static constexpr int KV_TILE = KBLK * KV_BLOCK;
-  static constexpr int NK = HD == 256 ? 3 : 4, NV = 4;     // ring depths
-  static constexpr int OFF_K = 0, OFF_V = NK * KV_TILE, OFF_BAR = OFF_V + NV * KV_TILE;
-  static constexpr int OFF_XCH = OFF_BAR + 192;            // float val[2 tile parities][2 column halves][128 rows], u16 seq[2][128]
+  static constexpr int K_BLOCK = 32 * 128;                 // this CTA's 32 keys x 128 bytes
+  static constexpr int K_HALF = KBLK * K_BLOCK;            // [block][key][128 B]
+  static constexpr int V_BLOCK = TC_BN * 128;              // 64 keys x 128 bytes
+  static constexpr int V_HALF = (KBLK / 2) * V_BLOCK;      // this CTA's HD/2 channels: [block][key][128 B]
+  static constexpr int NK = 4, NV = 6;                     // ring depths
+  static constexpr int OFF_K = 0, OFF_V = NK * K_HALF, OFF_BAR = OFF_V + NV * V_HALF;
+  static constexpr int OFF_XCH = OFF_BAR + 256;            // float val[2 tile parities][2 column halves][128 rows], u16 seq[2][128]
   static constexpr int TOTAL = OFF_XCH + 2 * 2 * 128 * 4 + 2 * 128 * 2;
   // TMEM columns (32-bit): two S buffers of 64 fp32 columns (P, fp16 pairs, is written over the S columns its
   // thread has read: 16 columns at +0 for keys 0-31, 16 at +32 for keys 32-63), O, and Q as fp16 pairs.
@@ -243,6 +254,7 @@ template <int HD> struct TcLay {
   static constexpr int TM_COLS = 512;
   static_assert(TOTAL <= 227 * 1024, "shared memory budget");
   static_assert(2 * TC_BN + HD + HD / 2 <= 512, "TMEM columns");
+  static_assert(K_HALF % 1024 == 0 && V_HALF % 1024 == 0, "swizzle atoms");
 };
 
 struct TcP {
@@ -253,55 +265,62 @@ struct TcP {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
 kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_constant__ CUtensorMap mapVd,
                    const __grid_constant__ CUtensorMap mapKs, const TcP P) {
   using L = TcLay<HD>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = s_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // barriers (8 bytes each): kfull[4] kempty[4] vfull[4] vempty[4] sready[2] pready[2] pvdone[2] qready | tmem slot | abort flag
+  const uint32_t rank = cluster_ctarank();                           // 0 = leader: issues the MMAs, owns the "full"/"ready" barriers
+  // barriers (8 bytes each), same offsets in both CTAs:
+  //   leader's copy only: kfull[NK] vfull[NV] pready[2] qready     each CTA's copy: kempty[NK] vempty[NV] sready[2] pvdone[2]
   const uint32_t B0 = sb + L::OFF_BAR;
-  const uint32_t b_kfull = B0, b_kempty = B0 + 32, b_vfull = B0 + 64, b_vempty = B0 + 96, b_sready = B0 + 128, b_pready = B0 + 144,
-                 b_pvdone = B0 + 160, b_q = B0 + 176;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 184);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 188);
+  const uint32_t b_kfull = B0, b_kempty = B0 + 32, b_vfull = B0 + 64, b_vempty = B0 + 112, b_sready = B0 + 160, b_pready = B0 + 176,
+                 b_pvdone = B0 + 192, b_q = B0 + 208;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 216);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 220);
+  const uint32_t lead_kfull = leader_addr(b_kfull), lead_vfull = leader_addr(b_vfull), lead_pready = leader_addr(b_pready), lead_q = leader_addr(b_q);
 
-  // ---- geometry (uniform over the CTA)
+  // ---- geometry: uniform over the pair except tok0
   const int G = P.G, TOK = 128 / G, kvh = blockIdx.z, S = P.splits, split = blockIdx.y;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;               // heaviest query tiles first
-  const int tok0 = qt * TOK, ntok = min(TOK, P.M - tok0);
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;               // heaviest query tiles first; gridDim.x is even
+  const int tok0 = qt * TOK;                                         // this CTA's first token
+  const int tokA = (qt & ~1) * TOK;                                  // the pair's first token (always < M)
   const int pos0 = *P.d_pos;
-  const int pmax = pos0 + tok0 + ntok - 1;                           // last key any row of this tile sees
+  const int pmax = pos0 + min(tokA + 2 * TOK, P.M) - 1;              // last key any row of the pair sees
   const int nt_all = pmax / TC_BN + 1;
   const int per = (pos0 / TC_BN + 1 + S - 1) / S;                    // split width in tiles: a function of *d_pos and S only
   const int j0 = min(split * per, nt_all), j1 = split == S - 1 ? nt_all : min((split + 1) * per, nt_all);
   const int n = j1 - j0;
-  const int jb = ((pos0 + tok0) / 32) / 2;                           // tiles below jb hold only groups before every row's own group
+  const int jb = ((pos0 + tokA) / 32) / 2;                           // tiles below jb hold only groups before every row's own group
   const int nbulk = max(0, min(n, jb - j0));
   const int ks0 = (pos0 / TC_BN) * TC_BN;
 
-  if (sb & 1023u) { if (threadIdx.x == 0) atomicExch(&g_tc_status, 3); return; }
+  if (sb & 1023u) { if (threadIdx.x == 0) atomicExch(&g_tc_status, 3); return; }   // same in both CTAs: nobody is left waiting
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 4; ++i) { bar_init(b_kfull + 8 * i, 1); bar_init(b_kempty + 8 * i, 1); bar_init(b_vfull + 8 * i, 1); bar_init(b_vempty + 8 * i, 1); }
-    for (int i = 0; i < 2; ++i) { bar_init(b_sready + 8 * i, 1); bar_init(b_pready + 8 * i, TC_SW); bar_init(b_pvdone + 8 * i, 1); }
-    bar_init(b_q, TC_SW);
+    for (int i = 0; i < L::NK; ++i) { bar_init(b_kfull + 8 * i, 1); bar_init(b_kempty + 8 * i, 1); }
+    for (int i = 0; i < L::NV; ++i) { bar_init(b_vfull + 8 * i, 1); bar_init(b_vempty + 8 * i, 1); }
+    for (int i = 0; i < 2; ++i) { bar_init(b_sready + 8 * i, 1); bar_init(b_pready + 8 * i, 2 * TC_SW); bar_init(b_pvdone + 8 * i, 1); }
+    bar_init(b_q, 2 * TC_SW);
     *s_abort = 0;
     for (int i = 0; i < 128; ++i) reinterpret_cast<volatile uint32_t*>(smem + L::OFF_XCH + 2 * 2 * 128 * 4)[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == TC_SW + 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 184), "n"(L::TM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (warp == TC_SW + 1) {                                           // the same warp of both CTAs allocates for the pair
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 216), "n"(L::TM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();                                                // both CTAs' barriers exist before anyone signals the other
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
   if (warp == TC_SW) {
-    // ======================================================================= TMA producer
-    // Two rings: K tiles are free again as soon as their S MMAs are done, V tiles only after P.V.
+    // ======================================================================= TMA producer (one per CTA)
+    // Two rings: K halves are free again as soon as their S MMAs are done, V halves only after P.V.  Every copy
+    // reports to the leader's "full" barrier; the leader posts the byte count of both CTAs' halves.
     if (lane == 0 && n > 0) {
       int kit = 0; bool ok = true;
       for (int i = 0; i < n && ok; ++i) {
@@ -310,62 +329,73 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
           const int st = kit % L::NK;
           if (kit >= L::NK && !bar_wait(b_kempty + 8 * st, (kit / L::NK - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
           if (*s_abort) { ok = false; break; }
-          const uint32_t dst = sb + L::OFF_K + st * L::KV_TILE, bar = b_kfull + 8 * st;
-          bar_expect_tx(bar, L::KV_TILE);
-          const int row = half == 0 ? kvh * P.max_ctx + j * TC_BN : kvh * P.ks_rows + j * TC_BN - ks0;
-          for (int kb = 0; kb < L::KBLK; ++kb) tma_load_2d(dst + kb * L::KV_BLOCK, half == 0 ? &mapKd : &mapKs, 64 * kb, row, bar);
+          if (rank == 0) bar_expect_tx(b_kfull + 8 * st, 2 * L::K_HALF);
+          const int row = (half == 0 ? kvh * P.max_ctx + j * TC_BN : kvh * P.ks_rows + j * TC_BN - ks0) + 32 * (int)rank;
+          tma_load_3d_pair(sb + L::OFF_K + st * L::K_HALF, half == 0 ? &mapKd : &mapKs, 0, row, 0, lead_kfull + 8 * st);
         }
         if (!ok) break;
         const int st = i % L::NV;                                    // V of tile i; its buffer was last read by P.V of tile i-NV
         if (i >= L::NV && !bar_wait(b_vempty + 8 * st, (i / L::NV - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
-        bar_expect_tx(b_vfull + 8 * st, L::KV_TILE);
-        for (int kb = 0; kb < L::KBLK; ++kb)
-          tma_load_2d(sb + L::OFF_V + st * L::KV_TILE + kb * L::KV_BLOCK, &mapVd, 64 * kb, kvh * P.max_ctx + j * TC_BN, b_vfull + 8 * st);
+        if (rank == 0) bar_expect_tx(b_vfull + 8 * st, 2 * L::V_HALF);
+        tma_load_3d_pair(sb + L::OFF_V + st * L::V_HALF, &mapVd, 0, kvh * P.max_ctx + j * TC_BN, (L::KBLK / 2) * (int)rank, lead_vfull + 8 * st);
       }
     }
   } else if (warp == TC_SW + 1) {
-    // ======================================================================= MMA issuer (one thread)
+    // ======================================================================= MMA issuer (one thread of the leader CTA)
     // The tensor pipe runs this thread's MMAs in issue order, so S of tile i+2, issued after P.V of tile i, may
     // overwrite the TMEM buffer that P.V reads P from without a barrier in between.
-    if (lane == 0 && n > 0) {
-      constexpr uint32_t ID_S = instr_desc(128, TC_BN, false), ID_PV = instr_desc(128, HD, true);
+    if (lane == 0 && n > 0 && rank == 0) {
+      constexpr uint32_t ID_S = instr_desc(256, TC_BN, false), ID_PV = instr_desc(256, HD, true);
       bool ok = true;
       auto fail = [&]() { atomicExch(&g_tc_status, 5); *s_abort = 1; ok = false; };
+      // K items and V tiles arrive long before they are needed; their barriers are checked right after a batch of
+      // MMAs has been queued, so that the checks run while the tensor pipe is busy.  Only the wait for P is exposed.
+      int kw = 0, vw = 0;                                            // K items / V tiles known to have landed
+      auto ensure_k = [&](int item) {
+        while (ok && kw <= item) { if (!bar_wait(b_kfull + 8 * (kw % L::NK), (kw / L::NK) & 1)) { fail(); return; } ++kw; }
+      };
+      auto ensure_v = [&](int tile_i) {
+        while (ok && vw <= tile_i) { if (!bar_wait(b_vfull + 8 * (vw % L::NV), (vw / L::NV) & 1)) { fail(); return; } ++vw; }
+      };
+      const uint64_t kdesc0 = smem_desc(sb + L::OFF_K, 16, 1024), vdesc0 = smem_desc(sb + L::OFF_V, L::V_BLOCK, 1024);
       auto issue_s = [&](int item, int buf) {                        // S[buf] = Q . K(item)^T, Q from TMEM
         const int st = item % L::NK;
-        if (!bar_wait(b_kfull + 8 * st, (item / L::NK) & 1)) { fail(); return; }
+        ensure_k(item); if (!ok) return;
         tc_fence_after();
-        const uint32_t kaddr = sb + L::OFF_K + st * L::KV_TILE;
+        const uint64_t kd = kdesc0 + (uint64_t)((st * L::K_HALF) >> 4);
         #pragma unroll
         for (int kb = 0; kb < L::KBLK; ++kb)
           #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            umma_ts(tmem + (buf ? L::TM_S1 : L::TM_S0), tmem + L::TM_Q + 32 * kb + 8 * ks,
-                    smem_desc(kaddr + kb * L::KV_BLOCK + ks * 32, 16, 1024), ID_S, (kb | ks) ? 1u : 0u);
-        umma_commit(b_sready + 8 * buf);
-        umma_commit(b_kempty + 8 * st);                              // the K tile may be overwritten once these MMAs are done
+            umma2_ts(tmem + (buf ? L::TM_S1 : L::TM_S0), tmem + L::TM_Q + 32 * kb + 8 * ks, kd + (uint64_t)((kb * L::K_BLOCK + ks * 32) >> 4), ID_S,
+                     (kb | ks) ? 1u : 0u);
+        umma2_commit(b_sready + 8 * buf);
+        umma2_commit(b_kempty + 8 * st);                             // the K halves may be overwritten once these MMAs are done
       };
       auto issue_pv = [&](int tile_i, int buf) {                     // O (+)= P . V(tile_i), P from TMEM (over S[buf])
         const int st = tile_i % L::NV;
+        ensure_v(tile_i); if (!ok) return;
         if (!bar_wait(b_pready + 8 * (tile_i & 1), (tile_i >> 1) & 1)) { fail(); return; }
-        if (!bar_wait(b_vfull + 8 * st, (tile_i / L::NV) & 1)) { fail(); return; }
         tc_fence_after();
-        const uint32_t vaddr = sb + L::OFF_V + st * L::KV_TILE, pcol = tmem + (buf ? L::TM_S1 : L::TM_S0);
+        const uint64_t vd = vdesc0 + (uint64_t)((st * L::V_HALF) >> 4);
+        const uint32_t pcol = tmem + (buf ? L::TM_S1 : L::TM_S0);
         #pragma unroll
         for (int ks = 0; ks < TC_BN / 16; ++ks)
-          umma_ts(tmem + L::TM_O, pcol + 32 * (ks >> 1) + 8 * (ks & 1), smem_desc(vaddr + ks * 2048, L::KV_BLOCK, 1024), ID_PV,
-                  (tile_i | ks) ? 1u : 0u);
-        umma_commit(b_pvdone + 8 * (tile_i & 1));                    // O may be rescaled
-        umma_commit(b_vempty + 8 * st);                              // the V tile may be overwritten
+          umma2_ts(tmem + L::TM_O, pcol + 32 * (ks >> 1) + 8 * (ks & 1), vd + (uint64_t)((ks * 2048) >> 4), ID_PV, (tile_i | ks) ? 1u : 0u);
+        umma2_commit(b_pvdone + 8 * (tile_i & 1));                   // O may be rescaled
+        umma2_commit(b_vempty + 8 * st);                             // the V halves may be overwritten
       };
       if (!bar_wait(b_q, 0)) fail();
       tc_fence_after();
       // bulk tiles: S of the next two tiles is done or in flight while the softmax warps work on this one
       if (ok && nbulk > 0) issue_s(0, 0);
       if (ok && nbulk > 1) issue_s(1, 1);
+      if (ok) ensure_v(0);
       for (int i = 0; i < nbulk && ok; ++i) {
         issue_pv(i, i & 1);
         if (ok && i + 2 < nbulk) issue_s(i + 2, i & 1);
+        if (ok && i + 1 < n) ensure_v(i + 1);
+        if (ok && i + 3 < nbulk) ensure_k(i + 3);
       }
       // edge tiles: S from the int4 keys and from the shadow keys, one after the other
       for (int i = nbulk, kit = nbulk; i < n && ok; ++i, kit += 2) {
@@ -400,7 +430,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) bar_arrive(b_q);
+      if (lane == 0) bar_arrive_cluster(lead_q);
     }
     // The row's two threads swap one float per tile through shared memory: value first, then a sequence number the
     // partner polls (bounded, like every wait here; a named barrier could not give up).
@@ -487,10 +517,11 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) bar_arrive(b_pready + 8 * (i & 1));
+      if (lane == 0) bar_arrive_cluster(lead_pready + 8 * (i & 1));
       TC_T(if (lane == 0 && warp == 0) { long long c5 = clock64(); atomicAdd(&g_tc_cycles[0], (unsigned long long)(c1 - c0)); atomicAdd(&g_tc_cycles[1], (unsigned long long)(c2 - c1));
              atomicAdd(&g_tc_cycles[2], (unsigned long long)(c3 - c2)); atomicAdd(&g_tc_cycles[3], (unsigned long long)(c4 - c3)); atomicAdd(&g_tc_cycles[4], (unsigned long long)(c5 - c4));
-             atomicAdd(&g_tc_cycles[5], 1ull); })
+             atomicAdd(&g_tc_cycles[5], 1ull);
+             if (blockIdx.x + blockIdx.y + blockIdx.z == 0 && i < 256) { g_tc_trace[i][5] = c0; g_tc_trace[i][6] = c1; g_tc_trace[i][7] = c5; } })
     }
     // ---- this split's result per (row, head): (m, l, O) partial, or the finished row when there is one split
     if (ok && n > 0 && !bar_wait(b_pvdone + 8 * ((n - 1) & 1), ((n - 1) >> 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; }
@@ -530,7 +561,8 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == TC_SW + 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(L::TM_COLS) : "memory");
+  cluster_sync_all();                                                // neither CTA's shared or tensor memory is in use by the other any more
+  if (warp == TC_SW + 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(L::TM_COLS) : "memory");
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -546,15 +578,17 @@ EncodeFn tc_encode_fn() {
   return fn;
 }
 
-// fp16 array viewed as [rows][hd]; box = 64 channels x 64 rows, 128-byte swizzle.
-bool tc_map_rows(CUtensorMap* out, const void* base, uint64_t rows, int hd) {
+// fp16 array [rows][hd] viewed as (64 channels, rows, hd/64 channel blocks): one copy of a box (64, box_rows, box_blocks)
+// lands in shared memory as [block][row][128 bytes], 128-byte swizzle -- the tensor core's operand layout.
+bool tc_map_rows(CUtensorMap* out, const void* base, uint64_t rows, int hd, int box_rows, int box_blocks) {
   EncodeFn fn = tc_encode_fn();
   if (!fn) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)hd, rows}, strides[1] = {(cuuint64_t)hd * 2};
-  const cuuint32_t box[2] = {64, 64}, es[2] = {1, 1};
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const cuuint64_t dims[3] = {64, rows, (cuuint64_t)(hd / 64)}, strides[2] = {(cuuint64_t)hd * 2, 128};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_blocks}, es[3] = {1, 1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
 struct TcWs { uint16_t* kd; uint16_t* vd; uint16_t* ks; int ks_rows; size_t bytes; };
 TcWs carve(void* ws, int kvh, int hd, int max_ctx, int M) {
   TcWs w; const size_t plane = (size_t)kvh * max_ctx * hd * 2;
@@ -575,13 +609,13 @@ int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int va
   if (int rc = launch_status("kv4_tc_prep_kernel")) return rc;
   CUtensorMap mkd, mvd, mks;
   const uint64_t rows = (uint64_t)a.kvh * a.max_ctx;
-  if (!tc_map_rows(&mkd, w.kd, rows, HD) || !tc_map_rows(&mvd, w.vd, rows, HD) ||
-      !tc_map_rows(&mks, w.ks, (uint64_t)a.kvh * w.ks_rows, HD))
+  if (!tc_map_rows(&mkd, w.kd, rows, HD, 32, L::KBLK) || !tc_map_rows(&mvd, w.vd, rows, HD, TC_BN, L::KBLK / 2) ||
+      !tc_map_rows(&mks, w.ks, (uint64_t)a.kvh * w.ks_rows, HD, 32, L::KBLK))
     KV4_REJECT("yskn_kv4_attention_tc: cuTensorMapEncodeTiled failed or is unavailable");
   auto kern = kv4_tc_attn_kernel<HD>;
   static bool attr = false;
   if (!attr) { KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL)); attr = true; }
-  const int tok = 128 / g, qtiles = (a.M + tok - 1) / tok;
+  const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;        // CTA pairs: an even number of query tiles
   TcP P{a.q16, a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv};
   kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mkd, mvd, mks, P);
   return launch_status("kv4_tc_attn_kernel");
@@ -609,10 +643,13 @@ int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int ac
 }
 
 #ifdef KV4_TC_TIMING
-extern "C" __attribute__((visibility("default"))) int yskn_kv4_tc_debug_cycles(unsigned long long* out8) {
-  if (cudaMemcpyFromSymbol(out8, g_tc_cycles, 64) != cudaSuccess) return 1;
-  unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  return cudaMemcpyToSymbol(g_tc_cycles, z, 64) != cudaSuccess;
+extern "C" __attribute__((visibility("default"))) int yskn_kv4_tc_debug_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 256 * 8) != cudaSuccess;
+}
+extern "C" __attribute__((visibility("default"))) int yskn_kv4_tc_debug_cycles(unsigned long long* out12) {
+  if (cudaMemcpyFromSymbol(out12, g_tc_cycles, 96) != cudaSuccess) return 1;
+  unsigned long long z[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  return cudaMemcpyToSymbol(g_tc_cycles, z, 96) != cudaSuccess;
 }
 #endif
 
