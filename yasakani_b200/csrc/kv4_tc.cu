@@ -49,6 +49,8 @@ __device__ long long g_tc_trace[256][8];   // leader CTA of block (0,0,0): per t
 
 namespace {
 
+constexpr int TC_BN = 128;                                 // keys per tile of the attention kernel
+
 // ------------------------------------------------------------------------------------------------ prep kernel
 struct PrepP {
   yskn_kv_layer kv; const int* d_pos; int M; int max_ctx; int kvh; const float* rope; int rd;
@@ -63,8 +65,8 @@ __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
   const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   const int t = (int)(w / P.kvh), head = (int)(w % P.kvh);
   const int pos0 = *P.d_pos, end = pos0 + P.M;                      // tokens [0, end) exist
-  const int end64 = min(P.max_ctx, (end + 63) / 64 * 64);           // tiles read whole 64-key rows: keep V finite there
-  if (t >= end64) return;
+  const int end_tile = min(P.max_ctx, (end + TC_BN - 1) / TC_BN * TC_BN);   // tiles read whole rows of keys: keep V finite there
+  if (t >= end_tile) return;
   const int c0 = lane * CPL, half = P.rd / 2, lanes_off = half > 0 ? half / CPL : 1;
   const bool rot = c0 < P.rd, lower = c0 < half;
   const size_t row = (size_t)head * P.max_ctx + t;
@@ -114,8 +116,8 @@ __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
     rotate(k);
     store(P.kd + row * HD + c0, k);
   }
-  // ---- Ks: rotated shadow keys from the 64-key tile that holds *d_pos onwards (row index relative to that tile)
-  const int ks0 = (pos0 / 64) * 64;
+  // ---- Ks: rotated shadow keys from the tile that holds *d_pos onwards (row index relative to that tile)
+  const int ks0 = (pos0 / TC_BN) * TC_BN;
   if (t >= ks0 && t - ks0 < P.ks_rows) {
     float k[CPL];
     if (t < end) {
@@ -164,6 +166,10 @@ __device__ __forceinline__ void bar_arrive_cluster(uint32_t cluster_bar) {
 __device__ __forceinline__ void cluster_sync_all() {                 // every thread of both CTAs
   asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* m, int x, int y, int z, int w, uint32_t cluster_bar) {
+  asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+               ::"r"(dst), "l"(m), "r"(x), "r"(y), "r"(z), "r"(w), "r"(cluster_bar) : "memory");
+}
 // One tiled copy into this CTA's shared memory that reports its bytes to a barrier of the pair's leader.
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, int x, int y, int z, uint32_t cluster_bar) {
   asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -182,6 +188,10 @@ __host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool b_mn_major)
   return (1u << 4) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 // A operand (128 rows x 16 k, fp16 pairs in 8 columns) from tensor memory, B from shared memory.
+__device__ __forceinline__ void umma2_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 // One instruction drives the tensor cores of both SMs of the pair (M = 256: 128 rows in each CTA's tensor memory).
 __device__ __forceinline__ void umma2_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}"
@@ -203,6 +213,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
   #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {            // two loads in flight, one wait
+  uint32_t r[64];
+  #pragma unroll
+  for (int h = 0; h < 2; ++h)
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[32 * h + 0]), "=r"(r[32 * h + 1]), "=r"(r[32 * h + 2]), "=r"(r[32 * h + 3]), "=r"(r[32 * h + 4]), "=r"(r[32 * h + 5]), "=r"(r[32 * h + 6]),
+                   "=r"(r[32 * h + 7]), "=r"(r[32 * h + 8]), "=r"(r[32 * h + 9]), "=r"(r[32 * h + 10]), "=r"(r[32 * h + 11]), "=r"(r[32 * h + 12]), "=r"(r[32 * h + 13]),
+                   "=r"(r[32 * h + 14]), "=r"(r[32 * h + 15]), "=r"(r[32 * h + 16]), "=r"(r[32 * h + 17]), "=r"(r[32 * h + 18]), "=r"(r[32 * h + 19]), "=r"(r[32 * h + 20]),
+                   "=r"(r[32 * h + 21]), "=r"(r[32 * h + 22]), "=r"(r[32 * h + 23]), "=r"(r[32 * h + 24]), "=r"(r[32 * h + 25]), "=r"(r[32 * h + 26]), "=r"(r[32 * h + 27]),
+                   "=r"(r[32 * h + 28]), "=r"(r[32 * h + 29]), "=r"(r[32 * h + 30]), "=r"(r[32 * h + 31])
+                 : "r"(taddr + 32 * h) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  #pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
@@ -230,35 +255,38 @@ __device__ __forceinline__ float tc_ex2(float x) { float y; asm("ex2.approx.ftz.
 __device__ __forceinline__ uint32_t tc_pack(float lo, float hi) { uint32_t d; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo)); return d; }
 
 // ------------------------------------------------------------------------------------------------ attention kernel
-constexpr int TC_BN = 64;                                  // keys per tile
-constexpr int TC_SW = 8;                                   // softmax warps: warp w owns rows 32*(w%4).., key columns 32*(w/4)..
+constexpr int TC_SW = 8;                                   // softmax warps: warp w owns rows 32*(w%4).., key columns 64*(w/4)..
 constexpr int TC_THREADS = (TC_SW + 2) * 32;               // + producer warp, + MMA issuer warp
 
 // A pair of CTAs (a cluster of two, tcgen05 cta_group::2) works on 256 query rows with MMAs of M = 256: each CTA keeps
-// its 128 rows of Q, S, P and O in its own tensor memory and stages HALF of every K tile (32 of the 64 keys) and half
-// of every V tile (HD/2 of the channels) in its shared memory; the tensor cores of both SMs read both halves.  An SM
-// takes in about 40-50 bytes per clock from L2, so bytes staged per SM and tile, not MMA rate, bound a one-CTA design.
+// its 128 rows of S, P and O in its own tensor memory, its Q rows in shared memory, and stages HALF of every K tile
+// (64 of the 128 keys) and half of every V tile (HD/2 of the channels); the tensor cores of both SMs read both halves.
+// Why these shapes: one thread issues every MMA of the pair and an MMA costs it 50-65 cycles whatever its size, and
+// M128 N64 steps run at two thirds of the rate of N128 steps, so S tiles are 128 keys wide (N = 128) -- which fills
+// tensor memory (2 x 128 S columns + 256 O columns) and sends Q to shared memory; an SM takes in only 40-50 bytes per
+// clock from L2, so each SM stages half a tile.
 template <int HD> struct TcLay {
   static constexpr int KBLK = HD / 64;                     // 64-channel (128-byte) operand blocks
-  static constexpr int K_BLOCK = 32 * 128;                 // this CTA's 32 keys x 128 bytes
+  static constexpr int Q_BLOCK = 128 * 128;                // 128 rows x 128 bytes
+  static constexpr int Q_BYTES = KBLK * Q_BLOCK;           // [block][row][128 B]
+  static constexpr int K_BLOCK = (TC_BN / 2) * 128;        // this CTA's 64 keys x 128 bytes
   static constexpr int K_HALF = KBLK * K_BLOCK;            // [block][key][128 B]
-  static constexpr int V_BLOCK = TC_BN * 128;              // 64 keys x 128 bytes
+  static constexpr int V_BLOCK = TC_BN * 128;              // 128 keys x 128 bytes
   static constexpr int V_HALF = (KBLK / 2) * V_BLOCK;      // this CTA's HD/2 channels: [block][key][128 B]
-  static constexpr int NK = 4, NV = 6;                     // ring depths
-  static constexpr int OFF_K = 0, OFF_V = NK * K_HALF, OFF_BAR = OFF_V + NV * V_HALF;
+  static constexpr int NK = 3, NV = 2;                     // ring depths
+  static constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + NK * K_HALF, OFF_BAR = OFF_V + NV * V_HALF;
   static constexpr int OFF_XCH = OFF_BAR + 256;            // float val[2 tile parities][2 column halves][128 rows], u16 seq[2][128]
   static constexpr int TOTAL = OFF_XCH + 2 * 2 * 128 * 4 + 2 * 128 * 2;
-  // TMEM columns (32-bit): two S buffers of 64 fp32 columns (P, fp16 pairs, is written over the S columns its
-  // thread has read: 16 columns at +0 for keys 0-31, 16 at +32 for keys 32-63), O, and Q as fp16 pairs.
-  static constexpr uint32_t TM_S0 = 0, TM_S1 = TC_BN, TM_O = 2 * TC_BN, TM_Q = 2 * TC_BN + HD;
+  // TMEM columns (32-bit): two S buffers of 128 fp32 columns and O.  P (fp16 pairs) is written over the S columns its
+  // thread has read: 32 columns at +0 for keys 0-63, 32 at +64 for keys 64-127.
+  static constexpr uint32_t TM_S0 = 0, TM_S1 = TC_BN, TM_O = 2 * TC_BN;
   static constexpr int TM_COLS = 512;
   static_assert(TOTAL <= 227 * 1024, "shared memory budget");
-  static_assert(2 * TC_BN + HD + HD / 2 <= 512, "TMEM columns");
-  static_assert(K_HALF % 1024 == 0 && V_HALF % 1024 == 0, "swizzle atoms");
+  static_assert(2 * TC_BN + HD <= 512, "TMEM columns");
+  static_assert(K_HALF % 1024 == 0 && V_HALF % 1024 == 0 && Q_BYTES % 1024 == 0, "swizzle atoms");
 };
 
 struct TcP {
-  const uint16_t* q16;                                     // [M][nh][HD]
   const int* d_pos; int M, splits, G, nh, max_ctx, ks_rows; float qscale;
   float* pm; float* pl; float* pacc;
   uint16_t* o16; const uint16_t* bv;                       // splits == 1 and o16 set: store the finished rows, no partials
@@ -266,20 +294,20 @@ struct TcP {
 
 template <int HD>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
-kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_constant__ CUtensorMap mapVd,
-                   const __grid_constant__ CUtensorMap mapKs, const TcP P) {
+kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapKd,
+                   const __grid_constant__ CUtensorMap mapVd, const __grid_constant__ CUtensorMap mapKs, const TcP P) {
   using L = TcLay<HD>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = s_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();                           // 0 = leader: issues the MMAs, owns the "full"/"ready" barriers
   // barriers (8 bytes each), same offsets in both CTAs:
-  //   leader's copy only: kfull[NK] vfull[NV] pready[2] qready     each CTA's copy: kempty[NK] vempty[NV] sready[2] pvdone[2]
+  //   leader's copy only: kfull[NK] vfull[NV] pready[2] qfull     each CTA's copy: kempty[NK] vempty[NV] sready[2] pvdone[2]
   const uint32_t B0 = sb + L::OFF_BAR;
-  const uint32_t b_kfull = B0, b_kempty = B0 + 32, b_vfull = B0 + 64, b_vempty = B0 + 112, b_sready = B0 + 160, b_pready = B0 + 176,
-                 b_pvdone = B0 + 192, b_q = B0 + 208;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 216);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 220);
+  const uint32_t b_kfull = B0, b_kempty = B0 + 32, b_vfull = B0 + 64, b_vempty = B0 + 96, b_sready = B0 + 128, b_pready = B0 + 144,
+                 b_pvdone = B0 + 160, b_q = B0 + 176;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + 184);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 188);
   const uint32_t lead_kfull = leader_addr(b_kfull), lead_vfull = leader_addr(b_vfull), lead_pready = leader_addr(b_pready), lead_q = leader_addr(b_q);
 
   // ---- geometry: uniform over the pair except tok0
@@ -293,7 +321,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
   const int per = (pos0 / TC_BN + 1 + S - 1) / S;                    // split width in tiles: a function of *d_pos and S only
   const int j0 = min(split * per, nt_all), j1 = split == S - 1 ? nt_all : min((split + 1) * per, nt_all);
   const int n = j1 - j0;
-  const int jb = ((pos0 + tokA) / 32) / 2;                           // tiles below jb hold only groups before every row's own group
+  const int jb = (pos0 + tokA) / TC_BN;                              // tiles below jb hold only groups before every row's own group
   const int nbulk = max(0, min(n, jb - j0));
   const int ks0 = (pos0 / TC_BN) * TC_BN;
 
@@ -302,13 +330,13 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
     for (int i = 0; i < L::NK; ++i) { bar_init(b_kfull + 8 * i, 1); bar_init(b_kempty + 8 * i, 1); }
     for (int i = 0; i < L::NV; ++i) { bar_init(b_vfull + 8 * i, 1); bar_init(b_vempty + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) { bar_init(b_sready + 8 * i, 1); bar_init(b_pready + 8 * i, 2 * TC_SW); bar_init(b_pvdone + 8 * i, 1); }
-    bar_init(b_q, 2 * TC_SW);
+    bar_init(b_q, 1);
     *s_abort = 0;
     for (int i = 0; i < 128; ++i) reinterpret_cast<volatile uint32_t*>(smem + L::OFF_XCH + 2 * 2 * 128 * 4)[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == TC_SW + 1) {                                           // the same warp of both CTAs allocates for the pair
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 216), "n"(L::TM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sb + L::OFF_BAR + 184), "n"(L::TM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -319,9 +347,11 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
 
   if (warp == TC_SW) {
     // ======================================================================= TMA producer (one per CTA)
-    // Two rings: K halves are free again as soon as their S MMAs are done, V halves only after P.V.  Every copy
-    // reports to the leader's "full" barrier; the leader posts the byte count of both CTAs' halves.
+    // Q once, then two rings: K halves are free again as soon as their S MMAs are done, V halves only after P.V.
+    // Every copy reports to the leader's "full" barrier; the leader posts the byte count of both CTAs' parts.
     if (lane == 0 && n > 0) {
+      if (rank == 0) bar_expect_tx(b_q, 2 * L::KBLK * G * TOK * 128);
+      for (int kb = 0; kb < L::KBLK; ++kb) tma_load_4d_pair(sb + L::OFF_Q + kb * L::Q_BLOCK, &mapQ, 64 * kb, 0, kvh, tok0, lead_q);
       int kit = 0; bool ok = true;
       for (int i = 0; i < n && ok; ++i) {
         const int j = j0 + i;
@@ -330,7 +360,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
           if (kit >= L::NK && !bar_wait(b_kempty + 8 * st, (kit / L::NK - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; break; }
           if (*s_abort) { ok = false; break; }
           if (rank == 0) bar_expect_tx(b_kfull + 8 * st, 2 * L::K_HALF);
-          const int row = (half == 0 ? kvh * P.max_ctx + j * TC_BN : kvh * P.ks_rows + j * TC_BN - ks0) + 32 * (int)rank;
+          const int row = (half == 0 ? kvh * P.max_ctx + j * TC_BN : kvh * P.ks_rows + j * TC_BN - ks0) + (TC_BN / 2) * (int)rank;
           tma_load_3d_pair(sb + L::OFF_K + st * L::K_HALF, half == 0 ? &mapKd : &mapKs, 0, row, 0, lead_kfull + 8 * st);
         }
         if (!ok) break;
@@ -348,40 +378,32 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
       constexpr uint32_t ID_S = instr_desc(256, TC_BN, false), ID_PV = instr_desc(256, HD, true);
       bool ok = true;
       auto fail = [&]() { atomicExch(&g_tc_status, 5); *s_abort = 1; ok = false; };
-      // K items and V tiles arrive long before they are needed; their barriers are checked right after a batch of
-      // MMAs has been queued, so that the checks run while the tensor pipe is busy.  Only the wait for P is exposed.
-      int kw = 0, vw = 0;                                            // K items / V tiles known to have landed
-      auto ensure_k = [&](int item) {
-        while (ok && kw <= item) { if (!bar_wait(b_kfull + 8 * (kw % L::NK), (kw / L::NK) & 1)) { fail(); return; } ++kw; }
-      };
-      auto ensure_v = [&](int tile_i) {
-        while (ok && vw <= tile_i) { if (!bar_wait(b_vfull + 8 * (vw % L::NV), (vw / L::NV) & 1)) { fail(); return; } ++vw; }
-      };
-      const uint64_t kdesc0 = smem_desc(sb + L::OFF_K, 16, 1024), vdesc0 = smem_desc(sb + L::OFF_V, L::V_BLOCK, 1024);
-      auto issue_s = [&](int item, int buf) {                        // S[buf] = Q . K(item)^T, Q from TMEM
+      const uint64_t qdesc0 = smem_desc(sb + L::OFF_Q, 16, 1024), kdesc0 = smem_desc(sb + L::OFF_K, 16, 1024),
+                     vdesc0 = smem_desc(sb + L::OFF_V, L::V_BLOCK, 1024);
+      auto issue_s = [&](int item, int buf) {                        // S[buf] = Q . K(item)^T
         const int st = item % L::NK;
-        ensure_k(item); if (!ok) return;
+        if (!bar_wait(b_kfull + 8 * st, (item / L::NK) & 1)) { fail(); return; }
         tc_fence_after();
         const uint64_t kd = kdesc0 + (uint64_t)((st * L::K_HALF) >> 4);
         #pragma unroll
         for (int kb = 0; kb < L::KBLK; ++kb)
           #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            umma2_ts(tmem + (buf ? L::TM_S1 : L::TM_S0), tmem + L::TM_Q + 32 * kb + 8 * ks, kd + (uint64_t)((kb * L::K_BLOCK + ks * 32) >> 4), ID_S,
-                     (kb | ks) ? 1u : 0u);
+            umma2_ss(tmem + (buf ? L::TM_S1 : L::TM_S0), qdesc0 + (uint64_t)((kb * L::Q_BLOCK + ks * 32) >> 4),
+                     kd + (uint64_t)((kb * L::K_BLOCK + ks * 32) >> 4), ID_S, (kb | ks) ? 1u : 0u);
         umma2_commit(b_sready + 8 * buf);
         umma2_commit(b_kempty + 8 * st);                             // the K halves may be overwritten once these MMAs are done
       };
       auto issue_pv = [&](int tile_i, int buf) {                     // O (+)= P . V(tile_i), P from TMEM (over S[buf])
         const int st = tile_i % L::NV;
-        ensure_v(tile_i); if (!ok) return;
         if (!bar_wait(b_pready + 8 * (tile_i & 1), (tile_i >> 1) & 1)) { fail(); return; }
+        if (!bar_wait(b_vfull + 8 * st, (tile_i / L::NV) & 1)) { fail(); return; }
         tc_fence_after();
         const uint64_t vd = vdesc0 + (uint64_t)((st * L::V_HALF) >> 4);
         const uint32_t pcol = tmem + (buf ? L::TM_S1 : L::TM_S0);
         #pragma unroll
-        for (int ks = 0; ks < TC_BN / 16; ++ks)
-          umma2_ts(tmem + L::TM_O, pcol + 32 * (ks >> 1) + 8 * (ks & 1), vd + (uint64_t)((ks * 2048) >> 4), ID_PV, (tile_i | ks) ? 1u : 0u);
+        for (int ks = 0; ks < TC_BN / 16; ++ks)                      // P columns: keys 0-63 at +0.., keys 64-127 at +64..
+          umma2_ts(tmem + L::TM_O, pcol + 64 * (ks >> 2) + 8 * (ks & 3), vd + (uint64_t)((ks * 2048) >> 4), ID_PV, (tile_i | ks) ? 1u : 0u);
         umma2_commit(b_pvdone + 8 * (tile_i & 1));                   // O may be rescaled
         umma2_commit(b_vempty + 8 * st);                             // the V halves may be overwritten
       };
@@ -390,12 +412,9 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
       // bulk tiles: S of the next two tiles is done or in flight while the softmax warps work on this one
       if (ok && nbulk > 0) issue_s(0, 0);
       if (ok && nbulk > 1) issue_s(1, 1);
-      if (ok) ensure_v(0);
       for (int i = 0; i < nbulk && ok; ++i) {
         issue_pv(i, i & 1);
         if (ok && i + 2 < nbulk) issue_s(i + 2, i & 1);
-        if (ok && i + 1 < n) ensure_v(i + 1);
-        if (ok && i + 3 < nbulk) ensure_k(i + 3);
       }
       // edge tiles: S from the int4 keys and from the shadow keys, one after the other
       for (int i = nbulk, kit = nbulk; i < n && ok; ++i, kit += 2) {
@@ -406,32 +425,13 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
     }
   } else {
     // ======================================================================= softmax warps: two threads per query row
-    const int quad = warp & 3, hf = warp >> 2;                       // TMEM lane quadrant; which 32 of the tile's 64 key columns
+    const int quad = warp & 3, hf = warp >> 2;                       // TMEM lane quadrant; which 64 of the tile's 128 key columns
     const int rho = quad * 32 + lane;                                // row of the tile = TMEM lane
     const int tok = tok0 + rho / G, head = rho % G;
     const bool valid = rho < TOK * G && tok < P.M;
     const int pr = pos0 + tok, cr = pr / 32;                         // row position and its own group
     const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
     const float cs = P.qscale * TC_LOG2E;
-    // ---- the row's Q into TMEM as the A operand of the S MMAs: column c = channels 2c, 2c+1; the row's two threads
-    //      take alternate 64-channel chunks
-    if (n > 0) {
-      const uint4* qrow = reinterpret_cast<const uint4*>(P.q16 + ((size_t)(valid ? tok : 0) * P.nh + kvh * G + head % G) * HD);
-      #pragma unroll 1
-      for (int c = hf; c < HD / 64; c += 2) {
-        uint32_t w[32];
-        #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint4 u = valid ? __ldg(qrow + 8 * c + k) : make_uint4(0u, 0u, 0u, 0u);
-          w[4 * k] = u.x; w[4 * k + 1] = u.y; w[4 * k + 2] = u.z; w[4 * k + 3] = u.w;
-        }
-        tmem_st32u(trow + L::TM_Q + 32 * c, w);
-      }
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) bar_arrive_cluster(lead_q);
-    }
     // The row's two threads swap one float per tile through shared memory: value first, then a sequence number the
     // partner polls (bounded, like every wait here; a named barrier could not give up).
     volatile float* xval = reinterpret_cast<volatile float*>(smem + L::OFF_XCH);
@@ -453,40 +453,43 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
       const int j = j0 + i;
       const bool edge = i >= nbulk;
       const int buf = edge ? 0 : (i & 1);
-      const uint32_t scol = trow + (buf ? L::TM_S1 : L::TM_S0) + 32 * hf;   // this thread's 32 S columns; P goes over the first 16
-      float x[32];                                                   // raw scores of this thread's 32 keys
+      const uint32_t scol = trow + (buf ? L::TM_S1 : L::TM_S0) + 64 * hf;   // this thread's 64 S columns; P goes over the first 32
+      float x[64];                                                   // raw scores of this thread's 64 keys
       TC_T(long long c0 = clock64();)
       if (!bar_wait(b_sready + 8 * buf, srd[buf] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
       tc_fence_after();
       TC_T(long long c1 = clock64();)
-      tmem_ld32(scol, x);
+      tmem_ld64(scol, x);
       ++srd[buf];
       if (edge) {
         if (!bar_wait(b_sready + 8, srd[1] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
         tc_fence_after();
-        float a[32];
-        tmem_ld32(trow + L::TM_S1 + 32 * hf, a);
         ++srd[1];
-        // this 32-key half is one group: before the row's own -> int4 keys; own group -> shadow keys up to the row; later -> nothing
-        const int gk = 2 * j + hf, tb = j * TC_BN + 32 * hf;
+        // each 32-key quarter is one group: before the row's own -> int4 keys; own group -> shadow keys up to the row; later -> nothing
         #pragma unroll
-        for (int k = 0; k < 32; ++k) x[k] = gk < cr ? x[k] : (gk == cr && tb + k <= pr) ? a[k] : -INFINITY;
+        for (int h2 = 0; h2 < 2; ++h2) {
+          float a[32];
+          tmem_ld32(trow + L::TM_S1 + 64 * hf + 32 * h2, a);
+          const int gk = 4 * j + 2 * hf + h2, tb = j * TC_BN + 64 * hf + 32 * h2;
+          #pragma unroll
+          for (int k = 0; k < 32; ++k) x[32 * h2 + k] = gk < cr ? x[32 * h2 + k] : (gk == cr && tb + k <= pr) ? a[k] : -INFINITY;
+        }
       }
       TC_T(long long c2 = clock64();)
       // ---- online softmax in the log2 domain on p = 2^(x*cs - m); lazy rescale (the running max may lag by up to 2^8)
-      float tmax = x[0];
+      float tmax = fmaxf(x[0], x[1]);
       #pragma unroll
-      for (int k = 1; k < 32; ++k) tmax = fmaxf(tmax, x[k]);
+      for (int k = 2; k < 64; k += 2) tmax = fmaxf(tmax, fmaxf(x[k], x[k + 1]));
       tmax = fmaxf(tmax, swap_with_partner(tmax, i + 1)) * cs;        // the row's two threads swap their maxima
       const bool bump = valid && tmax > m + 8.f;
       const float mn = bump ? tmax : m, alpha = bump ? tc_ex2(m - mn) : 1.f;
       m = mn; l *= alpha;
-      uint32_t pk[16];
+      uint32_t pk[32];
       {
         const float nm = -m;
         float ls0 = 0.f, ls1 = 0.f;
         #pragma unroll
-        for (int k = 0; k < 32; k += 4) {
+        for (int k = 0; k < 64; k += 4) {
           const float p0 = tc_ex2(fmaf(x[k], cs, nm)), p1 = tc_ex2(fmaf(x[k + 1], cs, nm));        // exp2(-inf) = 0 for masked keys
           const float p2 = tc_ex2(fmaf(x[k + 2], cs, nm)), p3 = tc_ex2(fmaf(x[k + 3], cs, nm));
           ls0 += p0 + p1; ls1 += p2 + p3; pk[k / 2] = tc_pack(p0, p1); pk[k / 2 + 1] = tc_pack(p2, p3);
@@ -495,7 +498,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
       }
       if (__any_sync(0xffffffffu, !valid) && !valid) {               // rows of the tile that hold no query: P = 0, state untouched
         #pragma unroll
-        for (int k = 0; k < 16; ++k) pk[k] = 0u;
+        for (int k = 0; k < 32; ++k) pk[k] = 0u;
         l = 0.f;
       }
       TC_T(long long c3 = clock64();)
@@ -513,15 +516,14 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapKd, const __grid_const
         }
       }
       TC_T(long long c4 = clock64();)
-      tmem_st16u(scol, pk);                                          // P as the A operand of P.V, over S columns this thread has read
+      tmem_st32u(scol, pk);                                          // P as the A operand of P.V, over S columns this thread has read
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) bar_arrive_cluster(lead_pready + 8 * (i & 1));
       TC_T(if (lane == 0 && warp == 0) { long long c5 = clock64(); atomicAdd(&g_tc_cycles[0], (unsigned long long)(c1 - c0)); atomicAdd(&g_tc_cycles[1], (unsigned long long)(c2 - c1));
              atomicAdd(&g_tc_cycles[2], (unsigned long long)(c3 - c2)); atomicAdd(&g_tc_cycles[3], (unsigned long long)(c4 - c3)); atomicAdd(&g_tc_cycles[4], (unsigned long long)(c5 - c4));
-             atomicAdd(&g_tc_cycles[5], 1ull);
-             if (blockIdx.x + blockIdx.y + blockIdx.z == 0 && i < 256) { g_tc_trace[i][5] = c0; g_tc_trace[i][6] = c1; g_tc_trace[i][7] = c5; } })
+             atomicAdd(&g_tc_cycles[5], 1ull); })
     }
     // ---- this split's result per (row, head): (m, l, O) partial, or the finished row when there is one split
     if (ok && n > 0 && !bar_wait(b_pvdone + 8 * ((n - 1) & 1), ((n - 1) >> 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; }
@@ -589,10 +591,21 @@ bool tc_map_rows(CUtensorMap* out, const void* base, uint64_t rows, int hd, int 
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// q16 [M][kvh][G][hd] viewed as 4-D; box = 64 channels x G heads x 1 kv-head x TOK tokens: rows land as (token, head).
+bool tc_map_q(CUtensorMap* out, const void* q16, int M, int kvh, int G, int hd) {
+  EncodeFn fn = tc_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)G, (cuuint64_t)kvh, (cuuint64_t)M};
+  const cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)G * hd * 2, (cuuint64_t)kvh * G * hd * 2};
+  const cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)(128 / G)}, es[4] = {1, 1, 1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(q16), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 struct TcWs { uint16_t* kd; uint16_t* vd; uint16_t* ks; int ks_rows; size_t bytes; };
 TcWs carve(void* ws, int kvh, int hd, int max_ctx, int M) {
   TcWs w; const size_t plane = (size_t)kvh * max_ctx * hd * 2;
-  w.ks_rows = 64 * ((M + 63) / 64 + 1);
+  w.ks_rows = TC_BN * ((M + TC_BN - 1) / TC_BN + 1);
   w.kd = static_cast<uint16_t*>(ws);
   w.vd = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(ws) + plane);
   w.ks = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(ws) + 2 * plane);
@@ -607,17 +620,17 @@ int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int va
   const long long warps = (long long)a.max_ctx * a.kvh;
   kv4_tc_prep_kernel<HD><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(pp);
   if (int rc = launch_status("kv4_tc_prep_kernel")) return rc;
-  CUtensorMap mkd, mvd, mks;
+  CUtensorMap mq, mkd, mvd, mks;
   const uint64_t rows = (uint64_t)a.kvh * a.max_ctx;
-  if (!tc_map_rows(&mkd, w.kd, rows, HD, 32, L::KBLK) || !tc_map_rows(&mvd, w.vd, rows, HD, TC_BN, L::KBLK / 2) ||
-      !tc_map_rows(&mks, w.ks, (uint64_t)a.kvh * w.ks_rows, HD, 32, L::KBLK))
+  if (!tc_map_q(&mq, a.q16, a.M, a.kvh, g, HD) || !tc_map_rows(&mkd, w.kd, rows, HD, TC_BN / 2, L::KBLK) ||
+      !tc_map_rows(&mvd, w.vd, rows, HD, TC_BN, L::KBLK / 2) || !tc_map_rows(&mks, w.ks, (uint64_t)a.kvh * w.ks_rows, HD, TC_BN / 2, L::KBLK))
     KV4_REJECT("yskn_kv4_attention_tc: cuTensorMapEncodeTiled failed or is unavailable");
   auto kern = kv4_tc_attn_kernel<HD>;
   static bool attr = false;
   if (!attr) { KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL)); attr = true; }
   const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;        // CTA pairs: an even number of query tiles
-  TcP P{a.q16, a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv};
-  kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mkd, mvd, mks, P);
+  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv};
+  kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mq, mkd, mvd, mks, P);
   return launch_status("kv4_tc_attn_kernel");
 }
 
