@@ -12,19 +12,22 @@
 //     kv_dequant_kernel does into fp32 (src/attention_kv4q.cu:198-243): Kd = rotated int4 keys of every complete
 //     group, Vd = int4 values of every token, Ks = rotated fp16-shadow keys of the groups the new rows live in.
 //     fp32 arithmetic, one rounding to fp16.  HBM-bound byte mover: one warp per (token, kv-head).
-//  2. kv4_tc_attn_kernel: one CTA = 128 query rows ((token, head) pairs of one kv-head) x one split of the keys.
-//       warp 8      TMA producer: Q tile once, then K and V tiles of 64 keys into two 2-stage mbarrier rings
-//       warp 9      issues tcgen05.mma: S = Q.K^T (M128 N64 K16 steps, both operands K-major, 128-byte swizzle) into one
-//                   of two TMEM buffers, and O += P.V (M128 N=HD, V as MN-major operand) into TMEM; commits to mbarriers
-//       warps 0-7   two threads per query row (32 of the tile's 64 keys each): tcgen05.ld of the S row, masks, online
-//                   softmax in the log2 domain with a lazy rescale of O, P -> fp16 -> shared memory (two buffers) in the
-//                   operand layout; final (m, l, O) store, or the finished fp16 row when there is a single split
-//     S of tile j+1 is issued before P.V of tile j, so the tensor pipe works while the softmax warps run.
-//     Tiles that contain a row's own group ("edge" tiles, at most two per CTA) get S twice, from Kd and from Ks, and
-//     each row picks per 32-key half: int4 keys for groups before its own, shadow keys (causally masked) for its own.
+//  2. kv4_tc_attn_kernel: a pair of CTAs (cluster of two, tcgen05 cta_group::2) = 256 query rows ((token, head) pairs
+//     of one kv-head, 128 per CTA) x one split of the keys, in tiles of 128 keys.  Per CTA:
+//       warp 8      TMA producer: its Q rows once, then its half of every K tile (64 keys) and V tile (HD/2 channels)
+//                   into two mbarrier rings, one tiled copy each; the copies report to the leader CTA's barriers
+//       warp 9      (leader CTA only) one thread issues every tcgen05.mma of the pair: S = Q.K^T (M256 N128 K16 steps, Q and
+//                   K from shared memory, K-major, 128-byte swizzle) into one of two TMEM buffers, and O += P.V (M256
+//                   N=HD, P from tensor memory, V as MN-major operand); commits arrive on both CTAs' barriers
+//       warps 0-7   two threads per query row (64 of the tile's 128 keys each): tcgen05.ld of the S row, masks, online
+//                   softmax in the log2 domain with a lazy rescale of O, P -> fp16 -> tensor memory over the S columns
+//                   just read; final (m, l, O) store, or the finished fp16 row when there is a single split
+//     S of tile i+2 is issued right after P.V of tile i, so the tensor pipe works while the softmax warps run.
+//     Tiles that contain a row's own group ("edge" tiles) get S twice, from Kd and from Ks, and each row picks per
+//     32-key group: int4 keys for groups before its own, shadow keys (causally masked) for its own.
 //
 // Rows are independent of one another inside every step (an MMA output row depends on its own A row only, the lazy
-// rescale multiplies other rows by exactly 1), tiles start at multiples of 64 keys and split boundaries depend on
+// rescale multiplies other rows by exactly 1), tiles start at multiples of 128 keys and split boundaries depend on
 // *d_pos and `splits` only, so a row's result does not depend on how many rows the pass holds.
 //
 // Every wait is bounded; a wait that runs out sets the device status word (4/5/6 = softmax / MMA / producer) and the CTA
@@ -244,11 +247,6 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&v)[3
                ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
                  "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
                  "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
-}
-__device__ __forceinline__ void tmem_st16u(uint32_t taddr, const uint32_t (&v)[16]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
-                 "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float tc_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
