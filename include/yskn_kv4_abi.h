@@ -188,6 +188,29 @@ YSKN_KV4_API int yskn_kv4_attention_host(const uint16_t* h_q16, const yskn_kv_la
                                          int splits, const float* h_rope, int kvh, int nh, int hd, int rd, float qscale,
                                          int act_dtype, uint16_t* h_o16, int reps, float* ms_out);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * Family-B row codec, step 1: sign-Hadamard-256 rotation + INT8 rows (reference src/kvx_codec.cuh, built with
+ * YSKN_KVX_MODE 3, CMakeLists.txt:56).  Rows are 256 values; q8 is [rows][256] int8, scales [rows] fp32.
+ * Bit-exact with the reference's kvx_sign / kvx_rotate / kvx_store and with the round trip of its probe.
+ * Device pointers, enqueue-only, nothing allocated; rows = 0 is a no-op. */
+
+/* kvx_rotate, src/kvx_codec.cuh:35-49: y = H(sign . x) / 16, or with inverse != 0: y = sign . H(x) / 16.  fp32 rows,
+ * 16-byte aligned; x == y is allowed.  This is what the reference applies to Q rows and, inverted, to the merged output
+ * (src/q35_kernels.cu:1420-1422). */
+YSKN_KV4_API int yskn_kvx_rotate(const float* d_x, float* d_y, long long rows, int inverse, void* cuda_stream);
+
+/* kvx_rotate (forward) + kvx_store, src/kvx_codec.cuh:35-70: scale = max|r| / 127, q = rne(r / scale) clamped to +-127
+ * (0 for an all-zero row).  x_dtype = YSKN_KV4_F32 / F16 / BF16 (values are widened to fp32 exactly first). */
+YSKN_KV4_API int yskn_kvx_encode(const void* d_x, int x_dtype, int8_t* d_q8, float* d_scales, long long rows, void* cuda_stream);
+
+/* (float)q * scale, then the inverse rotation (src/kvx_probe.cu:15-19); y_dtype F16/BF16 rounds the fp32 result once. */
+YSKN_KV4_API int yskn_kvx_decode(const int8_t* d_q8, const float* d_scales, void* d_y, int y_dtype, long long rows, void* cuda_stream);
+
+/* Host-pointer probe with the contract of the reference's yskn_kvx_probe (src/kvx_probe.cu:22-36): rows even and > 0,
+ * x[rows*256] in; q[rows*256], scales[rows], y[rows*256] (decoded) out.  Returns 0, -1 (bad rows) or a cudaError_t.
+ * Allocates and frees its own device memory. */
+YSKN_KV4_API int yskn_kvx_probe(const float* x, int8_t* q, float* scales, float* y, int rows);
+
 #ifdef __cplusplus
 }
 #endif

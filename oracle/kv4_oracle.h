@@ -84,6 +84,12 @@ void ysko_attention_exact(const uint16_t* q16, const ysko_kv_layer* kv, int max_
 void ysko_merge_triples(const float* parts, int R, int hq, int hd, float* out);
 
 int ysko_max_threads(void);
+
+/* ---- Family-B row codec, step 1 (kvx_oracle.c): rows of 256 fp32 values */
+float ysko_kvx_sign(int d);
+void ysko_kvx_rotate(const float* x, float* y, long rows, int inverse);
+void ysko_kvx_encode(const float* x, int8_t* q8, float* scales, long rows);
+void ysko_kvx_decode(const int8_t* q8, const float* scales, float* y, long rows);
 #ifdef __cplusplus
 }
 #endif

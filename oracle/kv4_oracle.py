@@ -18,8 +18,8 @@ _LIB = None
 def build(force: bool = False) -> str:
     """Compile the oracle (and, if the reference tree is mounted, oracle/_ref)."""
     so = os.path.join(_HERE, "libkv4_oracle.so")
-    src = os.path.join(_HERE, "kv4_oracle.c")
-    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+    srcs = [os.path.join(_HERE, f) for f in ("kv4_oracle.c", "kvx_oracle.c", "kv4_oracle.h")]
+    if force or not os.path.exists(so) or os.path.getmtime(so) < max(os.path.getmtime(f) for f in srcs):
         subprocess.run(["make", "-C", _HERE, "libkv4_oracle.so"], check=True, capture_output=True)
     return so
 
@@ -148,3 +148,30 @@ def merge_triples(parts: np.ndarray) -> np.ndarray:
 
 def max_threads() -> int:
     return int(lib().ysko_max_threads())
+
+
+# ---------------------------------------------------------------- Family-B row codec, step 1 (kvx_oracle.c)
+def kvx_sign() -> np.ndarray:
+    L = lib(); L.ysko_kvx_sign.restype = C.c_float; L.ysko_kvx_sign.argtypes = [C.c_int]
+    return np.array([L.ysko_kvx_sign(d) for d in range(256)], dtype=np.float32)
+
+
+def kvx_rotate(x: np.ndarray, inverse: bool = False) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, 256)
+    y = np.empty_like(x)
+    lib().ysko_kvx_rotate(_p(x), _p(y), C.c_long(x.shape[0]), C.c_int(1 if inverse else 0))
+    return y
+
+
+def kvx_encode(x: np.ndarray):
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, 256)
+    q = np.empty(x.shape, dtype=np.int8); sc = np.empty(x.shape[0], dtype=np.float32)
+    lib().ysko_kvx_encode(_p(x), _p(q), _p(sc), C.c_long(x.shape[0]))
+    return q, sc
+
+
+def kvx_decode(q: np.ndarray, sc: np.ndarray) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.int8).reshape(-1, 256); sc = np.ascontiguousarray(sc, dtype=np.float32)
+    y = np.empty(q.shape, dtype=np.float32)
+    lib().ysko_kvx_decode(_p(q), _p(sc), _p(y), C.c_long(q.shape[0]))
+    return y

@@ -82,3 +82,26 @@ def test_reference_attention_kernel_agrees_with_oracle_and_with_ours(oracle, ref
     assert_close(o_ref, exact, "reference vs exact oracle", atol=1e-3, rtol=2e-3)
     ours, _ = gpu_attention(kv4, layer, q, ctx, S, rope, shape)
     assert_close(ours, o_ref, "ours vs reference kernels")
+
+
+def test_rotate_int8_row_codec_equals_the_reference_probe_bit_for_bit(oracle):
+    """Family-B row codec, step 1: the reference's own probe (yskn_kvx_probe, src/kvx_probe.cu:22-36, compiled from its
+    source into oracle/_ref/libyskn_ref_kvx.so) against the CPU oracle and against this library's probe."""
+    from yasakani_b200 import kvx
+    path = os.path.join(os.path.dirname(REF), "libyskn_ref_kvx.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref not built (reference tree was not mounted at build time)")
+    ref = C.CDLL(path)
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal((256, 256)) * np.exp(rng.uniform(np.log(0.05), np.log(20.0), (256, 1)))).astype(np.float32)
+    x[5] = 0.0
+    q = np.empty((256, 256), dtype=np.int8); sc = np.empty(256, dtype=np.float32); y = np.empty_like(x)
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    assert ref.yskn_kvx_codec() in (2, 3)              # rotation + INT8 branches (src/kvx_codec.cuh:11-15)
+    assert ref.yskn_kvx_probe(p(x), p(q), p(sc), p(y), 256) == 0
+    oq, osc = oracle.kvx_encode(x)
+    assert np.array_equal(q, oq)
+    assert np.array_equal(sc.view(np.uint32), osc.view(np.uint32))
+    assert np.array_equal(y.view(np.uint32), oracle.kvx_decode(oq, osc).view(np.uint32))
+    gq, gsc, gy = kvx.probe(x)
+    assert np.array_equal(gq, q) and np.array_equal(gsc.view(np.uint32), sc.view(np.uint32)) and np.array_equal(gy.view(np.uint32), y.view(np.uint32))

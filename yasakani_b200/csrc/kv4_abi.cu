@@ -233,4 +233,36 @@ int yskn_kv4_attention_host(const uint16_t* h_q16, const yskn_kv_layer* h_kv, in
   return rc;
 }
 
+int yskn_kvx_rotate(const float* d_x, float* d_y, long long rows, int inverse, void* cuda_stream) {
+  return launch_kvx_rotate(d_x, d_y, rows, inverse, (cudaStream_t)cuda_stream);
+}
+int yskn_kvx_encode(const void* d_x, int x_dtype, int8_t* d_q8, float* d_scales, long long rows, void* cuda_stream) {
+  return launch_kvx_encode(d_x, x_dtype, d_q8, d_scales, rows, (cudaStream_t)cuda_stream);
+}
+int yskn_kvx_decode(const int8_t* d_q8, const float* d_scales, void* d_y, int y_dtype, long long rows, void* cuda_stream) {
+  return launch_kvx_decode(d_q8, d_scales, d_y, y_dtype, rows, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kvx_probe(const float* x, int8_t* q, float* scales, float* y, int rows) {
+  if (rows <= 0 || rows % 2) return -1;                  // the reference's probe takes row pairs
+  if (!x || !q || !scales || !y) KV4_REJECT("yskn_kvx_probe: null buffer");
+  const size_t n = (size_t)rows * 256;
+  float *dx = nullptr, *ds = nullptr, *dy = nullptr; int8_t* dq = nullptr;
+  cudaError_t rc = cudaMalloc(&dx, n * 4);
+  if (rc == cudaSuccess) rc = cudaMalloc(&dy, n * 4);
+  if (rc == cudaSuccess) rc = cudaMalloc(&dq, n);
+  if (rc == cudaSuccess) rc = cudaMalloc(&ds, (size_t)rows * 4);
+  if (rc == cudaSuccess) rc = cudaMemcpy(dx, x, n * 4, cudaMemcpyHostToDevice);
+  int lrc = 0;
+  if (rc == cudaSuccess) lrc = launch_kvx_encode(dx, YSKN_KV4_F32, dq, ds, rows, nullptr);
+  if (rc == cudaSuccess && !lrc) lrc = launch_kvx_decode(dq, ds, dy, YSKN_KV4_F32, rows, nullptr);
+  if (rc == cudaSuccess && !lrc) rc = cudaDeviceSynchronize();
+  if (rc == cudaSuccess && !lrc) rc = cudaMemcpy(y, dy, n * 4, cudaMemcpyDeviceToHost);
+  if (rc == cudaSuccess && !lrc) rc = cudaMemcpy(q, dq, n, cudaMemcpyDeviceToHost);
+  if (rc == cudaSuccess && !lrc) rc = cudaMemcpy(scales, ds, (size_t)rows * 4, cudaMemcpyDeviceToHost);
+  cudaFree(dx); cudaFree(dy); cudaFree(dq); cudaFree(ds);
+  if (rc != cudaSuccess) { set_error("yskn_kvx_probe: %s", cudaGetErrorString(rc)); return (int)rc; }
+  return lrc;
+}
+
 }  // extern "C"

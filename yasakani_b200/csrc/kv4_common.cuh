@@ -73,6 +73,11 @@ int launch_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, i
                         uint16_t* o16, int act_dtype, cudaStream_t st);
 int merge_status_fetch(int* out);
 
+// Family-B row codec, step 1 (kvx_codec.cu)
+int launch_kvx_rotate(const float* x, float* y, long long rows, int inverse, cudaStream_t st);
+int launch_kvx_encode(const void* x, int x_dtype, int8_t* q8, float* scales, long long rows, cudaStream_t st);
+int launch_kvx_decode(const int8_t* q8, const float* scales, void* y, int y_dtype, long long rows, cudaStream_t st);
+
 // Which attention kernel yskn_kv4_attention picks; set through yskn_kv4_set_algo (tests compare paths).
 enum Algo { ALGO_AUTO = 0, ALGO_SCALAR = 1, ALGO_MMA = 2 };
 

@@ -1,0 +1,58 @@
+"""Host-side mirror of the reference's Family-B row codec, step 1 (src/kvx_codec.cuh): sign-Hadamard-256 rotation and
+INT8 rows with one fp32 scale per row.  Same rules as kv4.py: torch tensors are device memory only, every call is
+enqueue-only on torch's current stream, all arithmetic happens in libyskn_kv4.so, no fallback."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import check
+from .kv4 import _ptr, _stream, _dtype_code
+
+
+def _rows(t: torch.Tensor) -> int:
+    if t.numel() % 256:
+        raise ValueError("rows are 256 values long")
+    return t.numel() // 256
+
+
+def rotate(x: torch.Tensor, inverse: bool = False, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """kvx_rotate (src/kvx_codec.cuh:35-49) on fp32 rows."""
+    if x.dtype != torch.float32:
+        raise TypeError("yskn_kvx_rotate takes fp32 rows")
+    out = torch.empty_like(x) if out is None else out
+    check(_lib.load().yskn_kvx_rotate(_ptr(x), _ptr(out), _rows(x), 1 if inverse else 0, _stream(stream)), "yskn_kvx_rotate")
+    return out
+
+
+def encode(x: torch.Tensor, q8: torch.Tensor | None = None, scales: torch.Tensor | None = None, stream=None):
+    """Rotation + kvx_store (src/kvx_codec.cuh:50-70): returns (q8 int8 [rows, 256], scales fp32 [rows])."""
+    rows = _rows(x)
+    q8 = torch.empty((rows, 256), dtype=torch.int8, device=x.device) if q8 is None else q8
+    scales = torch.empty((rows,), dtype=torch.float32, device=x.device) if scales is None else scales
+    check(_lib.load().yskn_kvx_encode(_ptr(x), _dtype_code(x), _ptr(q8), _ptr(scales), rows, _stream(stream)), "yskn_kvx_encode")
+    return q8, scales
+
+
+def decode(q8: torch.Tensor, scales: torch.Tensor, dtype=torch.float32, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """(float)q * scale, then the inverse rotation (src/kvx_probe.cu:15-19)."""
+    rows = _rows(q8)
+    out = torch.empty((rows, 256), dtype=dtype, device=q8.device) if out is None else out
+    check(_lib.load().yskn_kvx_decode(_ptr(q8), _ptr(scales), _ptr(out), _dtype_code(out), rows, _stream(stream)), "yskn_kvx_decode")
+    return out
+
+
+def probe(x: np.ndarray):
+    """The reference's yskn_kvx_probe contract over host arrays: (q, scales, y)."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, 256)
+    rows = x.shape[0]
+    q = np.empty((rows, 256), dtype=np.int8); sc = np.empty(rows, dtype=np.float32); y = np.empty_like(x)
+    rc = _lib.load().yskn_kvx_probe(x.ctypes.data_as(C.c_void_p), q.ctypes.data_as(C.c_void_p), sc.ctypes.data_as(C.c_void_p),
+                                    y.ctypes.data_as(C.c_void_p), rows)
+    if rc == -1 and (rows <= 0 or rows % 2):
+        raise ValueError("yskn_kvx_probe takes an even, positive number of rows")
+    check(rc, "yskn_kvx_probe")
+    return q, sc, y
