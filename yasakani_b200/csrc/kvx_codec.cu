@@ -14,10 +14,24 @@
 namespace kv4 {
 namespace {
 
-__device__ __forceinline__ float kvx_sign_of(int d) {
+// Bit 0 of the reference's 32-bit multiply-xorshift hash of d + 1: set = the element's sign is flipped.
+__host__ __device__ constexpr uint32_t kvx_sign_bit(int d) {
   uint32_t x = (uint32_t)d + 1u;
   x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
-  return (x & 1u) ? -1.f : 1.f;
+  return x & 1u;
+}
+struct SignTable { uint32_t w[8]; };                       // 256 sign bits, bit d of the table = kvx_sign_bit(d)
+constexpr SignTable make_signs() {
+  SignTable t{};
+  for (int d = 0; d < 256; ++d) t.w[d >> 5] |= kvx_sign_bit(d) << (d & 31);
+  return t;
+}
+__constant__ SignTable c_signs = make_signs();
+// Multiplying by +-1 is a sign-bit flip (exact, also for zeros and infinities): element i of lane L is d = 8L + i.
+__device__ __forceinline__ void apply_signs(float (&v)[8], int lane) {
+  const uint32_t bits = (c_signs.w[lane >> 2] >> (8 * (lane & 3))) & 0xFFu;
+  #pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(__float_as_uint(v[i]) ^ (((bits >> i) & 1u) << 31));
 }
 
 // Butterflies + 1/16 on the 256 elements a warp holds (v[i] = element 8*lane + i).  Lower index: a + b; upper: lower - upper.
@@ -30,11 +44,11 @@ __device__ __forceinline__ void hadamard256(float (&v)[8], int lane) {
   }
   #pragma unroll
   for (int m = 1; m < 32; m *= 2) {
-    const bool upper = (lane & m) != 0;
+    const uint32_t flip = (lane & m) ? 0x80000000u : 0u;          // upper lane: other - self = other + (-self), exactly
     #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float self = v[i], other = __shfl_xor_sync(0xffffffffu, self, m);
-      v[i] = upper ? __fsub_rn(other, self) : __fadd_rn(self, other);
+      v[i] = __fadd_rn(other, __uint_as_float(__float_as_uint(self) ^ flip));
     }
   }
   #pragma unroll
@@ -75,15 +89,9 @@ __global__ void __launch_bounds__(256) kvx_rotate_kernel(const float* x, float* 
   if (row >= rows) return;
   float v[8];
   load8<YSKN_KV4_F32>(x, (size_t)row, lane, v);
-  if (!inverse) {
-    #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], kvx_sign_of(8 * lane + i));
-  }
+  if (!inverse) apply_signs(v, lane);
   hadamard256(v, lane);
-  if (inverse) {
-    #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], kvx_sign_of(8 * lane + i));
-  }
+  if (inverse) apply_signs(v, lane);
   store8<YSKN_KV4_F32>(y, (size_t)row, lane, v);
 }
 
@@ -94,8 +102,7 @@ __global__ void __launch_bounds__(256) kvx_encode_kernel(const void* x, int8_t* 
   if (row >= rows) return;
   float v[8];
   load8<DT>(x, (size_t)row, lane, v);
-  #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], kvx_sign_of(8 * lane + i));
+  apply_signs(v, lane);
   hadamard256(v, lane);
   float amax = 0.f;
   #pragma unroll
@@ -103,10 +110,16 @@ __global__ void __launch_bounds__(256) kvx_encode_kernel(const void* x, int8_t* 
   #pragma unroll
   for (int m = 16; m; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
   const float sc = __fdiv_rn(amax, 127.f);
+  // q = rne(fl(v / sc)).  v * (1 / sc) is within a few ulp of the exact quotient, so rounding it gives the same integer
+  // unless it lies that close to a half-integer; only those elements (about one in 10^4) take the exact division.
+  const float inv = sc > 0.f ? __fdiv_rn(1.f, sc) : 0.f;
   uint32_t w[2] = {0u, 0u};
   #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    int q = sc > 0.f ? __float2int_rn(__fdiv_rn(v[i], sc)) : 0;
+    const float t = __fmul_rn(v[i], inv);
+    const float frac = fabsf(__fsub_rn(t, truncf(t)));               // exact: |t| < 2^8 here, distance from the integer below in magnitude
+    int q = __float2int_rn(t);
+    if (fabsf(__fsub_rn(frac, 0.5f)) < 6.2e-5f || !(fabsf(t) < 200.f)) q = sc > 0.f ? __float2int_rn(__fdiv_rn(v[i], sc)) : 0;
     q = max(-127, min(127, q));
     w[i >> 2] |= (uint32_t)(uint8_t)(int8_t)q << (8 * (i & 3));
   }
@@ -125,8 +138,7 @@ __global__ void __launch_bounds__(256) kvx_decode_kernel(const int8_t* q8, const
   #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] = __fmul_rn((float)(int8_t)(uint8_t)((i < 4 ? u.x : u.y) >> (8 * (i & 3))), sc);
   hadamard256(v, lane);
-  #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], kvx_sign_of(8 * lane + i));
+  apply_signs(v, lane);
   store8<DT>(y, (size_t)row, lane, v);
 }
 
