@@ -274,6 +274,10 @@ def run_ours(args, rank, world, local_rank):
     t_attn = ms_attn / K * 1e-3
     achieved = shard_bytes / t_attn / 1e9
     value = K / (ms_total * 1e-3)
+    # DRAM bytes of one decode-kernel launch: dram__bytes_read.sum + dram__bytes_write.sum from an ncu capture of this
+    # bench at 262,144 tokens on one GPU (308.47 MB read, 0.1-3.5 MB written: 1.013 x the algorithmic bytes); for a
+    # shard the figure scales with the tokens it holds.  --traffic overrides it with a fresh capture.
+    traffic = args.traffic if args.traffic is not None else NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * shard_bytes
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
@@ -284,7 +288,7 @@ def run_ours(args, rank, world, local_rank):
         "e2e": {"value": K / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(q_host.numel() * 2 + (kn_host.numel() + vn_host.numel()) * 2),
                 "d2h_bytes_per_step": int(o_host.numel() * 2), "ms_per_step": ms_e2e / K},
         "gpu_launches": launches_per_step * K,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": args.traffic,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                      "kernel": "decode attention (split-K partials)", "us_per_launch": t_attn * 1e6, "bytes_per_launch": shard_bytes,
                      "peak_kind": f"of {peak_kind}"},
     }
@@ -307,6 +311,9 @@ def run_ours(args, rank, world, local_rank):
         line["check"] = {"max_abs_err_vs_oracle": float(err.max()), "ok": bool((err <= 2e-3 + 1e-2 * np.abs(want)).all())}
     if rank == 0:
         print(json.dumps(line), flush=True)
+
+
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 310.27e6 / 306208768
 
 
 def main():
