@@ -211,6 +211,30 @@ YSKN_KV4_API int yskn_kvx_decode(const int8_t* d_q8, const float* d_scales, void
  * Allocates and frees its own device memory. */
 YSKN_KV4_API int yskn_kvx_probe(const float* x, int8_t* q, float* scales, float* y, int rows);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * Family-B decode attention over the INT8 rows above: the INT8 members of the reference's Q35AttnArgs
+ * (src/q35.hpp:126-130), with the head counts the reference fixes at compile time (Q35_NH, Q35_KVH) as fields.
+ * head_dim is 256.  q16 [M][nh][256] is bf16 (the reference's dtype) or fp16, already rotated (yskn_kvx_rotate);
+ * k8, v8 [kvh][max_ctx][256] int8 with ks, vs [kvh][max_ctx] fp32 (yskn_kvx_encode); row r sits at *d_pos + r and sees
+ * keys 0 .. *d_pos + r; partials in the reference's layout pm, pl [M][splits][nh], pacc [M][splits][nh][256]. */
+typedef struct yskn_kv8_attn_args {
+  const uint16_t* q16;
+  const int8_t* k8; const int8_t* v8; const float* ks; const float* vs;
+  int max_ctx; int M; const int* d_pos; int splits;
+  float* pm; float* pl; float* pacc;
+  int kvh; int nh; float qscale;            /* the reference multiplies q by 0.0625 = 1/sqrt(256) (src/q35_kernels.cu:1211) */
+} yskn_kv8_attn_args;
+
+/* launch_q35_attention, INT8 branch (q35_attention_kernel<true>, src/q35_kernels.cu:1176-1281).  nh / kvh <= 8,
+ * max_ctx a multiple of 64, k8/v8 16-byte aligned.  Split boundaries are multiples of 16 keys (the merge does not depend on them). */
+YSKN_KV4_API int yskn_kv8_attention(const yskn_kv8_attn_args* a, int act_dtype, void* cuda_stream);
+
+/* Merge of the splits as launch_q35_combine does up to the gated row (src/q35_kernels.cu:1400-1424): y = o / L, inverse
+ * rotation if inverse_rotate != 0, rounding to the activation dtype, then y * sigmoid(gate) with the reference's roundings
+ * if d_gate != NULL ([M][nh][256], activation dtype).  splits <= 64.  The int8 requantisation for the next GEMV is not part of this. */
+YSKN_KV4_API int yskn_kv8_combine(const float* d_pm, const float* d_pl, const float* d_pacc, int splits, int M, int nh, const void* d_gate,
+                                  void* d_o16, int act_dtype, int inverse_rotate, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -175,3 +175,14 @@ def kvx_decode(q: np.ndarray, sc: np.ndarray) -> np.ndarray:
     y = np.empty(q.shape, dtype=np.float32)
     lib().ysko_kvx_decode(_p(q), _p(sc), _p(y), C.c_long(q.shape[0]))
     return y
+
+
+def kv8_attention_exact(q: np.ndarray, k8: np.ndarray, v8: np.ndarray, ks: np.ndarray, vs: np.ndarray, pos0: int, qscale: float = 0.0625) -> np.ndarray:
+    """q [M, nh, 256] fp32 (rotated), k8/v8 [kvh, max_ctx, 256] int8, ks/vs [kvh, max_ctx] -> [M, nh, 256] in the rotated basis."""
+    q = np.ascontiguousarray(q, dtype=np.float32); k8 = np.ascontiguousarray(k8, dtype=np.int8); v8 = np.ascontiguousarray(v8, dtype=np.int8)
+    ks = np.ascontiguousarray(ks, dtype=np.float32); vs = np.ascontiguousarray(vs, dtype=np.float32)
+    M, nh, _ = q.shape; kvh, max_ctx, _ = k8.shape
+    out = np.empty_like(q)
+    lib().ysko_kv8_attention_exact(_p(q), _p(k8), _p(v8), _p(ks), _p(vs), C.c_int(max_ctx), C.c_int(M), C.c_int(pos0), C.c_int(kvh),
+                                   C.c_int(nh), C.c_float(qscale), _p(out))
+    return out

@@ -70,3 +70,33 @@ void ysko_kvx_decode(const int8_t* q8, const float* scales, float* y, long rows)
     rotate_row(v, y + r * 256, 1);
   }
 }
+
+/* Family-B decode attention over INT8 rows, restated from q35_attention_kernel<KV8> (src/q35_kernels.cu:1176-1281):
+ * row r at pos0 + r sees keys 0 .. pos0 + r; s_t = (sum_c (q_c * qscale) * k8_tc) * ks_t; softmax; O = sum_t p_t * vs_t * v8_t.
+ * q is the rotated query as fp32 values [M][nh][256]; out [M][nh][256] in the rotated basis.  Double accumulation:
+ * this is the exact answer the tolerance is measured against, not a bit-level model of the kernel. */
+void ysko_kv8_attention_exact(const float* q, const int8_t* k8, const int8_t* v8, const float* ks, const float* vs, int max_ctx,
+                              int M, int pos0, int kvh, int nh, float qscale, float* out) {
+  const int G = nh / kvh;
+  #pragma omp parallel for collapse(2) schedule(dynamic)
+  for (int r = 0; r < M; ++r)
+    for (int h = 0; h < nh; ++h) {
+      const int kv = h / G, len = pos0 + r + 1;
+      const float* qr = q + ((size_t)r * nh + h) * 256;
+      double mx = -1e300, l = 0.0, o[256];
+      for (int d = 0; d < 256; ++d) o[d] = 0.0;
+      for (int t = 0; t < len; ++t) {
+        const int8_t* kr = k8 + ((size_t)kv * max_ctx + t) * 256;
+        double s = 0.0;
+        for (int d = 0; d < 256; ++d) s += (double)(qr[d] * qscale) * (double)kr[d];
+        s *= (double)ks[(size_t)kv * max_ctx + t];
+        if (s > mx) { const double a = exp(mx - s); l *= a; for (int d = 0; d < 256; ++d) o[d] *= a; mx = s; }
+        const double p = exp(s - mx);
+        l += p;
+        const double pv = p * (double)vs[(size_t)kv * max_ctx + t];
+        const int8_t* vr = v8 + ((size_t)kv * max_ctx + t) * 256;
+        for (int d = 0; d < 256; ++d) o[d] += pv * (double)vr[d];
+      }
+      for (int d = 0; d < 256; ++d) out[((size_t)r * nh + h) * 256 + d] = (float)(o[d] / l);
+    }
+}

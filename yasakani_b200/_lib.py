@@ -38,6 +38,12 @@ class KvAppendArgsC(C.Structure):     # yskn_kv_append_args
                 ("d_pos", C.c_void_p), ("M", C.c_int), ("max_ctx", C.c_int), ("kvh", C.c_int), ("hd", C.c_int)]
 
 
+class Kv8AttnArgsC(C.Structure):
+    _fields_ = [("q16", C.c_void_p), ("k8", C.c_void_p), ("v8", C.c_void_p), ("ks", C.c_void_p), ("vs", C.c_void_p),
+                ("max_ctx", C.c_int), ("M", C.c_int), ("d_pos", C.c_void_p), ("splits", C.c_int),
+                ("pm", C.c_void_p), ("pl", C.c_void_p), ("pacc", C.c_void_p), ("kvh", C.c_int), ("nh", C.c_int), ("qscale", C.c_float)]
+
+
 class PeerExchangeC(C.Structure):     # yskn_kv4_peer_exchange
     _fields_ = [("buf", C.c_void_p * 8), ("world", C.c_int), ("rank", C.c_int)]
 
@@ -74,6 +80,8 @@ PROTOTYPES = {
     "yskn_kvx_encode": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]),
     "yskn_kvx_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_void_p]),
     "yskn_kvx_probe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
+    "yskn_kv8_attention": (C.c_int, [C.POINTER(Kv8AttnArgsC), C.c_int, C.c_void_p]),
+    "yskn_kv8_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_attention_host": (C.c_int, [C.c_void_p, C.POINTER(KvLayerC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                           C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_int,
                                           C.c_void_p]),

@@ -243,6 +243,15 @@ int yskn_kvx_decode(const int8_t* d_q8, const float* d_scales, void* d_y, int y_
   return launch_kvx_decode(d_q8, d_scales, d_y, y_dtype, rows, (cudaStream_t)cuda_stream);
 }
 
+int yskn_kv8_attention(const yskn_kv8_attn_args* a, int act_dtype, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_kv8_attention: null argument struct");
+  return launch_kv8_attention(*a, act_dtype, (cudaStream_t)cuda_stream);
+}
+int yskn_kv8_combine(const float* d_pm, const float* d_pl, const float* d_pacc, int splits, int M, int nh, const void* d_gate,
+                     void* d_o16, int act_dtype, int inverse_rotate, void* cuda_stream) {
+  return launch_kv8_combine(d_pm, d_pl, d_pacc, splits, M, nh, d_gate, d_o16, act_dtype, inverse_rotate, (cudaStream_t)cuda_stream);
+}
+
 int yskn_kvx_probe(const float* x, int8_t* q, float* scales, float* y, int rows) {
   if (rows <= 0 || rows % 2) return -1;                  // the reference's probe takes row pairs
   if (!x || !q || !scales || !y) KV4_REJECT("yskn_kvx_probe: null buffer");

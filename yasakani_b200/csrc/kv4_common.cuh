@@ -78,6 +78,11 @@ int launch_kvx_rotate(const float* x, float* y, long long rows, int inverse, cud
 int launch_kvx_encode(const void* x, int x_dtype, int8_t* q8, float* scales, long long rows, cudaStream_t st);
 int launch_kvx_decode(const int8_t* q8, const float* scales, void* y, int y_dtype, long long rows, cudaStream_t st);
 
+// Family-B decode attention over INT8 rows (kv8_decode.cu)
+int launch_kv8_attention(const yskn_kv8_attn_args& a, int act_dtype, cudaStream_t st);
+int launch_kv8_combine(const float* pm, const float* pl, const float* pacc, int splits, int M, int nh, const void* gate, void* o16,
+                       int act_dtype, int inverse_rotate, cudaStream_t st);
+
 // Which attention kernel yskn_kv4_attention picks; set through yskn_kv4_set_algo (tests compare paths).
 enum Algo { ALGO_AUTO = 0, ALGO_SCALAR = 1, ALGO_MMA = 2 };
 

@@ -9,7 +9,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import check
+from ._lib import check, Kv8AttnArgsC
 from .kv4 import _ptr, _stream, _dtype_code
 
 
@@ -56,3 +56,25 @@ def probe(x: np.ndarray):
         raise ValueError("yskn_kvx_probe takes an even, positive number of rows")
     check(rc, "yskn_kvx_probe")
     return q, sc, y
+
+
+def _dp(t):
+    return None if t is None else t.data_ptr()
+
+
+def launch_kv8_attention(q16: torch.Tensor, k8: torch.Tensor, v8: torch.Tensor, ks: torch.Tensor, vs: torch.Tensor, M: int,
+                         d_pos: torch.Tensor, splits: int, pm: torch.Tensor, pl: torch.Tensor, pacc: torch.Tensor, nh: int,
+                         qscale: float = 0.0625, stream=None) -> None:
+    """launch_q35_attention, INT8 branch (src/q35_kernels.cu:1176-1281): k8/v8 [kvh, max_ctx, 256] int8, ks/vs [kvh, max_ctx]."""
+    kvh, max_ctx = k8.shape[0], k8.shape[1]
+    for t in (q16, k8, v8, ks, vs, d_pos, pm, pl, pacc):
+        assert t.is_cuda and t.is_contiguous()
+    a = Kv8AttnArgsC(_dp(q16), _dp(k8), _dp(v8), _dp(ks), _dp(vs), max_ctx, M, _dp(d_pos), splits, _dp(pm), _dp(pl), _dp(pacc), kvh, nh, qscale)
+    check(_lib.load().yskn_kv8_attention(C.byref(a), _dtype_code(q16), _stream(stream)), "yskn_kv8_attention")
+
+
+def launch_kv8_combine(pm, pl, pacc, splits: int, M: int, nh: int, o16: torch.Tensor, gate: torch.Tensor | None = None,
+                       inverse_rotate: bool = True, stream=None) -> None:
+    """Split merge, inverse rotation, rounding, optional sigmoid gate (src/q35_kernels.cu:1400-1424)."""
+    check(_lib.load().yskn_kv8_combine(_ptr(pm), _ptr(pl), _ptr(pacc), splits, M, nh, _ptr(gate), _ptr(o16), _dtype_code(o16),
+                                       1 if inverse_rotate else 0, _stream(stream)), "yskn_kv8_combine")
