@@ -316,6 +316,106 @@ def run_ours(args, rank, world, local_rank):
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 310.27e6 / 306208768
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# Secondary workloads (--workload): the other kernels of the path, one GPU, device-timed, one JSON line each.
+# They are not the headline metric; they make the numbers quoted for these kernels reproducible from this file.
+def _timed(fn, steps, warmup):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps * 1e-3
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def run_secondary(args):
+    from yasakani_b200 import kv4, kvx
+    shape = synth.C2
+    hbm, tf, kind = _peaks()
+    K, W = args.steps, args.warmup
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    base = {"n_gpus": 1, "steps": K, "warmup": W, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic"}
+
+    def tc_case(ctx, M, splits, name):
+        max_ctx = ((ctx + M + 127) // 64) * 64
+        layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
+        d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for p in range(0, ctx + M, 8192):
+            n = min(8192, ctx + M - p)
+            k = torch.randn((n, shape.hkv, shape.hd), generator=g, device="cuda", dtype=torch.float16)
+            v = torch.randn((n, shape.hkv, shape.hd), generator=g, device="cuda", dtype=torch.float16)
+            d_pos.fill_(p)
+            kv4.launch_kv_append(layer, k, v, d_pos, n)
+        rope = torch.empty((max_ctx, shape.rd // 2, 2), dtype=torch.float32, device="cuda")
+        kv4.launch_rope_table_g(rope, max_ctx, shape.theta, shape.rd)
+        q = torch.randn((M, shape.hq, shape.hd), generator=g, device="cuda", dtype=torch.float16)
+        d_pos.fill_(ctx)
+        pm, pl, pacc = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
+        o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+        ws = kv4.tc_workspace(layer, M)
+        t = _timed(lambda i: kv4.launch_attention_prefill_tc(q, layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws), K, W)
+        flops = shape.attn_flops(sum(ctx + r + 1 for r in range(M)))
+        line = dict(base, metric="kv4_multirow_attn_tflops", value=flops / t / 1e12, unit="TFLOP/s", ms_per_step=t * 1e3, dtype="f16",
+                    config={"workload": name, "rows": M, "cached_tokens": ctx, "splits": splits, "l2": "K/V workspace is L2-resident by design; tensor-bound"},
+                    gpu_launches=(2 if splits == 1 else 3) * K,
+                    roofline={"bound": "tensor", "achieved": flops / t / 1e12, "peak": tf, "unit": "TFLOP/s", "frac": flops / t / 1e12 / tf, "traffic": None,
+                              "kernel": "dequant prep + tcgen05 attention" + ("" if splits == 1 else " + merge"), "peak_kind": f"of {kind}"})
+        print(json.dumps(line), flush=True)
+
+    if args.workload == "prefill":
+        tc_case(0, 8192, 1, "C5 causal prefill: 8192 rows from an empty cache, Hq24/Hkv4/hd256")
+    elif args.workload == "verify":
+        for M, S in ((64, 12), (32, 18), (16, 37)):
+            tc_case(32768, M, S, f"C3 verify: {M} rows against 32768 cached tokens, Hq24/Hkv4/hd256")
+    elif args.workload == "kv8":
+        kvh, nh, S = shape.hkv, shape.hq, args.splits
+        for ctx in (262144, 32768):
+            caches = []
+            for _ in range(2):
+                k8 = torch.randint(-127, 128, (kvh, ctx, 256), dtype=torch.int8, device="cuda", generator=g)
+                v8 = torch.randint(-127, 128, (kvh, ctx, 256), dtype=torch.int8, device="cuda", generator=g)
+                caches.append((k8, v8, torch.rand((kvh, ctx), device="cuda", generator=g) * 0.03, torch.rand((kvh, ctx), device="cuda", generator=g) * 0.03))
+            q = torch.randn((1, nh, 256), device="cuda", generator=g).to(torch.bfloat16)
+            d_pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda")
+            pm = torch.empty((1, S, nh), device="cuda"); pl = torch.empty_like(pm); pacc = torch.empty((1, S, nh, 256), device="cuda")
+            t = _timed(lambda i: kvx.launch_kv8_attention(q, *caches[i & 1], 1, d_pos, S, pm, pl, pacc, nh), K, W)
+            byt = kvh * ctx * 520
+            line = dict(base, metric="kv8_decode_attn_tokens_per_s", value=1.0 / t, unit="tokens/s", ms_per_step=t * 1e3, dtype="f16",
+                        config={"workload": f"Family-B decode over INT8 rows: 1 query token, Hq{nh}/Hkv{kvh}/hd256, {ctx} cached tokens", "splits": S,
+                                "l2": f"2 distinct cache copies cycled; {byt / 1e6:.1f} MB read per launch (L2 is 126 MB)"},
+                        gpu_launches=K,
+                        roofline={"bound": "hbm", "achieved": byt / t / 1e9, "peak": hbm, "unit": "GB/s", "frac": byt / t / 1e9 / hbm, "traffic": None,
+                                  "kernel": "kv8 decode attention (split-K partials)", "bytes_per_launch": byt, "peak_kind": f"of {kind}"})
+            print(json.dumps(line), flush=True)
+            del caches
+    elif args.workload == "kvx":
+        rows = 1 << 20
+        x = torch.randn((rows, 256), device="cuda", generator=g)
+        q8, sc = kvx.encode(x); y = torch.empty_like(x)
+        for name, fn in (("encode", lambda i: kvx.encode(x, q8, sc)), ("decode", lambda i: kvx.decode(q8, sc, out=y))):
+            t = _timed(fn, K, W)
+            byt = rows * 1284
+            line = dict(base, metric=f"kvx_{name}_rows_per_s", value=rows / t, unit="rows/s", ms_per_step=t * 1e3, dtype="f32",
+                        config={"workload": f"Family-B row codec {name}: {rows} fp32 rows of 256 (rotation + INT8)", "l2": f"{byt / 1e6:.0f} MB per launch (L2 is 126 MB)"},
+                        gpu_launches=K,
+                        roofline={"bound": "hbm", "achieved": byt / t / 1e9, "peak": hbm, "unit": "GB/s", "frac": byt / t / 1e9 / hbm, "traffic": None,
+                                  "kernel": f"kvx_{name}_kernel", "bytes_per_launch": byt, "peak_kind": f"of {kind}"})
+            print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -328,11 +428,17 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="N > 1: how the shards' (m, l, O) triples travel")
     ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch from an ncu capture, if known")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "verify", "kv8", "kvx"],
+                    help="decode = the headline metric (default); the others time the remaining kernels of the path on one GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload != "decode":
+        if rank == 0:
+            run_secondary(args)
         return
     if world > 1:
         import torch.distributed as dist

@@ -299,7 +299,7 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
     float acc[HD / 16][4];                                      // O^T: [m-tile][(even | odd channel) x (head 2j | 2j+1)]
     #pragma unroll
     for (int mt = 0; mt < HD / 16; ++mt) { acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f; }
-    float m[2] = {-1e30f, -1e30f}, l[2] = {0.f, 0.f}, zacc[2] = {0.f, 0.f};   // heads 2j, 2j+1 (log2 domain)
+    float m[2] = {-1e30f, -1e30f}, l[2] = {0.f, 0.f}, zacc[2] = {0.f, 0.f}, zs[2] = {0.f, 0.f};   // heads 2j, 2j+1 (log2 domain); zacc = sum p*vzero, zs = sum of the rounded p*vscale
 
     // per-lane constant offsets: K word i of row g (swizzled chunk), V chunk of rows 2j and 2j+1
     const int swz = HD == 256 ? (g & 7) : ((g >> 1) & 3);
@@ -425,26 +425,27 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
         for (int o = 4; o <= 16; o <<= 1) { t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, o)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, o)); }
         if (__any_sync(0xffffffffu, t0 > m[0] + 8.f || t1 > m[1] + 8.f)) {   // lazy rescale: the running max may lag by 2^8
           const float n0 = fmaxf(m[0], t0), n1 = fmaxf(m[1], t1), a0 = ex2(m[0] - n0), a1 = ex2(m[1] - n1);
-          m[0] = n0; m[1] = n1; l[0] *= a0; l[1] *= a1; zacc[0] *= a0; zacc[1] *= a1;
+          m[0] = n0; m[1] = n1; l[0] *= a0; l[1] *= a1; zacc[0] *= a0; zacc[1] *= a1; zs[0] *= a0; zs[1] *= a1;
           #pragma unroll
           for (int mt = 0; mt < HD / 16; ++mt) { acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1; }
         }
         const float p00 = v0 ? ex2(s00 - m[0]) : 0.f, p01 = v0 ? ex2(s01 - m[1]) : 0.f;
         const float p10 = v1 ? ex2(s10 - m[0]) : 0.f, p11 = v1 ? ex2(s11 - m[1]) : 0.f;
         l[0] += p00 + p10; l[1] += p01 + p11;
-        // V per-token scale folded into P (fp16), zero point into a per-head scalar: v = vs*(64+n) + (vz - 64*vs).
-        // The -64*vs*p part uses the ROUNDED p*vs the MMA consumes, so the offset cancels exactly.
+        // V per-token scale folded into P (fp16), zero point into a per-head scalar: v = vs*(off+n) + (vz - off*vs), off = 1024
+        // for even channels (low nibble read in place) and 64 for odd ones.  The -off*vs*p part uses the sum of the ROUNDED
+        // p*vs the MMA consumes, so the offset cancels exactly; it is subtracted once, after the loop.
         const float vs0 = v0 ? lds_h(vsa) : 0.f, vz0 = v0 ? lds_h(vsa + L::UG * 64) : 0.f;
         const float vs1 = v1 ? lds_h(vsa + 16) : 0.f, vz1 = v1 ? lds_h(vsa + L::UG * 64 + 16) : 0.f;
         const uint32_t pp0 = pack_h2(p00 * vs0, p01 * vs0), pp1 = pack_h2(p10 * vs1, p11 * vs1);
         const float2 pr0 = __half22float2(*reinterpret_cast<const __half2*>(&pp0)), pr1 = __half22float2(*reinterpret_cast<const __half2*>(&pp1));
-        zacc[0] += p00 * vz0 + p10 * vz1 - 64.f * (pr0.x + pr1.x);
-        zacc[1] += p01 * vz0 + p11 * vz1 - 64.f * (pr0.y + pr1.y);
+        zacc[0] += p00 * vz0 + p10 * vz1; zs[0] += pr0.x + pr1.x;
+        zacc[1] += p01 * vz0 + p11 * vz1; zs[1] += pr0.y + pr1.y;
         const uint32_t pb0 = movmatrix_t(pp0);                   // B regs: (tokens 2j,2j+1 | head g)
         const uint32_t pb1 = movmatrix_t(pp1);                   //         (tokens 2j+8,2j+9 | head g)
         // ---- O^T += V^T P^T.  Lane reads token rows A=2j, B=2j+1, C=2j+8, D=2j+9 at its channel block [HD/8*g, +HD/8).
         //      Byte b of word w holds channels (8w+2b, 8w+2b+1): PRMT puts that byte of rows A and B (C and D) into the low
-        //      byte of the two halves; the odd channel is read in place, the even one after a shift by 4.
+        //      byte of the two halves; both nibbles are read in place (even channel: 1024 + n, odd channel: 64 + n).
         {
           uint32_t wv[4][HD / 64];                               // [A,B,C,D][word]
           if (HD == 256) {
@@ -461,8 +462,8 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
             for (int b = 0; b < 4; ++b) {
               const uint32_t sel = ((4 + b) << 12) | ((4 + b) << 8) | (b << 4) | b;
               const uint32_t ab = __byte_perm(wv[0][w], wv[1][w], sel), cd = __byte_perm(wv[2][w], wv[3][w], sel);
-              mma16816(acc[4 * w + b], and_or(ab << 4, nk.m1, nk.o), and_or(ab, nk.m1, nk.o),
-                       and_or(cd << 4, nk.m1, nk.o), and_or(cd, nk.m1, nk.o), pb0, pb1);
+              mma16816(acc[4 * w + b], and_or(ab, nk.m0, nk.e), and_or(ab, nk.m1, nk.o),
+                       and_or(cd, nk.m0, nk.e), and_or(cd, nk.m1, nk.o), pb0, pb1);
             }
         }
         // next tile: sixteen rows further down
@@ -494,7 +495,9 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
     for (int o = 4; o <= 16; o <<= 1) {
       l[0] += __shfl_xor_sync(0xffffffffu, l[0], o); l[1] += __shfl_xor_sync(0xffffffffu, l[1], o);
       zacc[0] += __shfl_xor_sync(0xffffffffu, zacc[0], o); zacc[1] += __shfl_xor_sync(0xffffffffu, zacc[1], o);
+      zs[0] += __shfl_xor_sync(0xffffffffu, zs[0], o); zs[1] += __shfl_xor_sync(0xffffffffu, zs[1], o);
     }
+    const float ze[2] = {zacc[0] - 1024.f * zs[0], zacc[1] - 1024.f * zs[1]}, zo[2] = {zacc[0] - 64.f * zs[0], zacc[1] - 64.f * zs[1]};
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");  // nobody still reads a stage
     if (!*s_abort) {
       float* wb = mbuf + (size_t)warp * 8 * (HD + 2);
@@ -502,8 +505,8 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
       #pragma unroll
       for (int mt = 0; mt < HD / 16; ++mt) {
         const int c = (HD / 8) * g + 8 * (mt >> 2) + 2 * (mt & 3);     // even channel of the m-tile; the odd one is c + 1
-        wb[(2 * j) * (HD + 2) + 2 + c] = acc[mt][0] + zacc[0]; wb[(2 * j + 1) * (HD + 2) + 2 + c] = acc[mt][1] + zacc[1];
-        wb[(2 * j) * (HD + 2) + 2 + c + 1] = acc[mt][2] + zacc[0]; wb[(2 * j + 1) * (HD + 2) + 2 + c + 1] = acc[mt][3] + zacc[1];
+        wb[(2 * j) * (HD + 2) + 2 + c] = acc[mt][0] + ze[0]; wb[(2 * j + 1) * (HD + 2) + 2 + c] = acc[mt][1] + ze[1];
+        wb[(2 * j) * (HD + 2) + 2 + c + 1] = acc[mt][2] + zo[0]; wb[(2 * j + 1) * (HD + 2) + 2 + c + 1] = acc[mt][3] + zo[1];
       }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
