@@ -15,7 +15,7 @@
 // copies: K 128 x HD/2 bytes and V 128 x HD/2 bytes by tiled TMA (128-byte swizzle), four K scale rows, four K zero
 // rows, 128 V scales, 128 V zeros (bulk copies) and the four rope rows of the groups' first positions (one strided
 // TMA tile).  Few, large copies matter: the number of copies in flight per SM is limited, not only their bytes.
-// Eleven consumer warps take the groups round-robin and keep their own (m, l, O) state.  A group is two 16-token
+// Seven consumer warps take the groups round-robin and keep their own (m, l, O) state.  A group is two 16-token
 // MMA tiles:
 //   S^T[16 tok x 8 heads]  = K[16 tok x HD] . Q^T[HD x 8 heads]          (m16n8k16, HD/16 steps)
 //   O^T[HD x 8 heads]     += V^T[HD x 16 tok] . P^T[16 tok x 8 heads]    (HD/16 m-tiles)
@@ -56,10 +56,11 @@ __device__ unsigned long long g_decode_cycles[4] = {0, 0, 0, 0};
 namespace {
 
 #ifndef KV4_DECODE_NCW
-#define KV4_DECODE_NCW 11                    // consumer warps per CTA
+#define KV4_DECODE_NCW 7                     // consumer warps per CTA
 #endif
 #ifndef KV4_DECODE_MAXREG
-#define KV4_DECODE_MAXREG 168                // 3 warps per SM sub-partition (16384 / (168*32)) -> one CTA of 12 warps per SM
+#define KV4_DECODE_MAXREG 255                // 2 warps per SM sub-partition, one CTA of 8 warps per SM.  Measured at 262,144 tokens:
+                                             // 4 / 6 / 8 / 12 / 16 warps (255 / 255 / 255 / 168 / 128 registers) = 127 / 111 / 83.5 / 90.2 / 107 us per step
 #endif
 constexpr int NSTAGE = 5;                    // ring depth (128-token units in flight per CTA)
 constexpr int NCW = KV4_DECODE_NCW;
@@ -378,8 +379,19 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
       #pragma unroll 1
       for (int tile = 0; tile < 2; ++tile) {
         if (TAIL && tile * 16 >= nvalid) break;
+        // The tile's packed words and V rows are requested up front, so their shared-memory latency overlaps the arithmetic
+        // that follows (the loads are ordered asm statements: the compiler will not hoist them by itself).
+        uint32_t kw[2][NW];
+        if (!TAIL) {
+          #pragma unroll
+          for (int h = 0; h < 2; ++h)
+            #pragma unroll
+            for (int i = 0; i < NW; ++i) kw[h][i] = lds32(ka[i] + h * KROW8);
+        }
+        uint4 vx[4];
+        if (HD == 256) { vx[0] = lds128(va); vx[1] = lds128(vb); vx[2] = lds128(va + 8 * L::ROWB); vx[3] = lds128(vb + 8 * L::ROWB); }
         auto load_k = [&](int h, int i, uint32_t (&o)[4]) {     // A regs of word w = 4i+j, row g + 8h of the tile
-          if (TAIL) pair_regs(lds128(ka[i] + h * KROW8), o); else nib_regs(lds32(ka[i] + h * KROW8), o, nk);
+          if (TAIL) pair_regs(lds128(ka[i] + h * KROW8), o); else nib_regs(kw[h][i], o, nk);
         };
         // ---- S^T[16 tok x 8 heads] = K . Q^T, two independent accumulation chains
         float sa[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -449,7 +461,7 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
         {
           uint32_t wv[4][HD / 64];                               // [A,B,C,D][word]
           if (HD == 256) {
-            const uint4 xa = lds128(va), xb = lds128(vb), xc = lds128(va + 8 * L::ROWB), xd = lds128(vb + 8 * L::ROWB);
+            const uint4 xa = vx[0], xb = vx[1], xc = vx[2], xd = vx[3];
             wv[0][0] = xa.x; wv[0][1] = xa.y; wv[0][2] = xa.z; wv[0][3] = xa.w; wv[1][0] = xb.x; wv[1][1] = xb.y; wv[1][2] = xb.z; wv[1][3] = xb.w;
             wv[2][0] = xc.x; wv[2][1] = xc.y; wv[2][2] = xc.z; wv[2][3] = xc.w; wv[3][0] = xd.x; wv[3][1] = xd.y; wv[3][2] = xd.z; wv[3][3] = xd.w;
           } else {
