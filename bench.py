@@ -267,15 +267,31 @@ def run_ours(args, rank, world, local_rank):
         vn_host = v_new[(ctx - 1) % CHUNK:(ctx - 1) % CHUNK + 1].contiguous().pin_memory()
         kn_dev, vn_dev = kn_host.to(dev), vn_host.to(dev)
 
-        def e2e_step(i):
-            d = decs[i % n_copies]
+        def e2e_body(d):                                           # host buffers in, the step, host buffer out
             q_dev.copy_(q_host, non_blocking=True)
             if plan.is_last:
                 kn_dev.copy_(kn_host, non_blocking=True); vn_dev.copy_(vn_host, non_blocking=True)
                 d.append(kn_dev, vn_dev, ctx - 1)
-            graphs[i % n_copies].replay()
+            step(d)
             if rank == 0:
                 o_host.copy_(d.o16, non_blocking=True)
+
+        # the whole step, copies included, is one captured graph per cache copy (the copies become memcpy nodes that run on
+        # every replay); the host waits for the result after each step, as a caller that samples the next token would
+        e2e_graphs = []
+        with torch.cuda.stream(side):
+            for d in decs:
+                e2e_body(d)
+            torch.cuda.synchronize()
+            for d in decs:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    e2e_body(d)
+                e2e_graphs.append(g)
+        torch.cuda.synchronize()
+
+        def e2e_step(i):
+            e2e_graphs[i % n_copies].replay()
             torch.cuda.current_stream().synchronize()               # the caller consumes o16 on the host
 
         with torch.cuda.stream(side):
