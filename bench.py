@@ -202,7 +202,8 @@ def run_ours(args, rank, world, local_rank):
         else:
             kv4.launch_decode(q_dev, d.layer, 1, d.d_pos, splits, d.pm, d.pl, d.pacc, rope, shape.hq, shape.qscale, shape.rd, d.o16)
 
-    launches_per_step = 3 if world > 1 else 2          # attention, merge (N=1); attention, triple, merge of triples (N>1)
+    # attention + merge (N = 1); attention + fused push/wait/merge (N > 1, p2p); attention + triple + merge of triples (N > 1, nccl)
+    launches_per_step = 3 if (world > 1 and exchange == "nccl") else 2
 
     # CUDA graphs: the step is launch-bound otherwise (a few 10 us of kernels).  One graph per cache copy holds one step (used
     # by the end-to-end loop, which copies host buffers between steps); one more holds GSTEPS consecutive steps over the

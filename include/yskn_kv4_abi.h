@@ -85,7 +85,7 @@ YSKN_KV4_API int yskn_kv4_set_algo(int algo);
 /* Reads and clears the device status word of the tensor-core decode kernel on the current device (synchronises):
  * 0 = ok, 1/2 = a bounded wait on the decode staging ring ran out (consumer/producer), 3 = misaligned shared memory,
  * 4/5/6 = a bounded wait ran out in the tcgen05 kernel (softmax warps / MMA issuer / producer),
- * 7 = the wait for another shard's triple ran out (yskn_kv4_merge_pushed).
+ * 7 = the wait for another shard's triple ran out (yskn_kv4_merge_pushed, yskn_kv4_exchange_merge).
  * A non-zero status means the partials of that launch are invalid.  The kernels never trap; compare the reference's
  * device-side __trap() on bad input (src/kvq_gpu.cuh:91). */
 YSKN_KV4_API int yskn_kv4_device_status(int* status);
@@ -160,6 +160,12 @@ YSKN_KV4_API size_t yskn_kv4_exchange_bytes(int world, int M, int nh, int hd);
 YSKN_KV4_API int yskn_kv4_push_triple(const yskn_attn_g_combine_args* a, int hd, const yskn_kv4_peer_exchange* x, void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, int hd, const uint16_t* bv,
                                        const uint16_t* gate, uint16_t* o16, int act_dtype, void* cuda_stream);
+/* Push and merge in ONE launch: every block folds its splits, stores the triple to all ranks, waits (bounded, status 7) for
+ * theirs and merges into a->o16 (bias and gate as yskn_kv4_combine).  The blocks wait inside the kernel, so the grid of
+ * nh * M blocks must be resident as a whole: nh * M <= 148, larger requests are rejected (use push + merge).  Same buffer
+ * protocol as above: in a step a rank calls either this or the pair push/merge. */
+YSKN_KV4_API int yskn_kv4_exchange_merge(const yskn_attn_g_combine_args* a, int hd, int act_dtype, const yskn_kv4_peer_exchange* x,
+                                         void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_local_triple(const yskn_attn_g_combine_args* a, int hd, float* d_triple, void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd,
                                         const uint16_t* bv, const uint16_t* gate, uint16_t* o16, int act_dtype,

@@ -264,3 +264,59 @@ def test_peer_exchange_on_one_gpu_matches_the_gathered_merge(oracle, world):
             torch.cuda.synchronize()
             assert kv4.device_status() == 0
             assert_close(o16.float().cpu().numpy(), want, f"step {step} rank {rnk} of {world}")
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_fused_exchange_merge_on_one_gpu(oracle, world):
+    """yskn_kv4_exchange_merge (fold + push + wait + merge in one launch).  On one GPU the other 'ranks' push first with the
+    two-launch form (same buffer protocol), so the fused kernel finds their arrivals and never waits for a later launch;
+    the rank that runs fused rotates over three steps, the others close their step with merge_pushed."""
+    from yasakani_b200.sharded import plan_shards
+    shape, ctx = synth.C2, 2500
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, 1, seed=41)
+    k, v = synth.make_kv(shape, ctx + 1, seed=41)
+    bufs = [torch.zeros((kv4.exchange_bytes(world, 1, shape.hq, shape.hd) + 3) // 4, dtype=torch.float32, device="cuda") for _ in range(world)]
+    xs = [kv4.peer_exchange([b.data_ptr() for b in bufs], rnk) for rnk in range(world)]
+    lays, plans = [], []
+    for rnk in range(world):
+        plan = plan_shards(ctx, world, rnk, okv.max_ctx)
+        lay = kv4.KvLayer(shape.hkv, shape.hd, plan.capacity)
+        a, b = plan.local_rows(0, ctx + 1)
+        if b > a:
+            gpu_append_all(kv4, lay, k[a:b], v[a:b], [b - a], pos0=a - plan.start)
+        lays.append(lay); plans.append(plan)
+    want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    dq = q.cuda()
+    for step in range(3):
+        fused_rank = step % world
+        scratch = [kv4.attn_scratch(1, 9, shape.hq, shape.hd) for _ in range(world)]
+        outs = [torch.full((1, shape.hq, shape.hd), float("nan"), dtype=torch.float16, device="cuda") for _ in range(world)]
+        for rnk in range(world):
+            pm, pl, pacc = scratch[rnk]
+            kv4.launch_attention_shard(dq, lays[rnk], 1, d_pos, 9, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, plans[rnk].start, plans[rnk].capacity)
+            if rnk != fused_rank:
+                kv4.launch_push_triple(pm, pl, pacc, 9, 1, shape.hq, shape.hd, xs[rnk])
+        pm, pl, pacc = scratch[fused_rank]
+        kv4.launch_exchange_merge(pm, pl, pacc, 9, 1, shape.hq, shape.g, shape.hd, xs[fused_rank], outs[fused_rank])
+        for rnk in range(world):
+            if rnk != fused_rank:
+                kv4.launch_merge_pushed(xs[rnk], 1, shape.hq, shape.g, shape.hd, outs[rnk])
+        torch.cuda.synchronize()
+        assert kv4.device_status() == 0
+        for rnk in range(world):
+            assert_close(outs[rnk].float().cpu().numpy(), want, f"step {step} rank {rnk} of {world}")
+        assert torch.equal(outs[fused_rank], outs[(fused_rank + 1) % world])      # same triples, same merge order: same bits
+
+
+def test_fused_exchange_merge_rejects_grids_that_may_not_be_resident():
+    from yasakani_b200 import kv4
+    from yasakani_b200._lib import Kv4Error
+    shape = synth.C2
+    M = 8                                                     # 24 heads x 8 rows = 192 blocks
+    buf = torch.zeros((kv4.exchange_bytes(1, M, shape.hq, shape.hd) + 3) // 4, dtype=torch.float32, device="cuda")
+    x = kv4.peer_exchange([buf.data_ptr()], 0)
+    pm, pl, pacc = kv4.attn_scratch(M, 4, shape.hq, shape.hd)
+    o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+    with pytest.raises(Kv4Error):
+        kv4.launch_exchange_merge(pm, pl, pacc, 4, M, shape.hq, shape.g, shape.hd, x, o16)

@@ -69,6 +69,7 @@ PROTOTYPES = {
                                       C.c_size_t, C.c_int, C.c_void_p]),
     "yskn_kv4_exchange_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "yskn_kv4_push_triple": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.POINTER(PeerExchangeC), C.c_void_p]),
+    "yskn_kv4_exchange_merge": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_int, C.POINTER(PeerExchangeC), C.c_void_p]),
     "yskn_kv4_merge_pushed": (C.c_int, [C.POINTER(PeerExchangeC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_int, C.c_void_p]),
     "yskn_kv4_local_triple": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_void_p, C.c_void_p]),

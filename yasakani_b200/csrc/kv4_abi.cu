@@ -80,6 +80,11 @@ int yskn_kv4_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g,
   return launch_merge_pushed(x, M, nh, g, hd, bv, gate, o16, act_dtype, (cudaStream_t)cuda_stream);
 }
 
+int yskn_kv4_exchange_merge(const yskn_attn_g_combine_args* a, int hd, int act_dtype, const yskn_kv4_peer_exchange* x, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_kv4_exchange_merge: null argument struct");
+  return launch_exchange_merge(*a, hd, act_dtype, x, (cudaStream_t)cuda_stream);
+}
+
 size_t yskn_kv4_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M) {
   if (kvh <= 0 || (hd != 128 && hd != 256) || max_ctx <= 0 || M <= 0) return 0;
   return attention_tc_workspace_bytes(kvh, hd, max_ctx, M);

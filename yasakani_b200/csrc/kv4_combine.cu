@@ -38,15 +38,31 @@ constexpr int CB = 8;                                    // loads in flight per 
 // then one system-scope arrival per block and destination); with TRIPLE_IN, the block first waits (bounded) until every
 // rank's arrivals for this step are complete, and the last block of the grid opens the next step.
 // CQ = split runs per block: 4 when there are many splits to fetch (latency), 1 for short sums (prefill: thousands of rows).
+// Bounded wait (one thread) until every rank's arrival count for this step has reached `want`; 1 = gave up.
+__device__ __forceinline__ int wait_for_triples(const unsigned* flags, int world, unsigned want) {
+  for (int src = 0; src < world; ++src) {
+    unsigned polls = 0, got = 0;
+    for (;;) {                                             // acquire at system scope: the triple stored before the arrival is visible
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flags + src) : "memory");
+      if (got >= want) break;
+      __nanosleep(100);
+      if (++polls > PEER_WAIT_POLLS) { atomicExch(&g_merge_status, 7); return 1; }
+    }
+  }
+  return 0;
+}
+
 template <int HD, int DT, bool TRIPLE_IN, bool TRIPLE_OUT, bool PEER, int CQ>
 __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
+  // TRIPLE_IN && TRIPLE_OUT && PEER = the fused exchange: fold the splits, push the triple, wait for the other ranks' triples, merge.
+  constexpr bool FUSED = TRIPLE_IN && TRIPLE_OUT && PEER, READ_TRIPLES = TRIPLE_IN && !FUSED;
   extern __shared__ float sm[];                          // [S] m, [S] l, [S] w, [CQ][HD] partial sums
   float* s_m = sm; float* s_l = sm + P.S; float* s_w = sm + 2 * P.S; float* s_part = sm + 3 * P.S;
   const int head = blockIdx.x, r = blockIdx.y, tid = threadIdx.x, q = tid / HD, d = tid % HD;
   const int per = (P.S + CQ - 1) / CQ, s0 = min(P.S, q * per), s1 = min(P.S, s0 + per);
-  auto slot = [&](int s) -> size_t { return TRIPLE_IN ? (((size_t)s * P.M + r) * P.nh + head) * (HD + 2)
+  auto slot = [&](int s) -> size_t { return READ_TRIPLES ? (((size_t)s * P.M + r) * P.nh + head) * (HD + 2)
                                                       : ((size_t)r * P.S + s) * P.nh + head; };
-  auto ld_acc = [&](int s) -> float { return TRIPLE_IN ? __ldcg(P.triples + slot(s) + 2 + d) : __ldcg(P.pacc + slot(s) * HD + d); };
+  auto ld_acc = [&](int s) -> float { return READ_TRIPLES ? __ldcg(P.triples + slot(s) + 2 + d) : __ldcg(P.pacc + slot(s) * HD + d); };
   asm volatile("griddepcontrol.wait;" ::: "memory");     // the producer grid's writes are visible from here on
   __shared__ int s_bad;
   int par = 0;                                           // which half of the exchange buffers this step uses
@@ -54,23 +70,8 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   if (PEER) {
     unsigned* mine_flags = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata);
     par = *reinterpret_cast<volatile int*>(mine_flags + 2 * P.x.world) & 1;
-    if (TRIPLE_IN) {
-      if (tid == 0) {
-        int bad = 0;
-        const unsigned want = (unsigned)(P.M * P.nh);
-        for (int src = 0; src < P.x.world && !bad; ++src) {
-          const unsigned* f = mine_flags + par * P.x.world + src;
-          unsigned polls = 0, got = 0;
-          for (;;) {                                           // acquire at system scope: the triple stored before the arrival is visible
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(f) : "memory");
-            if (got >= want) break;
-            __nanosleep(100);
-            if (++polls > PEER_WAIT_POLLS) { bad = 1; break; }
-          }
-        }
-        if (bad) atomicExch(&g_merge_status, 7);
-        s_bad = bad;
-      }
+    if (READ_TRIPLES) {
+      if (tid == 0) s_bad = wait_for_triples(mine_flags + par * P.x.world, P.x.world, (unsigned)(P.M * P.nh));
       __syncthreads();
       if (s_bad) return;
       P.triples = P.x.buf[P.x.rank] + (size_t)par * (xdata / 2);
@@ -81,7 +82,7 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   #pragma unroll
   for (int k = 0; k < CB; ++k) v[k] = s0 + k < s1 ? ld_acc(s0 + k) : 0.f;
   for (int s = tid; s < P.S; s += CQ * HD) {
-    if (TRIPLE_IN) { s_m[s] = __ldcg(P.triples + slot(s)); s_l[s] = __ldcg(P.triples + slot(s) + 1); }
+    if (READ_TRIPLES) { s_m[s] = __ldcg(P.triples + slot(s)); s_l[s] = __ldcg(P.triples + slot(s) + 1); }
     else { s_m[s] = __ldcg(P.pm + slot(s)); s_l[s] = __ldcg(P.pl + slot(s)); }
   }
   __syncthreads();
@@ -125,9 +126,24 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
           atomicAdd_system(reinterpret_cast<unsigned*>(P.x.buf[w] + xdata) + par * P.x.world + P.x.rank, (unsigned)(P.M * P.nh));
       }
     }
-    return;
+    if (!FUSED) return;
+    // ---- fused: every block waits for all ranks' triples (the grid is small enough to be resident as a whole, so the
+    //      blocks that wait cannot keep the publishing block off the GPU), then merges them like yskn_kv4_merge_triples
+    if (d == 0) s_bad = wait_for_triples(reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata) + par * P.x.world, P.x.world, (unsigned)(P.M * P.nh));
+    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");
+    if (s_bad) return;
+    const float* trip = P.x.buf[P.x.rank] + (size_t)par * (xdata / 2);
+    auto tslot = [&](int src) -> size_t { return (((size_t)src * P.M + r) * P.nh + head) * (HD + 2); };
+    float Mw = -1e30f;
+    for (int src = 0; src < P.x.world; ++src) Mw = fmaxf(Mw, __ldcg(trip + tslot(src)));
+    float Lw = 0.f, ow = 0.f;
+    for (int src = 0; src < P.x.world; ++src) {
+      const float ms = __ldcg(trip + tslot(src)), wgt = ms > -1e29f ? expf(ms - Mw) : 0.f;
+      Lw += wgt * __ldcg(trip + tslot(src) + 1); ow += wgt * __ldcg(trip + tslot(src) + 2 + d);
+    }
+    o = ow; L2 = Lw;
   }
-  if (TRIPLE_OUT) {
+  if (TRIPLE_OUT && !FUSED) {
     float* t = P.triple_out + ((size_t)r * P.nh + head) * (HD + 2);
     if (d == 0) { t[0] = M2; t[1] = L2; }
     t[2 + d] = o;
@@ -227,6 +243,16 @@ int launch_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, i
   if (!o16) KV4_REJECT("yskn_kv4_merge_pushed: null output");
   CombineP P{nullptr, nullptr, nullptr, nullptr, x->world, M, nh, g, bv, gate, o16, nullptr, *x};
   return launch_p<true, false, true>(P, hd, act_dtype, st, "yskn_kv4_merge_pushed");
+}
+
+// One launch for the whole exchange: fold this shard's splits, push the triple to every rank, wait for theirs, merge.
+// Every block waits inside the kernel, so the grid must be resident as a whole: nh * M blocks of up to 1,024 threads.
+int launch_exchange_merge(const yskn_attn_g_combine_args& a, int hd, int act_dtype, const yskn_kv4_peer_exchange* x, cudaStream_t st) {
+  if (int rc = check_exchange(x, "yskn_kv4_exchange_merge")) return rc;
+  if (!a.pm || !a.pl || !a.pacc || !a.o16) KV4_REJECT("yskn_kv4_exchange_merge: null buffer");
+  if ((long long)a.nh * a.M > 148) KV4_REJECT("yskn_kv4_exchange_merge: nh * M = %lld blocks may not all be resident; use yskn_kv4_push_triple + yskn_kv4_merge_pushed", (long long)a.nh * a.M);
+  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g > 0 ? a.g : 1, a.bv, a.gate, a.o16, nullptr, *x};
+  return launch_p<true, true, true>(P, hd, act_dtype, st, "yskn_kv4_exchange_merge");
 }
 
 int merge_status_fetch(int* out) {

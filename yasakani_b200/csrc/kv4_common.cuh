@@ -71,6 +71,7 @@ size_t exchange_bytes(int world, int M, int nh, int hd);
 int launch_push_triple(const yskn_attn_g_combine_args& a, int hd, const yskn_kv4_peer_exchange* x, cudaStream_t st);
 int launch_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, int hd, const uint16_t* bv, const uint16_t* gate,
                         uint16_t* o16, int act_dtype, cudaStream_t st);
+int launch_exchange_merge(const yskn_attn_g_combine_args& a, int hd, int act_dtype, const yskn_kv4_peer_exchange* x, cudaStream_t st);
 int merge_status_fetch(int* out);
 
 // Family-B row codec, step 1 (kvx_codec.cu)

@@ -4,11 +4,10 @@
 // CMakeLists.txt:56): kvx_sign (:28-32), kvx_rotate (:35-49), kvx_store (:50-70); the decode direction is the one its
 // probe runs (src/kvx_probe.cu:15-19).  Bit-exact: every operation is one IEEE fp32 operation in the reference's order.
 //
-// Mapping: one warp per row of 256; lane L holds elements 8L .. 8L+7, so a row is read as two 16-byte loads per lane
-// (fp32) or one (fp16/bf16) and written as one 8-byte store per lane.  The butterfly stages run in the reference's
-// order h = 1, 2, ... 128: h = 1, 2, 4 pair registers of one lane, h = 8 ... 128 pair lanes L and L ^ (h / 8) through
-// shuffles.  HBM-bound byte mover (1,284 B per fp32 row in + out, 772 B per fp16 row); the eight exact divisions per
-// lane are the only heavy arithmetic.
+// Mapping: eight lanes per row of 256 (a warp holds four rows); a lane keeps 32 elements in registers, so five of the eight
+// butterfly stages pair registers and only three go through shuffles, and every load/store instruction of a row's lanes
+// covers one contiguous run.  The stages run in the reference's order h = 1, 2, ... 128.  HBM-bound byte mover by design
+// (1,284 B per fp32 row in + out, 772 B per fp16 row).
 #include "kv4_common.cuh"
 
 namespace kv4 {
@@ -27,124 +26,142 @@ constexpr SignTable make_signs() {
   return t;
 }
 __constant__ SignTable c_signs = make_signs();
-// Multiplying by +-1 is a sign-bit flip (exact, also for zeros and infinities): element i of lane L is d = 8L + i.
-__device__ __forceinline__ void apply_signs(float (&v)[8], int lane) {
-  const uint32_t bits = (c_signs.w[lane >> 2] >> (8 * (lane & 3))) & 0xFFu;
+// Element layout of a row over 8 lanes: lane ll (0..7) holds v[4k + e] = element d = 32k + 4ll + e (k 0..7, e 0..3), so every
+// load and store instruction of the 8 lanes covers one contiguous run of the row.  A warp holds 4 rows (lanes 8s .. 8s+7).
+// Multiplying by +-1 is a sign-bit flip (exact, also for zeros and infinities).
+__device__ __forceinline__ void apply_signs(float (&v)[32], int ll) {
   #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(__float_as_uint(v[i]) ^ (((bits >> i) & 1u) << 31));
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t bits = c_signs.w[k] >> (4 * ll);
+    #pragma unroll
+    for (int e = 0; e < 4; ++e) v[4 * k + e] = __uint_as_float(__float_as_uint(v[4 * k + e]) ^ (((bits >> e) & 1u) << 31));
+  }
 }
 
-// Butterflies + 1/16 on the 256 elements a warp holds (v[i] = element 8*lane + i).  Lower index: a + b; upper: lower - upper.
-__device__ __forceinline__ void hadamard256(float (&v)[8], int lane) {
+// Butterflies + 1/16 in the reference's stage order h = 1, 2, ... 128.  Bits 0-1 of d are register bits (e), bits 2-4 the lane
+// within the row (shuffles), bits 5-7 register bits again (k).  Lower index: a + b; upper: lower - upper.
+__device__ __forceinline__ void hadamard256(float (&v)[32], int ll) {
   #pragma unroll
-  for (int h = 1; h < 8; h *= 2) {
+  for (int rb = 1; rb < 4; rb *= 2) {                      // h = 1, 2
     #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (!(i & h)) { const float lo = v[i], up = v[i + h]; v[i] = __fadd_rn(lo, up); v[i + h] = __fsub_rn(lo, up); }
+    for (int i = 0; i < 32; ++i)
+      if (!(i & rb)) { const float lo = v[i], up = v[i + rb]; v[i] = __fadd_rn(lo, up); v[i + rb] = __fsub_rn(lo, up); }
   }
   #pragma unroll
-  for (int m = 1; m < 32; m *= 2) {
-    const uint32_t flip = (lane & m) ? 0x80000000u : 0u;          // upper lane: other - self = other + (-self), exactly
+  for (int m = 1; m < 8; m *= 2) {                         // h = 4, 8, 16
+    const uint32_t flip = (ll & m) ? 0x80000000u : 0u;     // upper lane: other - self = other + (-self), exactly
     #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 32; ++i) {
       const float self = v[i], other = __shfl_xor_sync(0xffffffffu, self, m);
       v[i] = __fadd_rn(other, __uint_as_float(__float_as_uint(self) ^ flip));
     }
   }
   #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], 0.0625f);
+  for (int rb = 4; rb < 32; rb *= 2) {                     // h = 32, 64, 128
+    #pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (!(i & rb)) { const float lo = v[i], up = v[i + rb]; v[i] = __fadd_rn(lo, up); v[i + rb] = __fsub_rn(lo, up); }
+  }
+  #pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(v[i], 0.0625f);
 }
 
-template <int DT> __device__ __forceinline__ void load8(const void* base, size_t row, int lane, float (&v)[8]) {
-  if (DT == YSKN_KV4_F32) {
-    const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + row * 256 + 8 * lane);
-    const float4 a = __ldg(p), b = __ldg(p + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  } else {
-    const uint4 u = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + row * 256 + 8 * lane));
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-    #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      v[2 * k] = DT == YSKN_KV4_F16 ? h2f((uint16_t)w[k]) : bf2f((uint16_t)w[k]);
-      v[2 * k + 1] = DT == YSKN_KV4_F16 ? h2f((uint16_t)(w[k] >> 16)) : bf2f((uint16_t)(w[k] >> 16));
+template <int DT> __device__ __forceinline__ void load_row(const void* base, size_t row, int ll, bool live, float (&v)[32]) {
+  #pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const size_t d = row * 256 + 32 * k + 4 * ll;
+    if (DT == YSKN_KV4_F32) {
+      const float4 a = live ? __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[4 * k] = a.x; v[4 * k + 1] = a.y; v[4 * k + 2] = a.z; v[4 * k + 3] = a.w;
+    } else {
+      const uint2 u = live ? __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(base) + d)) : make_uint2(0u, 0u);
+      v[4 * k] = DT == YSKN_KV4_F16 ? h2f((uint16_t)u.x) : bf2f((uint16_t)u.x); v[4 * k + 1] = DT == YSKN_KV4_F16 ? h2f((uint16_t)(u.x >> 16)) : bf2f((uint16_t)(u.x >> 16));
+      v[4 * k + 2] = DT == YSKN_KV4_F16 ? h2f((uint16_t)u.y) : bf2f((uint16_t)u.y); v[4 * k + 3] = DT == YSKN_KV4_F16 ? h2f((uint16_t)(u.y >> 16)) : bf2f((uint16_t)(u.y >> 16));
     }
   }
 }
-template <int DT> __device__ __forceinline__ void store8(void* base, size_t row, int lane, const float (&v)[8]) {
-  if (DT == YSKN_KV4_F32) {
-    float4* p = reinterpret_cast<float4*>(static_cast<float*>(base) + row * 256 + 8 * lane);
-    p[0] = make_float4(v[0], v[1], v[2], v[3]); p[1] = make_float4(v[4], v[5], v[6], v[7]);
-  } else {
-    uint32_t w[4];
-    #pragma unroll
-    for (int k = 0; k < 4; ++k) w[k] = (uint32_t)act_store16<DT>(v[2 * k]) | ((uint32_t)act_store16<DT>(v[2 * k + 1]) << 16);
-    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + row * 256 + 8 * lane) = make_uint4(w[0], w[1], w[2], w[3]);
+template <int DT> __device__ __forceinline__ void store_row(void* base, size_t row, int ll, const float (&v)[32]) {
+  #pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const size_t d = row * 256 + 32 * k + 4 * ll;
+    if (DT == YSKN_KV4_F32) *reinterpret_cast<float4*>(static_cast<float*>(base) + d) = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+    else *reinterpret_cast<uint2*>(static_cast<uint16_t*>(base) + d) =
+        make_uint2((uint32_t)act_store16<DT>(v[4 * k]) | ((uint32_t)act_store16<DT>(v[4 * k + 1]) << 16),
+                   (uint32_t)act_store16<DT>(v[4 * k + 2]) | ((uint32_t)act_store16<DT>(v[4 * k + 3]) << 16));
   }
 }
 
+constexpr int ROWS_PER_BLOCK = 32;                         // 8 warps x 4 rows
+
 // mode 0: rotate, 1: inverse rotate (fp32 in, fp32 out)
 __global__ void __launch_bounds__(256) kvx_rotate_kernel(const float* x, float* y, long long rows, int inverse) {
-  const int lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  float v[8];
-  load8<YSKN_KV4_F32>(x, (size_t)row, lane, v);
-  if (!inverse) apply_signs(v, lane);
-  hadamard256(v, lane);
-  if (inverse) apply_signs(v, lane);
-  store8<YSKN_KV4_F32>(y, (size_t)row, lane, v);
+  const int lane = threadIdx.x & 31, ll = lane & 7;
+  const long long row = (long long)blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5) * 4 + (lane >> 3);
+  const bool live = row < rows;
+  float v[32];
+  load_row<YSKN_KV4_F32>(x, (size_t)row, ll, live, v);
+  if (!inverse) apply_signs(v, ll);
+  hadamard256(v, ll);
+  if (inverse) apply_signs(v, ll);
+  if (live) store_row<YSKN_KV4_F32>(y, (size_t)row, ll, v);
 }
 
 template <int DT>
 __global__ void __launch_bounds__(256) kvx_encode_kernel(const void* x, int8_t* q8, float* scales, long long rows) {
-  const int lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  float v[8];
-  load8<DT>(x, (size_t)row, lane, v);
-  apply_signs(v, lane);
-  hadamard256(v, lane);
+  const int lane = threadIdx.x & 31, ll = lane & 7;
+  const long long row = (long long)blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5) * 4 + (lane >> 3);
+  const bool live = row < rows;
+  float v[32];
+  load_row<DT>(x, (size_t)row, ll, live, v);
+  apply_signs(v, ll);
+  hadamard256(v, ll);
   float amax = 0.f;
   #pragma unroll
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
   #pragma unroll
-  for (int m = 16; m; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+  for (int m = 4; m; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
   const float sc = __fdiv_rn(amax, 127.f);
-  // q = rne(fl(v / sc)).  v * (1 / sc) is within a few ulp of the exact quotient, so rounding it gives the same integer
-  // unless it lies that close to a half-integer; only those elements (about one in 10^4) take the exact division.
+  // q = rne(fl(v / sc)).  v * (1 / sc) is within 3.8e-5 of the correctly rounded quotient (|q| <= 127), so rounding it gives
+  // the same integer unless it lies that close to a half-integer; only those elements (about one in 10^4) take the exact division.
   const float inv = sc > 0.f ? __fdiv_rn(1.f, sc) : 0.f;
-  uint32_t w[2] = {0u, 0u};
   #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float t = __fmul_rn(v[i], inv);
-    const float frac = fabsf(__fsub_rn(t, truncf(t)));               // exact: |t| < 2^8 here, distance from the integer below in magnitude
-    int q = __float2int_rn(t);
-    if (fabsf(__fsub_rn(frac, 0.5f)) < 6.2e-5f || !(fabsf(t) < 200.f)) q = sc > 0.f ? __float2int_rn(__fdiv_rn(v[i], sc)) : 0;
-    q = max(-127, min(127, q));
-    w[i >> 2] |= (uint32_t)(uint8_t)(int8_t)q << (8 * (i & 3));
+  for (int k = 0; k < 8; ++k) {
+    uint32_t w = 0u;
+    #pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float xv = v[4 * k + e], t = __fmul_rn(xv, inv);
+      int q = __float2int_rn(t);
+      // distance of t from the integer it rounds to; near 0.5 (or NaN: 1/scale overflowed) -> the reference's own arithmetic.
+      // |v| <= max|v| makes |v / scale| <= 127 (1 + 2^-23), so the reference's clamp to +-127 can only act on that path.
+      if (!(fabsf(__fsub_rn(t, (float)q)) <= 0.5f - 6.2e-5f)) q = max(-127, min(127, sc > 0.f ? __float2int_rn(__fdiv_rn(xv, sc)) : 0));
+      w |= ((uint32_t)q & 0xFFu) << (8 * e);
+    }
+    if (live) *reinterpret_cast<uint32_t*>(q8 + (size_t)row * 256 + 32 * k + 4 * ll) = w;
   }
-  *reinterpret_cast<uint2*>(q8 + (size_t)row * 256 + 8 * lane) = make_uint2(w[0], w[1]);
-  if (lane == 0) scales[row] = sc;
+  if (live && ll == 0) scales[row] = sc;
 }
 
 template <int DT>
 __global__ void __launch_bounds__(256) kvx_decode_kernel(const int8_t* q8, const float* scales, void* y, long long rows) {
-  const int lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const uint2 u = __ldg(reinterpret_cast<const uint2*>(q8 + (size_t)row * 256 + 8 * lane));
-  const float sc = __ldg(scales + row);
-  float v[8];
+  const int lane = threadIdx.x & 31, ll = lane & 7;
+  const long long row = (long long)blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5) * 4 + (lane >> 3);
+  const bool live = row < rows;
+  const float sc = live ? __ldg(scales + row) : 0.f;
+  float v[32];
   #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __fmul_rn((float)(int8_t)(uint8_t)((i < 4 ? u.x : u.y) >> (8 * (i & 3))), sc);
-  hadamard256(v, lane);
-  apply_signs(v, lane);
-  store8<DT>(y, (size_t)row, lane, v);
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t u = live ? __ldg(reinterpret_cast<const uint32_t*>(q8 + (size_t)row * 256 + 32 * k + 4 * ll)) : 0u;
+    #pragma unroll
+    for (int e = 0; e < 4; ++e) v[4 * k + e] = __fmul_rn((float)(int8_t)(uint8_t)(u >> (8 * e)), sc);
+  }
+  hadamard256(v, ll);
+  apply_signs(v, ll);
+  if (live) store_row<DT>(y, (size_t)row, ll, v);
 }
 
 int grid_for(long long rows, unsigned* grid, const char* who) {
   if (rows < 0 || rows > (1ll << 34)) { set_error("%s: bad row count %lld", who, rows); return -1; }
-  *grid = (unsigned)((rows + 7) / 8);
+  *grid = (unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK);
   return 0;
 }
 

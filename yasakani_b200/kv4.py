@@ -256,5 +256,12 @@ def launch_merge_pushed(x: PeerExchangeC, M: int, nh: int, g: int, hd: int, o16,
           "yskn_kv4_merge_pushed")
 
 
+def launch_exchange_merge(pm, pl, pacc, splits: int, M: int, nh: int, g: int, hd: int, x: PeerExchangeC, o16, bv=None, gate=None, stream=None) -> None:
+    """Push and merge in one launch (nh * M <= 148): fold, store to all ranks, wait for theirs, merge into o16."""
+    a = AttnGCombineArgsC(pm.data_ptr(), pl.data_ptr(), pacc.data_ptr(), splits, M, bv.data_ptr() if bv is not None else None, o16.data_ptr(),
+                          gate.data_ptr() if gate is not None else None, nh, g)
+    check(_lib.load().yskn_kv4_exchange_merge(C.byref(a), hd, _dtype_code(o16), C.byref(x), _stream(stream)), "yskn_kv4_exchange_merge")
+
+
 def default_qscale(hd: int) -> float:
     return 1.0 / math.sqrt(hd)

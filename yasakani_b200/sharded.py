@@ -9,7 +9,8 @@ rank merges them with the arithmetic of the single-GPU split merge.  The referen
 
 Two forms of the exchange: the NCCL all-gather (`exchange="nccl"`), and direct peer stores (`exchange="p2p"`): the
 kernel that folds a shard's partials writes the triple into every rank's exchange buffer over NVLink and raises an
-arrival counter there; the merge kernel waits for the counters.  The peer buffers are torch symmetric memory (plain
+arrival counter there, waits for the other ranks' counters and merges (one launch; two launches when the grid is too
+large to be resident as a whole).  The peer buffers are torch symmetric memory (plain
 peer mappings; NVLink multicast is switched off) and NCCL is used only to set them up.
 """
 from __future__ import annotations
@@ -115,8 +116,11 @@ class ShardedDecoder:
         if self.exchange == "p2p":
             self.kv4.launch_attention_shard(q16, self.layer, self.M, self.d_pos, self.splits, self.pm, self.pl, self.pacc, self.rope,
                                             s.hq, s.qscale, s.rd, self.plan.start, self.plan.capacity)
-            self.kv4.launch_push_triple(self.pm, self.pl, self.pacc, self.splits, self.M, s.hq, s.hd, self.x)
-            self.kv4.launch_merge_pushed(self.x, self.M, s.hq, s.g, s.hd, self.o16)
+            if s.hq * self.M <= 148:                                 # one launch: fold, push, wait, merge
+                self.kv4.launch_exchange_merge(self.pm, self.pl, self.pacc, self.splits, self.M, s.hq, s.g, s.hd, self.x, self.o16)
+            else:
+                self.kv4.launch_push_triple(self.pm, self.pl, self.pacc, self.splits, self.M, s.hq, s.hd, self.x)
+                self.kv4.launch_merge_pushed(self.x, self.M, s.hq, s.g, s.hd, self.o16)
             return self.o16
         self.local_step(q16)
         gather_triples(self.mine, self.gathered, self.group)
