@@ -60,6 +60,16 @@ struct PrepP {
   uint16_t* kd; uint16_t* vd; uint16_t* ks; int ks_rows; int valid_tokens;
 };
 
+// CPL nibbles (CPL/2 bytes) or CPL fp16 values of one lane in a single load
+template <int CPL> __device__ __forceinline__ uint32_t load_packed(const uint8_t* p) {
+  if (CPL == 8) return __ldg(reinterpret_cast<const uint32_t*>(p));
+  return (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p));
+}
+template <int CPL> __device__ __forceinline__ void load_halves(const uint16_t* p, uint32_t (&o)[CPL / 2]) {
+  if (CPL == 8) { const uint4 u = __ldg(reinterpret_cast<const uint4*>(p)); o[0] = u.x; o[1] = u.y; o[CPL / 2 - 2] = u.z; o[CPL / 2 - 1] = u.w; }
+  else { const uint2 u = __ldg(reinterpret_cast<const uint2*>(p)); o[0] = u.x; o[CPL / 2 - 1] = u.y; }
+}
+
 // One warp per (token t, kv-head); lane owns HD/32 contiguous channels.
 template <int HD>
 __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
@@ -93,9 +103,9 @@ __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
     float v[CPL];
     if (t < end) {
       const float vs = h2f(P.kv.vscale[row]), vz = h2f(P.kv.vzero[row]);
-      const uint8_t* vb = P.kv.vq + row * (HD / 2) + c0 / 2;
+      const uint32_t vw = load_packed<CPL>(P.kv.vq + row * (HD / 2) + c0 / 2);      // this lane's CPL nibbles in one load
       #pragma unroll
-      for (int e = 0; e < CPL; e += 2) { const uint8_t b = vb[e / 2]; v[e] = (float)(b & 15) * vs + vz; v[e + 1] = (float)(b >> 4) * vs + vz; }
+      for (int e = 0; e < CPL; e += 2) { const uint32_t b = (vw >> (4 * e)) & 0xFFu; v[e] = (float)(b & 15) * vs + vz; v[e + 1] = (float)(b >> 4) * vs + vz; }
     } else {
       #pragma unroll
       for (int e = 0; e < CPL; ++e) v[e] = 0.f;
@@ -106,13 +116,14 @@ __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
   const int gi = t / 32;
   if (gi * 32 + 31 < end && t >= (P.valid_tokens / 32) * 32) {       // a group completed since the last pass is (re)written whole
     const size_t gb = (size_t)head * (P.max_ctx / 32) + gi;
-    const uint8_t* kb = P.kv.kq + (gb * 32 + (t & 31)) * (HD / 2) + c0 / 2;
+    const uint32_t kw = load_packed<CPL>(P.kv.kq + (gb * 32 + (t & 31)) * (HD / 2) + c0 / 2);
+    uint32_t sw[CPL / 2], zw[CPL / 2];                                 // this lane's CPL scales and zeros in one load each
+    load_halves<CPL>(P.kv.kscale + gb * HD + c0, sw); load_halves<CPL>(P.kv.kzero + gb * HD + c0, zw);
     float k[CPL];
     #pragma unroll
     for (int e = 0; e < CPL; e += 2) {
-      const uint8_t b = kb[e / 2];
-      const uint32_t s2 = *reinterpret_cast<const uint32_t*>(P.kv.kscale + gb * HD + c0 + e);
-      const uint32_t z2 = *reinterpret_cast<const uint32_t*>(P.kv.kzero + gb * HD + c0 + e);
+      const uint32_t b = (kw >> (4 * e)) & 0xFFu;
+      const uint32_t s2 = sw[e / 2], z2 = zw[e / 2];
       k[e] = __fadd_rn(__fmul_rn((float)(b & 15), h2f((uint16_t)s2)), h2f((uint16_t)z2));
       k[e + 1] = __fadd_rn(__fmul_rn((float)(b >> 4), h2f((uint16_t)(s2 >> 16))), h2f((uint16_t)(z2 >> 16)));
     }
