@@ -105,3 +105,50 @@ def test_rotate_int8_row_codec_equals_the_reference_probe_bit_for_bit(oracle):
     assert np.array_equal(y.view(np.uint32), oracle.kvx_decode(oq, osc).view(np.uint32))
     gq, gsc, gy = kvx.probe(x)
     assert np.array_equal(gq, q) and np.array_equal(gsc.view(np.uint32), sc.view(np.uint32)) and np.array_equal(gy.view(np.uint32), y.view(np.uint32))
+
+
+@pytest.mark.parametrize("ctx,M", [(3000, 1), (700, 3)])
+def test_int8_row_decode_agrees_with_the_reference_kernel_and_the_oracle(oracle, ctx, M):
+    """Family-B decode over INT8 rows: the reference's q35_attention_kernel<KV8> (src/q35_kernels.cu:1176-1281, compiled
+    from its source into oracle/_ref/libyskn_ref_q35.so) against the exact oracle and against this library's kernel,
+    each merged by yskn_kv8_combine without the rotation."""
+    from yasakani_b200 import kvx
+    path = os.path.join(os.path.dirname(REF), "libyskn_ref_q35.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref not built (reference tree was not mounted at build time)")
+    ref = C.CDLL(path)
+    nh, kvh, hd = C.c_int(), C.c_int(), C.c_int()
+    ref.yref_q35_shape(C.byref(nh), C.byref(kvh), C.byref(hd))
+    nh, kvh = nh.value, kvh.value
+    assert hd.value == 256
+    rng = np.random.default_rng(ctx)
+    n = ctx + M
+    max_ctx = ((n + 63) // 64) * 64
+    k8 = np.zeros((kvh, max_ctx, 256), np.int8); v8 = np.zeros_like(k8)
+    ks = np.zeros((kvh, max_ctx), np.float32); vs = np.zeros_like(ks)
+    for h in range(kvh):
+        k8[h, :n], ks[h, :n] = oracle.kvx_encode(rng.standard_normal((n, 256)).astype(np.float32) * 1.5)
+        v8[h, :n], vs[h, :n] = oracle.kvx_encode(rng.standard_normal((n, 256)).astype(np.float32))
+    q = torch.from_numpy(oracle.kvx_rotate(rng.standard_normal((M * nh, 256)).astype(np.float32)).reshape(M, nh, 256)).to(torch.bfloat16).cuda()
+    d = [torch.from_numpy(a).cuda() for a in (k8, v8, ks, vs)]
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    S = 32
+    want = oracle.kv8_attention_exact(q.float().cpu().numpy(), k8, v8, ks, vs, ctx)
+
+    def merged(pm, pl, pacc):
+        o = torch.empty((M, nh, 256), dtype=torch.float16, device="cuda")
+        kvx.launch_kv8_combine(pm, pl, pacc, S, M, nh, o, inverse_rotate=False)
+        torch.cuda.synchronize()
+        return o.float().cpu().numpy()
+
+    pm = torch.empty((M, S, nh), device="cuda"); pl = torch.empty_like(pm); pacc = torch.empty((M, S, nh, 256), device="cuda")
+    p = lambda t: C.c_void_p(t.data_ptr())
+    assert ref.yref_q35_attention_kv8(p(q), p(d[0]), p(d[1]), p(d[2]), p(d[3]), max_ctx, M, p(d_pos), S, p(pm), p(pl), p(pacc), None) == 0
+    torch.cuda.synchronize()
+    theirs = merged(pm, pl, pacc)
+    assert_close(theirs, want, "reference INT8-row kernel vs exact oracle")
+    pm2 = torch.empty_like(pm); pl2 = torch.empty_like(pl); pacc2 = torch.empty_like(pacc)
+    kvx.launch_kv8_attention(q, *d, M, d_pos, S, pm2, pl2, pacc2, nh)
+    ours = merged(pm2, pl2, pacc2)
+    assert_close(ours, want, "this library's INT8-row kernel vs exact oracle")
+    assert_close(ours, theirs, "this library's INT8-row kernel vs the reference kernel")
