@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
+#include <atomic>
 #include <cstdint>
 #include <cstdio>
 #include "../../include/yskn_kv4_abi.h"
@@ -22,6 +23,16 @@ inline int launch_status(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("%s: %s", what, cudaGetErrorString(e)); return (int)e; }
   return 0;
+}
+
+// Function attributes are per device: true the first time a launcher runs on the current device (flags = one word per
+// launcher, bit d = done on device d).  The reference sets them once per process (src/q35_fa.cu:305-307) because an engine
+// owns one GPU; a process that drives several GPUs through this library gets them on each.
+inline bool first_use_on_device(std::atomic<unsigned long long>& flags) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+  const unsigned long long bit = 1ull << dev;
+  return (flags.fetch_or(bit) & bit) == 0;
 }
 
 // ---- device scalar helpers ----

@@ -603,11 +603,10 @@ template <int HD, int RD, int DT>
 int launch_t(const yskn_attn_g_args& a, int g, Shard sh, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mr, cudaStream_t st) {
   using L = Lay<HD, RD>;
   auto kern = kv4_decode_mma_kernel<HD, RD, DT>;
-  static bool attr = false;                                     // one-time, like the reference's launchers (src/q35_fa.cu:305-307)
-  if (!attr) {
+  static std::atomic<unsigned long long> attr{0};               // once per device, like the reference's launchers once per process
+  if (first_use_on_device(attr)) {
     KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-    attr = true;
   }
   DecodeP P{a, sh, g};
   kern<<<dim3(a.splits, a.kvh, a.M), NTHREADS, L::TOTAL, st>>>(mk, mv, mr, P);

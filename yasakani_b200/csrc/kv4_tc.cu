@@ -635,8 +635,8 @@ int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int va
       !tc_map_rows(&mvd, w.vd, rows, HD, TC_BN, L::KBLK / 2) || !tc_map_rows(&mks, w.ks, (uint64_t)a.kvh * w.ks_rows, HD, TC_BN / 2, L::KBLK))
     KV4_REJECT("yskn_kv4_attention_tc: cuTensorMapEncodeTiled failed or is unavailable");
   auto kern = kv4_tc_attn_kernel<HD>;
-  static bool attr = false;
-  if (!attr) { KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL)); attr = true; }
+  static std::atomic<unsigned long long> attr{0};
+  if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;        // CTA pairs: an even number of query tiles
   TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv};
   kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mq, mkd, mvd, mks, P);

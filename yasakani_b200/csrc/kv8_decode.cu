@@ -251,12 +251,12 @@ int launch_kv8_attention(const yskn_kv8_attn_args& a, int act_dtype, cudaStream_
   Kv8P P{a, a.nh / a.kvh};
   const dim3 grid(a.splits, a.kvh, a.M);
   if (act_dtype == YSKN_KV4_BF16) {
-    static bool attr = false;
-    if (!attr) { KV4_CUDA(cudaFuncSetAttribute(kv8_decode_kernel<YSKN_KV4_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr = true; }
+    static std::atomic<unsigned long long> attr{0};
+    if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(kv8_decode_kernel<YSKN_KV4_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kv8_decode_kernel<YSKN_KV4_BF16><<<grid, KV8_WARPS * 32, smem, st>>>(P);
   } else if (act_dtype == YSKN_KV4_F16) {
-    static bool attr = false;
-    if (!attr) { KV4_CUDA(cudaFuncSetAttribute(kv8_decode_kernel<YSKN_KV4_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr = true; }
+    static std::atomic<unsigned long long> attr{0};
+    if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(kv8_decode_kernel<YSKN_KV4_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kv8_decode_kernel<YSKN_KV4_F16><<<grid, KV8_WARPS * 32, smem, st>>>(P);
   } else KV4_REJECT("yskn_kv8_attention: q16 is bf16 or fp16 (act_dtype %d)", act_dtype);
   return launch_status("kv8_decode_kernel");
