@@ -63,6 +63,7 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   auto slot = [&](int s) -> size_t { return READ_TRIPLES ? (((size_t)s * P.M + r) * P.nh + head) * (HD + 2)
                                                       : ((size_t)r * P.S + s) * P.nh + head; };
   auto ld_acc = [&](int s) -> float { return READ_TRIPLES ? __ldcg(P.triples + slot(s) + 2 + d) : __ldcg(P.pacc + slot(s) * HD + d); };
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next step's attention grid may be scheduled; it waits for this one
   asm volatile("griddepcontrol.wait;" ::: "memory");     // the producer grid's writes are visible from here on
   __shared__ int s_bad;
   int par = 0;                                           // which half of the exchange buffers this step uses

@@ -190,8 +190,11 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
   const int G = P.g;
-  // Let a dependent launch (the merge kernel, launched with programmatic stream serialization) be scheduled early; it
-  // still waits for this grid to finish before it reads the partials (src/pdl.cuh:15-21 is the reference's form of this).
+  // Programmatic dependent launch in both directions (src/pdl.cuh:15-30 is the reference's form of this): this grid may be
+  // scheduled while the previous kernel of the stream drains and waits here before it reads anything that kernel wrote
+  // (position, query, appended rows); the merge kernel that follows may be scheduled early in turn and waits for this grid
+  // to finish before it reads the partials.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ---- which groups this CTA owns (local token indices of this shard)
@@ -609,7 +612,12 @@ int launch_t(const yskn_attn_g_args& a, int g, Shard sh, const CUtensorMap& mk, 
     KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
   }
   DecodeP P{a, sh, g};
-  kern<<<dim3(a.splits, a.kvh, a.M), NTHREADS, L::TOTAL, st>>>(mk, mv, mr, P);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(a.splits, a.kvh, a.M); cfg.blockDim = dim3(NTHREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  KV4_CUDA(cudaLaunchKernelEx(&cfg, kern, mk, mv, mr, P));
   return launch_status("kv4_decode_mma_kernel");
 }
 
