@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(256) kv8_combine_kernel(const float* pm, const
 
 int launch_kv8_attention(const yskn_kv8_attn_args& a, int act_dtype, cudaStream_t st) {
   if (!a.q16 || !a.k8 || !a.v8 || !a.ks || !a.vs || !a.d_pos || !a.pm || !a.pl || !a.pacc) KV4_REJECT("yskn_kv8_attention: null buffer");
-  if (a.kvh <= 0 || a.nh <= 0 || a.nh % a.kvh || a.nh / a.kvh > 8 || a.M <= 0 || a.splits <= 0 || a.splits > 65535 || a.max_ctx <= 0 || a.max_ctx % 64)
+  if (a.kvh <= 0 || a.nh <= 0 || a.nh % a.kvh || a.nh / a.kvh > 8 || a.M <= 0 || a.M > 65535 || a.kvh > 65535 || a.splits <= 0 || a.max_ctx <= 0 || a.max_ctx % 64)
     KV4_REJECT("yskn_kv8_attention: bad shape (kvh %d, nh %d, M %d, splits %d, max_ctx %d): at most 8 query heads per kv-head, max_ctx a multiple of 64",
                a.kvh, a.nh, a.M, a.splits, a.max_ctx);
   if (((uintptr_t)a.k8 | (uintptr_t)a.v8) & 15) KV4_REJECT("yskn_kv8_attention: k8 and v8 must be 16-byte aligned");
