@@ -65,6 +65,11 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def wait_started(self, timeout_s: float = 1.5):
+        t0 = time.time()
+        while self.proc is not None and not self.rows and time.time() - t0 < timeout_s:
+            time.sleep(0.01)
+
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([x.strip() for x in line.split(",")])
@@ -253,8 +258,13 @@ def run_ours(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     with sampler:
         # ---- value: inputs resident in HBM, whole step (attention + merge [+ exchange])
+        sampler.wait_started()                                     # nvidia-smi takes ~0.1 s to deliver its first sample
         timed(lambda i: run_steps(W), 1)
-        ms_total = timed(lambda i: run_steps(K), 1)
+        # exactly K steps per measurement; short runs are measured several times (median reported, the same number of times
+        # on every rank) so that the clock samples, 20 ms apart, fall inside timed regions
+        probe = timed(lambda i: run_steps(K), 1)
+        reps = int(min(7, max(1, math.ceil(150.0 / max(probe, 1e-3))))) | 1
+        ms_total = float(np.median([probe] + [timed(lambda i: run_steps(K), 1) for _ in range(reps - 1)]))
         # ---- roofline: the decode-attention kernel alone, same stream, same copies
         def attn_only(i):
             d = decs[i % n_copies]

@@ -127,7 +127,8 @@ YSKN_KV4_API int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int 
  * (src/attention_kv4q.cu:198-323, src/args.hpp:37-40), whose caller-owned KvF32 arrays become one caller-owned fp16
  * workspace of yskn_kv4_tc_workspace_bytes(kvh, hd, max_ctx, M) bytes (16-byte aligned).  Each call first brings the
  * workspace up to date for tokens [valid_tokens, *d_pos + M): pass 0 unless the same workspace already holds the
- * dequantised tokens [0, valid_tokens) of this cache from an earlier call.  q16 must be fp16.  Semantics, partial
+ * dequantised tokens [0, valid_tokens) of this cache from an earlier call (valid_tokens <= *d_pos; nothing below the
+ * 128-token tile of valid_tokens is touched).  q16 must be fp16.  Semantics, partial
  * layout and `splits` are those of yskn_kv4_attention; yskn_kv4_prefill_tc also merges to o16 (+ optional bias). */
 YSKN_KV4_API size_t yskn_kv4_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M);
 YSKN_KV4_API int yskn_kv4_attention_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, void* d_workspace,

@@ -58,6 +58,7 @@ constexpr int TC_BN = 128;                                 // keys per tile of t
 struct PrepP {
   yskn_kv_layer kv; const int* d_pos; int M; int max_ctx; int kvh; const float* rope; int rd;
   uint16_t* kd; uint16_t* vd; uint16_t* ks; int ks_rows; int valid_tokens;
+  int t_begin;                                             // first token the grid covers: nothing below it needs (re)writing
 };
 
 // CPL nibbles (CPL/2 bytes) or CPL fp16 values of one lane in a single load
@@ -76,7 +77,7 @@ __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
   constexpr int CPL = HD / 32;
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int t = (int)(w / P.kvh), head = (int)(w % P.kvh);
+  const int t = P.t_begin + (int)(w / P.kvh), head = (int)(w % P.kvh);
   const int pos0 = *P.d_pos, end = pos0 + P.M;                      // tokens [0, end) exist
   const int end_tile = min(P.max_ctx, (end + TC_BN - 1) / TC_BN * TC_BN);   // tiles read whole rows of keys: keep V finite there
   if (t >= end_tile) return;
@@ -625,8 +626,12 @@ TcWs carve(void* ws, int kvh, int hd, int max_ctx, int M) {
 template <int HD>
 int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int valid_tokens, uint16_t* o16, const uint16_t* bv, cudaStream_t st) {
   using L = TcLay<HD>;
-  PrepP pp{a.kv, a.d_pos, a.M, a.max_ctx, a.kvh, a.rope, rd, w.kd, w.vd, w.ks, w.ks_rows, valid_tokens};
-  const long long warps = (long long)a.max_ctx * a.kvh;
+  // Tokens below valid_tokens are in the workspace already (the caller guarantees valid_tokens <= *d_pos); the group that
+  // holds valid_tokens may have been completed since, and the shadow rows start at the 128-token tile of *d_pos.
+  const int t_begin = (valid_tokens / TC_BN) * TC_BN;
+  PrepP pp{a.kv, a.d_pos, a.M, a.max_ctx, a.kvh, a.rope, rd, w.kd, w.vd, w.ks, w.ks_rows, valid_tokens, t_begin};
+  const long long warps = (long long)(a.max_ctx - t_begin) * a.kvh;
+  if (warps <= 0) KV4_REJECT("yskn_kv4_attention_tc: valid_tokens %d is beyond max_ctx %d", valid_tokens, a.max_ctx);
   kv4_tc_prep_kernel<HD><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(pp);
   if (int rc = launch_status("kv4_tc_prep_kernel")) return rc;
   CUtensorMap mq, mkd, mvd, mks;
