@@ -197,8 +197,15 @@ def run_ours(args, rank, world, local_rank):
         decs.append(d)
     for d in decs:
         d.d_pos.fill_(ctx - 1)                                      # the query is the last cached token: ctx keys visible
-    q_host = synth.make_q(shape, 1, synth.seed_for(CONFIG_INDEX)).pin_memory()
-    q_dev = q_host.to(dev)
+    # one staging buffer per side for a step's inputs: the query row and the new token's K and V rows, so that the
+    # end-to-end step moves them with a single host-to-device copy
+    nq, nkv = shape.hq * shape.hd, shape.hkv * shape.hd
+    in_host = torch.empty(nq + 2 * nkv, dtype=torch.float16).pin_memory()
+    in_dev = torch.empty(nq + 2 * nkv, dtype=torch.float16, device=dev)
+    q_host = in_host[:nq].view(1, shape.hq, shape.hd)
+    q_host.copy_(synth.make_q(shape, 1, synth.seed_for(CONFIG_INDEX)))
+    q_dev = in_dev[:nq].view(1, shape.hq, shape.hd)
+    q_dev.copy_(q_host)
     o_host = torch.empty((1, shape.hq, shape.hd), dtype=torch.float16).pin_memory()
 
     def step(d):
@@ -274,15 +281,16 @@ def run_ours(args, rank, world, local_rank):
         ms_attn = timed(attn_only, K)
         # ---- e2e: host buffers in, host buffer out, every step (q, and the new token's k/v on the owning rank)
         k_new, v_new = chunk_rows(shape, (ctx - 1) // CHUNK)
-        kn_host = k_new[(ctx - 1) % CHUNK:(ctx - 1) % CHUNK + 1].contiguous().pin_memory()
-        vn_host = v_new[(ctx - 1) % CHUNK:(ctx - 1) % CHUNK + 1].contiguous().pin_memory()
-        kn_dev, vn_dev = kn_host.to(dev), vn_host.to(dev)
+        kn_host = in_host[nq:nq + nkv].view(1, shape.hkv, shape.hd); vn_host = in_host[nq + nkv:].view(1, shape.hkv, shape.hd)
+        kn_host.copy_(k_new[(ctx - 1) % CHUNK:(ctx - 1) % CHUNK + 1]); vn_host.copy_(v_new[(ctx - 1) % CHUNK:(ctx - 1) % CHUNK + 1])
+        kn_dev = in_dev[nq:nq + nkv].view(1, shape.hkv, shape.hd); vn_dev = in_dev[nq + nkv:].view(1, shape.hkv, shape.hd)
+        for d in decs:                                             # the new token's local position: constant over the run
+            d.d_lpos.fill_(ctx - 1 - plan.start)
 
         def e2e_body(d):                                           # host buffers in, the step, host buffer out
-            q_dev.copy_(q_host, non_blocking=True)
+            in_dev.copy_(in_host, non_blocking=True)
             if plan.is_last:
-                kn_dev.copy_(kn_host, non_blocking=True); vn_dev.copy_(vn_host, non_blocking=True)
-                d.append(kn_dev, vn_dev, ctx - 1)
+                kv4.launch_kv_append(d.layer, kn_dev, vn_dev, d.d_lpos, 1)
             step(d)
             if rank == 0:
                 o_host.copy_(d.o16, non_blocking=True)
