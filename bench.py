@@ -427,7 +427,7 @@ def run_secondary(args):
     if args.workload == "prefill":
         tc_case(0, 8192, 1, "C5 causal prefill: 8192 rows from an empty cache, Hq24/Hkv4/hd256")
     elif args.workload == "verify":
-        for M, S in ((64, 12), (32, 18), (16, 37)):
+        for M, S in ((64, 9), (32, 18), (16, 18)):                 # splits: one wave of CTA pairs (74) over 4 kv-heads
             tc_case(32768, M, S, f"C3 verify: {M} rows against 32768 cached tokens, Hq24/Hkv4/hd256")
     elif args.workload == "kv8":
         kvh, nh, S = shape.hkv, shape.hq, args.splits

@@ -37,7 +37,8 @@ constexpr int CB = 8;                                    // loads in flight per 
 // PEER: with TRIPLE_OUT, the triple goes into every rank's exchange buffer (plain stores through NVLink peer mappings,
 // then one system-scope arrival per block and destination); with TRIPLE_IN, the block first waits (bounded) until every
 // rank's arrivals for this step are complete, and the last block of the grid opens the next step.
-// CQ = split runs per block: 4 when there are many splits to fetch (latency), 1 for short sums (prefill: thousands of rows).
+// CQ = split runs per block: 4 when there are many splits to fetch and few blocks (decode: latency), 2 when the grid of
+// 1,024-thread blocks would not fit the GPU at once (verify: hundreds of rows x heads), 1 for short sums (prefill).
 // Bounded wait (one thread) until every rank's arrival count for this step has reached `want`; 1 = gave up.
 __device__ __forceinline__ int wait_for_triples(const unsigned* flags, int world, unsigned want) {
   for (int src = 0; src < world; ++src) {
@@ -104,6 +105,7 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   __syncthreads();
   if (q != 0) return;
   if (CQ == 4) o = (s_part[d] + s_part[HD + d]) + (s_part[2 * HD + d] + s_part[3 * HD + d]);
+  if (CQ == 2) o = s_part[d] + s_part[HD + d];
   float L2 = 0.f;
   for (int s = 0; s < P.S; ++s) L2 += s_w[s] * s_l[s];
   if (TRIPLE_OUT && PEER) {
@@ -173,13 +175,15 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
 
 template <int HD, int DT, bool TI, bool TO, bool PEER>
 int launch_k(const CombineP& P, size_t smem, cudaStream_t st) {
-  const int CQ = P.S >= 8 ? 4 : 1;
+  const long long blocks = (long long)P.nh * P.M;
+  const int CQ = P.S < 8 ? 1 : (blocks <= 296 ? 4 : 2);          // 296 = two 1,024-thread blocks on each of 148 SMs
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(P.nh, P.M); cfg.blockDim = dim3(CQ * HD); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
   if (CQ == 4) KV4_CUDA(cudaLaunchKernelEx(&cfg, kv4_combine_kernel<HD, DT, TI, TO, PEER, 4>, P));
+  else if (CQ == 2) KV4_CUDA(cudaLaunchKernelEx(&cfg, kv4_combine_kernel<HD, DT, TI, TO, PEER, 2>, P));
   else KV4_CUDA(cudaLaunchKernelEx(&cfg, kv4_combine_kernel<HD, DT, TI, TO, PEER, 1>, P));
   return 0;
 }

@@ -61,6 +61,12 @@ struct PrepP {
   int t_begin;                                             // first token the grid covers: nothing below it needs (re)writing
 };
 
+// Nibble e of a packed word as an exact float: the nibble placed in the low mantissa bits of 2^23 reads as 8388608 + n.
+__device__ __forceinline__ float nib_f32(uint32_t w, int e) {
+  return __fsub_rn(__uint_as_float(((w >> (4 * e)) & 15u) | 0x4B000000u), 8388608.f);
+}
+__device__ __forceinline__ uint32_t tc_pack(float lo, float hi);
+
 // CPL nibbles (CPL/2 bytes) or CPL fp16 values of one lane in a single load
 template <int CPL> __device__ __forceinline__ uint32_t load_packed(const uint8_t* p) {
   if (CPL == 8) return __ldg(reinterpret_cast<const uint32_t*>(p));
@@ -76,26 +82,34 @@ template <int HD>
 __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
   constexpr int CPL = HD / 32;
   const int lane = threadIdx.x & 31;
-  const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int t = P.t_begin + (int)(w / P.kvh), head = (int)(w % P.kvh);
+  const int t = P.t_begin + (int)blockIdx.x * 4 + (int)(threadIdx.x >> 5), head = blockIdx.y;   // grid (tokens / 4, kv-heads)
   const int pos0 = *P.d_pos, end = pos0 + P.M;                      // tokens [0, end) exist
   const int end_tile = min(P.max_ctx, (end + TC_BN - 1) / TC_BN * TC_BN);   // tiles read whole rows of keys: keep V finite there
   if (t >= end_tile) return;
   const int c0 = lane * CPL, half = P.rd / 2, lanes_off = half > 0 ? half / CPL : 1;
   const bool rot = c0 < P.rd, lower = c0 < half;
   const size_t row = (size_t)head * P.max_ctx + t;
-  auto store = [&](uint16_t* dst, const float (&v)[CPL]) {
+  auto store = [&](uint16_t* dst, const float (&v)[CPL]) {        // one 16-byte (hd 256) or 8-byte (hd 128) store per lane
+    uint32_t w2[CPL / 2];
     #pragma unroll
-    for (int e = 0; e < CPL; e += 2) *reinterpret_cast<uint32_t*>(dst + e) = (uint32_t)f2h(v[e]) | ((uint32_t)f2h(v[e + 1]) << 16);
+    for (int e = 0; e < CPL; e += 2) w2[e / 2] = tc_pack(v[e], v[e + 1]);      // one conversion per pair
+    if (CPL == 8) *reinterpret_cast<uint4*>(dst) = make_uint4(w2[0], w2[1], w2[CPL / 2 - 2], w2[CPL / 2 - 1]);
+    else *reinterpret_cast<uint2*>(dst) = make_uint2(w2[0], w2[CPL / 2 - 1]);
   };
   auto rotate = [&](float (&k)[CPL]) {
     if (P.rd <= 0) return;
+    float4 cs2[CPL / 2];                                             // (cos, sin) of this lane's CPL frequencies: consecutive table entries
+    if (rot) {
+      const float4* rp = reinterpret_cast<const float4*>(P.rope + ((size_t)t * half + (c0 % half)) * 2);
+      #pragma unroll
+      for (int e = 0; e < CPL / 2; ++e) cs2[e] = __ldg(rp + e);
+    }
     #pragma unroll
     for (int e = 0; e < CPL; ++e) {
       const float other = __shfl_xor_sync(0xffffffffu, k[e], lanes_off);
       if (rot) {
-        const float2 cs = *reinterpret_cast<const float2*>(P.rope + ((size_t)t * half + ((c0 + e) % half)) * 2);
-        k[e] = lower ? (k[e] * cs.x - other * cs.y) : (other * cs.y + k[e] * cs.x);
+        const float cx = (e & 1) ? cs2[e / 2].z : cs2[e / 2].x, sy = (e & 1) ? cs2[e / 2].w : cs2[e / 2].y;
+        k[e] = lower ? (k[e] * cx - other * sy) : (other * sy + k[e] * cx);
       }
     }
   };
@@ -106,7 +120,7 @@ __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
       const float vs = h2f(P.kv.vscale[row]), vz = h2f(P.kv.vzero[row]);
       const uint32_t vw = load_packed<CPL>(P.kv.vq + row * (HD / 2) + c0 / 2);      // this lane's CPL nibbles in one load
       #pragma unroll
-      for (int e = 0; e < CPL; e += 2) { const uint32_t b = (vw >> (4 * e)) & 0xFFu; v[e] = (float)(b & 15) * vs + vz; v[e + 1] = (float)(b >> 4) * vs + vz; }
+      for (int e = 0; e < CPL; e += 2) { v[e] = nib_f32(vw, e) * vs + vz; v[e + 1] = nib_f32(vw, e + 1) * vs + vz; }
     } else {
       #pragma unroll
       for (int e = 0; e < CPL; ++e) v[e] = 0.f;
@@ -123,10 +137,9 @@ __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
     float k[CPL];
     #pragma unroll
     for (int e = 0; e < CPL; e += 2) {
-      const uint32_t b = (kw >> (4 * e)) & 0xFFu;
       const uint32_t s2 = sw[e / 2], z2 = zw[e / 2];
-      k[e] = __fadd_rn(__fmul_rn((float)(b & 15), h2f((uint16_t)s2)), h2f((uint16_t)z2));
-      k[e + 1] = __fadd_rn(__fmul_rn((float)(b >> 4), h2f((uint16_t)(s2 >> 16))), h2f((uint16_t)(z2 >> 16)));
+      k[e] = __fadd_rn(__fmul_rn(nib_f32(kw, e), h2f((uint16_t)s2)), h2f((uint16_t)z2));
+      k[e + 1] = __fadd_rn(__fmul_rn(nib_f32(kw, e + 1), h2f((uint16_t)(s2 >> 16))), h2f((uint16_t)(z2 >> 16)));
     }
     rotate(k);
     store(P.kd + row * HD + c0, k);
@@ -136,9 +149,10 @@ __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
   if (t >= ks0 && t - ks0 < P.ks_rows) {
     float k[CPL];
     if (t < end) {
-      const uint16_t* sh = P.kv.kshadow + row * HD + c0;
+      uint32_t sw2[CPL / 2];
+      load_halves<CPL>(P.kv.kshadow + row * HD + c0, sw2);
       #pragma unroll
-      for (int e = 0; e < CPL; e += 2) { const uint32_t u = *reinterpret_cast<const uint32_t*>(sh + e); k[e] = h2f((uint16_t)u); k[e + 1] = h2f((uint16_t)(u >> 16)); }
+      for (int e = 0; e < CPL; e += 2) { const uint32_t u = sw2[e / 2]; k[e] = h2f((uint16_t)u); k[e + 1] = h2f((uint16_t)(u >> 16)); }
       rotate(k);
     } else {
       #pragma unroll
@@ -630,9 +644,9 @@ int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int va
   // holds valid_tokens may have been completed since, and the shadow rows start at the 128-token tile of *d_pos.
   const int t_begin = (valid_tokens / TC_BN) * TC_BN;
   PrepP pp{a.kv, a.d_pos, a.M, a.max_ctx, a.kvh, a.rope, rd, w.kd, w.vd, w.ks, w.ks_rows, valid_tokens, t_begin};
-  const long long warps = (long long)(a.max_ctx - t_begin) * a.kvh;
-  if (warps <= 0) KV4_REJECT("yskn_kv4_attention_tc: valid_tokens %d is beyond max_ctx %d", valid_tokens, a.max_ctx);
-  kv4_tc_prep_kernel<HD><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(pp);
+  const int span = a.max_ctx - t_begin;
+  if (span <= 0) KV4_REJECT("yskn_kv4_attention_tc: valid_tokens %d is beyond max_ctx %d", valid_tokens, a.max_ctx);
+  kv4_tc_prep_kernel<HD><<<dim3((unsigned)((span + 3) / 4), (unsigned)a.kvh), 128, 0, st>>>(pp);
   if (int rc = launch_status("kv4_tc_prep_kernel")) return rc;
   CUtensorMap mq, mkd, mvd, mks;
   const uint64_t rows = (uint64_t)a.kvh * a.max_ctx;
