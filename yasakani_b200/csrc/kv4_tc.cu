@@ -98,20 +98,20 @@ __global__ void __launch_bounds__(128) kv4_tc_prep_kernel(PrepP P) {
   };
   auto rotate = [&](float (&k)[CPL]) {
     if (P.rd <= 0) return;
-    float4 cs2[CPL / 2];                                             // (cos, sin) of this lane's CPL frequencies: consecutive table entries
-    if (rot) {
-      const float4* rp = reinterpret_cast<const float4*>(P.rope + ((size_t)t * half + (c0 % half)) * 2);
-      #pragma unroll
-      for (int e = 0; e < CPL / 2; ++e) cs2[e] = __ldg(rp + e);
-    }
+    // (cos, sin) of this lane's CPL frequencies: consecutive table entries (rd / 2 is a power of two).  Lanes outside the
+    // rotary width read entry 0 and keep their values by a select, so the loop has no divergent branches.
+    const float4* rp = reinterpret_cast<const float4*>(P.rope + ((size_t)t * half + (rot ? (c0 & (half - 1)) : 0)) * 2);
+    float4 cs2[CPL / 2];
+    #pragma unroll
+    for (int e = 0; e < CPL / 2; ++e) cs2[e] = __ldg(rp + e);
     #pragma unroll
     for (int e = 0; e < CPL; ++e) {
       const float other = __shfl_xor_sync(0xffffffffu, k[e], lanes_off);
-      if (rot) {
-        const float cx = (e & 1) ? cs2[e / 2].z : cs2[e / 2].x, sy = (e & 1) ? cs2[e / 2].w : cs2[e / 2].y;
-        k[e] = lower ? (k[e] * cx - other * sy) : (other * sy + k[e] * cx);
-      }
+      const float cx = (e & 1) ? cs2[e / 2].z : cs2[e / 2].x, sy = (e & 1) ? cs2[e / 2].w : cs2[e / 2].y;
+      const float r = lower ? (k[e] * cx - other * sy) : (other * sy + k[e] * cx);
+      k[e] = rot ? r : k[e];
     }
+
   };
   // ---- V: every token below `end`, zero rows up to the tile boundary
   if (t >= P.valid_tokens) {
