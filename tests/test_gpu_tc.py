@@ -102,3 +102,41 @@ def test_tc_rejects_what_it_does_not_cover():
         kv4.launch_attention_tc(q, layer, 16, d_pos, 1, pm, pl, pacc, None, 24, 0.0625, 0, kv4.tc_workspace(layer, 16))
     with pytest.raises(Kv4Error, match="workspace of"):
         kv4.launch_attention_tc(q.half(), layer, 16, d_pos, 1, pm, pl, pacc, None, 24, 0.0625, 0, torch.empty(1024, dtype=torch.uint8, device="cuda"))
+
+
+def test_tc_workspace_kept_across_passes_gives_the_same_bits(oracle):
+    """Two verify passes on one cache: the second reuses the workspace of the first (valid_tokens = tokens the workspace
+    already holds) and must equal a pass that dequantises everything again, bit for bit, and the oracle within the bar.
+    The first pass ends inside a group, so the second has to rewrite that group once its last token has arrived."""
+    from yasakani_b200 import kv4
+    shape, ctx, M1, M2, splits = synth.C2, 1000, 20, 24, 4
+    n = ctx + M1 + M2
+    k, v = synth.make_kv(shape, n, seed=61)
+    max_ctx = ((n + 127) // 64) * 64
+    layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
+    okv = oracle.KvCache(shape.hkv, shape.hd, max_ctx)
+    gpu_append_all(kv4, layer, k[:ctx + M1], v[:ctx + M1], [ctx, M1])
+    rope_np = oracle.rope_table(max_ctx, shape.theta, shape.rd)
+    rope = torch.from_numpy(rope_np).cuda()
+    ws = kv4.tc_workspace(layer, max(M1, M2))
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+
+    def run(q, M, valid, workspace):
+        pm, pl, pacc = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
+        o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+        kv4.launch_attention_prefill_tc(q.cuda(), layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, workspace,
+                                        valid_tokens=valid)
+        torch.cuda.synchronize()
+        assert kv4.device_status() == 0
+        return o16
+
+    run(synth.make_q(shape, M1, seed=62), M1, 0, ws)                       # pass 1 fills the workspace for tokens [0, ctx + M1)
+    gpu_append_all(kv4, layer, k[ctx + M1:], v[ctx + M1:], [M2], pos0=ctx + M1)
+    d_pos.fill_(ctx + M1)
+    q2 = synth.make_q(shape, M2, seed=63)
+    kept = run(q2, M2, ctx + M1, ws)                                       # pass 2 on the kept workspace
+    fresh = run(q2, M2, 0, kv4.tc_workspace(layer, M2))                    # the same pass from scratch
+    assert torch.equal(kept, fresh)
+    oracle.append(okv, 0, f16_bits(k), f16_bits(v))
+    want = oracle.attention_exact(f16_bits(q2), okv, ctx + M1, rope_np, shape.hq, shape.rd, shape.qscale)
+    assert_close(kept.float().cpu().numpy(), want, "second pass on a kept workspace")
