@@ -46,6 +46,21 @@ def workload_name(shape, ctx):
     return f"C4 long-context decode: 1 query token, Hq{shape.hq}/Hkv{shape.hkv}/hd{shape.hd}, KV4 cache of {ctx} tokens"
 
 
+def bench_config(shape, ctx, world):
+    """What is measured; printed identically by both arms (how our arm runs it is under `run`)."""
+    return {"workload": workload_name(shape, ctx), "context_tokens": ctx, "parallelism": f"sequence-sharded x{world}",
+            "l2": "inputs larger than L2: consecutive launches read different cache copies, at least 256 MB per cycle (L2 is 126 MB)"}
+
+
+def host_threads():
+    """Threads for the CPU arm: the cores this process may run on.  torch.distributed.run exports OMP_NUM_THREADS=1,
+    which would otherwise hold the OpenMP oracle to one thread."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 # ------------------------------------------------------------------------------------------ clocks
 
 class ClockSampler:
@@ -99,17 +114,19 @@ class ClockSampler:
 
 # ------------------------------------------------------------------------------------------ CPU arm
 
-def cpu_decode_rate(shape, ctx, sample_ctx, steps, warmup, threads):
-    """Times the oracle's reference-literal decode (split-K partials + merge) over a cache of `sample_ctx` tokens and
-    scales the step time by ctx/sample_ctx (the work is linear in the number of keys)."""
+def cpu_decode_rate(shape, ctx, sample_ctx, steps, warmup, threads, kv=None):
+    """Times the oracle's reference-literal decode (split-K partials + merge) over the first `sample_ctx` tokens of a cache
+    and scales the step time by ctx/sample_ctx (the work is linear in the number of keys).  `kv`: a cache that already
+    holds at least `sample_ctx` tokens; built with the oracle's codec otherwise."""
     from oracle import kv4_oracle as o
     bits = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16)
-    max_ctx = ((sample_ctx + 63) // 64) * 64
-    kv = o.KvCache(shape.hkv, shape.hd, max_ctx)
-    for c in range((sample_ctx + CHUNK - 1) // CHUNK):
-        k, v = chunk_rows(shape, c)
-        n = min(CHUNK, sample_ctx - c * CHUNK)
-        o.append(kv, c * CHUNK, bits(k[:n]), bits(v[:n]))
+    if kv is None:
+        kv = o.KvCache(shape.hkv, shape.hd, ((sample_ctx + 63) // 64) * 64)
+        for c in range((sample_ctx + CHUNK - 1) // CHUNK):
+            k, v = chunk_rows(shape, c)
+            n = min(CHUNK, sample_ctx - c * CHUNK)
+            o.append(kv, c * CHUNK, bits(k[:n]), bits(v[:n]))
+    max_ctx = kv.max_ctx
     rope = o.rope_table(max_ctx, shape.theta, shape.rd)
     q16 = bits(synth.make_q(shape, 1, synth.seed_for(CONFIG_INDEX)))
     times = []
@@ -129,7 +146,7 @@ def run_reference(args, rank, world):
         return
     from oracle import kv4_oracle as o
     shape, ctx = synth.C2, args.ctx
-    threads = o.max_threads()
+    threads = host_threads()
     budget = max(0.05, min(2.0, 100.0 / (args.steps + args.warmup)))          # seconds of CPU work per step
     probe_s, _, _ = cpu_decode_rate(shape, 4096, 4096, 1, 1, threads)         # seconds per step at 4,096 keys
     sample_ctx = int(min(ctx, max(4096, (budget / probe_s * 4096) // 4096 * 4096)))
@@ -138,7 +155,7 @@ def run_reference(args, rank, world):
     sample = f"each step = reference-literal decode over the first {sample_ctx} of {ctx} keys, time scaled by {ctx / sample_ctx:.1f}"
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "impl": "reference", "config": {"workload": workload_name(shape, ctx)},
+            "data": "synthetic", "impl": "reference", "config": bench_config(shape, ctx, world),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -272,13 +289,21 @@ def run_ours(args, rank, world, local_rank):
         probe = timed(lambda i: run_steps(K), 1)
         reps = int(min(7, max(1, math.ceil(150.0 / max(probe, 1e-3))))) | 1
         ms_total = float(np.median([probe] + [timed(lambda i: run_steps(K), 1) for _ in range(reps - 1)]))
-        # ---- roofline: the decode-attention kernel alone, same stream, same copies
-        def attn_only(i):
-            d = decs[i % n_copies]
+        # ---- roofline: the decode-attention kernel alone, same stream, same copies, GSTEPS launches per captured graph so that
+        #      the figure is a kernel time and not the host's launch rate (short shards run faster than ctypes can launch)
+        def attn_only(d):
             kv4.launch_attention_shard(q_dev, d.layer, 1, d.d_pos, splits, d.pm, d.pl, d.pacc, rope, shape.hq, shape.qscale, shape.rd,
                                        plan.start, plan.capacity)
-        timed(attn_only, W)
-        ms_attn = timed(attn_only, K)
+        with torch.cuda.stream(side):
+            attn_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(attn_graph, stream=side):
+                for s_ in range(GSTEPS):
+                    attn_only(decs[s_ % n_copies])
+        torch.cuda.synchronize()
+        attn_replays = max(1, (K + GSTEPS - 1) // GSTEPS)
+        timed(lambda i: attn_graph.replay(), max(1, W // GSTEPS))
+        ms_attn = timed(lambda i: attn_graph.replay(), attn_replays)
+        attn_launches = attn_replays * GSTEPS
         # ---- e2e: host buffers in, host buffer out, every step (q, and the new token's k/v on the owning rank)
         k_new, v_new = chunk_rows(shape, (ctx - 1) // CHUNK)
         kn_host = in_host[nq:nq + nkv].view(1, shape.hkv, shape.hd); vn_host = in_host[nq + nkv:].view(1, shape.hkv, shape.hd)
@@ -319,7 +344,7 @@ def run_ours(args, rank, world, local_rank):
     clocks = sampler.summary()
 
     peak, peak_kind = peak_hbm()
-    t_attn = ms_attn / K * 1e-3
+    t_attn = ms_attn / attn_launches * 1e-3
     achieved = shard_bytes / t_attn / 1e9
     value = K / (ms_total * 1e-3)
     # DRAM bytes of one decode-kernel launch: dram__bytes_read.sum + dram__bytes_write.sum from an ncu capture of this
@@ -329,36 +354,87 @@ def run_ours(args, rank, world, local_rank):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": workload_name(shape, ctx), "splits": splits, "graph": f"{GSTEPS} steps (layers) per CUDA graph replay", "parallelism": f"sequence-sharded x{world}" + (f", triples by {exchange}" if world > 1 else ""),
-                   "l2": f"{n_copies} distinct cache copies cycled; {shard_bytes / 1e6:.1f} MB read per launch (L2 is 126 MB)",
-                   "kv_tokens_scanned_per_s": ctx * value},
+        "config": bench_config(shape, ctx, world),
+        "run": {"splits": splits, "graph": f"{GSTEPS} steps (layers) per CUDA graph replay", "exchange": exchange if world > 1 else None,
+                "cache_copies": n_copies, "mb_read_per_launch": shard_bytes / 1e6, "kv_tokens_scanned_per_s": ctx * value},
         "clocks": clocks,
         "e2e": {"value": K / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(q_host.numel() * 2 + (kn_host.numel() + vn_host.numel()) * 2),
                 "d2h_bytes_per_step": int(o_host.numel() * 2), "ms_per_step": ms_e2e / K},
         "gpu_launches": launches_per_step * K,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                      "kernel": "decode attention (split-K partials)", "us_per_launch": t_attn * 1e6, "bytes_per_launch": shard_bytes,
-                     "peak_kind": f"of {peak_kind}"},
+                     "peak_kind": f"of {peak_kind}", "timing": f"CUDA events around graph replays of {GSTEPS} launches over the cache copies"},
     }
 
-    # ---- CPU baseline beside it (rank 0, N = 1): the oracle on the host cores, bounded sample; doubles as a result check
-    if world == 1 and not args.no_cpu_baseline:
-        from oracle import kv4_oracle as o
-        threads = o.max_threads()
-        sample_ctx = min(ctx, args.cpu_sample_ctx)
-        step_s, o16_cpu, (okv, rope_np, q16) = cpu_decode_rate(shape, ctx, sample_ctx, 3, 1, threads)
-        line["cpu_baseline"] = {"value": 1.0 / step_s, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": f"3 reference-literal decode steps over the first {sample_ctx} of {ctx} keys, time scaled by {ctx / sample_ctx:.1f}"}
-        # check: the GPU path over the same sample prefix against the exact oracle
-        d = decs[0]
-        d.d_pos.fill_(sample_ctx - 1)
-        step(d)
-        torch.cuda.synchronize()
-        want = o.attention_exact(q16, okv, sample_ctx - 1, rope_np, shape.hq, shape.rd, shape.qscale)
-        err = np.abs(d.o16.float().cpu().numpy() - want)
-        line["check"] = {"max_abs_err_vs_oracle": float(err.max()), "ok": bool((err <= 2e-3 + 1e-2 * np.abs(want)).all())}
+    # ---- result check at every N: one more step at the full context on every rank; rank 0 compares the (sharded) o16 with the
+    #      exact oracle over ALL `ctx` keys of the same packed cache and, for N > 1, with the 1-GPU decode of the unsharded
+    #      cache; every rank's device status word (bounded waits that ran out) is reduced with MAX.
+    from oracle import kv4_oracle as o
+    bits = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16)
+    d = decs[0]
+    d.d_pos.fill_(ctx - 1)
+    step(d)
+    torch.cuda.synchronize()
+    st = torch.tensor([kv4.device_status()], dtype=torch.int32, device=dev)
+    if world > 1:
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    status = int(st.item())
+    ok = True
     if rank == 0:
+        got = d.o16.float().cpu().numpy()
+        check = {"device_status_max_over_ranks": status}
+        if world == 1:
+            full = first.layer
+        else:                                                       # the unsharded cache on rank 0's GPU, built by the same codec
+            full = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
+            fpos = torch.zeros(1, dtype=torch.int32, device=dev)
+            for c in range((ctx + CHUNK - 1) // CHUNK):
+                k, v = chunk_rows(shape, c)
+                n = min(CHUNK, ctx - c * CHUNK)
+                fpos.fill_(c * CHUNK)
+                kv4.launch_kv_append(full, k[:n].to(dev), v[:n].to(dev), fpos, n)
+            fpos.fill_(ctx - 1)
+            pm1, pl1, pacc1 = kv4.attn_scratch(1, splits, shape.hq, shape.hd)
+            o1 = torch.empty((1, shape.hq, shape.hd), dtype=torch.float16, device=dev)
+            kv4.launch_decode(q_dev, full, 1, fpos, splits, pm1, pl1, pacc1, rope, shape.hq, shape.qscale, shape.rd, o1)
+            torch.cuda.synchronize()
+            one = o1.float().cpu().numpy()
+            e1 = np.abs(got - one)
+            check["max_abs_diff_vs_1gpu"] = float(e1.max())
+            check["ok_vs_1gpu"] = bool((e1 <= 2e-3 + 1e-2 * np.abs(one)).all())
+        okv = o.KvCache(shape.hkv, shape.hd, max_ctx)
+        for name, arr in full.to_numpy().items():
+            getattr(okv, name)[...] = arr.reshape(getattr(okv, name).shape)
+        # the packed cache itself: the first chunk re-encoded by the oracle's codec must give the same bytes
+        ochk = o.KvCache(shape.hkv, shape.hd, CHUNK)
+        k0, v0 = chunk_rows(shape, 0)
+        o.append(ochk, 0, bits(k0), bits(v0))
+        check["codec_first_chunk_bit_exact"] = bool(all(np.array_equal(getattr(ochk, nm)[:, :a], getattr(okv, nm)[:, :a])
+                                                        for nm, a in (("kq", CHUNK // 32), ("kscale", CHUNK // 32), ("kzero", CHUNK // 32),
+                                                                      ("vq", CHUNK), ("vscale", CHUNK), ("vzero", CHUNK))))
+        threads = host_threads()
+        want = o.attention_exact(bits(q_host), okv, ctx - 1, rope.cpu().numpy(), shape.hq, shape.rd, shape.qscale, threads=threads)
+        err = np.abs(got - want)
+        check.update({"keys": ctx, "max_abs_err_vs_oracle": float(err.max()), "ok_vs_oracle": bool((err <= 2e-3 + 1e-2 * np.abs(want)).all())})
+        ok = bool(check["ok_vs_oracle"] and check.get("ok_vs_1gpu", True) and check["codec_first_chunk_bit_exact"] and status == 0)
+        check["ok"] = ok
+        line["check"] = check
+        # ---- CPU baseline beside it (N = 1 only): the oracle's reference-literal decode on the host cores, bounded sample
+        if world == 1 and not args.no_cpu_baseline:
+            sample_ctx = min(ctx, args.cpu_sample_ctx)
+            step_s, _, _ = cpu_decode_rate(shape, ctx, sample_ctx, 3, 1, threads, kv=okv)
+            line["cpu_baseline"] = {"value": 1.0 / step_s, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": f"3 reference-literal decode steps over the first {sample_ctx} of {ctx} keys, time scaled by {ctx / sample_ctx:.1f}"}
+        del okv, full
+        if world == 1 and not args.no_secondary:
+            del decs[1:]
+            torch.cuda.empty_cache()
+            line["secondary"] = secondary_lines(shape, splits, dev)
         print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+    if not ok:
+        sys.exit(3)
 
 
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 310.27e6 / 306208768
@@ -387,6 +463,100 @@ def _peaks():
         p = json.load(open(path))
         return p["hbm_gbs"], p["bf16_tflops"], "measured"
     return 6650.0, 1590.0, "fallback"
+
+
+def secondary_lines(shape, splits, dev):
+    """Device-timed figures of the rest of the metric for the headline JSON line (N = 1): the decode kernel at 32,768 and
+    131,072 tokens as a fraction of the HBM peak, the 8,192-row causal prefill and the 16/32/64-row verify passes as a
+    fraction of the bf16 tensor peak.  Same timing rules as the headline: graph replays over cache copies larger than L2
+    for the HBM-bound kernel; CUDA events; warm-up first."""
+    from yasakani_b200 import kv4
+    hbm, tf, kind = _peaks()
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    tf_sus = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    out = {"peak_kind": f"of {kind}"}
+    side = torch.cuda.Stream(device=dev)
+    q = synth.make_q(shape, 1, synth.seed_for(CONFIG_INDEX)).to(dev)
+
+    def graph_time(fn, launches_per_graph, replays, warm):
+        with torch.cuda.stream(side):
+            fn(0); torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(launches_per_graph):
+                    fn(i)
+            for _ in range(warm):
+                g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(replays):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / (replays * launches_per_graph)
+
+    # ---- decode at the shorter contexts of the metric
+    for ctx in (32768, 131072):
+        max_ctx = ctx + 64
+        rope = torch.empty((max_ctx, shape.rd // 2, 2), dtype=torch.float32, device=dev)
+        kv4.launch_rope_table_g(rope, max_ctx, shape.theta, shape.rd)
+        first = kv4.KvLayer(shape.hkv, shape.hd, max_ctx, device=dev)
+        pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        for c in range(ctx // CHUNK):
+            k, v = chunk_rows(shape, c)
+            pos.fill_(c * CHUNK)
+            kv4.launch_kv_append(first, k.to(dev), v.to(dev), pos, CHUNK)
+        byt = shape.decode_bytes(ctx)
+        n_copies = max(2, int(math.ceil(256e6 / byt)) + 1)
+        layers = [first]
+        for _ in range(n_copies - 1):
+            l2 = kv4.KvLayer(shape.hkv, shape.hd, max_ctx, device=dev)
+            for a, b in zip(l2.tensors(), first.tensors()):
+                a.copy_(b)
+            layers.append(l2)
+        pos.fill_(ctx - 1)
+        pm, pl, pacc = kv4.attn_scratch(1, splits, shape.hq, shape.hd)
+        o16 = torch.empty((1, shape.hq, shape.hd), dtype=torch.float16, device=dev)
+        n_graph = max(GSTEPS, n_copies)
+        t_attn = graph_time(lambda i: kv4.launch_attention_gqa(q, layers[i % n_copies], 1, pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd),
+                            n_graph, 8, 2)
+        t_step = graph_time(lambda i: kv4.launch_decode(q, layers[i % n_copies], 1, pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16),
+                            n_graph, 8, 2)
+        out[f"decode_ctx{ctx}"] = {"us_per_launch": t_attn * 1e6, "us_per_step": t_step * 1e6, "tokens_per_s": 1.0 / t_step, "bytes_per_launch": byt,
+                                   "achieved_gbs": byt / t_attn / 1e9, "frac_of_hbm_peak": byt / t_attn / 1e9 / hbm, "cache_copies": n_copies}
+        del layers, first, l2
+        torch.cuda.empty_cache()
+
+    # ---- multi-row passes on the tensor-core kernel
+    g = torch.Generator(device=dev).manual_seed(1234)
+
+    def tc_case(ctx, M, S):
+        max_ctx = ((ctx + M + 127) // 64) * 64
+        layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx, device=dev)
+        pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        for p in range(0, ctx + M, CHUNK):
+            n = min(CHUNK, ctx + M - p)
+            k = torch.randn((n, shape.hkv, shape.hd), generator=g, device=dev, dtype=torch.float16)
+            v = torch.randn((n, shape.hkv, shape.hd), generator=g, device=dev, dtype=torch.float16)
+            pos.fill_(p)
+            kv4.launch_kv_append(layer, k, v, pos, n)
+        rope = torch.empty((max_ctx, shape.rd // 2, 2), dtype=torch.float32, device=dev)
+        kv4.launch_rope_table_g(rope, max_ctx, shape.theta, shape.rd)
+        qm = torch.randn((M, shape.hq, shape.hd), generator=g, device=dev, dtype=torch.float16)
+        pos.fill_(ctx)
+        pm, pl, pacc = kv4.attn_scratch(M, S, shape.hq, shape.hd)
+        o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device=dev)
+        ws = kv4.tc_workspace(layer, M)
+        t = _timed(lambda i: kv4.launch_attention_prefill_tc(qm, layer, M, pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws), 10, 3)
+        flops = shape.attn_flops(sum(ctx + r + 1 for r in range(M)))
+        return {"us_per_pass": t * 1e6, "tflops": flops / t / 1e12, "frac_of_bf16_burst_peak": flops / t / 1e12 / tf,
+                "frac_of_bf16_sustained_peak": flops / t / 1e12 / tf_sus, "splits": S, "includes": "dequant prep + attention" + ("" if S == 1 else " + merge")}
+
+    out["prefill_8192_rows"] = tc_case(0, 8192, 1)
+    for M, S in ((64, 9), (32, 18), (16, 18)):
+        out[f"verify_{M}_rows_ctx32768"] = tc_case(32768, M, S)
+    return out
 
 
 def run_secondary(args):
@@ -475,6 +645,7 @@ def main():
     ap.add_argument("--splits", type=int, default=37, help="split-K factor; splits*Hkv = 148 = one CTA per SM")
     ap.add_argument("--cpu-sample-ctx", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the device-timed figures of the other contexts and kernels (`secondary`)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="N > 1: how the shards' (m, l, O) triples travel")
     ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch from an ncu capture, if known")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "verify", "kv8", "kvx"],

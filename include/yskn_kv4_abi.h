@@ -128,8 +128,9 @@ YSKN_KV4_API int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int 
  * workspace of yskn_kv4_tc_workspace_bytes(kvh, hd, max_ctx, M) bytes (16-byte aligned).  Each call first brings the
  * workspace up to date for tokens [valid_tokens, *d_pos + M): pass 0 unless the same workspace already holds the
  * dequantised tokens [0, valid_tokens) of this cache from an earlier call (valid_tokens <= *d_pos; nothing below the
- * 128-token tile of valid_tokens is touched).  q16 must be fp16.  Semantics, partial
- * layout and `splits` are those of yskn_kv4_attention; yskn_kv4_prefill_tc also merges to o16 (+ optional bias). */
+ * 128-token tile of valid_tokens is touched).  q16 must be fp16; q16, pacc and o16 must be 16-byte aligned (vector
+ * stores).  Semantics, partial layout and `splits` are those of yskn_kv4_attention; yskn_kv4_prefill_tc also merges to
+ * o16 (+ optional bias). */
 YSKN_KV4_API size_t yskn_kv4_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M);
 YSKN_KV4_API int yskn_kv4_attention_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, void* d_workspace,
                                        size_t workspace_bytes, int valid_tokens, void* cuda_stream);
@@ -139,7 +140,8 @@ YSKN_KV4_API int yskn_kv4_prefill_tc(const yskn_attn_g_args* a, int g, int hd, i
 
 /* Sequence-sharded decode (no reference counterpart: the reference is single-GPU, README.md:37).
  * yskn_kv4_attention_shard is yskn_kv4_attention over a cache that holds only the global tokens
- * [shard_start, shard_start + shard_len) (shard_start a multiple of 32; local token t = global t + shard_start):
+ * [shard_start, shard_start + shard_len) (both multiples of 32, so that no K group and no rope-table row of a
+ * group straddles a shard; local token t = global t - shard_start):
  * *d_pos stays the GLOBAL position of row 0, `a->rope` the full table, `a->max_ctx` the local capacity.  Keys outside
  * the shard contribute nothing; a shard with no visible key writes pm = -1e30 in every slot.
  * yskn_kv4_local_triple folds the `splits` partials of each (row, head) into one un-normalised
@@ -155,8 +157,14 @@ YSKN_KV4_API int yskn_kv4_decode_shard_triple(const yskn_attn_g_args* a, int g, 
  * about half a second, then device status 7) for all sources and merges.  buf[w] is rank w's exchange buffer as mapped
  * into THIS process (buf[rank] is the local one), each of yskn_kv4_exchange_bytes(world, M, nh, hd) bytes, 16-byte
  * aligned and zero-filled once before the first step.  Two halves are used alternately, so the ranks need no other
- * synchronisation between steps; every rank must run push and merge exactly once per step, in this order. */
+ * synchronisation between steps; every rank must run push and merge exactly once per step, in this order.
+ * After a wait ran out (device status 7) the step is abandoned half way: the arrival counters and the step word of
+ * that rank no longer agree with its peers'.  Recover by stopping all ranks between steps, zero-filling every rank's
+ * exchange buffer again and resuming; the library does not repair it on its own. */
 typedef struct yskn_kv4_peer_exchange { float* buf[8]; int world; int rank; } yskn_kv4_peer_exchange;
+/* Limit of the wait above in polls of about 100 ns (process-wide, read at launch; 0 restores the default of 2^22,
+ * about half a second).  A short limit lets a host-made failure -- a rank that never pushed -- be observed quickly. */
+YSKN_KV4_API int yskn_kv4_set_peer_wait_polls(unsigned polls);
 YSKN_KV4_API size_t yskn_kv4_exchange_bytes(int world, int M, int nh, int hd);
 YSKN_KV4_API int yskn_kv4_push_triple(const yskn_attn_g_combine_args* a, int hd, const yskn_kv4_peer_exchange* x, void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, int hd, const uint16_t* bv,

@@ -57,4 +57,24 @@ int yref_attn_combine_gqa_xform(const float* pm, const float* pl, const float* p
   return finish();
 }
 
+// src/post_kernels.cu:26-82 (qkv_post_kernel<false>, the hd-128 / 4-kv-head epilogue), driven so that the K and the V
+// branch see the same row: one GEMV slice (nw = 1), tau = 1, no bias, no fused group quant, the same `part` and the same
+// sign vector for both.  Block 7 then stores round_f16(inv_h512(part)) to kshadow and block 8 quantises that same fp16
+// row into vq / vscale / vzero, so kshadow is the witness of the V codec's input.  The seven query blocks get zero-filled
+// dummies (q_dummy: 3584 floats per row, also used as tau_q / bias / sign sources through the pointers below).
+int yref_qkv_post_kv(const float* part_kv, const float* ones512, const int8_t* signs512, const uint16_t* zeros_bias,
+                     const float* q_zero_part, const float* q_tau, const int8_t* q_signs, const uint16_t* q_bias, uint16_t* q16_out,
+                     uint8_t* kq, uint16_t* ks, uint16_t* kz, uint16_t* ksh, uint8_t* vq, uint16_t* vs, uint16_t* vz,
+                     const int* d_pos, int M, int max_ctx, void* st) {
+  yskn::QkvPostArgs A{};
+  A.part_q = q_zero_part; A.part_k = part_kv; A.part_v = part_kv;
+  A.tau_q = q_tau; A.tau_k = ones512; A.tau_v = ones512;
+  A.nw_q = 1; A.nw_k = 1; A.nw_v = 1;
+  A.sg_q = q_signs; A.sg_k = signs512; A.sg_v = signs512; A.bq = q_bias; A.bk = zeros_bias;
+  A.M = M; A.d_pos = d_pos; A.q16 = q16_out; A.kv = mk(kq, ks, kz, ksh, vq, vs, vz); A.max_ctx = max_ctx; A.rope_theta = 1e6f;
+  A.rope = nullptr; A.us = nullptr; A.rr = nullptr; A.kvfuse = 0; A.fy = 0;
+  try { yskn::launch_qkv_post(A, (cudaStream_t)st); } catch (const std::exception&) { return -1; }
+  return finish();
+}
+
 }  // extern "C"

@@ -320,3 +320,57 @@ def test_fused_exchange_merge_rejects_grids_that_may_not_be_resident():
     o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
     with pytest.raises(Kv4Error):
         kv4.launch_exchange_merge(pm, pl, pacc, 4, M, shape.hq, shape.g, shape.hd, x, o16)
+
+
+def test_withheld_push_runs_the_bounded_wait_out_and_the_next_step_works(oracle):
+    """A host-made failure: in a world of two (both 'ranks' on this GPU) rank 1 never pushes its triple.  With a short poll
+    limit rank 0's merge must return by itself, leave o16 untouched, and report device status 7; after every exchange
+    buffer is zero-filled again (the documented recovery) a normal step gives the right answer.  Nothing faults or spins
+    without a bound."""
+    from yasakani_b200.sharded import plan_shards
+    shape, ctx, world = synth.C2, 1500, 2
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, 1, seed=43)
+    k, v = synth.make_kv(shape, ctx + 1, seed=43)
+    bufs = [torch.zeros((kv4.exchange_bytes(world, 1, shape.hq, shape.hd) + 3) // 4, dtype=torch.float32, device="cuda") for _ in range(world)]
+    xs = [kv4.peer_exchange([b.data_ptr() for b in bufs], rnk) for rnk in range(world)]
+    lays, plans = [], []
+    for rnk in range(world):
+        plan = plan_shards(ctx, world, rnk, okv.max_ctx)
+        lay = kv4.KvLayer(shape.hkv, shape.hd, plan.capacity)
+        a, b = plan.local_rows(0, ctx + 1)
+        gpu_append_all(kv4, lay, k[a:b], v[a:b], [b - a], pos0=a - plan.start)
+        lays.append(lay); plans.append(plan)
+    want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    dq = q.cuda()
+
+    def shard_partials(rnk):
+        pm, pl, pacc = kv4.attn_scratch(1, 9, shape.hq, shape.hd)
+        kv4.launch_attention_shard(dq, lays[rnk], 1, d_pos, 9, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, plans[rnk].start, plans[rnk].capacity)
+        return pm, pl, pacc
+
+    assert kv4.device_status() == 0
+    kv4.set_peer_wait_polls(2000)                                  # about 0.2 ms instead of half a second
+    try:
+        kv4.launch_push_triple(*shard_partials(0), 9, 1, shape.hq, shape.hd, xs[0])      # rank 1 withholds its push
+        o16 = torch.full((1, shape.hq, shape.hd), 7.0, dtype=torch.float16, device="cuda")
+        kv4.launch_merge_pushed(xs[0], 1, shape.hq, shape.g, shape.hd, o16)
+        torch.cuda.synchronize()                                   # returns: the wait gave up
+        assert kv4.device_status() == 7
+        assert kv4.device_status() == 0                            # reading clears it
+        assert bool((o16 == 7.0).all())                            # no row was written from incomplete triples
+    finally:
+        kv4.set_peer_wait_polls(0)
+    for b in bufs:                                                 # recovery: all ranks stopped, buffers cleared
+        b.zero_()
+    outs = []
+    for rnk in range(world):
+        kv4.launch_push_triple(*shard_partials(rnk), 9, 1, shape.hq, shape.hd, xs[rnk])
+    for rnk in range(world):
+        o = torch.empty((1, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+        kv4.launch_merge_pushed(xs[rnk], 1, shape.hq, shape.g, shape.hd, o)
+        outs.append(o)
+    torch.cuda.synchronize()
+    assert kv4.device_status() == 0
+    for rnk in range(world):
+        assert_close(outs[rnk].float().cpu().numpy(), want, f"rank {rnk} after recovery")

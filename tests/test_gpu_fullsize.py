@@ -58,14 +58,29 @@ def test_config5_prefill_8192_rows_sampled_against_oracle(oracle):
         assert_close(got[lo:hi], want[lo:hi], f"prefill rows {lo}..{hi}")
 
 
+def _oracle_view(oracle, layer):
+    """The oracle's cache object over the bytes of a GPU-built cache (the codec's bit-exactness is tested on its own)."""
+    okv = oracle.KvCache(layer.hkv, layer.hd, layer.max_ctx)
+    for name, arr in layer.to_numpy().items():
+        getattr(okv, name)[...] = arr.reshape(getattr(okv, name).shape)
+    return okv
+
+
 def test_config5_decode_batch_at_mixed_contexts(oracle):
-    """Eight independent single-token decodes at 2k ... 128k; the oracle checks the small ones, the large ones compare the
-    tensor-core kernel with the CUDA-core kernel (itself oracle-checked on the small ones)."""
+    """Eight independent single-token decodes at 2k ... 128k, every one against the exact oracle over all its keys (the long
+    ones are where the rotation by angle addition is furthest from the table); the tensor-core kernel is also compared with
+    the CUDA-core kernel.  Up to 16,384 tokens the oracle encodes the cache itself; beyond, it reads the GPU-built bytes."""
     from yasakani_b200 import kv4
     shape = synth.C2
     for i, ctx in enumerate((2048, 4096, 8192, 16384, 32768, 65536, 98304, 131072)):
         small = ctx <= 16384
         layer, okv, max_ctx = _build(kv4, oracle, shape, ctx, seed=80 + i, want_oracle=small)
+        if small:
+            got_cache = layer.to_numpy()
+            for name, want in okv.arrays().items():
+                assert np.array_equal(got_cache[name].reshape(want.shape), want), f"ctx {ctx}: {name}"
+        else:
+            okv = _oracle_view(oracle, layer)
         rope = _rope(kv4, shape, max_ctx)
         q = synth.make_q(shape, 1, seed=80 + i)
         d_pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda")
@@ -80,10 +95,10 @@ def test_config5_decode_batch_at_mixed_contexts(oracle):
         kv4.set_algo(ALGO_AUTO)
         assert kv4.device_status() == 0
         assert_close(outs[ALGO_AUTO], outs[ALGO_SCALAR], f"ctx {ctx}: tensor-core vs CUDA-core")
-        if small:
-            want = oracle.attention_exact(f16_bits(q), okv, ctx - 1, rope.cpu().numpy(), shape.hq, shape.rd, shape.qscale)
-            assert_close(outs[ALGO_AUTO], want, f"ctx {ctx} vs oracle")
-        del layer, rope
+        want = oracle.attention_exact(f16_bits(q), okv, ctx - 1, rope.cpu().numpy(), shape.hq, shape.rd, shape.qscale)
+        worst = assert_close(outs[ALGO_AUTO], want, f"ctx {ctx} vs oracle")
+        print(f"decode ctx {ctx}: max abs err vs exact oracle {worst:.3e}")
+        del layer, rope, okv
         torch.cuda.empty_cache()
 
 
@@ -116,6 +131,11 @@ def test_config3_verify_widths_over_32768_tokens(oracle):
     oracle.append(okv, ctx, f16_bits(k_new), f16_bits(v_new))
     rope_np = rope.cpu().numpy()
     got = outs[64].float().numpy()
-    for lo, hi in ((0, 2), (31, 33), (62, 64)):
-        want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale, rows=(lo, hi))
-        assert_close(got[lo:hi], want[lo:hi], f"verify rows {lo}..{hi}")
+    # every row of the widest pass against the exact oracle, and the distribution of the error relative to the bar
+    want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    assert_close(got, want, "verify, all 64 rows")
+    err = np.abs(got - want)
+    ratio = err / (2e-3 + 1e-2 * np.abs(want))
+    print(f"verify 64 rows vs 32768 tokens: max abs err {err.max():.3e}, p99 {np.percentile(err, 99):.3e}, "
+          f"largest fraction of the bar {ratio.max():.3f}, p99 {np.percentile(ratio, 99):.3f}")
+    assert np.percentile(ratio, 99) <= 0.5, "the bulk of the verify error should sit well inside the bar"

@@ -2,9 +2,9 @@
 
 oracle/_ref/libyskn_ref_kv4.so is compiled from the reference's source files where they lie
 (oracle/Makefile, target `ref`) and travels to the GPU box as a built file.  It covers the K group codec
-(kv_group_quant_g_kernel), the generic GQA decode kernel and its merge kernel.  The per-token V codec lives
-inside the reference's fused QKV epilogue, which cannot be driven without its GEMV inputs; it shares the
-K codec's formula line for line (src/post_kernels.cu:76-77 vs src/attention_gqa.cu:149-152).
+(kv_group_quant_g_kernel), the generic GQA decode kernel and its merge kernel, and the per-token V codec inside
+the reference's fused QKV epilogue (qkv_post_kernel, src/post_kernels.cu:26-82), driven so that its K branch
+stores the very fp16 row its V branch quantises.
 """
 import ctypes as C
 import os
@@ -45,6 +45,54 @@ def test_oracle_group_codec_equals_reference_kernel_bit_for_bit(oracle, ref, sha
     got = ours.to_numpy()
     for name in ("kq", "kscale", "kzero"):
         assert np.array_equal(got[name].reshape(getattr(okv, name).shape), getattr(okv, name)), name
+
+
+def test_v_codec_equals_reference_qkv_epilogue_bit_for_bit(oracle, ref):
+    """The reference's V branch (src/post_kernels.cu:64-82) exists for hd 128 / 4 kv-heads only.  With one GEMV slice,
+    tau = 1, no bias and the same `part` and sign vector for K and V, block 7 stores round_f16(inv_h512(part)) into
+    kshadow and block 8 quantises the identical fp16 row into vq / vscale / vzero: kshadow is the witness of the V
+    codec's input.  The oracle's and the library's V codec over those shadow rows must reproduce the reference's bytes."""
+    from yasakani_b200 import kv4
+    hkv, hd, M, max_ctx, pos0 = 4, 128, 77, 192, 23
+    g = torch.Generator().manual_seed(4242)
+    part = torch.randn((M, 512), generator=g) * torch.exp(torch.rand((1, 512), generator=g) * 3.0 - 1.5)
+    part[5, 128:256] = 0.25                                        # a constant row: hi == lo, scale 0 (src/post_kernels.cu:76)
+    part[6] = 0.0
+    signs = (torch.randint(0, 2, (512,), generator=g) * 2 - 1).to(torch.int8)
+    dev = "cuda"
+    d = dict(part=part.to(dev), ones=torch.ones(512, device=dev), signs=signs.to(dev), zb=torch.zeros(512, dtype=torch.float16, device=dev),
+             qpart=torch.zeros((M, 3584), device=dev), qtau=torch.ones(3584, device=dev), qsigns=torch.ones(3584, dtype=torch.int8, device=dev),
+             qbias=torch.zeros(3584, dtype=torch.float16, device=dev), q16=torch.zeros((M, 28, 128), dtype=torch.float16, device=dev))
+    theirs = kv4.KvLayer(hkv, hd, max_ctx)
+    d_pos = torch.tensor([pos0], dtype=torch.int32, device=dev)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    rc = ref.yref_qkv_post_kv(P(d["part"]), P(d["ones"]), P(d["signs"]), P(d["zb"]), P(d["qpart"]), P(d["qtau"]), P(d["qsigns"]), P(d["qbias"]),
+                              P(d["q16"]), *_ptrs(theirs), P(d_pos), M, max_ctx, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    got = theirs.to_numpy()
+    shadow = got["kshadow"].reshape(hkv, max_ctx, hd)[:, pos0:pos0 + M]            # [hkv][M][hd] fp16 bits: the rows both branches saw
+    rows = np.ascontiguousarray(shadow.transpose(1, 0, 2))                         # [M][hkv][hd]
+    assert len(np.unique(rows)) > 1000                                             # the epilogue really ran on the random rows
+    # oracle: the V codec over the witnessed rows
+    okv = oracle.KvCache(hkv, hd, max_ctx)
+    oracle.append(okv, pos0, rows, rows)
+    for name in ("vq", "vscale", "vzero"):
+        want = getattr(okv, name)[:, pos0:pos0 + M]
+        have = got[name].reshape(getattr(okv, name).shape)[:, pos0:pos0 + M]
+        assert np.array_equal(have, want), f"oracle V codec differs from the reference's qkv_post_kernel in {name}"
+    # the library's codec over the same rows
+    ours = kv4.KvLayer(hkv, hd, max_ctx)
+    r16 = torch.from_numpy(rows.view(np.int16)).view(torch.float16).cuda()
+    kv4.launch_kv_append(ours, r16, r16, d_pos, M)
+    torch.cuda.synchronize()
+    mine = ours.to_numpy()
+    for name in ("vq", "vscale", "vzero", "kshadow"):
+        a = mine[name].reshape(getattr(okv, name).shape)[:, pos0:pos0 + M]
+        b = got[name].reshape(getattr(okv, name).shape)[:, pos0:pos0 + M]
+        if name == "kshadow":                                                      # -0.0 + 0.0 bias = +0.0 in the reference's K branch
+            a = np.where(a == 0x8000, 0, a); b = np.where(b == 0x8000, 0, b)
+        assert np.array_equal(a, b), f"library V codec differs from the reference's qkv_post_kernel in {name}"
 
 
 @pytest.mark.parametrize("shape,ctx,M", [(synth.C2, 2100, 1), (synth.C2, 700, 3), (synth.Shape(28, 4, 128, 128, 1e6), 1500, 2)])

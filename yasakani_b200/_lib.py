@@ -67,6 +67,7 @@ PROTOTYPES = {
     "yskn_kv4_attention_tc": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
     "yskn_kv4_prefill_tc": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_size_t, C.c_int, C.c_void_p]),
+    "yskn_kv4_set_peer_wait_polls": (C.c_int, [C.c_uint]),
     "yskn_kv4_exchange_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "yskn_kv4_push_triple": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.POINTER(PeerExchangeC), C.c_void_p]),
     "yskn_kv4_exchange_merge": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_int, C.POINTER(PeerExchangeC), C.c_void_p]),
@@ -103,7 +104,7 @@ def load():
     """Load the CUDA library (building it first if sources are newer). Raises if that is impossible."""
     global _LIB
     if _LIB is None:
-        path = os.environ.get("YSKN_KV4_LIB") or _build.LIB          # an explicit library (e.g. a diagnostic build) wins
+        path = _build.LIB
         if not os.path.exists(path) or os.environ.get("YSKN_KV4_REBUILD"):
             path = _build.build()
         L = C.CDLL(path)

@@ -11,7 +11,8 @@
 namespace kv4 {
 
 static thread_local char g_err[512] = "";
-static int g_algo = ALGO_AUTO;
+static std::atomic<int> g_algo{ALGO_AUTO};
+int current_algo() { return g_algo.load(std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap; va_start(ap, fmt); vsnprintf(g_err, sizeof(g_err), fmt, ap); va_end(ap);
@@ -33,8 +34,9 @@ static int attention_dispatch(const yskn_attn_g_args* a, int g, int hd, int rd, 
   if (act_dtype != YSKN_KV4_F16 && act_dtype != YSKN_KV4_BF16) KV4_REJECT("yskn_kv4_attention: act_dtype must be F16 or BF16");
   if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_attention: rotary width %d needs a rope table", rd);
   const bool mma_ok = decode_mma_supports(g, hd, rd, a->M);
-  if (g_algo == ALGO_MMA && !mma_ok) KV4_REJECT("yskn_kv4_attention: tensor-core path does not cover (g %d, hd %d, rd %d, M %d)", g, hd, rd, a->M);
-  if (mma_ok && g_algo != ALGO_SCALAR) return launch_decode_mma(*a, g, hd, rd, act_dtype, sh, st);
+  const int algo = current_algo();
+  if (algo == ALGO_MMA && !mma_ok) KV4_REJECT("yskn_kv4_attention: tensor-core path does not cover (g %d, hd %d, rd %d, M %d)", g, hd, rd, a->M);
+  if (mma_ok && algo != ALGO_SCALAR) return launch_decode_mma(*a, g, hd, rd, act_dtype, sh, st);
   return launch_attention_scalar(*a, g, hd, rd, act_dtype, sh, st);
 }
 
@@ -52,7 +54,7 @@ const char* yskn_kv4_build_info(void) {
 
 int yskn_kv4_set_algo(int algo) {
   if (algo < ALGO_AUTO || algo > ALGO_MMA) KV4_REJECT("yskn_kv4_set_algo: unknown algorithm %d", algo);
-  g_algo = algo; return 0;
+  g_algo.store(algo, std::memory_order_relaxed); return 0;
 }
 
 int yskn_kv4_device_status(int* status) {
@@ -64,6 +66,8 @@ int yskn_kv4_device_status(int* status) {
   if (int rc = merge_status_fetch(&c)) return rc;
   *status = a ? a : (b ? b : c); return 0;
 }
+
+int yskn_kv4_set_peer_wait_polls(unsigned polls) { set_peer_wait_polls(polls); return 0; }
 
 size_t yskn_kv4_exchange_bytes(int world, int M, int nh, int hd) {
   if (world < 1 || world > 8 || M <= 0 || nh <= 0 || hd <= 0) return 0;
@@ -135,8 +139,8 @@ int yskn_kv4_attention(const yskn_attn_g_args* a, int g, int hd, int rd, int act
 int yskn_kv4_attention_shard(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, int shard_start, int shard_len,
                              void* cuda_stream) {
   if (int rc = check_attn(a, g, hd, "yskn_kv4_attention_shard")) return rc;
-  if (shard_start < 0 || shard_start % 32 || shard_len < 0 || shard_len > a->max_ctx)
-    KV4_REJECT("yskn_kv4_attention_shard: shard [%d, +%d) must start on a multiple of 32 and fit max_ctx %d", shard_start, shard_len, a->max_ctx);
+  if (shard_start < 0 || shard_start % 32 || shard_len < 0 || shard_len % 32 || shard_len > a->max_ctx)
+    KV4_REJECT("yskn_kv4_attention_shard: shard [%d, +%d) must start and end on multiples of 32 and fit max_ctx %d", shard_start, shard_len, a->max_ctx);
   return attention_dispatch(a, g, hd, rd, act_dtype, Shard{shard_start, shard_len}, (cudaStream_t)cuda_stream);
 }
 
@@ -155,8 +159,8 @@ int yskn_kv4_decode_shard_triple(const yskn_attn_g_args* a, int g, int hd, int r
                                  float* d_triple, void* cuda_stream) {
   if (int rc = check_attn(a, g, hd, "yskn_kv4_decode_shard_triple")) return rc;
   if (!d_triple) KV4_REJECT("yskn_kv4_decode_shard_triple: null output");
-  if (shard_start < 0 || shard_start % 32 || shard_len < 0 || shard_len > a->max_ctx)
-    KV4_REJECT("yskn_kv4_decode_shard_triple: shard [%d, +%d) must start on a multiple of 32 and fit max_ctx %d", shard_start, shard_len, a->max_ctx);
+  if (shard_start < 0 || shard_start % 32 || shard_len < 0 || shard_len % 32 || shard_len > a->max_ctx)
+    KV4_REJECT("yskn_kv4_decode_shard_triple: shard [%d, +%d) must start and end on multiples of 32 and fit max_ctx %d", shard_start, shard_len, a->max_ctx);
   if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_decode_shard_triple: rotary width %d needs a rope table", rd);
   cudaStream_t st = (cudaStream_t)cuda_stream;
   const Shard sh{shard_start, shard_len};

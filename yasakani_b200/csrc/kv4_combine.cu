@@ -23,6 +23,7 @@ struct CombineP {
   int S, M, nh, g;
   const void* bv; const void* gate; uint16_t* o16; float* triple_out;
   yskn_kv4_peer_exchange x;                              // PEER modes only
+  unsigned wait_polls;                                   // PEER modes: polls (about 100 ns each) before a wait gives up
 };
 
 __device__ int g_merge_status = 0;                       // 7 = the wait for the other shards' triples ran out
@@ -30,7 +31,8 @@ __device__ int g_merge_status = 0;                       // 7 = the wait for the
 // Exchange buffer of one rank (yskn_kv4_peer_exchange): float data[2][world][M*nh*(HD+2)], then unsigned arrived[2][world],
 // then int step, unsigned merge ticket, unsigned push ticket.  Buffer `step & 1` is the one in use; a rank is never more than one step ahead of another.
 __device__ __forceinline__ size_t xch_data_floats(int world, int M, int nh, int hd) { return (size_t)2 * world * M * nh * (hd + 2); }
-constexpr unsigned PEER_WAIT_POLLS = 1u << 22;           // x ~100 ns: about half a second
+constexpr unsigned PEER_WAIT_POLLS = 1u << 22;           // default limit, x ~100 ns: about half a second
+std::atomic<unsigned> g_peer_wait_polls{PEER_WAIT_POLLS}; // yskn_kv4_set_peer_wait_polls
 
 constexpr int CB = 8;                                    // loads in flight per thread and batch
 
@@ -40,14 +42,14 @@ constexpr int CB = 8;                                    // loads in flight per 
 // CQ = split runs per block: 4 when there are many splits to fetch and few blocks (decode: latency), 2 when the grid of
 // 1,024-thread blocks would not fit the GPU at once (verify: hundreds of rows x heads), 1 for short sums (prefill).
 // Bounded wait (one thread) until every rank's arrival count for this step has reached `want`; 1 = gave up.
-__device__ __forceinline__ int wait_for_triples(const unsigned* flags, int world, unsigned want) {
+__device__ __forceinline__ int wait_for_triples(const unsigned* flags, int world, unsigned want, unsigned limit) {
   for (int src = 0; src < world; ++src) {
     unsigned polls = 0, got = 0;
     for (;;) {                                             // acquire at system scope: the triple stored before the arrival is visible
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flags + src) : "memory");
       if (got >= want) break;
       __nanosleep(100);
-      if (++polls > PEER_WAIT_POLLS) { atomicExch(&g_merge_status, 7); return 1; }
+      if (++polls > limit) { atomicExch(&g_merge_status, 7); return 1; }
     }
   }
   return 0;
@@ -73,7 +75,7 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
     unsigned* mine_flags = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata);
     par = *reinterpret_cast<volatile int*>(mine_flags + 2 * P.x.world) & 1;
     if (READ_TRIPLES) {
-      if (tid == 0) s_bad = wait_for_triples(mine_flags + par * P.x.world, P.x.world, (unsigned)(P.M * P.nh));
+      if (tid == 0) s_bad = wait_for_triples(mine_flags + par * P.x.world, P.x.world, (unsigned)(P.M * P.nh), P.wait_polls);
       __syncthreads();
       if (s_bad) return;
       P.triples = P.x.buf[P.x.rank] + (size_t)par * (xdata / 2);
@@ -132,7 +134,7 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
     if (!FUSED) return;
     // ---- fused: every block waits for all ranks' triples (the grid is small enough to be resident as a whole, so the
     //      blocks that wait cannot keep the publishing block off the GPU), then merges them like yskn_kv4_merge_triples
-    if (d == 0) s_bad = wait_for_triples(reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata) + par * P.x.world, P.x.world, (unsigned)(P.M * P.nh));
+    if (d == 0) s_bad = wait_for_triples(reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata) + par * P.x.world, P.x.world, (unsigned)(P.M * P.nh), P.wait_polls);
     asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");
     if (s_bad) return;
     const float* trip = P.x.buf[P.x.rank] + (size_t)par * (xdata / 2);
@@ -208,20 +210,20 @@ template <bool TI, bool TO, bool PEER = false> int launch_p(const CombineP& P, i
 
 int launch_combine(const yskn_attn_g_combine_args& a, int hd, int act_dtype, cudaStream_t st) {
   if (!a.pm || !a.pl || !a.pacc || !a.o16) KV4_REJECT("yskn_kv4_combine: null buffer");
-  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g, a.bv, a.gate, a.o16, nullptr, {}};
+  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g, a.bv, a.gate, a.o16, nullptr, {}, 0u};
   return launch_p<false, false>(P, hd, act_dtype, st, "yskn_kv4_combine");
 }
 
 int launch_local_triple(const yskn_attn_g_combine_args& a, int hd, float* d_triple, cudaStream_t st) {
   if (!a.pm || !a.pl || !a.pacc || !d_triple) KV4_REJECT("yskn_kv4_local_triple: null buffer");
-  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g > 0 ? a.g : 1, nullptr, nullptr, nullptr, d_triple, {}};
+  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g > 0 ? a.g : 1, nullptr, nullptr, nullptr, d_triple, {}, 0u};
   return launch_p<false, true>(P, hd, YSKN_KV4_F16, st, "yskn_kv4_local_triple");
 }
 
 int launch_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd, const uint16_t* bv,
                          const uint16_t* gate, uint16_t* o16, int act_dtype, cudaStream_t st) {
   if (!d_triples || !o16) KV4_REJECT("yskn_kv4_merge_triples: null buffer");
-  CombineP P{nullptr, nullptr, nullptr, d_triples, ranks, M, nh, g, bv, gate, o16, nullptr, {}};
+  CombineP P{nullptr, nullptr, nullptr, d_triples, ranks, M, nh, g, bv, gate, o16, nullptr, {}, 0u};
   return launch_p<true, false>(P, hd, act_dtype, st, "yskn_kv4_merge_triples");
 }
 
@@ -238,7 +240,7 @@ size_t exchange_bytes(int world, int M, int nh, int hd) {
 int launch_push_triple(const yskn_attn_g_combine_args& a, int hd, const yskn_kv4_peer_exchange* x, cudaStream_t st) {
   if (int rc = check_exchange(x, "yskn_kv4_push_triple")) return rc;
   if (!a.pm || !a.pl || !a.pacc) KV4_REJECT("yskn_kv4_push_triple: null buffer");
-  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g > 0 ? a.g : 1, nullptr, nullptr, nullptr, nullptr, *x};
+  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g > 0 ? a.g : 1, nullptr, nullptr, nullptr, nullptr, *x, g_peer_wait_polls.load()};
   return launch_p<false, true, true>(P, hd, YSKN_KV4_F16, st, "yskn_kv4_push_triple");
 }
 
@@ -246,7 +248,7 @@ int launch_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, i
                         uint16_t* o16, int act_dtype, cudaStream_t st) {
   if (int rc = check_exchange(x, "yskn_kv4_merge_pushed")) return rc;
   if (!o16) KV4_REJECT("yskn_kv4_merge_pushed: null output");
-  CombineP P{nullptr, nullptr, nullptr, nullptr, x->world, M, nh, g, bv, gate, o16, nullptr, *x};
+  CombineP P{nullptr, nullptr, nullptr, nullptr, x->world, M, nh, g, bv, gate, o16, nullptr, *x, g_peer_wait_polls.load()};
   return launch_p<true, false, true>(P, hd, act_dtype, st, "yskn_kv4_merge_pushed");
 }
 
@@ -255,10 +257,16 @@ int launch_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, i
 int launch_exchange_merge(const yskn_attn_g_combine_args& a, int hd, int act_dtype, const yskn_kv4_peer_exchange* x, cudaStream_t st) {
   if (int rc = check_exchange(x, "yskn_kv4_exchange_merge")) return rc;
   if (!a.pm || !a.pl || !a.pacc || !a.o16) KV4_REJECT("yskn_kv4_exchange_merge: null buffer");
-  if ((long long)a.nh * a.M > 148) KV4_REJECT("yskn_kv4_exchange_merge: nh * M = %lld blocks may not all be resident; use yskn_kv4_push_triple + yskn_kv4_merge_pushed", (long long)a.nh * a.M);
-  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g > 0 ? a.g : 1, a.bv, a.gate, a.o16, nullptr, *x};
+  int dev = 0, sms = 0;
+  KV4_CUDA(cudaGetDevice(&dev));
+  KV4_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if ((long long)a.nh * a.M > sms)
+    KV4_REJECT("yskn_kv4_exchange_merge: nh * M = %lld blocks may not all be resident on %d SMs; use yskn_kv4_push_triple + yskn_kv4_merge_pushed", (long long)a.nh * a.M, sms);
+  CombineP P{a.pm, a.pl, a.pacc, nullptr, a.splits, a.M, a.nh, a.g > 0 ? a.g : 1, a.bv, a.gate, a.o16, nullptr, *x, g_peer_wait_polls.load()};
   return launch_p<true, true, true>(P, hd, act_dtype, st, "yskn_kv4_exchange_merge");
 }
+
+void set_peer_wait_polls(unsigned polls) { g_peer_wait_polls.store(polls ? polls : PEER_WAIT_POLLS); }
 
 int merge_status_fetch(int* out) {
   int v = 0;

@@ -84,6 +84,7 @@ int launch_merge_pushed(const yskn_kv4_peer_exchange* x, int M, int nh, int g, i
                         uint16_t* o16, int act_dtype, cudaStream_t st);
 int launch_exchange_merge(const yskn_attn_g_combine_args& a, int hd, int act_dtype, const yskn_kv4_peer_exchange* x, cudaStream_t st);
 int merge_status_fetch(int* out);
+void set_peer_wait_polls(unsigned polls);
 
 // Family-B row codec, step 1 (kvx_codec.cu)
 int launch_kvx_rotate(const float* x, float* y, long long rows, int inverse, cudaStream_t st);
@@ -97,5 +98,6 @@ int launch_kv8_combine(const float* pm, const float* pl, const float* pacc, int 
 
 // Which attention kernel yskn_kv4_attention picks; set through yskn_kv4_set_algo (tests compare paths).
 enum Algo { ALGO_AUTO = 0, ALGO_SCALAR = 1, ALGO_MMA = 2 };
+int current_algo();
 
 }  // namespace kv4

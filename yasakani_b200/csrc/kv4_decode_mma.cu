@@ -44,14 +44,6 @@
 namespace kv4 {
 
 __device__ int g_decode_status = 0;          // 0 ok; 1 = a consumer wait ran out; 2 = a producer wait ran out
-#ifdef KV4_DECODE_TIMING
-// Diagnostic build only: cycles summed over warps {consumer waiting for data, consumer loop, producer waiting for a
-// free stage, producer loop}.
-__device__ unsigned long long g_decode_cycles[4] = {0, 0, 0, 0};
-#define KV4_T(x) x
-#else
-#define KV4_T(x)
-#endif
 
 namespace {
 
@@ -226,14 +218,11 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
     if (nu > 0) {
       const size_t row0 = (size_t)kvh * A.max_ctx;              // first row of this kv-head in the [Hkv*max_ctx] arrays
       int issued = 0;
-      KV4_T(long long tw = 0; const long long tb = clock64();)
       for (int k = 0; k < nu; ++k) {
         const int s = k % NSTAGE, u = u0 + k;
         int go = 1;
         if (lane == 0) {
-          KV4_T(const long long t0 = clock64();)
           if (k >= NSTAGE && !mbar_wait(bar_empty + 8 * s, ((k / NSTAGE) - 1) & 1)) { atomicExch(&g_decode_status, 2); *s_abort = 1; }
-          KV4_T(tw += clock64() - t0;)
           if (*s_abort) go = 0;
         }
         go = __shfl_sync(0xffffffffu, go, 0);
@@ -258,7 +247,6 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
         }
         issued = k + 1;
       }
-      KV4_T(if (lane == 0) { atomicAdd(&g_decode_cycles[2], (unsigned long long)tw); atomicAdd(&g_decode_cycles[3], (unsigned long long)(clock64() - tb)); })
       // After an abort nobody may have consumed the last copies: wait (bounded) until they have landed before the CTA ends.
       if (lane == 0 && *s_abort)
         for (int k = max(0, issued - NSTAGE); k < issued; ++k) mbar_wait(bar_full + 8 * (k % NSTAGE), (k / NSTAGE) & 1);
@@ -489,22 +477,18 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
     };
 
     bool ok = true;
-    KV4_T(long long tw = 0; const long long tb = clock64();)
     for (int kk = warp; kk < nu * L::UG && ok; kk += NCW) {      // slot kk = (unit kk/4 of this CTA, group kk%4 of the unit)
       const int k = kk / L::UG, sub = kk % L::UG, u = u0 + k, s = k % NSTAGE;
       const bool tail = has_tail && u == nu4;
       if (tail ? sub != 0 : u * L::UG + sub >= nq) continue;     // the unit holds fewer than four groups
       const uint32_t st = sbase + L::OFF_STAGES + s * L::STAGE;
-      KV4_T(const long long t0 = clock64();)
       if (!mbar_wait(bar_full + 8 * s, (k / NSTAGE) & 1)) { atomicExch(&g_decode_status, 1); *s_abort = 1; ok = false; break; }
-      KV4_T(tw += clock64() - t0;)
       if (tail) group(std::true_type{}, st, 0, len - nq * 32);
       else group(std::false_type{}, st, sub, 32);
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_empty + 8 * s);             // one of the four arrivals that free the stage
     }
 
-    KV4_T(if (lane == 0) { atomicAdd(&g_decode_cycles[0], (unsigned long long)tw); atomicAdd(&g_decode_cycles[1], (unsigned long long)(clock64() - tb)); })
     // ---- all consumers done with the ring: publish per-warp (m, l, O) into the merge buffer
     #pragma unroll
     for (int o = 4; o <= 16; o <<= 1) {
@@ -650,14 +634,6 @@ int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_
   if (hd == 256) return rd ? launch_dt<256, 64>(a, g, act_dtype, sh, mk, mv, mr, st) : launch_dt<256, 0>(a, g, act_dtype, sh, mk, mv, mr, st);
   return rd ? launch_dt<128, 128>(a, g, act_dtype, sh, mk, mv, mr, st) : launch_dt<128, 0>(a, g, act_dtype, sh, mk, mv, mr, st);
 }
-
-#ifdef KV4_DECODE_TIMING
-extern "C" __attribute__((visibility("default"))) int yskn_kv4_debug_cycles(unsigned long long* out4) {
-  if (cudaMemcpyFromSymbol(out4, g_decode_cycles, 32) != cudaSuccess) return 1;
-  unsigned long long z[4] = {0, 0, 0, 0};
-  return cudaMemcpyToSymbol(g_decode_cycles, z, 32) != cudaSuccess;
-}
-#endif
 
 int decode_status_fetch(int* out) {
   int v = 0;

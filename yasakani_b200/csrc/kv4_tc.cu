@@ -41,14 +41,6 @@ namespace kv4 {
 
 __device__ int g_tc_status = 0;              // 0 ok; 4/5/6 = a bounded wait ran out in the softmax warps / MMA warp / producer
 
-#ifdef KV4_TC_TIMING
-// Diagnostic build only: cycles summed over softmax threads' lane 0 {wait S, TMEM load, math, wait PV/P buffer, P store+signal, tiles}.
-__device__ unsigned long long g_tc_cycles[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};   // [6..9]: issuer waits for K, P, V; issuer tiles
-__device__ long long g_tc_trace[256][8];   // leader CTA of block (0,0,0): per tile {P seen, V seen, PV issued, K seen, S(i+2) issued, softmax start, S seen, P signalled}
-#define TC_T(x) x
-#else
-#define TC_T(x)
-#endif
 
 namespace {
 
@@ -479,10 +471,8 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       const int buf = edge ? 0 : (i & 1);
       const uint32_t scol = trow + (buf ? L::TM_S1 : L::TM_S0) + 64 * hf;   // this thread's 64 S columns; P goes over the first 32
       float x[64];                                                   // raw scores of this thread's 64 keys
-      TC_T(long long c0 = clock64();)
       if (!bar_wait(b_sready + 8 * buf, srd[buf] & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
       tc_fence_after();
-      TC_T(long long c1 = clock64();)
       tmem_ld64(scol, x);
       ++srd[buf];
       if (edge) {
@@ -499,7 +489,6 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           for (int k = 0; k < 32; ++k) x[32 * h2 + k] = gk < cr ? x[32 * h2 + k] : (gk == cr && tb + k <= pr) ? a[k] : -INFINITY;
         }
       }
-      TC_T(long long c2 = clock64();)
       // ---- online softmax in the log2 domain on p = 2^(x*cs - m); lazy rescale (the running max may lag by up to 2^8)
       float tmax = fmaxf(x[0], x[1]);
       #pragma unroll
@@ -525,7 +514,6 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         for (int k = 0; k < 32; ++k) pk[k] = 0u;
         l = 0.f;
       }
-      TC_T(long long c3 = clock64();)
       // ---- O may be rescaled once P.V of tile i-1 is done (P.V of this tile waits for the signal below)
       if (i > 0 && __any_sync(0xffffffffu, bump)) {                  // rows that did not bump multiply by exactly 1
         if (!bar_wait(b_pvdone + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; break; }
@@ -539,15 +527,11 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           tmem_st32(trow + L::TM_O + 32 * c, o);
         }
       }
-      TC_T(long long c4 = clock64();)
       tmem_st32u(scol, pk);                                          // P as the A operand of P.V, over S columns this thread has read
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) bar_arrive_cluster(lead_pready + 8 * (i & 1));
-      TC_T(if (lane == 0 && warp == 0) { long long c5 = clock64(); atomicAdd(&g_tc_cycles[0], (unsigned long long)(c1 - c0)); atomicAdd(&g_tc_cycles[1], (unsigned long long)(c2 - c1));
-             atomicAdd(&g_tc_cycles[2], (unsigned long long)(c3 - c2)); atomicAdd(&g_tc_cycles[3], (unsigned long long)(c4 - c3)); atomicAdd(&g_tc_cycles[4], (unsigned long long)(c5 - c4));
-             atomicAdd(&g_tc_cycles[5], 1ull); })
     }
     // ---- this split's result per (row, head): (m, l, O) partial, or the finished row when there is one split
     if (ok && n > 0 && !bar_wait(b_pvdone + 8 * ((n - 1) & 1), ((n - 1) >> 1) & 1)) { atomicExch(&g_tc_status, 4); *s_abort = 1; ok = false; }
@@ -604,26 +588,54 @@ EncodeFn tc_encode_fn() {
   return fn;
 }
 
+// Encoded maps are kept per (kind, base, extents): a decode loop calls with the same buffers every step and
+// cuTensorMapEncodeTiled costs a few microseconds of host time per map.
+struct TcMapKey {
+  int kind; const void* base; uint64_t a, b, c, d;
+  bool operator==(const TcMapKey& o) const { return kind == o.kind && base == o.base && a == o.a && b == o.b && c == o.c && d == o.d; }
+};
+struct TcMapHash {
+  size_t operator()(const TcMapKey& k) const {
+    size_t h = std::hash<const void*>()(k.base) ^ (size_t)k.kind * 0x9E3779B97F4A7C15ull;
+    for (uint64_t v : {k.a, k.b, k.c, k.d}) h = (h ^ v) * 0x100000001B3ull;
+    return h;
+  }
+};
+template <class Make> bool tc_cached_map(CUtensorMap* out, const TcMapKey& key, Make make) {
+  static std::mutex mu; static std::unordered_map<TcMapKey, CUtensorMap, TcMapHash> cache;
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  if (!make(out)) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
 // fp16 array [rows][hd] viewed as (64 channels, rows, hd/64 channel blocks): one copy of a box (64, box_rows, box_blocks)
 // lands in shared memory as [block][row][128 bytes], 128-byte swizzle -- the tensor core's operand layout.
 bool tc_map_rows(CUtensorMap* out, const void* base, uint64_t rows, int hd, int box_rows, int box_blocks) {
-  EncodeFn fn = tc_encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[3] = {64, rows, (cuuint64_t)(hd / 64)}, strides[2] = {(cuuint64_t)hd * 2, 128};
-  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_blocks}, es[3] = {1, 1, 1};
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return tc_cached_map(out, TcMapKey{0, base, rows, (uint64_t)hd, (uint64_t)box_rows, (uint64_t)box_blocks}, [&](CUtensorMap* m) {
+    EncodeFn fn = tc_encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {64, rows, (cuuint64_t)(hd / 64)}, strides[2] = {(cuuint64_t)hd * 2, 128};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_blocks}, es[3] = {1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  });
 }
 
 // q16 [M][kvh][G][hd] viewed as 4-D; box = 64 channels x G heads x 1 kv-head x TOK tokens: rows land as (token, head).
 bool tc_map_q(CUtensorMap* out, const void* q16, int M, int kvh, int G, int hd) {
-  EncodeFn fn = tc_encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)G, (cuuint64_t)kvh, (cuuint64_t)M};
-  const cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)G * hd * 2, (cuuint64_t)kvh * G * hd * 2};
-  const cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)(128 / G)}, es[4] = {1, 1, 1, 1};
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(q16), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return tc_cached_map(out, TcMapKey{1, q16, (uint64_t)M, (uint64_t)kvh, (uint64_t)G, (uint64_t)hd}, [&](CUtensorMap* m) {
+    EncodeFn fn = tc_encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)G, (cuuint64_t)kvh, (cuuint64_t)M};
+    const cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)G * hd * 2, (cuuint64_t)kvh * G * hd * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)(128 / G)}, es[4] = {1, 1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(q16), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  });
 }
 
 struct TcWs { uint16_t* kd; uint16_t* vd; uint16_t* ks; int ks_rows; size_t bytes; };
@@ -680,19 +692,9 @@ int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int ac
   if (((uintptr_t)workspace | (uintptr_t)a.q16) & 15) KV4_REJECT("yskn_kv4_attention_tc: workspace and q16 must be 16-byte aligned");
   if (valid_tokens < 0) valid_tokens = 0;
   if (o16_direct && ((uintptr_t)o16_direct & 15)) KV4_REJECT("yskn_kv4_prefill_tc: o16 must be 16-byte aligned");
+  if (!o16_direct && ((uintptr_t)a.pacc & 15)) KV4_REJECT("yskn_kv4_attention_tc: pacc must be 16-byte aligned");
   return hd == 256 ? launch_tc_hd<256>(a, g, rd, w, valid_tokens, o16_direct, bv, st) : launch_tc_hd<128>(a, g, rd, w, valid_tokens, o16_direct, bv, st);
 }
-
-#ifdef KV4_TC_TIMING
-extern "C" __attribute__((visibility("default"))) int yskn_kv4_tc_debug_trace(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 256 * 8) != cudaSuccess;
-}
-extern "C" __attribute__((visibility("default"))) int yskn_kv4_tc_debug_cycles(unsigned long long* out12) {
-  if (cudaMemcpyFromSymbol(out12, g_tc_cycles, 96) != cudaSuccess) return 1;
-  unsigned long long z[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  return cudaMemcpyToSymbol(g_tc_cycles, z, 96) != cudaSuccess;
-}
-#endif
 
 int tc_status_fetch(int* out) {
   int v = 0;

@@ -230,6 +230,11 @@ def decode_noalloc(q16, kv: KvLayer, d_pos, splits: int, rope, nh: int, qscale: 
           "yskn_kv4_decode_noalloc")
 
 
+def set_peer_wait_polls(polls: int) -> None:
+    """Limit of the wait for the other shards' triples in polls of ~100 ns; 0 restores the default (yskn_kv4_set_peer_wait_polls)."""
+    check(_lib.load().yskn_kv4_set_peer_wait_polls(int(polls)), "yskn_kv4_set_peer_wait_polls")
+
+
 def exchange_bytes(world: int, M: int, nh: int, hd: int) -> int:
     return int(_lib.load().yskn_kv4_exchange_bytes(world, M, nh, hd))
 
