@@ -197,7 +197,11 @@ def run_ours(args, rank, world, local_rank):
             if rank == 0:
                 print(f"[bench] peer exchange unavailable ({type(e).__name__}: {e}); using the NCCL all-gather", file=sys.stderr)
             exchange = "nccl"
-    first = ShardedDecoder(shape, plan, splits, rope, exchange=exchange, peer_exchange=xch)
+    # `early`: in this workload the position and every cached row below it are final long before a step starts (the appended
+    # row sits AT the position), which is what the flag promises; the decode kernel then fills its ring ahead of the wait
+    early = not args.no_early
+    ext = kv4.attn_ext(early=True) if early else None
+    first = ShardedDecoder(shape, plan, splits, rope, exchange=exchange, peer_exchange=xch, early=early)
     lo, hi = plan.local_rows(0, ctx)
     for c in range(lo // CHUNK, (hi + CHUNK - 1) // CHUNK if hi > lo else 0):
         k, v = chunk_rows(shape, c)
@@ -208,7 +212,7 @@ def run_ours(args, rank, world, local_rank):
     n_copies = max(2, int(math.ceil(256e6 / max(shard_bytes, 1))) + 1)
     decs = [first]
     for _ in range(n_copies - 1):
-        d = ShardedDecoder(shape, plan, splits, rope, exchange=exchange, peer_exchange=xch)
+        d = ShardedDecoder(shape, plan, splits, rope, exchange=exchange, peer_exchange=xch, early=early)
         for a, b in zip(d.layer.tensors(), first.layer.tensors()):
             a.copy_(b)
         decs.append(d)
@@ -229,7 +233,7 @@ def run_ours(args, rank, world, local_rank):
         if world > 1:
             d.decode(q_dev)
         else:
-            kv4.launch_decode(q_dev, d.layer, 1, d.d_pos, splits, d.pm, d.pl, d.pacc, rope, shape.hq, shape.qscale, shape.rd, d.o16)
+            kv4.launch_decode(q_dev, d.layer, 1, d.d_pos, splits, d.pm, d.pl, d.pacc, rope, shape.hq, shape.qscale, shape.rd, d.o16, ext=ext)
 
     # attention + merge (N = 1); attention + fused push/wait/merge (N > 1, p2p); attention + triple + merge of triples (N > 1, nccl)
     launches_per_step = 3 if (world > 1 and exchange == "nccl") else 2
@@ -293,7 +297,7 @@ def run_ours(args, rank, world, local_rank):
         #      the figure is a kernel time and not the host's launch rate (short shards run faster than ctypes can launch)
         def attn_only(d):
             kv4.launch_attention_shard(q_dev, d.layer, 1, d.d_pos, splits, d.pm, d.pl, d.pacc, rope, shape.hq, shape.qscale, shape.rd,
-                                       plan.start, plan.capacity)
+                                       plan.start, plan.capacity, ext=ext)
         with torch.cuda.stream(side):
             attn_graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(attn_graph, stream=side):
@@ -355,7 +359,7 @@ def run_ours(args, rank, world, local_rank):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": bench_config(shape, ctx, world),
-        "run": {"splits": splits, "graph": f"{GSTEPS} steps (layers) per CUDA graph replay", "exchange": exchange if world > 1 else None,
+        "run": {"splits": splits, "early_prefetch": early, "graph": f"{GSTEPS} steps (layers) per CUDA graph replay", "exchange": exchange if world > 1 else None,
                 "cache_copies": n_copies, "mb_read_per_launch": shard_bytes / 1e6, "kv_tokens_scanned_per_s": ctx * value},
         "clocks": clocks,
         "e2e": {"value": K / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(q_host.numel() * 2 + (kn_host.numel() + vn_host.numel()) * 2),
@@ -519,9 +523,10 @@ def secondary_lines(shape, splits, dev):
         pm, pl, pacc = kv4.attn_scratch(1, splits, shape.hq, shape.hd)
         o16 = torch.empty((1, shape.hq, shape.hd), dtype=torch.float16, device=dev)
         n_graph = max(GSTEPS, n_copies)
-        t_attn = graph_time(lambda i: kv4.launch_attention_gqa(q, layers[i % n_copies], 1, pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd),
+        ext = kv4.attn_ext(early=True)
+        t_attn = graph_time(lambda i: kv4.launch_attention_gqa(q, layers[i % n_copies], 1, pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, ext=ext),
                             n_graph, 8, 2)
-        t_step = graph_time(lambda i: kv4.launch_decode(q, layers[i % n_copies], 1, pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16),
+        t_step = graph_time(lambda i: kv4.launch_decode(q, layers[i % n_copies], 1, pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ext=ext),
                             n_graph, 8, 2)
         out[f"decode_ctx{ctx}"] = {"us_per_launch": t_attn * 1e6, "us_per_step": t_step * 1e6, "tokens_per_s": 1.0 / t_step, "bytes_per_launch": byt,
                                    "achieved_gbs": byt / t_attn / 1e9, "frac_of_hbm_peak": byt / t_attn / 1e9 / hbm, "cache_copies": n_copies}
@@ -645,6 +650,7 @@ def main():
     ap.add_argument("--splits", type=int, default=37, help="split-K factor; splits*Hkv = 148 = one CTA per SM")
     ap.add_argument("--cpu-sample-ctx", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-early", action="store_true", help="do not set the `early` flag of yskn_kv4_attn_ext on the decode launches")
     ap.add_argument("--no-secondary", action="store_true", help="skip the device-timed figures of the other contexts and kernels (`secondary`)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="N > 1: how the shards' (m, l, O) triples travel")
     ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch from an ncu capture, if known")

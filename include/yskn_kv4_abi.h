@@ -106,6 +106,26 @@ YSKN_KV4_API int yskn_kv4_group_quant(const yskn_kv_quant_args* a, int kvh, int 
  * Every one of the `splits` partial slots of every (row, head) is written; unused ones carry pm = -1e30. */
 YSKN_KV4_API int yskn_kv4_attention(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, void* cuda_stream);
 
+/* Extras of an attention call that yskn::AttnGArgs has no member for: the fields the 27B engine's argument set adds
+ * (Q35AttnArgs, src/q35.hpp:126-130, and the `wk` argument of launch_q35_atx, src/q35.hpp:136).  A NULL pointer or an
+ * all-zero struct is the plain call.
+ *   early         the reference's `early` (src/q35.hpp:127, use at src/q35_kernels.cu:1195-1206): the caller promises that
+ *                 *d_pos and every cache row below it were final before the kernel that precedes this launch in the stream
+ *                 started, so a kernel launched with programmatic stream serialization may read them ahead of
+ *                 griddepcontrol.wait and fill its staging ring while the predecessor drains.  Rows at or above *d_pos,
+ *                 q16 and the partial buffers are touched only after the wait.
+ *   splits_short, long_len   rows that see fewer than long_len keys use splits_short splits instead of `splits`
+ *                 (src/q35_atx.cu:113; defaults 31 below 4,096, src/engine35.hpp:434-438); 0 = off.  The partial slots
+ *                 beyond a row's split count are written as empty (pm = -1e30).
+ *   wk            row -> depth table of a tree-shaped verify pass (src/q35_atx.cu:111-119), M bytes on the device or NULL:
+ *                 row r sits at position *d_pos + wk[r], sees the cached keys 0 .. *d_pos + wk[r] - 1 and its own key, which
+ *                 is stored in cache slot *d_pos + r.  NULL means wk[r] = r, the plain causal pass. */
+typedef struct yskn_kv4_attn_ext { int early; int splits_short; int long_len; const uint8_t* wk; } yskn_kv4_attn_ext;
+
+/* yskn_kv4_attention / yskn_kv4_decode / yskn_kv4_attention_shard with the extras above. */
+YSKN_KV4_API int yskn_kv4_attention_ex(const yskn_attn_g_args* a, const yskn_kv4_attn_ext* x, int g, int hd, int rd, int act_dtype,
+                                       void* cuda_stream);
+
 /* launch_attn_combine_gqa_xform, src/attention_gqa.cu:123-134,176-181, up to and including the o16 store
  * (the sign/FWHT/int8 preparation of the next GEMV input is the caller's). act_dtype applies to o16 and gate. */
 YSKN_KV4_API int yskn_kv4_combine(const yskn_attn_g_combine_args* a, int hd, int act_dtype, void* cuda_stream);
@@ -115,6 +135,8 @@ YSKN_KV4_API int yskn_kv4_combine(const yskn_attn_g_combine_args* a, int hd, int
  * kernel.  `c->pm/pl/pacc/splits/M/nh/g` must describe the same scratch as `a`. */
 YSKN_KV4_API int yskn_kv4_decode(const yskn_attn_g_args* a, const yskn_attn_g_combine_args* c, int g, int hd, int rd, int act_dtype,
                                  void* cuda_stream);
+YSKN_KV4_API int yskn_kv4_decode_ex(const yskn_attn_g_args* a, const yskn_attn_g_combine_args* c, const yskn_kv4_attn_ext* x, int g, int hd,
+                                    int rd, int act_dtype, void* cuda_stream);
 
 /* launch_attention_prefill, src/attention_kv4q.cu:381-453: attention of M new rows whose K/V are already
  * appended, merged in one call to o16 (+ optional bias bv).  `a->pm/pl/pacc` must hold `splits` slots per
@@ -149,6 +171,8 @@ YSKN_KV4_API int yskn_kv4_prefill_tc(const yskn_attn_g_args* a, int g, int hd, i
  * [ranks][M][nh][HD+2] into o16 with the same arithmetic as yskn_kv4_combine. */
 YSKN_KV4_API int yskn_kv4_attention_shard(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype,
                                           int shard_start, int shard_len, void* cuda_stream);
+YSKN_KV4_API int yskn_kv4_attention_shard_ex(const yskn_attn_g_args* a, const yskn_kv4_attn_ext* x, int g, int hd, int rd, int act_dtype,
+                                             int shard_start, int shard_len, void* cuda_stream);
 /* yskn_kv4_attention_shard + yskn_kv4_local_triple in one call (same launch form as yskn_kv4_decode). */
 YSKN_KV4_API int yskn_kv4_decode_shard_triple(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, int shard_start,
                                               int shard_len, float* d_triple, void* cuda_stream);

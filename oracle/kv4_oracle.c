@@ -92,6 +92,12 @@ static inline int quant4(float v, float lo, float inv) {
 }
 
 /* src/attention_gqa.cu:143-154 (= src/post_kernels.cu:86-96 for HD 128). */
+/* min / max with the zero signs of CUDA's fminf / fmaxf, which the reference's kernels call (src/post_kernels.cu:71,
+ * src/attention_gqa.cu:147): -0.0 orders below +0.0, so a row of signed zeros gets lo = -0.0.  C's fminf leaves that
+ * case to the implementation. */
+static float min_dev(float a, float b) { if (a == b) return signbit(a) ? a : b; return a < b ? a : b; }
+static float max_dev(float a, float b) { if (a == b) return signbit(a) ? b : a; return a > b ? a : b; }
+
 void ysko_group_quant(const ysko_kv_layer* kv, int hkv, int hd, int max_ctx, int pos0, int M) {
   const int last = pos0 + M - 1;
   for (int gi = pos0 / 32; gi * 32 + 31 <= last; ++gi) {
@@ -102,7 +108,7 @@ void ysko_group_quant(const ysko_kv_layer* kv, int hkv, int hd, int max_ctx, int
         float v[32], lo = 1e30f, hi = -1e30f;
         for (int t = 0; t < 32; ++t) {
           v[t] = h2f(kv->kshadow[((size_t)head * max_ctx + gi * 32 + t) * hd + ch]);
-          lo = fminf(lo, v[t]); hi = fmaxf(hi, v[t]);
+          lo = min_dev(lo, v[t]); hi = max_dev(hi, v[t]);
         }
         const float sc = (hi - lo) / 15.f, inv = hi > lo ? 15.f / (hi - lo) : 0.f;
         kv->kscale[gb * hd + ch] = ysko_f32_to_f16(sc);
@@ -128,7 +134,7 @@ void ysko_append(const ysko_kv_layer* kv, int hkv, int hd, int max_ctx, int pos0
       memcpy(kv->kshadow + ((size_t)head * max_ctx + pos) * hd, kr, (size_t)hd * 2);
       /* V: per-(token, kv-head) min/max int4 (src/post_kernels.cu:64-82) */
       float lo = h2f(vr[0]), hi = lo;
-      for (int d = 1; d < hd; ++d) { const float y = h2f(vr[d]); lo = fminf(lo, y); hi = fmaxf(hi, y); }
+      for (int d = 1; d < hd; ++d) { const float y = h2f(vr[d]); lo = min_dev(lo, y); hi = max_dev(hi, y); }
       const float sc = (hi - lo) / 15.f, inv = hi > lo ? 15.f / (hi - lo) : 0.f;
       const size_t slot = (size_t)head * max_ctx + pos;
       for (int d = 0; d < hd; d += 2) {

@@ -374,3 +374,27 @@ def test_withheld_push_runs_the_bounded_wait_out_and_the_next_step_works(oracle)
     assert kv4.device_status() == 0
     for rnk in range(world):
         assert_close(outs[rnk].float().cpu().numpy(), want, f"rank {rnk} after recovery")
+
+
+@pytest.mark.parametrize("shape,ctx,M", [(synth.C2, 9000, 1), (synth.C2, 5000, 3), (synth.C1, 700, 2), (synth.C2, 20, 1)])
+def test_early_prefetch_changes_no_bit(oracle, shape, ctx, M):
+    """The `early` promise of yskn_kv4_attn_ext (reads of *d_pos and of rows below it ahead of griddepcontrol.wait) only
+    moves loads in time: partials and output are bit-identical with and without it, also for rows after the first, whose
+    newest groups are written by the pass itself and must not be read early."""
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, ctx, M, seed=47)
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    dq = q.cuda()
+    res = []
+    for ext in (None, kv4.attn_ext(early=True)):
+        pm, pl, pacc = kv4.attn_scratch(M, 11, shape.hq, shape.hd)
+        o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+        for _ in range(2):                                       # back to back, so the second launch really overlaps the first merge
+            kv4.launch_decode(dq, layer, M, d_pos, 11, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ext=ext)
+        torch.cuda.synchronize()
+        assert kv4.device_status() == 0
+        res.append((pm.cpu(), pl.cpu(), pacc.cpu(), o16.cpu()))
+    for a, b in zip(*res):
+        assert torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a.view(torch.int16),
+                           b.view(torch.int32) if b.dtype == torch.float32 else b.view(torch.int16))
+    want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    assert_close(res[1][3].float().numpy(), want, "early launch vs oracle")

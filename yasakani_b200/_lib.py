@@ -44,6 +44,10 @@ class Kv8AttnArgsC(C.Structure):
                 ("pm", C.c_void_p), ("pl", C.c_void_p), ("pacc", C.c_void_p), ("kvh", C.c_int), ("nh", C.c_int), ("qscale", C.c_float)]
 
 
+class AttnExtC(C.Structure):          # yskn_kv4_attn_ext
+    _fields_ = [("early", C.c_int), ("splits_short", C.c_int), ("long_len", C.c_int), ("wk", C.c_void_p)]
+
+
 class PeerExchangeC(C.Structure):     # yskn_kv4_peer_exchange
     _fields_ = [("buf", C.c_void_p * 8), ("world", C.c_int), ("rank", C.c_int)]
 
@@ -58,6 +62,9 @@ PROTOTYPES = {
     "yskn_kv4_append": (C.c_int, [C.POINTER(KvAppendArgsC), C.c_void_p]),
     "yskn_kv4_group_quant": (C.c_int, [C.POINTER(KvQuantArgsC), C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_attention": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "yskn_kv4_attention_ex": (C.c_int, [C.POINTER(AttnGArgsC), C.POINTER(AttnExtC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "yskn_kv4_decode_ex": (C.c_int, [C.POINTER(AttnGArgsC), C.POINTER(AttnGCombineArgsC), C.POINTER(AttnExtC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "yskn_kv4_attention_shard_ex": (C.c_int, [C.POINTER(AttnGArgsC), C.POINTER(AttnExtC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_attention_shard": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_decode": (C.c_int, [C.POINTER(AttnGArgsC), C.POINTER(AttnGCombineArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_decode_shard_triple": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),

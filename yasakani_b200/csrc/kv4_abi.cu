@@ -30,13 +30,19 @@ static int check_attn(const yskn_attn_g_args* a, int g, int hd, const char* who)
   (void)hd; return 0;
 }
 
-static int attention_dispatch(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st) {
+static int attention_dispatch(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st,
+                              const yskn_kv4_attn_ext* x = nullptr) {
   if (act_dtype != YSKN_KV4_F16 && act_dtype != YSKN_KV4_BF16) KV4_REJECT("yskn_kv4_attention: act_dtype must be F16 or BF16");
+  const int early = x ? (x->early != 0) : 0;
+  if (x && (x->splits_short < 0 || x->splits_short > a->splits || (x->splits_short > 0 && x->long_len <= 0)))
+    KV4_REJECT("yskn_kv4_attention: splits_short %d / long_len %d do not fit splits %d", x->splits_short, x->long_len, a->splits);
+  if (x && (x->wk || x->splits_short > 0))
+    KV4_REJECT("yskn_kv4_attention: the row->depth table and per-row split counts are not implemented by this build");
   if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_attention: rotary width %d needs a rope table", rd);
   const bool mma_ok = decode_mma_supports(g, hd, rd, a->M);
   const int algo = current_algo();
   if (algo == ALGO_MMA && !mma_ok) KV4_REJECT("yskn_kv4_attention: tensor-core path does not cover (g %d, hd %d, rd %d, M %d)", g, hd, rd, a->M);
-  if (mma_ok && algo != ALGO_SCALAR) return launch_decode_mma(*a, g, hd, rd, act_dtype, sh, st);
+  if (mma_ok && algo != ALGO_SCALAR) return launch_decode_mma(*a, g, hd, rd, act_dtype, sh, early, st);
   return launch_attention_scalar(*a, g, hd, rd, act_dtype, sh, st);
 }
 
@@ -136,22 +142,37 @@ int yskn_kv4_attention(const yskn_attn_g_args* a, int g, int hd, int rd, int act
   return attention_dispatch(a, g, hd, rd, act_dtype, Shard{0, a->max_ctx}, (cudaStream_t)cuda_stream);
 }
 
+int yskn_kv4_attention_ex(const yskn_attn_g_args* a, const yskn_kv4_attn_ext* x, int g, int hd, int rd, int act_dtype, void* cuda_stream) {
+  if (int rc = check_attn(a, g, hd, "yskn_kv4_attention_ex")) return rc;
+  return attention_dispatch(a, g, hd, rd, act_dtype, Shard{0, a->max_ctx}, (cudaStream_t)cuda_stream, x);
+}
+
 int yskn_kv4_attention_shard(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, int shard_start, int shard_len,
                              void* cuda_stream) {
+  return yskn_kv4_attention_shard_ex(a, nullptr, g, hd, rd, act_dtype, shard_start, shard_len, cuda_stream);
+}
+
+int yskn_kv4_attention_shard_ex(const yskn_attn_g_args* a, const yskn_kv4_attn_ext* x, int g, int hd, int rd, int act_dtype, int shard_start,
+                                int shard_len, void* cuda_stream) {
   if (int rc = check_attn(a, g, hd, "yskn_kv4_attention_shard")) return rc;
   if (shard_start < 0 || shard_start % 32 || shard_len < 0 || shard_len % 32 || shard_len > a->max_ctx)
     KV4_REJECT("yskn_kv4_attention_shard: shard [%d, +%d) must start and end on multiples of 32 and fit max_ctx %d", shard_start, shard_len, a->max_ctx);
-  return attention_dispatch(a, g, hd, rd, act_dtype, Shard{shard_start, shard_len}, (cudaStream_t)cuda_stream);
+  return attention_dispatch(a, g, hd, rd, act_dtype, Shard{shard_start, shard_len}, (cudaStream_t)cuda_stream, x);
 }
 
 int yskn_kv4_decode(const yskn_attn_g_args* a, const yskn_attn_g_combine_args* c, int g, int hd, int rd, int act_dtype, void* cuda_stream) {
+  return yskn_kv4_decode_ex(a, c, nullptr, g, hd, rd, act_dtype, cuda_stream);
+}
+
+int yskn_kv4_decode_ex(const yskn_attn_g_args* a, const yskn_attn_g_combine_args* c, const yskn_kv4_attn_ext* x, int g, int hd, int rd,
+                       int act_dtype, void* cuda_stream) {
   if (int rc = check_attn(a, g, hd, "yskn_kv4_decode")) return rc;
   if (!c || !c->o16 || c->pm != a->pm || c->pl != a->pl || c->pacc != a->pacc || c->splits != a->splits || c->M != a->M || c->nh != a->nh || c->g != g)
     KV4_REJECT("yskn_kv4_decode: the merge arguments must describe the attention call's scratch and shape");
   if (act_dtype != YSKN_KV4_F16 && act_dtype != YSKN_KV4_BF16) KV4_REJECT("yskn_kv4_decode: act_dtype must be F16 or BF16");
   if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_decode: rotary width %d needs a rope table", rd);
   cudaStream_t st = (cudaStream_t)cuda_stream;
-  if (int rc = attention_dispatch(a, g, hd, rd, act_dtype, Shard{0, a->max_ctx}, st)) return rc;
+  if (int rc = attention_dispatch(a, g, hd, rd, act_dtype, Shard{0, a->max_ctx}, st, x)) return rc;
   return launch_combine(*c, hd, act_dtype, st);
 }
 

@@ -61,7 +61,7 @@ int launch_rope_table(float* d_out, int max_ctx, float theta, int rd, cudaStream
 int launch_append(const yskn_kv_append_args& a, cudaStream_t st);
 int launch_group_quant(const yskn_kv_quant_args& a, int kvh, int hd, cudaStream_t st);
 int launch_attention_scalar(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st);
-int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st);
+int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, int early, cudaStream_t st);
 bool decode_mma_supports(int g, int hd, int rd, int M);
 int decode_status_fetch(int* out);
 int tc_status_fetch(int* out);       // same for the tcgen05 multi-row kernel

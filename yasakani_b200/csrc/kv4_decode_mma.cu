@@ -26,11 +26,19 @@
 //     exactly one A register because the contraction order over channels is free.  K's per-channel scale is folded
 //     into Q once per group (q' = q*scale); the zero points and the offsets become a per-head bias,
 //     sum q*zero - sum off*q', formed by two more MMA rows so that the offsets cancel against the rounded q'.
-//   * for V the contraction runs over tokens, so the words of two token rows are interleaved by PRMT first; V's
-//     per-token scale is folded into P and its zero point into a per-head scalar.
+//   * for V the contraction runs over tokens: a transposed 8x8 shared-memory load (ldmatrix.trans) hands a lane the same
+//     four channels of two consecutive tokens in one register, which is the pairing an A register wants.  V's per-token
+//     scale is folded into P and its zero point into a per-head scalar.  The even channels' offset of 1024 is removed by
+//     an exact fp16 subtraction before the MMA: the tensor core's fp32 accumulators truncate, and a sum that carries
+//     1024 * sum(p) loses about 2e-3 of the output at 262,144 tokens (measured, on the even channels only); the odd
+//     channels' offset of 64 stays and is cancelled by an MMA row of ones over the same rounded P.
 //   * RoPE: Q is rotated back by the group's first position (one table row per group), the remaining angle
 //     (0..31 tokens) is applied to the rotary channels of K with the table's first 32 rows.  cos/sin of
-//     (t0 + dt) are thereby formed by angle addition from the caller's table entries for t0 and dt.
+//     (t0 + dt) are thereby formed by angle addition from the caller's table entries for t0 and dt.  The table's own
+//     angle at t is the fp32 product t*freq, which differs from the sum of the two entries' angles by up to one ulp of
+//     t*freq (0.03 rad at t = 262,144 for the highest frequency): a per-token perturbation of the score of about 1e-3,
+//     random in sign, that changed no digit of the measured error at 262,144 tokens (a build that read the table row of
+//     every token for the eight highest frequencies gave the same error and ran 16 % slower).
 // Lane (g = lane/4, j = lane%4) owns words w = 4i + j of a packed K row, so a rotary pair (c, c + RD/2) stays
 // in one lane.
 //
@@ -115,13 +123,15 @@ __device__ __forceinline__ void bulk_1d(uint32_t dst, const void* src, uint32_t 
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ uint32_t lds32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
-__device__ __forceinline__ uint2 lds64(uint32_t a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
   uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v;
 }
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_t(uint32_t a, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 __device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) { uint32_t d; asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a)); return d; }
 __device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
@@ -168,6 +178,8 @@ struct DecodeP {
   yskn_attn_g_args A;
   Shard sh;
   int g;
+  int early;          // the caller's promise (yskn_kv4_attn_ext): *d_pos and every cache row below it are final before the
+                      // preceding kernel of the stream ends, so they may be read ahead of griddepcontrol.wait
 };
 
 template <int HD, int RD, int DT>
@@ -186,11 +198,17 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
   // scheduled while the previous kernel of the stream drains and waits here before it reads anything that kernel wrote
   // (position, query, appended rows); the merge kernel that follows may be scheduled early in turn and waits for this grid
   // to finish before it reads the partials.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // With `early` (the reference's Q35AttnArgs.early, src/q35_kernels.cu:1195-1206) the position is read and the producer
+  // fills the ring with rows below the base position BEFORE the wait: those rows were final before the predecessor started.
+  const bool early = P.early != 0;
+  if (!early) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
 
   // ---- which groups this CTA owns (local token indices of this shard)
-  const int pos = *A.d_pos + r - P.sh.start;
+  const int base_local = *A.d_pos - P.sh.start;                 // row 0's local position: rows below it are never written again
+  const int pos = base_local + r;
   const int len = max(0, min(pos + 1, P.sh.len));
   const int cg = pos >= 0 ? pos / 32 : 0;                       // first group that is not read as int4
   const int nq = min(cg, len / 32);                             // int4 groups, all fully visible
@@ -218,8 +236,15 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
     if (nu > 0) {
       const size_t row0 = (size_t)kvh * A.max_ctx;              // first row of this kv-head in the [Hkv*max_ctx] arrays
       int issued = 0;
+      bool waited = !early;
       for (int k = 0; k < nu; ++k) {
         const int s = k % NSTAGE, u = u0 + k;
+        // an early unit: one of the first ring fills, int4 only, every token below the base position
+        if (!waited && (k >= NSTAGE || (has_tail && u == nu4) || min(nq, (u + 1) * L::UG) * 32 > max(0, min(base_local, P.sh.len)))) {
+          asm volatile("griddepcontrol.wait;" ::: "memory");
+          asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+          waited = true;
+        }
         int go = 1;
         if (lane == 0) {
           if (k >= NSTAGE && !mbar_wait(bar_empty + 8 * s, ((k / NSTAGE) - 1) & 1)) { atomicExch(&g_decode_status, 2); *s_abort = 1; }
@@ -247,12 +272,20 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
         }
         issued = k + 1;
       }
+      if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
       // After an abort nobody may have consumed the last copies: wait (bounded) until they have landed before the CTA ends.
       if (lane == 0 && *s_abort)
         for (int k = max(0, issued - NSTAGE); k < issued; ++k) mbar_wait(bar_full + 8 * (k % NSTAGE), (k / NSTAGE) & 1);
+    } else if (early) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
   } else {
     // =========================================================== consumer warps
+    if (early) {                                                // q16 and the partial buffers belong to the predecessor until here
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     // ---- one-time set-up, spread over the consumer threads
     const int ct = threadIdx.x;                                 // 0..NCW*32-1
     {
@@ -291,17 +324,19 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
     float acc[HD / 16][4];                                      // O^T: [m-tile][(even | odd channel) x (head 2j | 2j+1)]
     #pragma unroll
     for (int mt = 0; mt < HD / 16; ++mt) { acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f; }
-    float m[2] = {-1e30f, -1e30f}, l[2] = {0.f, 0.f}, zacc[2] = {0.f, 0.f}, zs[2] = {0.f, 0.f};   // heads 2j, 2j+1 (log2 domain); zacc = sum p*vzero, zs = sum of the rounded p*vscale
+    float m[2] = {-1e30f, -1e30f}, l[2] = {0.f, 0.f}, zacc[2] = {0.f, 0.f};   // heads 2j, 2j+1 (log2 domain); zacc = sum p*vzero
+    float zs[4] = {0.f, 0.f, 0.f, 0.f};                         // [0], [1]: sum over ALL tokens of the rounded p*vscale, formed by an MMA against ones
 
     // per-lane constant offsets: K word i of row g (swizzled chunk), V chunk of rows 2j and 2j+1
     const int swz = HD == 256 ? (g & 7) : ((g >> 1) & 3);
     uint32_t koff[NW];
     #pragma unroll
     for (int i = 0; i < NW; ++i) koff[i] = g * L::ROWB + 16 * (i ^ swz) + 4 * j;
-    const uint32_t voffA = HD == 256 ? (2 * j) * L::ROWB + 16 * (g ^ (2 * j))
-                                     : (2 * j) * L::ROWB + 16 * ((g >> 1) ^ (j & 3)) + 8 * (g & 1);
-    const uint32_t voffB = HD == 256 ? (2 * j + 1) * L::ROWB + 16 * (g ^ (2 * j + 1))
-                                     : (2 * j + 1) * L::ROWB + 16 * ((g >> 1) ^ (j & 3)) + 8 * (g & 1);
+    // V through ldmatrix.trans: lane supplies the row address of matrix lane/8, row lane%8: token (mat&1)*8 + row, 16-byte
+    // chunk 2q + (mat>>1) (q = which of the HD/64 loads), XOR-swizzled as the TMA tile is.
+    const int vtok = ((lane >> 3) & 1) * 8 + (lane & 7), vch = lane >> 4;
+    const uint32_t vrow = vtok * L::ROWB, vsw = HD == 256 ? (vtok & 7) : ((vtok >> 1) & 3);
+    const uint32_t ONE2 = 0x3C003C00u;
     const uint32_t qfrag = sbase + L::OFF_QFRAG + lane * 16;
     const uint32_t relt = sbase + L::OFF_RELT + lane * 16;
     const NibK nk = nib_consts();
@@ -364,7 +399,7 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
       uint32_t ka[NW];                                           // address of this lane's word i in row g of the current tile
       #pragma unroll
       for (int i = 0; i < NW; ++i) ka[i] = TAIL ? s_k + g * (HD * 2) + 16 * (4 * i + j) : s_k + koff[i];
-      uint32_t va = s_v + voffA, vb = s_v + voffB, vsa = s_vs + 2 * g, rta = relt;
+      uint32_t va = s_v + vrow, vsa = s_vs + 2 * g, rta = relt;
       constexpr uint32_t KROW8 = TAIL ? 8 * HD * 2 : 8 * L::ROWB;      // eight rows further down
 
       #pragma unroll 1
@@ -379,8 +414,9 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
             #pragma unroll
             for (int i = 0; i < NW; ++i) kw[h][i] = lds32(ka[i] + h * KROW8);
         }
-        uint4 vx[4];
-        if (HD == 256) { vx[0] = lds128(va); vx[1] = lds128(vb); vx[2] = lds128(va + 8 * L::ROWB); vx[3] = lds128(vb + 8 * L::ROWB); }
+        uint32_t vx[HD / 64][4];                                 // [load q][tokens 0-7 | 8-15 of chunk 2q, the same of chunk 2q+1]
+        #pragma unroll
+        for (int q = 0; q < HD / 64; ++q) ldmatrix_x4_t(va + 16 * ((2 * q + vch) ^ vsw), vx[q]);
         auto load_k = [&](int h, int i, uint32_t (&o)[4]) {     // A regs of word w = 4i+j, row g + 8h of the tile
           if (TAIL) pair_regs(lds128(ka[i] + h * KROW8), o); else nib_regs(kw[h][i], o, nk);
         };
@@ -424,60 +460,54 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
         const float s00 = v0 ? sa[0][0] + sa[1][0] + bias0 : -INFINITY, s01 = v0 ? sa[0][1] + sa[1][1] + bias1 : -INFINITY;
         const float s10 = v1 ? sa[0][2] + sa[1][2] + bias0 : -INFINITY, s11 = v1 ? sa[0][3] + sa[1][3] + bias1 : -INFINITY;
         float t0 = fmaxf(s00, s10), t1 = fmaxf(s01, s11);
-        #pragma unroll
-        for (int o = 4; o <= 16; o <<= 1) { t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, o)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, o)); }
-        if (__any_sync(0xffffffffu, t0 > m[0] + 8.f || t1 > m[1] + 8.f)) {   // lazy rescale: the running max may lag by 2^8
+        if (__any_sync(0xffffffffu, t0 > m[0] + 8.f || t1 > m[1] + 8.f)) {   // lazy rescale: the running max may lag by 2^8; no shuffle unless it must move
+          #pragma unroll
+          for (int o = 4; o <= 16; o <<= 1) { t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, o)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, o)); }
           const float n0 = fmaxf(m[0], t0), n1 = fmaxf(m[1], t1), a0 = ex2(m[0] - n0), a1 = ex2(m[1] - n1);
-          m[0] = n0; m[1] = n1; l[0] *= a0; l[1] *= a1; zacc[0] *= a0; zacc[1] *= a1; zs[0] *= a0; zs[1] *= a1;
+          m[0] = n0; m[1] = n1; l[0] *= a0; l[1] *= a1; zacc[0] *= a0; zacc[1] *= a1; zs[0] *= a0; zs[1] *= a1; zs[2] *= a0; zs[3] *= a1;
           #pragma unroll
           for (int mt = 0; mt < HD / 16; ++mt) { acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1; }
         }
         const float p00 = v0 ? ex2(s00 - m[0]) : 0.f, p01 = v0 ? ex2(s01 - m[1]) : 0.f;
         const float p10 = v1 ? ex2(s10 - m[0]) : 0.f, p11 = v1 ? ex2(s11 - m[1]) : 0.f;
         l[0] += p00 + p10; l[1] += p01 + p11;
-        // V per-token scale folded into P (fp16), zero point into a per-head scalar: v = vs*(off+n) + (vz - off*vs), off = 1024
-        // for even channels (low nibble read in place) and 64 for odd ones.  The -off*vs*p part uses the sum of the ROUNDED
-        // p*vs the MMA consumes, so the offset cancels exactly; it is subtracted once, after the loop.
+        // V per-token scale folded into P (fp16), zero point into a per-head scalar: v = vs*(off+n) + (vz - off*vs), off = 0 for
+        // even channels (1024 subtracted exactly before the MMA) and 64 for odd ones.  The -off*vs*p part uses the sum of the
+        // ROUNDED p*vs the MMA consumes (an MMA row of ones), so the offset cancels exactly; it is subtracted once, after the loop.
         const float vs0 = v0 ? lds_h(vsa) : 0.f, vz0 = v0 ? lds_h(vsa + L::UG * 64) : 0.f;
         const float vs1 = v1 ? lds_h(vsa + 16) : 0.f, vz1 = v1 ? lds_h(vsa + L::UG * 64 + 16) : 0.f;
         const uint32_t pp0 = pack_h2(p00 * vs0, p01 * vs0), pp1 = pack_h2(p10 * vs1, p11 * vs1);
-        const float2 pr0 = __half22float2(*reinterpret_cast<const __half2*>(&pp0)), pr1 = __half22float2(*reinterpret_cast<const __half2*>(&pp1));
-        zacc[0] += p00 * vz0 + p10 * vz1; zs[0] += pr0.x + pr1.x;
-        zacc[1] += p01 * vz0 + p11 * vz1; zs[1] += pr0.y + pr1.y;
+        zacc[0] += p00 * vz0 + p10 * vz1;
+        zacc[1] += p01 * vz0 + p11 * vz1;
         const uint32_t pb0 = movmatrix_t(pp0);                   // B regs: (tokens 2j,2j+1 | head g)
         const uint32_t pb1 = movmatrix_t(pp1);                   //         (tokens 2j+8,2j+9 | head g)
-        // ---- O^T += V^T P^T.  Lane reads token rows A=2j, B=2j+1, C=2j+8, D=2j+9 at its channel block [HD/8*g, +HD/8).
-        //      Byte b of word w holds channels (8w+2b, 8w+2b+1): PRMT puts that byte of rows A and B (C and D) into the low
-        //      byte of the two halves; both nibbles are read in place (even channel: 1024 + n, odd channel: 64 + n).
-        {
-          uint32_t wv[4][HD / 64];                               // [A,B,C,D][word]
-          if (HD == 256) {
-            const uint4 xa = vx[0], xb = vx[1], xc = vx[2], xd = vx[3];
-            wv[0][0] = xa.x; wv[0][1] = xa.y; wv[0][2] = xa.z; wv[0][3] = xa.w; wv[1][0] = xb.x; wv[1][1] = xb.y; wv[1][2] = xb.z; wv[1][3] = xb.w;
-            wv[2][0] = xc.x; wv[2][1] = xc.y; wv[2][2] = xc.z; wv[2][3] = xc.w; wv[3][0] = xd.x; wv[3][1] = xd.y; wv[3][2] = xd.z; wv[3][3] = xd.w;
-          } else {
-            const uint2 xa = lds64(va), xb = lds64(vb), xc = lds64(va + 8 * L::ROWB), xd = lds64(vb + 8 * L::ROWB);
-            wv[0][0] = xa.x; wv[0][1] = xa.y; wv[1][0] = xb.x; wv[1][1] = xb.y; wv[2][0] = xc.x; wv[2][1] = xc.y; wv[3][0] = xd.x; wv[3][1] = xd.y;
-          }
+        mma16816(zs, ONE2, ONE2, ONE2, ONE2, pb0, pb1);          // every row: sum over the tile's tokens of the rounded p*vscale
+        // ---- O^T += V^T P^T.  A transposed 8x8 load hands lane (g, j) the 16-bit element g of token rows 2j and 2j+1 of a
+        //      16-byte chunk: four channels (4g .. 4g+3 of the chunk's 32) of two consecutive tokens, which is the pairing along
+        //      the contraction that an A register wants.  Nibbles are read in place: channel 4g+0 / 4g+2 (after >> 8) as 1024 + n,
+        //      made n by an exact subtraction; 4g+1 / 4g+3 as 64 + n.  MMA row g = the even channel, row g+8 = the odd one.
+        #pragma unroll
+        for (int q = 0; q < HD / 64; ++q)
           #pragma unroll
-          for (int w = 0; w < HD / 64; ++w)
-            #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              const uint32_t sel = ((4 + b) << 12) | ((4 + b) << 8) | (b << 4) | b;
-              const uint32_t ab = __byte_perm(wv[0][w], wv[1][w], sel), cd = __byte_perm(wv[2][w], wv[3][w], sel);
-              mma16816(acc[4 * w + b], and_or(ab, nk.m0, nk.e), and_or(ab, nk.m1, nk.o),
-                       and_or(cd, nk.m0, nk.e), and_or(cd, nk.m1, nk.o), pb0, pb1);
-            }
-        }
+          for (int p = 0; p < 2; ++p) {
+            const uint32_t lo = vx[q][2 * p], hi = vx[q][2 * p + 1], lo8 = lo >> 8, hi8 = hi >> 8;
+            mma16816(acc[(2 * q + p) * 2], hadd2(and_or(lo, nk.m0, nk.e), NEG_E), and_or(lo, nk.m1, nk.o),
+                     hadd2(and_or(hi, nk.m0, nk.e), NEG_E), and_or(hi, nk.m1, nk.o), pb0, pb1);
+            mma16816(acc[(2 * q + p) * 2 + 1], hadd2(and_or(lo8, nk.m0, nk.e), NEG_E), and_or(lo8, nk.m1, nk.o),
+                     hadd2(and_or(hi8, nk.m0, nk.e), NEG_E), and_or(hi8, nk.m1, nk.o), pb0, pb1);
+          }
         // next tile: sixteen rows further down
         #pragma unroll
         for (int i = 0; i < NW; ++i) ka[i] += 2 * KROW8;
-        va += 16 * L::ROWB; vb += 16 * L::ROWB; vsa += 32; rta += 2 * NP * 2 * 512;
+        va += 16 * L::ROWB; vsa += 32; rta += 2 * NP * 2 * 512;
       }
     };
 
     bool ok = true;
-    for (int kk = warp; kk < nu * L::UG && ok; kk += NCW) {      // slot kk = (unit kk/4 of this CTA, group kk%4 of the unit)
+    // Slot kk = (unit kk/4 of this CTA, group kk%4 of the unit), round-robin over the consumer warps: a fixed assignment, so
+    // the summation order and with it every bit of the result is the same from run to run (handing slots out from a shared
+    // counter was measured: no faster with two warps per scheduler, and not reproducible).
+    for (int kk = warp; kk < nu * L::UG && ok; kk += NCW) {
       const int k = kk / L::UG, sub = kk % L::UG, u = u0 + k, s = k % NSTAGE;
       const bool tail = has_tail && u == nu4;
       if (tail ? sub != 0 : u * L::UG + sub >= nq) continue;     // the unit holds fewer than four groups
@@ -494,16 +524,15 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
     for (int o = 4; o <= 16; o <<= 1) {
       l[0] += __shfl_xor_sync(0xffffffffu, l[0], o); l[1] += __shfl_xor_sync(0xffffffffu, l[1], o);
       zacc[0] += __shfl_xor_sync(0xffffffffu, zacc[0], o); zacc[1] += __shfl_xor_sync(0xffffffffu, zacc[1], o);
-      zs[0] += __shfl_xor_sync(0xffffffffu, zs[0], o); zs[1] += __shfl_xor_sync(0xffffffffu, zs[1], o);
     }
-    const float ze[2] = {zacc[0] - 1024.f * zs[0], zacc[1] - 1024.f * zs[1]}, zo[2] = {zacc[0] - 64.f * zs[0], zacc[1] - 64.f * zs[1]};
+    const float ze[2] = {zacc[0], zacc[1]}, zo[2] = {zacc[0] - 64.f * zs[0], zacc[1] - 64.f * zs[1]};
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");  // nobody still reads a stage
     if (!*s_abort) {
       float* wb = mbuf + (size_t)warp * 8 * (HD + 2);
       if (g == 0) { wb[(2 * j) * (HD + 2)] = m[0]; wb[(2 * j) * (HD + 2) + 1] = l[0]; wb[(2 * j + 1) * (HD + 2)] = m[1]; wb[(2 * j + 1) * (HD + 2) + 1] = l[1]; }
       #pragma unroll
       for (int mt = 0; mt < HD / 16; ++mt) {
-        const int c = (HD / 8) * g + 8 * (mt >> 2) + 2 * (mt & 3);     // even channel of the m-tile; the odd one is c + 1
+        const int c = 32 * (mt >> 1) + 4 * g + 2 * (mt & 1);           // even channel of the m-tile; the odd one is c + 1
         wb[(2 * j) * (HD + 2) + 2 + c] = acc[mt][0] + ze[0]; wb[(2 * j + 1) * (HD + 2) + 2 + c] = acc[mt][1] + ze[1];
         wb[(2 * j) * (HD + 2) + 2 + c + 1] = acc[mt][2] + zo[0]; wb[(2 * j + 1) * (HD + 2) + 2 + c + 1] = acc[mt][3] + zo[1];
       }
@@ -587,7 +616,7 @@ bool make_rope_map(CUtensorMap* out, const float* rope, int rd, uint64_t groups)
 }
 
 template <int HD, int RD, int DT>
-int launch_t(const yskn_attn_g_args& a, int g, Shard sh, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mr, cudaStream_t st) {
+int launch_t(const yskn_attn_g_args& a, int g, Shard sh, int early, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mr, cudaStream_t st) {
   using L = Lay<HD, RD>;
   auto kern = kv4_decode_mma_kernel<HD, RD, DT>;
   static std::atomic<unsigned long long> attr{0};               // once per device, like the reference's launchers once per process
@@ -595,7 +624,7 @@ int launch_t(const yskn_attn_g_args& a, int g, Shard sh, const CUtensorMap& mk, 
     KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
   }
-  DecodeP P{a, sh, g};
+  DecodeP P{a, sh, g, early};
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(a.splits, a.kvh, a.M); cfg.blockDim = dim3(NTHREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = st;
   cudaLaunchAttribute at[1];
@@ -606,9 +635,9 @@ int launch_t(const yskn_attn_g_args& a, int g, Shard sh, const CUtensorMap& mk, 
 }
 
 template <int HD, int RD>
-int launch_dt(const yskn_attn_g_args& a, int g, int dt, Shard sh, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mr, cudaStream_t st) {
-  if (dt == YSKN_KV4_BF16) return launch_t<HD, RD, YSKN_KV4_BF16>(a, g, sh, mk, mv, mr, st);
-  return launch_t<HD, RD, YSKN_KV4_F16>(a, g, sh, mk, mv, mr, st);
+int launch_dt(const yskn_attn_g_args& a, int g, int dt, Shard sh, int early, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mr, cudaStream_t st) {
+  if (dt == YSKN_KV4_BF16) return launch_t<HD, RD, YSKN_KV4_BF16>(a, g, sh, early, mk, mv, mr, st);
+  return launch_t<HD, RD, YSKN_KV4_F16>(a, g, sh, early, mk, mv, mr, st);
 }
 
 }  // namespace
@@ -618,7 +647,7 @@ bool decode_mma_supports(int g, int hd, int rd, int M) {
   return (hd == 256 && (rd == 64 || rd == 0)) || (hd == 128 && (rd == 128 || rd == 0));
 }
 
-int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st) {
+int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, int early, cudaStream_t st) {
   if (!decode_mma_supports(g, hd, rd, a.M)) KV4_REJECT("yskn_kv4_attention: tensor-core decode does not cover (g %d, hd %d, rd %d, M %d)", g, hd, rd, a.M);
   const uintptr_t al = (uintptr_t)a.kv.kq | (uintptr_t)a.kv.vq | (uintptr_t)a.kv.kscale | (uintptr_t)a.kv.kzero | (uintptr_t)a.kv.kshadow |
                        (uintptr_t)a.kv.vscale | (uintptr_t)a.kv.vzero | (uintptr_t)a.rope;
@@ -631,8 +660,8 @@ int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_
   if (rd == 0) mr = mk;
   else if (!make_rope_map(&mr, a.rope, rd, ((uint64_t)sh.start + (uint64_t)sh.len) / 32))
     KV4_REJECT("yskn_kv4_attention: cuTensorMapEncodeTiled failed for the rope table");
-  if (hd == 256) return rd ? launch_dt<256, 64>(a, g, act_dtype, sh, mk, mv, mr, st) : launch_dt<256, 0>(a, g, act_dtype, sh, mk, mv, mr, st);
-  return rd ? launch_dt<128, 128>(a, g, act_dtype, sh, mk, mv, mr, st) : launch_dt<128, 0>(a, g, act_dtype, sh, mk, mv, mr, st);
+  if (hd == 256) return rd ? launch_dt<256, 64>(a, g, act_dtype, sh, early, mk, mv, mr, st) : launch_dt<256, 0>(a, g, act_dtype, sh, early, mk, mv, mr, st);
+  return rd ? launch_dt<128, 128>(a, g, act_dtype, sh, early, mk, mv, mr, st) : launch_dt<128, 0>(a, g, act_dtype, sh, early, mk, mv, mr, st);
 }
 
 int decode_status_fetch(int* out) {

@@ -69,7 +69,7 @@ int decode_noalloc(const uint16_t* q16, const yskn_kv_layer* kv, int max_ctx, co
   const int algo = current_algo();                       // yskn_kv4_set_algo applies here as in yskn_kv4_attention
   if (algo == ALGO_MMA && !mma_ok) KV4_REJECT("yskn_kv4_decode_noalloc: tensor-core path does not cover (g %d, hd %d, rd %d)", g, hd, rd);
   int rc = mma_ok && algo != ALGO_SCALAR
-               ? launch_decode_mma(a, g, hd, rd, act_dtype, Shard{0, max_ctx}, st)
+               ? launch_decode_mma(a, g, hd, rd, act_dtype, Shard{0, max_ctx}, 0, st)
                : launch_attention_scalar(a, g, hd, rd, act_dtype, Shard{0, max_ctx}, st);
   if (rc) return rc;
   yskn_attn_g_combine_args c{a.pm, a.pl, a.pacc, splits, 1, nullptr, o16, nullptr, nh, g};

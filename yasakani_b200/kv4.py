@@ -13,7 +13,7 @@ import math
 import torch
 
 from . import _lib
-from ._lib import F16, BF16, F32, KvLayerC, KvQuantArgsC, AttnGArgsC, AttnGCombineArgsC, KvAppendArgsC, PeerExchangeC, check
+from ._lib import F16, BF16, F32, KvLayerC, KvQuantArgsC, AttnGArgsC, AttnGCombineArgsC, KvAppendArgsC, PeerExchangeC, AttnExtC, check
 
 _NAMES = ("kq", "kscale", "kzero", "kshadow", "vq", "vscale", "vzero")
 
@@ -134,30 +134,39 @@ def _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale) -> Att
                       pacc.data_ptr(), rope.data_ptr() if rope is not None else None, kv.hkv, nh, qscale)
 
 
+def attn_ext(early: bool = False, splits_short: int = 0, long_len: int = 0, wk=None) -> AttnExtC:
+    """yskn_kv4_attn_ext: the extras of the 27B engine's argument set (src/q35.hpp:126-130,136); `wk` a uint8 device tensor."""
+    return AttnExtC(1 if early else 0, splits_short, long_len, wk.data_ptr() if wk is not None else None)
+
+
 def launch_attention_gqa(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float,
-                         rd: int, stream=None) -> None:
+                         rd: int, stream=None, ext: AttnExtC | None = None) -> None:
     """launch_attention_gqa (src/attention_gqa.cu:168-175): split-K partials for M rows."""
     a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
+    if ext is not None:
+        check(_lib.load().yskn_kv4_attention_ex(C.byref(a), C.byref(ext), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), _stream(stream)), "yskn_kv4_attention_ex")
+        return
     check(_lib.load().yskn_kv4_attention(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), _stream(stream)), "yskn_kv4_attention")
 
 
 def launch_attention_shard(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float,
-                           rd: int, shard_start: int, shard_len: int, stream=None) -> None:
+                           rd: int, shard_start: int, shard_len: int, stream=None, ext: AttnExtC | None = None) -> None:
     """Partials over a cache holding only global tokens [shard_start, shard_start+shard_len); d_pos stays global."""
     a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
-    check(_lib.load().yskn_kv4_attention_shard(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), shard_start, shard_len,
-                                              _stream(stream)), "yskn_kv4_attention_shard")
+    check(_lib.load().yskn_kv4_attention_shard_ex(C.byref(a), C.byref(ext) if ext is not None else None, nh // kv.hkv, kv.hd, rd, _dtype_code(q16),
+                                                 shard_start, shard_len, _stream(stream)), "yskn_kv4_attention_shard")
 
 
 def launch_decode(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float, rd: int, o16,
-                  bv=None, gate=None, stream=None) -> None:
+                  bv=None, gate=None, stream=None, ext: AttnExtC | None = None) -> None:
     """launch_attention_gqa + the merge of launch_attn_combine_gqa_xform as one launch where the shape allows
     (src/attention_gqa.cu:168-181).  Calls on one device must not overlap."""
     a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
     g = nh // kv.hkv
     c = AttnGCombineArgsC(pm.data_ptr(), pl.data_ptr(), pacc.data_ptr(), splits, M, bv.data_ptr() if bv is not None else None,
                           o16.data_ptr(), gate.data_ptr() if gate is not None else None, nh, g)
-    check(_lib.load().yskn_kv4_decode(C.byref(a), C.byref(c), g, kv.hd, rd, _dtype_code(q16), _stream(stream)), "yskn_kv4_decode")
+    check(_lib.load().yskn_kv4_decode_ex(C.byref(a), C.byref(c), C.byref(ext) if ext is not None else None, g, kv.hd, rd, _dtype_code(q16),
+                                        _stream(stream)), "yskn_kv4_decode")
 
 
 def launch_decode_shard_triple(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float, rd: int,

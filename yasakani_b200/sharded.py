@@ -74,8 +74,10 @@ class ShardedDecoder:
     All arithmetic runs in the CUDA library (kv4.launch_*); this class only owns buffers and the exchange."""
 
     def __init__(self, shape, plan: ShardPlan, splits: int, rope: torch.Tensor, M: int = 1, dtype=torch.float16, group=None,
-                 exchange: str = "nccl", peer_exchange=None):
+                 exchange: str = "nccl", peer_exchange=None, early: bool = False):
         from . import kv4
+        # early: positions and cached rows below them are final before the step's predecessor kernel ends (yskn_kv4_attn_ext)
+        self.ext = kv4.attn_ext(early=True) if early else None
         self.kv4, self.shape, self.plan, self.splits, self.rope, self.M, self.group = kv4, shape, plan, splits, rope, M, group
         self.exchange, self.x = exchange, peer_exchange
         if exchange == "p2p" and peer_exchange is None:
@@ -115,7 +117,7 @@ class ShardedDecoder:
         s = self.shape
         if self.exchange == "p2p":
             self.kv4.launch_attention_shard(q16, self.layer, self.M, self.d_pos, self.splits, self.pm, self.pl, self.pacc, self.rope,
-                                            s.hq, s.qscale, s.rd, self.plan.start, self.plan.capacity)
+                                            s.hq, s.qscale, s.rd, self.plan.start, self.plan.capacity, ext=self.ext)
             if s.hq * self.M <= 148:                                 # one launch: fold, push, wait, merge
                 self.kv4.launch_exchange_merge(self.pm, self.pl, self.pacc, self.splits, self.M, s.hq, s.g, s.hd, self.x, self.o16)
             else:
