@@ -177,8 +177,9 @@ YSKN_KV4_API int yskn_kv4_attention_shard_ex(const yskn_attn_g_args* a, const ys
 YSKN_KV4_API int yskn_kv4_decode_shard_triple(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, int shard_start,
                                               int shard_len, float* d_triple, void* cuda_stream);
 /* The same exchange without a library collective: every rank stores its triple straight into every rank's exchange
- * buffer through NVLink peer mappings and raises a per-source arrival counter there; the merge kernel waits (bounded,
- * about half a second, then device status 7) for all sources and merges.  buf[w] is rank w's exchange buffer as mapped
+ * buffer through NVLink peer mappings, each float together with the step's number in one 8-byte store, so that a reader
+ * that finds the number has the value (no fence, no arrival counter: one network latency); the merge kernel polls
+ * (bounded, about half a second, then device status 7) until all sources carry this step's number and merges.  buf[w] is rank w's exchange buffer as mapped
  * into THIS process (buf[rank] is the local one), each of yskn_kv4_exchange_bytes(world, M, nh, hd) bytes, 16-byte
  * aligned and zero-filled once before the first step.  Two halves are used alternately, so the ranks need no other
  * synchronisation between steps; every rank must run push and merge exactly once per step, in this order.
@@ -186,8 +187,8 @@ YSKN_KV4_API int yskn_kv4_decode_shard_triple(const yskn_attn_g_args* a, int g, 
  * that rank no longer agree with its peers'.  Recover by stopping all ranks between steps, zero-filling every rank's
  * exchange buffer again and resuming; the library does not repair it on its own. */
 typedef struct yskn_kv4_peer_exchange { float* buf[8]; int world; int rank; } yskn_kv4_peer_exchange;
-/* Limit of the wait above in polls of about 100 ns (process-wide, read at launch; 0 restores the default of 2^22,
- * about half a second).  A short limit lets a host-made failure -- a rank that never pushed -- be observed quickly. */
+/* Limit of the wait above in poll rounds of about half a microsecond (process-wide, read at launch; 0 restores the
+ * default of 2^20, about half a second).  A short limit lets a host-made failure -- a rank that never pushed -- be observed quickly. */
 YSKN_KV4_API int yskn_kv4_set_peer_wait_polls(unsigned polls);
 YSKN_KV4_API size_t yskn_kv4_exchange_bytes(int world, int M, int nh, int hd);
 YSKN_KV4_API int yskn_kv4_push_triple(const yskn_attn_g_combine_args* a, int hd, const yskn_kv4_peer_exchange* x, void* cuda_stream);

@@ -28,33 +28,29 @@ struct CombineP {
 
 __device__ int g_merge_status = 0;                       // 7 = the wait for the other shards' triples ran out
 
-// Exchange buffer of one rank (yskn_kv4_peer_exchange): float data[2][world][M*nh*(HD+2)], then unsigned arrived[2][world],
-// then int step, unsigned merge ticket, unsigned push ticket.  Buffer `step & 1` is the one in use; a rank is never more than one step ahead of another.
-__device__ __forceinline__ size_t xch_data_floats(int world, int M, int nh, int hd) { return (size_t)2 * world * M * nh * (hd + 2); }
-constexpr unsigned PEER_WAIT_POLLS = 1u << 22;           // default limit, x ~100 ns: about half a second
+// Exchange buffer of one rank (yskn_kv4_peer_exchange): uint2 slot[2][world][M*nh*(HD+2)], then int step, unsigned merge
+// ticket.  A slot is one float of a triple together with the number of the step that wrote it, stored with ONE 8-byte
+// store (delivered whole over NVLink), so a reader that finds the step's tag has the value: no fence, no arrival counter,
+// one network latency.  Half `step & 1` is the one in use; a rank is never more than one step ahead of another, so a
+// half is rewritten only after every rank has read it.
+__device__ __forceinline__ size_t xch_data_floats(int world, int M, int nh, int hd) { return (size_t)2 * world * M * nh * (hd + 2) * 2; }
+__device__ __forceinline__ void st_slot(float* base, size_t i, float v, unsigned tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(reinterpret_cast<uint2*>(base) + i), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_slot(const float* base, size_t i) {
+  uint2 v; asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(reinterpret_cast<const uint2*>(base) + i) : "memory");
+  return v;
+}
+constexpr unsigned PEER_WAIT_POLLS = 1u << 20;           // default limit, x ~0.5 us per poll round: about half a second
 std::atomic<unsigned> g_peer_wait_polls{PEER_WAIT_POLLS}; // yskn_kv4_set_peer_wait_polls
 
-constexpr int CB = 8;                                    // loads in flight per thread and batch
+constexpr int CB = 10;                                   // loads in flight per thread and batch: 4 runs x 10 cover 37-40 splits in one round trip
 
-// PEER: with TRIPLE_OUT, the triple goes into every rank's exchange buffer (plain stores through NVLink peer mappings,
-// then one system-scope arrival per block and destination); with TRIPLE_IN, the block first waits (bounded) until every
-// rank's arrivals for this step are complete, and the last block of the grid opens the next step.
+// PEER: with TRIPLE_OUT, the triple goes into every rank's exchange buffer (8-byte value+tag stores through NVLink peer
+// mappings); with TRIPLE_IN, every thread polls (bounded) the slots it needs -- (m, l) of each rank and its own channel of
+// each rank's O -- until they carry this step's tag, and the last block of the grid opens the next step.
 // CQ = split runs per block: 4 when there are many splits to fetch and few blocks (decode: latency), 2 when the grid of
 // 1,024-thread blocks would not fit the GPU at once (verify: hundreds of rows x heads), 1 for short sums (prefill).
-// Bounded wait (one thread) until every rank's arrival count for this step has reached `want`; 1 = gave up.
-__device__ __forceinline__ int wait_for_triples(const unsigned* flags, int world, unsigned want, unsigned limit) {
-  for (int src = 0; src < world; ++src) {
-    unsigned polls = 0, got = 0;
-    for (;;) {                                             // acquire at system scope: the triple stored before the arrival is visible
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flags + src) : "memory");
-      if (got >= want) break;
-      __nanosleep(100);
-      if (++polls > limit) { atomicExch(&g_merge_status, 7); return 1; }
-    }
-  }
-  return 0;
-}
-
 template <int HD, int DT, bool TRIPLE_IN, bool TRIPLE_OUT, bool PEER, int CQ>
 __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   // TRIPLE_IN && TRIPLE_OUT && PEER = the fused exchange: fold the splits, push the triple, wait for the other ranks' triples, merge.
@@ -70,16 +66,78 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   asm volatile("griddepcontrol.wait;" ::: "memory");     // the producer grid's writes are visible from here on
   __shared__ int s_bad;
   int par = 0;                                           // which half of the exchange buffers this step uses
-  const size_t xdata = PEER ? xch_data_floats(P.x.world, P.M, P.nh, HD) : 0;
+  unsigned tag = 0;                                      // this step's number + 1 (a zero-filled buffer carries tag 0)
+  const size_t xdata = PEER ? xch_data_floats(P.x.world, P.M, P.nh, HD) : 0;    // floats: two per slot
+  const size_t xhalf = xdata / 4;                        // slots of one half
   if (PEER) {
-    unsigned* mine_flags = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata);
-    par = *reinterpret_cast<volatile int*>(mine_flags + 2 * P.x.world) & 1;
-    if (READ_TRIPLES) {
-      if (tid == 0) s_bad = wait_for_triples(mine_flags + par * P.x.world, P.x.world, (unsigned)(P.M * P.nh), P.wait_polls);
-      __syncthreads();
-      if (s_bad) return;
-      P.triples = P.x.buf[P.x.rank] + (size_t)par * (xdata / 2);
+    const int step = *reinterpret_cast<volatile int*>(P.x.buf[P.x.rank] + xdata);
+    par = step & 1; tag = (unsigned)step + 1u;
+  }
+  // Polls (bounded) until this step's tag is on the slots this thread is responsible for: its channel of every rank's O,
+  // and -- threads 0 .. 2*world-1 -- one rank's m or l, which go to shared memory for the whole block.  Call with the HD
+  // threads of run 0 only; false = some thread of the block gave up (device status 7).
+  __shared__ float s_tm[8], s_tl[8];
+  auto poll_triples = [&](float (&tm)[8], float (&tl)[8], float (&to)[8]) -> bool {
+    const float* mine = P.x.buf[P.x.rank];
+    const size_t base = (size_t)par * xhalf + ((size_t)r * P.nh + head) * (HD + 2), rstride = (size_t)P.M * P.nh * (HD + 2);
+    const unsigned all = (1u << P.x.world) - 1u;
+    const bool ml = d < 2 * P.x.world;                   // this thread also fetches m (even d) or l (odd d) of rank d/2
+    unsigned have = 0;                                   // bit src: O slot seen; bit 8: the m/l slot seen
+    int ok = 1;
+    for (unsigned polls = 0; ; ++polls) {
+      uint2 c[8], e = make_uint2(0u, tag);
+      #pragma unroll
+      for (int src = 0; src < 8; ++src) c[src] = ld_slot(mine, base + (size_t)min(src, P.x.world - 1) * rstride + 2 + d);   // all loads in flight at once
+      if (ml) e = ld_slot(mine, base + (size_t)(d >> 1) * rstride + (d & 1));
+      #pragma unroll
+      for (int src = 0; src < 8; ++src) if (src < P.x.world && c[src].y == tag) { have |= 1u << src; to[src] = __uint_as_float(c[src].x); }
+      if (e.y == tag) { have |= 256u; if (ml) { if (d & 1) s_tl[d >> 1] = __uint_as_float(e.x); else s_tm[d >> 1] = __uint_as_float(e.x); } }
+      if (have == (all | 256u)) break;
+      if (polls > P.wait_polls) { atomicExch(&g_merge_status, 7); ok = 0; break; }
+      __nanosleep(64);
     }
+    if (d == 0) s_bad = 0;
+    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");
+    if (!ok) s_bad = 1;
+    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");      // also: s_tm / s_tl are complete
+    if (s_bad) return false;
+    #pragma unroll
+    for (int src = 0; src < 8; ++src) {
+      if (src < P.x.world) { tm[src] = s_tm[src]; tl[src] = s_tl[src]; }
+      else { tm[src] = -1e30f; tl[src] = 0.f; to[src] = 0.f; }
+    }
+    return true;
+  };
+  auto merge_triples = [&](const float (&tm)[8], const float (&tl)[8], const float (&to)[8], float& o_out, float& l_out) {
+    float Mw = -1e30f;
+    #pragma unroll
+    for (int src = 0; src < 8; ++src) Mw = fmaxf(Mw, tm[src]);
+    float Lw = 0.f, ow = 0.f;
+    #pragma unroll
+    for (int src = 0; src < 8; ++src) { const float wgt = tm[src] > -1e29f ? expf(tm[src] - Mw) : 0.f; Lw += wgt * tl[src]; ow += wgt * to[src]; }
+    o_out = ow; l_out = Lw;
+  };
+  if (PEER && READ_TRIPLES) {                            // merge of pushed triples: nothing to fold, only HD threads work
+    if (q != 0) return;
+    float tm[8], tl[8], to[8], o, L2;
+    if (!poll_triples(tm, tl, to)) return;               // some thread of the block gave up: no row from incomplete triples
+    merge_triples(tm, tl, to, o, L2);
+    float y = round_f16(o / L2);
+    const size_t e = ((size_t)r * P.nh + head) * HD + d;
+    if (P.bv) y = __fadd_rn(y, act_load<DT>(P.bv, (size_t)(head / P.g) * HD + d));
+    if (P.gate) { const float gt = act_load<DT>(P.gate, e); y = __fmul_rn(y, __fdiv_rn(1.f, __fadd_rn(1.f, expf(-gt)))); }
+    P.o16[e] = act_store16<DT>(y);
+    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");      // every thread of the block has read its slots
+    if (d == 0) {
+      unsigned* ticket = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata) + 1;
+      if (atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1) {
+        *ticket = 0u;
+        __threadfence();
+        volatile int* step = reinterpret_cast<volatile int*>(P.x.buf[P.x.rank] + xdata);
+        *step = *step + 1;                             // every block of this grid has read it already
+      }
+    }
+    return;
   }
 
   float v[CB];                                           // first batch of this thread's values: in flight with pm/pl
@@ -90,10 +148,22 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
     else { s_m[s] = __ldcg(P.pm + slot(s)); s_l[s] = __ldcg(P.pl + slot(s)); }
   }
   __syncthreads();
-  float M2 = -1e30f;
-  for (int s = 0; s < P.S; ++s) M2 = fmaxf(M2, s_m[s]);
-  for (int s = tid; s < P.S; s += CQ * HD) s_w[s] = (s_m[s] > -1e29f) ? expf(s_m[s] - M2) : 0.f;
+  // One warp forms the maximum, the weights and the weighted sum of l (lane-strided, then a fixed shuffle tree: the same
+  // bits on every run); the other threads only wait for their loads meanwhile.
+  __shared__ float s_M2, s_L2;
+  if (tid < 32) {
+    float mx = -1e30f;
+    for (int s = tid; s < P.S; s += 32) mx = fmaxf(mx, s_m[s]);
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float ls = 0.f;
+    for (int s = tid; s < P.S; s += 32) { const float w = (s_m[s] > -1e29f) ? expf(s_m[s] - mx) : 0.f; s_w[s] = w; ls += w * s_l[s]; }
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+    if (tid == 0) { s_M2 = mx; s_L2 = ls; }
+  }
   __syncthreads();
+  const float M2 = s_M2;
   float o = 0.f;
   #pragma unroll
   for (int k = 0; k < CB; ++k) if (s0 + k < s1) o += s_w[s0 + k] * v[k];
@@ -108,45 +178,20 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   if (q != 0) return;
   if (CQ == 4) o = (s_part[d] + s_part[HD + d]) + (s_part[2 * HD + d] + s_part[3 * HD + d]);
   if (CQ == 2) o = s_part[d] + s_part[HD + d];
-  float L2 = 0.f;
-  for (int s = 0; s < P.S; ++s) L2 += s_w[s] * s_l[s];
+  float L2 = s_L2;
   if (TRIPLE_OUT && PEER) {
-    const size_t off = (size_t)par * (xdata / 2) + (((size_t)P.x.rank * P.M + r) * P.nh + head) * (HD + 2);
+    const size_t off = (size_t)par * xhalf + (((size_t)P.x.rank * P.M + r) * P.nh + head) * (HD + 2);
     for (int w = 0; w < P.x.world; ++w) {
-      float* t = P.x.buf[w] + off;
-      if (d == 0) { t[0] = M2; t[1] = L2; }
-      t[2 + d] = o;
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");     // the HD threads of run 0 have stored
-    if (d == 0) {
-      // Blocks meet at a device-scope ticket; the last one publishes the whole grid's stores with ONE system-scope
-      // fence and one arrival per destination (a system fence per block cost several microseconds each).
-      unsigned* mine_flags = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata);
-      unsigned* ticket = mine_flags + 2 * P.x.world + 2;
-      __threadfence();
-      if (atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1) {
-        *ticket = 0u;
-        __threadfence_system();
-        for (int w = 0; w < P.x.world; ++w)
-          atomicAdd_system(reinterpret_cast<unsigned*>(P.x.buf[w] + xdata) + par * P.x.world + P.x.rank, (unsigned)(P.M * P.nh));
-      }
+      float* t = P.x.buf[w];
+      if (d == 0) { st_slot(t, off, M2, tag); st_slot(t, off + 1, L2, tag); }
+      st_slot(t, off + 2 + d, o, tag);
     }
     if (!FUSED) return;
-    // ---- fused: every block waits for all ranks' triples (the grid is small enough to be resident as a whole, so the
-    //      blocks that wait cannot keep the publishing block off the GPU), then merges them like yskn_kv4_merge_triples
-    if (d == 0) s_bad = wait_for_triples(reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata) + par * P.x.world, P.x.world, (unsigned)(P.M * P.nh), P.wait_polls);
-    asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");
-    if (s_bad) return;
-    const float* trip = P.x.buf[P.x.rank] + (size_t)par * (xdata / 2);
-    auto tslot = [&](int src) -> size_t { return (((size_t)src * P.M + r) * P.nh + head) * (HD + 2); };
-    float Mw = -1e30f;
-    for (int src = 0; src < P.x.world; ++src) Mw = fmaxf(Mw, __ldcg(trip + tslot(src)));
-    float Lw = 0.f, ow = 0.f;
-    for (int src = 0; src < P.x.world; ++src) {
-      const float ms = __ldcg(trip + tslot(src)), wgt = ms > -1e29f ? expf(ms - Mw) : 0.f;
-      Lw += wgt * __ldcg(trip + tslot(src) + 1); ow += wgt * __ldcg(trip + tslot(src) + 2 + d);
-    }
-    o = ow; L2 = Lw;
+    // ---- fused: every thread waits for its slots of all ranks' triples (the grid is small enough to be resident as a
+    //      whole, so blocks that wait cannot keep a block that still has to push off the GPU), then merges them
+    float tm[8], tl[8], to[8];
+    if (!poll_triples(tm, tl, to)) return;
+    merge_triples(tm, tl, to, o, L2);
   }
   if (TRIPLE_OUT && !FUSED) {
     float* t = P.triple_out + ((size_t)r * P.nh + head) * (HD + 2);
@@ -162,13 +207,11 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
   if (PEER && TRIPLE_IN) {                               // the last block of the grid closes this step
     asm volatile("bar.sync 1, %0;" ::"n"(HD) : "memory");      // every thread of the block has read its triples
     if (d == 0) {
-      unsigned* flags = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata);
-      unsigned* ticket = flags + 2 * P.x.world + 1;
+      unsigned* ticket = reinterpret_cast<unsigned*>(P.x.buf[P.x.rank] + xdata) + 1;
       if (atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1) {
-        for (int src = 0; src < P.x.world; ++src) flags[par * P.x.world + src] = 0u;
         *ticket = 0u;
         __threadfence();
-        volatile int* step = reinterpret_cast<volatile int*>(flags + 2 * P.x.world);
+        volatile int* step = reinterpret_cast<volatile int*>(P.x.buf[P.x.rank] + xdata);
         *step = *step + 1;                             // every block of this grid has read it already
       }
     }
@@ -178,7 +221,7 @@ __global__ void __launch_bounds__(CQ * HD) kv4_combine_kernel(CombineP P) {
 template <int HD, int DT, bool TI, bool TO, bool PEER>
 int launch_k(const CombineP& P, size_t smem, cudaStream_t st) {
   const long long blocks = (long long)P.nh * P.M;
-  const int CQ = P.S < 8 ? 1 : (blocks <= 296 ? 4 : 2);          // 296 = two 1,024-thread blocks on each of 148 SMs
+  const int CQ = (P.S < 8 || (TI && !TO && PEER)) ? 1 : (blocks <= 296 ? 4 : 2);   // 296 = two 1,024-thread blocks on each of 148 SMs; the merge of pushed triples folds nothing
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(P.nh, P.M); cfg.blockDim = dim3(CQ * HD); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];
@@ -234,7 +277,7 @@ static int check_exchange(const yskn_kv4_peer_exchange* x, const char* who) {
 }
 
 size_t exchange_bytes(int world, int M, int nh, int hd) {
-  return ((size_t)2 * world * M * nh * (hd + 2)) * 4 + ((size_t)2 * world + 4) * 4;   // data, arrived[2][world], step, merge ticket, push ticket, pad
+  return ((size_t)2 * world * M * nh * (hd + 2)) * 8 + 16;   // value+tag slots of both halves, then step, merge ticket, pad
 }
 
 int launch_push_triple(const yskn_attn_g_combine_args& a, int hd, const yskn_kv4_peer_exchange* x, cudaStream_t st) {

@@ -240,7 +240,7 @@ def decode_noalloc(q16, kv: KvLayer, d_pos, splits: int, rope, nh: int, qscale: 
 
 
 def set_peer_wait_polls(polls: int) -> None:
-    """Limit of the wait for the other shards' triples in polls of ~100 ns; 0 restores the default (yskn_kv4_set_peer_wait_polls)."""
+    """Limit of the wait for the other shards' triples in poll rounds of ~0.5 us; 0 restores the default (yskn_kv4_set_peer_wait_polls)."""
     check(_lib.load().yskn_kv4_set_peer_wait_polls(int(polls)), "yskn_kv4_set_peer_wait_polls")
 
 
