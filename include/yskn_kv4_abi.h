@@ -126,9 +126,38 @@ typedef struct yskn_kv4_attn_ext { int early; int splits_short; int long_len; co
 YSKN_KV4_API int yskn_kv4_attention_ex(const yskn_attn_g_args* a, const yskn_kv4_attn_ext* x, int g, int hd, int rd, int act_dtype,
                                        void* cuda_stream);
 
+/* Rows of several sequences in one pass: the multi-request rows of the reference (Q35MsRows, src/q35.hpp:27-35, kernels in
+ * src/q35_atxpk_ms.cu), each row with its own position and its own cache, so that a batch of independent decodes is ONE
+ * launch.  All tables live in device memory:
+ *   pos[r]   absolute position of row r in its sequence; the row sees keys 0 .. pos[r] of that sequence
+ *   slot[r]  index of row r's sequence in `layers` / `maps`
+ *   layers   [n_slots] cache arrays of each sequence (same kvh, head_dim and max_ctx for all)
+ *   maps     [n_slots][2] the K and V tensor maps of each sequence, 128 bytes each, 128-byte aligned
+ * yskn_kv4_ms_prepare fills `layers` and `maps` (yskn_kv4_ms_maps_bytes(n_slots) bytes) from a HOST array of cache
+ * descriptors; it is the set-up step made when sequences are bound to slots (it copies from host memory and synchronises
+ * the stream, so it is not for graph capture).  yskn_kv4_attention_ms then only enqueues: partials as
+ * yskn_kv4_attention writes them ([M][splits][nh]; a->kv and a->d_pos are ignored, a->max_ctx is the common capacity),
+ * to be merged by yskn_kv4_combine.  Covers the shapes of the tensor-core decode kernel (g <= 8, head_dim 128 / 256),
+ * M <= 64 rows, n_slots <= 64. */
+typedef struct yskn_kv4_ms_rows { const int* pos; const int* slot; const yskn_kv_layer* layers; const void* maps; int n_slots; } yskn_kv4_ms_rows;
+YSKN_KV4_API size_t yskn_kv4_ms_maps_bytes(int n_slots);
+YSKN_KV4_API int yskn_kv4_ms_prepare(const yskn_kv_layer* h_layers, int n_slots, int kvh, int hd, int max_ctx, yskn_kv_layer* d_layers,
+                                     void* d_maps, void* cuda_stream);
+YSKN_KV4_API int yskn_kv4_attention_ms(const yskn_attn_g_args* a, const yskn_kv4_ms_rows* ms, int g, int hd, int rd, int act_dtype,
+                                       void* cuda_stream);
+
 /* launch_attn_combine_gqa_xform, src/attention_gqa.cu:123-134,176-181, up to and including the o16 store
  * (the sign/FWHT/int8 preparation of the next GEMV input is the caller's). act_dtype applies to o16 and gate. */
 YSKN_KV4_API int yskn_kv4_combine(const yskn_attn_g_combine_args* a, int hd, int act_dtype, void* cuda_stream);
+
+/* The rest of launch_attn_combine_gqa_xform (src/attention_gqa.cu:135-139 through a8_group512_tail,
+ * src/a8_prologue.cuh:86-98,122-133): the int8 input of the projection that follows attention.  Per 512 values of a merged
+ * fp16 row o16 [M][n] (n = nh * head_dim, a multiple of 512): x = o16 * signs[i]; Walsh-Hadamard transform of length 512;
+ * * 1/sqrt(512); fp16 rounding; alpha = max|x| / 127; qx = rne(x / alpha) clamped to +-127 (0 when alpha is 0).
+ * signs [n] are +-1, qx [M][n] int8, alpha [M][n/512] fp32.  Bit-exact with the reference's kernel on the same o16.
+ * Launched with programmatic stream serialization right behind the merge. */
+YSKN_KV4_API int yskn_kv4_xform_a8(const uint16_t* d_o16, const int8_t* d_signs, int8_t* d_qx, float* d_alpha, int M, int n,
+                                   void* cuda_stream);
 
 /* yskn_kv4_attention followed by yskn_kv4_combine in one call: the merge kernel is launched with programmatic stream
  * serialization (the reference's PDL launches, src/pdl.cuh:23-30), so its launch latency hides behind the attention

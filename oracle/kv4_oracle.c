@@ -152,8 +152,17 @@ void ysko_append(const ysko_kv_layer* kv, int hkv, int hd, int max_ctx, int pos0
 
 /* Dequantised, rotated key and value of token t as query row at `pos` sees them
  * (src/attention_gqa.cu:38-70).  kd, vd: float[hd]. */
+/* Key and value of the token at position t.  `slot` is where its rows are stored: t itself, except for the own key of a
+ * row of a tree-shaped pass (src/q35_atx.cu:111-119: position base + depth, cache slot base + row), which is read from
+ * the shadow like every key of the row's own group. */
+static void load_token_at(const ysko_kv_layer* kv, int max_ctx, int kvh, int hd, int rd, const float* rope,
+                          int t, int slot_t, int cur_group, float* kd, float* vd);
 static void load_token(const ysko_kv_layer* kv, int max_ctx, int kvh, int hd, int rd, const float* rope,
                        int t, int cur_group, float* kd, float* vd) {
+  load_token_at(kv, max_ctx, kvh, hd, rd, rope, t, t, cur_group, kd, vd);
+}
+static void load_token_at(const ysko_kv_layer* kv, int max_ctx, int kvh, int hd, int rd, const float* rope,
+                          int t, int slot_t, int cur_group, float* kd, float* vd) {
   if (t / 32 < cur_group) {                         /* 4-bit group: nib*scale + zero, separate mul and add */
     const size_t gb = (size_t)kvh * (max_ctx / 32) + t / 32; const int tt = t & 31;
     for (int ch = 0; ch < hd; ++ch) {
@@ -163,14 +172,14 @@ static void load_token(const ysko_kv_layer* kv, int max_ctx, int kvh, int hd, in
       kd[ch] = m + h2f(kv->kzero[gb * hd + ch]);
     }
   } else {                                          /* the query's own group stays fp16 */
-    for (int ch = 0; ch < hd; ++ch) kd[ch] = h2f(kv->kshadow[((size_t)kvh * max_ctx + t) * hd + ch]);
+    for (int ch = 0; ch < hd; ++ch) kd[ch] = h2f(kv->kshadow[((size_t)kvh * max_ctx + slot_t) * hd + ch]);
   }
   for (int i = 0; i < rd / 2; ++i) {                /* rotate-half on the first rd dims */
     const float c = rope[((size_t)t * (rd / 2) + i) * 2], s = rope[((size_t)t * (rd / 2) + i) * 2 + 1];
     const float a = kd[i], b = kd[i + rd / 2];
     kd[i] = a * c - b * s; kd[i + rd / 2] = a * s + b * c;
   }
-  const size_t slot = (size_t)kvh * max_ctx + t;
+  const size_t slot = (size_t)kvh * max_ctx + slot_t;
   const float vs = h2f(kv->vscale[slot]), vz = h2f(kv->vzero[slot]);
   for (int ch = 0; ch < hd; ++ch) {
     const uint8_t b = kv->vq[slot * (hd / 2) + (ch >> 1)];
@@ -254,6 +263,14 @@ void ysko_combine(const float* pm, const float* pl, const float* pacc, int S, in
 void ysko_attention_exact(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
                           const float* rope, int hkv, int hq, int hd, int rd, float qscale,
                           float* out, int row_begin, int row_end, int threads) {
+  ysko_attention_exact_wk(q16, kv, max_ctx, M, pos0, rope, hkv, hq, hd, rd, qscale, out, row_begin, row_end, threads, NULL);
+}
+
+/* wk: row -> depth table of a tree-shaped verify pass or NULL (depth = row index): row r sits at position pos0 + wk[r], sees
+ * the cached keys 0 .. pos0 + wk[r] - 1 and its own key, stored in slot pos0 + r (src/q35_atx.cu:111-119). */
+void ysko_attention_exact_wk(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
+                             const float* rope, int hkv, int hq, int hd, int rd, float qscale,
+                             float* out, int row_begin, int row_end, int threads, const uint8_t* wk) {
   const int g = hq / hkv;
   if (row_begin < 0) row_begin = 0;
   if (row_end > M) row_end = M;
@@ -262,7 +279,7 @@ void ysko_attention_exact(const uint16_t* q16, const ysko_kv_layer* kv, int max_
   #pragma omp parallel for schedule(dynamic, 1) num_threads(threads)
   for (int job = 0; job < jobs; ++job) {
     const int r = row_begin + job / hkv, kvh = job % hkv;
-    const int pos = pos0 + r, len = pos + 1, cur_group = pos / 32;
+    const int pos = pos0 + (wk ? (int)wk[r] : r), own = pos0 + r, len = pos + 1, cur_group = pos / 32;
     float* kd = (float*)malloc(sizeof(float) * hd * 2); float* vd = kd + hd;
     float* q = (float*)malloc(sizeof(float) * (size_t)g * hd);
     double* sc = (double*)malloc(sizeof(double) * (size_t)g * len);
@@ -272,7 +289,7 @@ void ysko_attention_exact(const uint16_t* q16, const ysko_kv_layer* kv, int max_
     double mx[8];
     for (int i = 0; i < g; ++i) mx[i] = -1e300;
     for (int t = 0; t < len; ++t) {                                   /* pass 1: scores */
-      load_token(kv, max_ctx, kvh, hd, rd, rope, t, cur_group, kd, vd);
+      load_token_at(kv, max_ctx, kvh, hd, rd, rope, t, t == pos ? own : t, cur_group, kd, vd);
       for (int i = 0; i < g; ++i) {
         double s = 0.0;
         for (int d = 0; d < hd; ++d) s += (double)q[i * hd + d] * (double)kd[d];
@@ -281,7 +298,7 @@ void ysko_attention_exact(const uint16_t* q16, const ysko_kv_layer* kv, int max_
     }
     double l[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int t = 0; t < len; ++t) {                                   /* pass 2: weights and values */
-      load_token(kv, max_ctx, kvh, hd, rd, rope, t, cur_group, kd, vd);
+      load_token_at(kv, max_ctx, kvh, hd, rd, rope, t, t == pos ? own : t, cur_group, kd, vd);
       for (int i = 0; i < g; ++i) {
         const double p = exp(sc[(size_t)i * len + t] - mx[i]);
         l[i] += p;
@@ -292,6 +309,31 @@ void ysko_attention_exact(const uint16_t* q16, const ysko_kv_layer* kv, int max_
       for (int d = 0; d < hd; ++d) out[((size_t)r * hq + kvh * g + i) * hd + d] = (float)(acc[i * hd + d] / l[i]);
     free(kd); free(q); free(sc); free(acc);
   }
+}
+
+/* The int8 input of the next projection: attn_combine_gqa_xform_kernel's tail (src/attention_gqa.cu:135-139) through
+ * a8_group512_tail and fwht512_v (src/a8_prologue.cuh:86-98,122-133).  o16 [M][n] fp16 bits, signs [n], qx [M][n], alpha [M][n/512]. */
+void ysko_xform_a8(const uint16_t* o16, const int8_t* signs, int8_t* qx, float* alpha, int M, int n) {
+  const int ng = n / 512;
+  for (int tok = 0; tok < M; ++tok)
+    for (int blk = 0; blk < ng; ++blk) {
+      float v[512], w[512];
+      for (int p = 0; p < 512; ++p) v[p] = h2f(o16[(size_t)tok * n + blk * 512 + p]) * (float)signs[blk * 512 + p];
+      for (int h = 1; h < 512; h <<= 1) {                     /* the upper element of a pair gets lower - upper */
+        for (int p = 0; p < 512; ++p) { const float q = v[p ^ h]; w[p] = (p & h) ? (q - v[p]) : (v[p] + q); }
+        memcpy(v, w, sizeof(v));
+      }
+      float amax = 0.f;
+      for (int p = 0; p < 512; ++p) { v[p] = round_f16(v[p] * 0.044194173824159216f); if (fabsf(v[p]) > amax) amax = fabsf(v[p]); }
+      const float al = amax / 127.f;
+      alpha[(size_t)tok * ng + blk] = al;
+      for (int p = 0; p < 512; ++p) {
+        const float r = al > 0.f ? v[p] / al : 0.f;
+        /* __float2int_rn: NaN gives 0 and infinities saturate (a group whose transform overflows fp16 has alpha = inf) */
+        int q = r != r ? 0 : (r >= 127.f ? 127 : (r <= -127.f ? -127 : (int)nearbyintf(r)));
+        qx[(size_t)tok * n + blk * 512 + p] = (int8_t)q;
+      }
+    }
 }
 
 void ysko_merge_triples(const float* parts, int R, int hq, int hd, float* out) {

@@ -75,6 +75,10 @@ void ysko_combine(const float* pm, const float* pl, const float* pacc, int S, in
  * no splits; row r sees keys 0..pos0+r with the own-group-from-shadow rule
  * (src/attention_gqa.cu:24,38-43,55-70).  out: float [M][Hq][HD] (no bias/gate).
  * row_begin/row_end select a subset of rows (others left untouched). */
+void ysko_xform_a8(const uint16_t* o16, const int8_t* signs, int8_t* qx, float* alpha, int M, int n);
+void ysko_attention_exact_wk(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
+                             const float* rope, int hkv, int hq, int hd, int rd, float qscale,
+                             float* out, int row_begin, int row_end, int threads, const uint8_t* wk);
 void ysko_attention_exact(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
                           const float* rope, int hkv, int hq, int hd, int rd, float qscale,
                           float* out, int row_begin, int row_end, int threads);

@@ -126,16 +126,27 @@ def combine(pm, pl, pacc, g: int, bv=None, gate=None) -> np.ndarray:
 
 
 def attention_exact(q16, kv: KvCache, pos0: int, rope, hq: int, rd: int, qscale: float,
-                    rows=None, threads: int = 0) -> np.ndarray:
-    """float32 [M][Hq][HD]; rows=(begin,end) restricts the computed rows (others stay 0)."""
+                    rows=None, threads: int = 0, wk=None) -> np.ndarray:
+    """float32 [M][Hq][HD]; rows=(begin,end) restricts the computed rows (others stay 0).  wk: optional uint8 row -> depth
+    table of a tree-shaped pass (row r at position pos0 + wk[r], own key in slot pos0 + r)."""
     q16 = np.ascontiguousarray(q16, np.uint16)
     M = q16.shape[0]
     out = np.zeros((M, hq, kv.hd), np.float32)
     b, e = rows if rows is not None else (0, M)
     s = kv.struct()
-    lib().ysko_attention_exact(_p(q16), C.byref(s), kv.max_ctx, M, pos0, _p(rope), kv.hkv, hq, kv.hd, rd,
-                               C.c_float(qscale), _p(out), b, e, threads or lib().ysko_max_threads())
+    wk = None if wk is None else np.ascontiguousarray(wk, np.uint8)
+    lib().ysko_attention_exact_wk(_p(q16), C.byref(s), kv.max_ctx, M, pos0, _p(rope), kv.hkv, hq, kv.hd, rd,
+                                  C.c_float(qscale), _p(out), b, e, threads or lib().ysko_max_threads(), _p(wk))
     return out
+
+
+def xform_a8(o16: np.ndarray, signs: np.ndarray):
+    """o16 uint16 fp16 bits [M][n] (n a multiple of 512), signs int8 [n] -> (qx int8 [M][n], alpha float32 [M][n/512])."""
+    o16 = np.ascontiguousarray(o16, np.uint16); M = o16.shape[0]; o16 = o16.reshape(M, -1); n = o16.shape[1]
+    signs = np.ascontiguousarray(signs, np.int8)
+    qx = np.empty((M, n), np.int8); alpha = np.empty((M, n // 512), np.float32)
+    lib().ysko_xform_a8(_p(o16), _p(signs), _p(qx), _p(alpha), M, n)
+    return qx, alpha
 
 
 def merge_triples(parts: np.ndarray) -> np.ndarray:

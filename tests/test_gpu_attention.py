@@ -398,3 +398,78 @@ def test_early_prefetch_changes_no_bit(oracle, shape, ctx, M):
                            b.view(torch.int32) if b.dtype == torch.float32 else b.view(torch.int16))
     want = oracle.attention_exact(f16_bits(q), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
     assert_close(res[1][3].float().numpy(), want, "early launch vs oracle")
+
+
+@pytest.mark.parametrize("shape,base", [(synth.C2, 777), (synth.C1, 95)])
+def test_tree_verify_rows_with_depth_table_and_per_row_split_counts(oracle, shape, base):
+    """The extras of the 27B engine's argument set (src/q35.hpp:126-130,136; use at src/q35_atx.cu:111-119): rows of one pass
+    with different visible ranges.  Row r sits at depth wk[r]: it sees the cached keys below *d_pos + wk[r] and its own key,
+    stored in slot *d_pos + r.  Rows that see fewer than long_len keys use splits_short splits; their other slots are empty."""
+    M, S, S_short = 8, 16, 5
+    wk_host = np.array([0, 1, 2, 3, 3, 3, 4, 4], dtype=np.uint8)          # a chain of four, then alternatives at depths 3 and 4
+    kv4, okv, layer, q, rope_np, rope = _setup(oracle, shape, base, M, seed=53)
+    wk = torch.from_numpy(wk_host).cuda()
+    long_len = base + 4                                                    # rows at depth 0..2 are "short"
+    ext = kv4.attn_ext(splits_short=S_short, long_len=long_len, wk=wk)
+    d_pos = torch.tensor([base], dtype=torch.int32, device="cuda")
+    pm, pl, pacc = kv4.attn_scratch(M, S, shape.hq, shape.hd)
+    pm.fill_(float("nan")); pl.fill_(float("nan")); pacc.fill_(float("nan"))
+    kv4.launch_attention_gqa(q.cuda(), layer, M, d_pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, ext=ext)
+    o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+    kv4.launch_attn_combine_gqa(pm, pl, pacc, S, M, o16, shape.hq, shape.g)
+    torch.cuda.synchronize()
+    assert torch.isfinite(pm).all() and torch.isfinite(pacc).all(), "a partial slot was not written"
+    want = oracle.attention_exact(f16_bits(q), okv, base, rope_np, shape.hq, shape.rd, shape.qscale, wk=wk_host)
+    assert_close(o16.float().cpu().numpy(), want, "tree verify")
+    plain = oracle.attention_exact(f16_bits(q), okv, base, rope_np, shape.hq, shape.rd, shape.qscale)
+    assert np.abs(plain[4:] - want[4:]).max() > 1e-3                       # the table really changes what rows 4..7 see
+    pmh = pm.cpu().numpy()
+    for r in range(M):
+        short = base + int(wk_host[r]) + 1 < long_len
+        assert (pmh[r, S_short:] <= -1e29).all() == short, f"row {r}: split count"
+    # the same pass through the fused decode entry, and the rejection on the tensor-core-only setting
+    o2 = torch.empty_like(o16)
+    kv4.launch_decode(q.cuda(), layer, M, d_pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o2, ext=ext)
+    torch.cuda.synchronize()
+    assert torch.equal(o2, o16)
+    from yasakani_b200._lib import Kv4Error
+    kv4.set_algo(ALGO_MMA)
+    with pytest.raises(Kv4Error):
+        kv4.launch_attention_gqa(q.cuda(), layer, M, d_pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, ext=ext)
+
+
+def test_rows_of_several_sequences_in_one_launch(oracle):
+    """yskn_kv4_attention_ms: five rows from three sequences (one with two consecutive rows, as a verify pass has) in ONE
+    launch; every row equals, bit for bit, the single-sequence launch of that row, and the exact oracle within the bar."""
+    from yasakani_b200 import kv4
+    shape, max_ctx, S = synth.C2, 5184, 13
+    ctxs = [300, 2100, 5000]
+    layers, okvs = [], []
+    for i, ctx in enumerate(ctxs):
+        okv, _, _ = build_oracle_cache(oracle, shape, ctx + 2, seed=60 + i, max_ctx=max_ctx)
+        layers.append(kv4.KvLayer(shape.hkv, shape.hd, max_ctx).load_numpy(okv.arrays())); okvs.append(okv)
+    rope_np = oracle.rope_table(max_ctx, shape.theta, shape.rd)
+    rope = torch.from_numpy(rope_np).cuda()
+    rows = [(0, ctxs[0]), (2, ctxs[2]), (2, ctxs[2] + 1), (1, ctxs[1]), (0, ctxs[0] + 1)]          # (slot, position), interleaved on purpose
+    M = len(rows)
+    q = synth.make_q(shape, M, seed=66)
+    dq = q.cuda()
+    slots = kv4.MsSlots(layers)
+    pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device="cuda")
+    slot = torch.tensor([s for s, _ in rows], dtype=torch.int32, device="cuda")
+    pm, pl, pacc = kv4.attn_scratch(M, S, shape.hq, shape.hd)
+    pm.fill_(float("nan")); pl.fill_(float("nan")); pacc.fill_(float("nan"))
+    kv4.launch_attention_ms(dq, slots, M, pos, slot, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd)
+    o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+    kv4.launch_attn_combine_gqa(pm, pl, pacc, S, M, o16, shape.hq, shape.g)
+    torch.cuda.synchronize()
+    assert kv4.device_status() == 0
+    assert torch.isfinite(pm).all() and torch.isfinite(pacc).all(), "a partial slot was not written"
+    for r, (s, p) in enumerate(rows):
+        d_pos = torch.tensor([p], dtype=torch.int32, device="cuda")
+        pm1, pl1, pacc1 = kv4.attn_scratch(1, S, shape.hq, shape.hd)
+        kv4.launch_attention_gqa(dq[r:r + 1].contiguous(), layers[s], 1, d_pos, S, pm1, pl1, pacc1, rope, shape.hq, shape.qscale, shape.rd)
+        torch.cuda.synchronize()
+        assert torch.equal(pacc[r].view(torch.int32), pacc1[0].view(torch.int32)) and torch.equal(pm[r].view(torch.int32), pm1[0].view(torch.int32)), f"row {r}"
+        want = oracle.attention_exact(f16_bits(q[r:r + 1]), okvs[s], p, rope_np, shape.hq, shape.rd, shape.qscale)
+        assert_close(o16[r:r + 1].float().cpu().numpy(), want, f"row {r} (slot {s}, position {p})")

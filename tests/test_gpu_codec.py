@@ -22,6 +22,8 @@ def _compare(layer, okv):
 @pytest.mark.parametrize("shape,ctx,passes", [
     (synth.C1, 200, [1] * 40 + [31, 33, 64, 32]),               # single-token decode appends, then ragged chunks
     (synth.C2, 291, [97, 1, 1, 30, 2, 160]),
+    (synth.C2, 100, [30] + [1] * 70),                           # one-row passes that close groups 0, 1 and 2 inside the append launch
+    (synth.Shape(4, 1, 64, 64, 1e4), 70, [1] * 70),
     (synth.Shape(4, 1, 64, 64, 1e4), 96, [96]),
     (synth.C2, 8192, [8192]),                                   # one prefill-sized pass (C5's prompt length)
 ])
@@ -117,3 +119,22 @@ def test_bad_arguments_are_rejected_with_a_message():
     layer.hd = 96                                                 # unsupported head_dim
     with pytest.raises(Kv4Error, match="unsupported head_dim"):
         kv4.launch_kv_append(layer, rows[:, :, :96].contiguous(), rows[:, :, :96].contiguous(), d_pos, 1)
+
+
+def test_projection_input_transform_is_bit_exact(oracle):
+    """yskn_kv4_xform_a8 (sign flip, Hadamard-512, int8 + scale per 512 values) against the oracle, on rows that include
+    an all-zero group (scale 0) and large values."""
+    from yasakani_b200 import kv4
+    M, n = 5, 24 * 256
+    g = torch.Generator().manual_seed(77)
+    rows = (torch.randn((M, n), generator=g) * torch.exp(torch.randn((M, 1), generator=g))).to(torch.float16)
+    rows[2, 512:1024] = 0
+    rows[3, :512] = 60000.0
+    signs = (torch.randint(0, 2, (n,), generator=g) * 2 - 1).to(torch.int8)
+    qx = torch.empty((M, n), dtype=torch.int8, device="cuda"); alpha = torch.empty((M, n // 512), dtype=torch.float32, device="cuda")
+    kv4.launch_xform_a8(rows.cuda().view(M, 24, 256), signs.cuda(), qx, alpha)
+    torch.cuda.synchronize()
+    want_q, want_a = oracle.xform_a8(f16_bits(rows), signs.numpy())
+    assert np.array_equal(qx.cpu().numpy(), want_q)
+    assert np.array_equal(alpha.cpu().numpy().view(np.uint32), want_a.view(np.uint32))
+    assert float(alpha[2, 1]) == 0.0 and not qx[2, 512:1024].any()

@@ -102,6 +102,48 @@ def test_config5_decode_batch_at_mixed_contexts(oracle):
         torch.cuda.empty_cache()
 
 
+def test_config5_eight_decodes_as_one_launch(oracle):
+    """The decode batch of config 5 as ONE launch (yskn_kv4_attention_ms): eight sequences at 2k ... 128k, one row each;
+    every row equals the single-sequence launch bit for bit and the exact oracle within the bar."""
+    from yasakani_b200 import kv4
+    shape, S = synth.C2, 19
+    ctxs = (2048, 4096, 8192, 16384, 32768, 65536, 98304, 131072)
+    max_ctx = 131072 + 64
+    layers = []
+    for i, ctx in enumerate(ctxs):
+        layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
+        d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for c in range(ctx // CHUNK if ctx >= CHUNK else 1):
+            n = min(CHUNK, ctx)
+            k, v = synth.make_kv(shape, n, seed=(80 + i) * 1000 + c)
+            d_pos.fill_(c * CHUNK)
+            kv4.launch_kv_append(layer, k.cuda(), v.cuda(), d_pos, n)
+        layers.append(layer)
+    rope = _rope(kv4, shape, max_ctx)
+    M = len(ctxs)
+    q = synth.make_q(shape, M, seed=88)
+    dq = q.cuda()
+    slots = kv4.MsSlots(layers)
+    pos = torch.tensor([c - 1 for c in ctxs], dtype=torch.int32, device="cuda")
+    slot = torch.arange(M, dtype=torch.int32, device="cuda")
+    pm, pl, pacc = kv4.attn_scratch(M, S, shape.hq, shape.hd)
+    o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+    kv4.launch_attention_ms(dq, slots, M, pos, slot, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd)
+    kv4.launch_attn_combine_gqa(pm, pl, pacc, S, M, o16, shape.hq, shape.g)
+    torch.cuda.synchronize()
+    assert kv4.device_status() == 0
+    rope_np = rope.cpu().numpy()
+    for r, ctx in enumerate(ctxs):
+        d_pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda")
+        pm1, pl1, pacc1 = kv4.attn_scratch(1, S, shape.hq, shape.hd)
+        kv4.launch_attention_gqa(dq[r:r + 1].contiguous(), layers[r], 1, d_pos, S, pm1, pl1, pacc1, rope, shape.hq, shape.qscale, shape.rd)
+        torch.cuda.synchronize()
+        assert torch.equal(pacc[r].view(torch.int32), pacc1[0].view(torch.int32)), f"ctx {ctx}"
+        if ctx <= 32768:
+            want = oracle.attention_exact(f16_bits(q[r:r + 1]), _oracle_view(oracle, layers[r]), ctx - 1, rope_np, shape.hq, shape.rd, shape.qscale)
+            assert_close(o16[r:r + 1].float().cpu().numpy(), want, f"ctx {ctx} vs oracle")
+
+
 def test_config3_verify_widths_over_32768_tokens(oracle):
     """16-, 32- and 64-row verify passes over a 32,768-token cache: shared rows bitwise identical; sampled rows vs oracle."""
     from yasakani_b200 import kv4

@@ -132,3 +132,15 @@ def test_own_group_is_read_from_the_fp16_shadow(oracle):
 
 def test_tolerance_constants():
     assert (ATOL, RTOL) == (2e-3, 1e-2)
+
+
+def test_projection_input_transform_properties(oracle):
+    """ysko_xform_a8: a unit vector becomes a row of +-1/sqrt(512) whose codes are all +-127; the transform is its own inverse."""
+    n = 1024
+    x = np.zeros((1, n), np.float32); x[0, 3] = 1.0; x[0, 512 + 100] = -2.0
+    signs = np.ones(n, np.int8); signs[3] = -1
+    qx, alpha = oracle.xform_a8(oracle.f32_to_f16_bits(x), signs)
+    assert set(np.abs(qx[0, :512]).tolist()) == {127} and set(np.abs(qx[0, 512:]).tolist()) == {127}
+    want0 = np.float32(np.float16(np.float32(1.0) * np.float32(0.044194173824159216))) / np.float32(127)
+    assert alpha[0, 0] == want0 and alpha[0, 1] == np.float32(np.float16(np.float32(2.0) * np.float32(0.044194173824159216))) / np.float32(127)
+    assert qx[0, 0] == -127                                  # H[0][3] = +1, times the flipped sign

@@ -116,7 +116,8 @@ def test_reference_attention_kernel_agrees_with_oracle_and_with_ours(oracle, ref
                                 C.c_void_p(rope.data_ptr()), shape.hkv, shape.hq, C.c_float(shape.qscale), shape.g, shape.hd, shape.rd, None)
     assert rc == 0
     n = shape.hq * shape.hd
-    signs = torch.ones(n, dtype=torch.int8, device="cuda"); qx = torch.empty((M, n), dtype=torch.int8, device="cuda")
+    signs = (torch.randint(0, 2, (n,), generator=torch.Generator().manual_seed(9)) * 2 - 1).to(torch.int8).cuda()
+    qx = torch.empty((M, n), dtype=torch.int8, device="cuda")
     alpha = torch.empty((M, n // 512), dtype=torch.float32, device="cuda")
     o_ref = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
     rc = ref.yref_attn_combine_gqa_xform(C.c_void_p(pm.data_ptr()), C.c_void_p(pl.data_ptr()), C.c_void_p(pacc.data_ptr()), S, M, None,
@@ -124,6 +125,14 @@ def test_reference_attention_kernel_agrees_with_oracle_and_with_ours(oracle, ref
                                          C.c_void_p(qx.data_ptr()), C.c_void_p(alpha.data_ptr()), None)
     assert rc == 0
     torch.cuda.synchronize()
+    # (0) the int8 input of the next projection: the library's and the oracle's transform of the reference's own o16 rows
+    #     reproduce the reference kernel's codes and scales bit for bit (src/attention_gqa.cu:135-139, src/a8_prologue.cuh:122-133)
+    qx2 = torch.empty_like(qx); alpha2 = torch.empty_like(alpha)
+    kv4.launch_xform_a8(o_ref, signs, qx2, alpha2)
+    torch.cuda.synchronize()
+    assert torch.equal(qx2, qx) and torch.equal(alpha2.view(torch.int32), alpha.view(torch.int32)), "library transform differs from the reference's"
+    oqx, oal = oracle.xform_a8(f16_bits(o_ref.cpu()).reshape(M, n), signs.cpu().numpy())
+    assert np.array_equal(oqx, qx.cpu().numpy()) and np.array_equal(oal.view(np.uint32), alpha.cpu().numpy().view(np.uint32)), "oracle transform differs"
     o_ref = o_ref.float().cpu().numpy()
     # (1) the reference's partials against the oracle's literal restatement of the same kernel
     opm, opl, opacc = oracle.attention_partials(f16_bits(q), okv, ctx, S, rope_np, shape.hq, shape.rd, shape.qscale)

@@ -48,6 +48,10 @@ class AttnExtC(C.Structure):          # yskn_kv4_attn_ext
     _fields_ = [("early", C.c_int), ("splits_short", C.c_int), ("long_len", C.c_int), ("wk", C.c_void_p)]
 
 
+class MsRowsC(C.Structure):           # yskn_kv4_ms_rows
+    _fields_ = [("pos", C.c_void_p), ("slot", C.c_void_p), ("layers", C.c_void_p), ("maps", C.c_void_p), ("n_slots", C.c_int)]
+
+
 class PeerExchangeC(C.Structure):     # yskn_kv4_peer_exchange
     _fields_ = [("buf", C.c_void_p * 8), ("world", C.c_int), ("rank", C.c_int)]
 
@@ -65,10 +69,14 @@ PROTOTYPES = {
     "yskn_kv4_attention_ex": (C.c_int, [C.POINTER(AttnGArgsC), C.POINTER(AttnExtC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_decode_ex": (C.c_int, [C.POINTER(AttnGArgsC), C.POINTER(AttnGCombineArgsC), C.POINTER(AttnExtC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_attention_shard_ex": (C.c_int, [C.POINTER(AttnGArgsC), C.POINTER(AttnExtC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "yskn_kv4_ms_maps_bytes": (C.c_size_t, [C.c_int]),
+    "yskn_kv4_ms_prepare": (C.c_int, [C.POINTER(KvLayerC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "yskn_kv4_attention_ms": (C.c_int, [C.POINTER(AttnGArgsC), C.POINTER(MsRowsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_attention_shard": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_decode": (C.c_int, [C.POINTER(AttnGArgsC), C.POINTER(AttnGCombineArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_decode_shard_triple": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "yskn_kv4_combine": (C.c_int, [C.POINTER(AttnGCombineArgsC), C.c_int, C.c_int, C.c_void_p]),
+    "yskn_kv4_xform_a8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_prefill": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "yskn_kv4_tc_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "yskn_kv4_attention_tc": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),

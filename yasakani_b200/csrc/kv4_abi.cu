@@ -36,8 +36,13 @@ static int attention_dispatch(const yskn_attn_g_args* a, int g, int hd, int rd, 
   const int early = x ? (x->early != 0) : 0;
   if (x && (x->splits_short < 0 || x->splits_short > a->splits || (x->splits_short > 0 && x->long_len <= 0)))
     KV4_REJECT("yskn_kv4_attention: splits_short %d / long_len %d do not fit splits %d", x->splits_short, x->long_len, a->splits);
-  if (x && (x->wk || x->splits_short > 0))
-    KV4_REJECT("yskn_kv4_attention: the row->depth table and per-row split counts are not implemented by this build");
+  // A row -> depth table or per-row split counts: the CUDA-core kernel partitions keys per row and implements both; the
+  // tensor-core kernels partition per pass and take the plain causal pass only.
+  if (x && (x->wk || x->splits_short > 0)) {
+    if (x->wk && (sh.start != 0 || sh.len != a->max_ctx)) KV4_REJECT("yskn_kv4_attention: a row->depth table is not supported on a sequence shard");
+    if (current_algo() == ALGO_MMA) KV4_REJECT("yskn_kv4_attention: the tensor-core kernels do not take a row->depth table or per-row split counts");
+    return launch_attention_scalar(*a, g, hd, rd, act_dtype, sh, st, x);
+  }
   if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_attention: rotary width %d needs a rope table", rd);
   const bool mma_ok = decode_mma_supports(g, hd, rd, a->M);
   const int algo = current_algo();
@@ -147,6 +152,27 @@ int yskn_kv4_attention_ex(const yskn_attn_g_args* a, const yskn_kv4_attn_ext* x,
   return attention_dispatch(a, g, hd, rd, act_dtype, Shard{0, a->max_ctx}, (cudaStream_t)cuda_stream, x);
 }
 
+size_t yskn_kv4_ms_maps_bytes(int n_slots) { return n_slots > 0 ? (size_t)n_slots * 2 * 128 : 0; }
+
+int yskn_kv4_ms_prepare(const yskn_kv_layer* h_layers, int n_slots, int kvh, int hd, int max_ctx, yskn_kv_layer* d_layers, void* d_maps,
+                        void* cuda_stream) {
+  return ms_prepare(h_layers, n_slots, kvh, hd, max_ctx, d_layers, d_maps, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_attention_ms(const yskn_attn_g_args* a, const yskn_kv4_ms_rows* ms, int g, int hd, int rd, int act_dtype, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_kv4_attention_ms: null argument struct");
+  if (!ms || !ms->pos || !ms->slot || !ms->layers || !ms->maps || ms->n_slots <= 0 || ms->n_slots > 64)
+    KV4_REJECT("yskn_kv4_attention_ms: incomplete row tables");
+  if (!a->q16 || !a->pm || !a->pl || !a->pacc) KV4_REJECT("yskn_kv4_attention_ms: null buffer");
+  if (a->M <= 0 || a->M > 64 || a->splits <= 0 || a->splits > 65535 || a->kvh <= 0 || g <= 0 || a->nh != a->kvh * g)
+    KV4_REJECT("yskn_kv4_attention_ms: bad shape (M %d, splits %d, kvh %d, nh %d, g %d)", a->M, a->splits, a->kvh, a->nh, g);
+  if (a->max_ctx <= 0 || a->max_ctx % 64) KV4_REJECT("yskn_kv4_attention_ms: max_ctx %d is not a positive multiple of 64", a->max_ctx);
+  if (act_dtype != YSKN_KV4_F16 && act_dtype != YSKN_KV4_BF16) KV4_REJECT("yskn_kv4_attention_ms: act_dtype must be F16 or BF16");
+  if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_attention_ms: rotary width %d needs a rope table", rd);
+  if ((uintptr_t)ms->maps & 127) KV4_REJECT("yskn_kv4_attention_ms: the map table must be 128-byte aligned");
+  return launch_decode_mma(*a, g, hd, rd, act_dtype, Shard{0, a->max_ctx}, 0, (cudaStream_t)cuda_stream, ms);
+}
+
 int yskn_kv4_attention_shard(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, int shard_start, int shard_len,
                              void* cuda_stream) {
   return yskn_kv4_attention_shard_ex(a, nullptr, g, hd, rd, act_dtype, shard_start, shard_len, cuda_stream);
@@ -193,6 +219,10 @@ int yskn_kv4_decode_shard_triple(const yskn_attn_g_args* a, int g, int hd, int r
 int yskn_kv4_combine(const yskn_attn_g_combine_args* a, int hd, int act_dtype, void* cuda_stream) {
   if (!a) KV4_REJECT("yskn_kv4_combine: null argument struct");
   return launch_combine(*a, hd, act_dtype, (cudaStream_t)cuda_stream);
+}
+
+int yskn_kv4_xform_a8(const uint16_t* d_o16, const int8_t* d_signs, int8_t* d_qx, float* d_alpha, int M, int n, void* cuda_stream) {
+  return launch_xform_a8(d_o16, d_signs, d_qx, d_alpha, M, n, (cudaStream_t)cuda_stream);
 }
 
 int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, const uint16_t* bv, uint16_t* o16,

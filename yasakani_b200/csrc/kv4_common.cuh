@@ -60,8 +60,11 @@ struct Shard { int start; int len; };
 int launch_rope_table(float* d_out, int max_ctx, float theta, int rd, cudaStream_t st);
 int launch_append(const yskn_kv_append_args& a, cudaStream_t st);
 int launch_group_quant(const yskn_kv_quant_args& a, int kvh, int hd, cudaStream_t st);
-int launch_attention_scalar(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st);
-int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, int early, cudaStream_t st);
+int launch_attention_scalar(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, cudaStream_t st,
+                            const yskn_kv4_attn_ext* ext = nullptr);
+int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, int early, cudaStream_t st,
+                      const yskn_kv4_ms_rows* ms = nullptr);
+int ms_prepare(const yskn_kv_layer* h_layers, int n_slots, int kvh, int hd, int max_ctx, yskn_kv_layer* d_layers, void* d_maps, cudaStream_t st);
 bool decode_mma_supports(int g, int hd, int rd, int M);
 int decode_status_fetch(int* out);
 int tc_status_fetch(int* out);       // same for the tcgen05 multi-row kernel
@@ -71,6 +74,7 @@ size_t attention_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M);
 int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, void* workspace, size_t workspace_bytes,
                         int valid_tokens, uint16_t* o16_direct, const uint16_t* bv, cudaStream_t st);   // reads and clears the device status word of the tensor-core decode kernel
 int launch_combine(const yskn_attn_g_combine_args& a, int hd, int act_dtype, cudaStream_t st);
+int launch_xform_a8(const uint16_t* o16, const int8_t* signs, int8_t* qx, float* alpha, int M, int n, cudaStream_t st);
 int launch_local_triple(const yskn_attn_g_combine_args& a, int hd, float* d_triple, cudaStream_t st);
 int launch_merge_triples(const float* d_triples, int ranks, int M, int nh, int g, int hd, const uint16_t* bv,
                          const uint16_t* gate, uint16_t* o16, int act_dtype, cudaStream_t st);

@@ -48,6 +48,8 @@
 #include <mutex>
 #include <type_traits>
 #include <unordered_map>
+#include <cstring>
+#include <vector>
 
 namespace kv4 {
 
@@ -180,6 +182,7 @@ struct DecodeP {
   int g;
   int early;          // the caller's promise (yskn_kv4_attn_ext): *d_pos and every cache row below it are final before the
                       // preceding kernel of the stream ends, so they may be read ahead of griddepcontrol.wait
+  yskn_kv4_ms_rows ms;  // rows of several sequences (ms.pos != nullptr): row r reads the cache ms.layers[ms.slot[r]] at position ms.pos[r]
 };
 
 template <int HD, int RD, int DT>
@@ -207,8 +210,9 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
   }
 
   // ---- which groups this CTA owns (local token indices of this shard)
-  const int base_local = *A.d_pos - P.sh.start;                 // row 0's local position: rows below it are never written again
-  const int pos = base_local + r;
+  const bool multi = P.ms.pos != nullptr;                       // rows of several sequences: per-row position and cache
+  const int base_local = multi ? P.ms.pos[r] : *A.d_pos - P.sh.start;   // row 0's local position: rows below it are never written again
+  const int pos = multi ? base_local : base_local + r;
   const int len = max(0, min(pos + 1, P.sh.len));
   const int cg = pos >= 0 ? pos / 32 : 0;                       // first group that is not read as int4
   const int nq = min(cg, len / 32);                             // int4 groups, all fully visible
@@ -235,6 +239,10 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
     // =========================================================== producer warp
     if (nu > 0) {
       const size_t row0 = (size_t)kvh * A.max_ctx;              // first row of this kv-head in the [Hkv*max_ctx] arrays
+      const int slot = multi ? P.ms.slot[r] : 0;
+      const yskn_kv_layer kvl = multi ? P.ms.layers[slot] : A.kv;
+      const CUtensorMap* const mk = multi ? static_cast<const CUtensorMap*>(P.ms.maps) + 2 * slot : &mapK;
+      const CUtensorMap* const mv = multi ? static_cast<const CUtensorMap*>(P.ms.maps) + 2 * slot + 1 : &mapV;
       int issued = 0;
       bool waited = !early;
       for (int k = 0; k < nu; ++k) {
@@ -260,13 +268,13 @@ kv4_decode_mma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_con
         __syncwarp();                                            // the barrier is armed before any copy is issued
         const size_t tok0 = row0 + (size_t)g0 * 32, gb = ((size_t)kvh * (A.max_ctx / 32) + g0) * HD;
         switch (lane) {                                          // one copy per lane: seven issue slots in parallel
-          case 0: if (tail) bulk_1d(st + L::OFF_K, A.kv.kshadow + tok0 * HD, L::SHADOW, bar);
-                  else tma_2d(st + L::OFF_K, &mapK, 0, (int)tok0, bar); break;
-          case 1: tma_2d(st + L::OFF_V, &mapV, 0, (int)tok0, bar); break;   // always the swizzled tile; rows past the unit are unused
-          case 2: if (!tail) bulk_1d(st + L::OFF_KS, A.kv.kscale + gb, ngr * L::SCB, bar); break;
-          case 3: if (!tail) bulk_1d(st + L::OFF_KZ, A.kv.kzero + gb, ngr * L::SCB, bar); break;
-          case 4: bulk_1d(st + L::OFF_VS, A.kv.vscale + tok0, ngr * 64, bar); break;
-          case 5: bulk_1d(st + L::OFF_VZ, A.kv.vzero + tok0, ngr * 64, bar); break;
+          case 0: if (tail) bulk_1d(st + L::OFF_K, kvl.kshadow + tok0 * HD, L::SHADOW, bar);
+                  else tma_2d(st + L::OFF_K, mk, 0, (int)tok0, bar); break;
+          case 1: tma_2d(st + L::OFF_V, mv, 0, (int)tok0, bar); break;   // always the swizzled tile; rows past the unit are unused
+          case 2: if (!tail) bulk_1d(st + L::OFF_KS, kvl.kscale + gb, ngr * L::SCB, bar); break;
+          case 3: if (!tail) bulk_1d(st + L::OFF_KZ, kvl.kzero + gb, ngr * L::SCB, bar); break;
+          case 4: bulk_1d(st + L::OFF_VS, kvl.vscale + tok0, ngr * 64, bar); break;
+          case 5: bulk_1d(st + L::OFF_VZ, kvl.vzero + tok0, ngr * 64, bar); break;
           case 6: if (RD > 0) tma_2d(st + L::OFF_ROPE, &mapR, 0, g0 + P.sh.start / 32, bar); break;   // rows 32*(g0..g0+3) of the table
           default: break;
         }
@@ -616,7 +624,7 @@ bool make_rope_map(CUtensorMap* out, const float* rope, int rd, uint64_t groups)
 }
 
 template <int HD, int RD, int DT>
-int launch_t(const yskn_attn_g_args& a, int g, Shard sh, int early, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mr, cudaStream_t st) {
+int launch_t(const yskn_attn_g_args& a, int g, Shard sh, int early, const yskn_kv4_ms_rows& ms, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mr, cudaStream_t st) {
   using L = Lay<HD, RD>;
   auto kern = kv4_decode_mma_kernel<HD, RD, DT>;
   static std::atomic<unsigned long long> attr{0};               // once per device, like the reference's launchers once per process
@@ -624,7 +632,7 @@ int launch_t(const yskn_attn_g_args& a, int g, Shard sh, int early, const CUtens
     KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
   }
-  DecodeP P{a, sh, g, early};
+  DecodeP P{a, sh, g, early, ms};
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(a.splits, a.kvh, a.M); cfg.blockDim = dim3(NTHREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = st;
   cudaLaunchAttribute at[1];
@@ -635,9 +643,9 @@ int launch_t(const yskn_attn_g_args& a, int g, Shard sh, int early, const CUtens
 }
 
 template <int HD, int RD>
-int launch_dt(const yskn_attn_g_args& a, int g, int dt, Shard sh, int early, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mr, cudaStream_t st) {
-  if (dt == YSKN_KV4_BF16) return launch_t<HD, RD, YSKN_KV4_BF16>(a, g, sh, early, mk, mv, mr, st);
-  return launch_t<HD, RD, YSKN_KV4_F16>(a, g, sh, early, mk, mv, mr, st);
+int launch_dt(const yskn_attn_g_args& a, int g, int dt, Shard sh, int early, const yskn_kv4_ms_rows& ms, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mr, cudaStream_t st) {
+  if (dt == YSKN_KV4_BF16) return launch_t<HD, RD, YSKN_KV4_BF16>(a, g, sh, early, ms, mk, mv, mr, st);
+  return launch_t<HD, RD, YSKN_KV4_F16>(a, g, sh, early, ms, mk, mv, mr, st);
 }
 
 }  // namespace
@@ -647,21 +655,49 @@ bool decode_mma_supports(int g, int hd, int rd, int M) {
   return (hd == 256 && (rd == 64 || rd == 0)) || (hd == 128 && (rd == 128 || rd == 0));
 }
 
-int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, int early, cudaStream_t st) {
-  if (!decode_mma_supports(g, hd, rd, a.M)) KV4_REJECT("yskn_kv4_attention: tensor-core decode does not cover (g %d, hd %d, rd %d, M %d)", g, hd, rd, a.M);
-  const uintptr_t al = (uintptr_t)a.kv.kq | (uintptr_t)a.kv.vq | (uintptr_t)a.kv.kscale | (uintptr_t)a.kv.kzero | (uintptr_t)a.kv.kshadow |
-                       (uintptr_t)a.kv.vscale | (uintptr_t)a.kv.vzero | (uintptr_t)a.rope;
+// Uploads the table of per-sequence cache arrays and their K / V tensor maps for yskn_kv4_attention_ms (set-up: it copies from host memory).
+int ms_prepare(const yskn_kv_layer* h_layers, int n_slots, int kvh, int hd, int max_ctx, yskn_kv_layer* d_layers, void* d_maps, cudaStream_t st) {
+  if (!h_layers || !d_layers || !d_maps || n_slots <= 0 || n_slots > 64) KV4_REJECT("yskn_kv4_ms_prepare: bad arguments (n_slots %d)", n_slots);
+  if (kvh <= 0 || (hd != 128 && hd != 256) || max_ctx <= 0 || max_ctx % 64) KV4_REJECT("yskn_kv4_ms_prepare: bad shape (kvh %d, hd %d, max_ctx %d)", kvh, hd, max_ctx);
+  if ((uintptr_t)d_maps & 127) KV4_REJECT("yskn_kv4_ms_prepare: the map table must be 128-byte aligned");
+  std::vector<CUtensorMap> maps(2 * (size_t)n_slots);
+  const uint64_t rows = (uint64_t)kvh * max_ctx;
+  for (int s = 0; s < n_slots; ++s) {
+    const yskn_kv_layer& l = h_layers[s];
+    const uintptr_t al = (uintptr_t)l.kq | (uintptr_t)l.vq | (uintptr_t)l.kscale | (uintptr_t)l.kzero | (uintptr_t)l.kshadow | (uintptr_t)l.vscale | (uintptr_t)l.vzero;
+    if (!l.kq || !l.vq || !l.kscale || !l.kzero || !l.kshadow || !l.vscale || !l.vzero || (al & 15))
+      KV4_REJECT("yskn_kv4_ms_prepare: cache arrays of slot %d missing or not 16-byte aligned", s);
+    if (!make_map(&maps[2 * s], l.kq, rows, hd / 2) || !make_map(&maps[2 * s + 1], l.vq, rows, hd / 2))
+      KV4_REJECT("yskn_kv4_ms_prepare: cuTensorMapEncodeTiled failed or is unavailable");
+  }
+  KV4_CUDA(cudaMemcpyAsync(d_maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, st));
+  KV4_CUDA(cudaMemcpyAsync(d_layers, h_layers, (size_t)n_slots * sizeof(yskn_kv_layer), cudaMemcpyHostToDevice, st));
+  KV4_CUDA(cudaStreamSynchronize(st));                            // the host vectors go out of scope
+  return 0;
+}
+
+int launch_decode_mma(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, Shard sh, int early, cudaStream_t st,
+                      const yskn_kv4_ms_rows* ms) {
+  const bool multi = ms != nullptr;
+  if (multi ? !decode_mma_supports(g, hd, rd, 1) || a.M < 1 || a.M > 64 : !decode_mma_supports(g, hd, rd, a.M))
+    KV4_REJECT("yskn_kv4_attention: tensor-core decode does not cover (g %d, hd %d, rd %d, M %d)", g, hd, rd, a.M);
+  const uintptr_t al = multi ? (uintptr_t)a.rope
+                             : (uintptr_t)a.kv.kq | (uintptr_t)a.kv.vq | (uintptr_t)a.kv.kscale | (uintptr_t)a.kv.kzero | (uintptr_t)a.kv.kshadow |
+                               (uintptr_t)a.kv.vscale | (uintptr_t)a.kv.vzero | (uintptr_t)a.rope;
   if (al & 15) KV4_REJECT("yskn_kv4_attention: cache arrays and rope table must be 16-byte aligned");
   CUtensorMap mk, mv, mr;
   const uint64_t rows = (uint64_t)a.kvh * a.max_ctx;
-  if (!make_map(&mk, a.kv.kq, rows, hd / 2) || !make_map(&mv, a.kv.vq, rows, hd / 2))
+  if (multi) { memset(&mk, 0, sizeof(mk)); memset(&mv, 0, sizeof(mv)); }      // the kernel takes the maps of the row's sequence from ms->maps
+  else if (!make_map(&mk, a.kv.kq, rows, hd / 2) || !make_map(&mv, a.kv.vq, rows, hd / 2))
     KV4_REJECT("yskn_kv4_attention: cuTensorMapEncodeTiled failed or is unavailable");
+  const yskn_kv4_ms_rows msv = multi ? *ms : yskn_kv4_ms_rows{nullptr, nullptr, nullptr, nullptr, 0};
+  if (multi) early = 0;                                           // rows of one sequence in the same pass are appended by the predecessor
   // The rope table must cover positions [0, shard start + shard length); groups past that read as zero and are never used.
   if (rd == 0) mr = mk;
   else if (!make_rope_map(&mr, a.rope, rd, ((uint64_t)sh.start + (uint64_t)sh.len) / 32))
     KV4_REJECT("yskn_kv4_attention: cuTensorMapEncodeTiled failed for the rope table");
-  if (hd == 256) return rd ? launch_dt<256, 64>(a, g, act_dtype, sh, early, mk, mv, mr, st) : launch_dt<256, 0>(a, g, act_dtype, sh, early, mk, mv, mr, st);
-  return rd ? launch_dt<128, 128>(a, g, act_dtype, sh, early, mk, mv, mr, st) : launch_dt<128, 0>(a, g, act_dtype, sh, early, mk, mv, mr, st);
+  if (hd == 256) return rd ? launch_dt<256, 64>(a, g, act_dtype, sh, early, msv, mk, mv, mr, st) : launch_dt<256, 0>(a, g, act_dtype, sh, early, msv, mk, mv, mr, st);
+  return rd ? launch_dt<128, 128>(a, g, act_dtype, sh, early, msv, mk, mv, mr, st) : launch_dt<128, 0>(a, g, act_dtype, sh, early, msv, mk, mv, mr, st);
 }
 
 int decode_status_fetch(int* out) {

@@ -13,7 +13,7 @@ import math
 import torch
 
 from . import _lib
-from ._lib import F16, BF16, F32, KvLayerC, KvQuantArgsC, AttnGArgsC, AttnGCombineArgsC, KvAppendArgsC, PeerExchangeC, AttnExtC, check
+from ._lib import F16, BF16, F32, KvLayerC, KvQuantArgsC, AttnGArgsC, AttnGCombineArgsC, KvAppendArgsC, PeerExchangeC, AttnExtC, MsRowsC, check
 
 _NAMES = ("kq", "kscale", "kzero", "kshadow", "vq", "vscale", "vzero")
 
@@ -149,6 +149,34 @@ def launch_attention_gqa(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, p
     check(_lib.load().yskn_kv4_attention(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), _stream(stream)), "yskn_kv4_attention")
 
 
+class MsSlots:
+    """Sequences bound to the slots of a multi-request pass (yskn_kv4_ms_prepare): device tables of their cache arrays and
+    tensor maps.  All layers must share kvh, head_dim and max_ctx."""
+
+    def __init__(self, layers: list):
+        kv0 = layers[0]
+        assert all(l.hkv == kv0.hkv and l.hd == kv0.hd and l.max_ctx == kv0.max_ctx for l in layers)
+        self.layers, self.n, self.hkv, self.hd, self.max_ctx = layers, len(layers), kv0.hkv, kv0.hd, kv0.max_ctx
+        L = _lib.load()
+        self.d_layers = torch.empty(self.n * C.sizeof(KvLayerC), dtype=torch.uint8, device="cuda")
+        self.d_maps = torch.empty(int(L.yskn_kv4_ms_maps_bytes(self.n)) + 128, dtype=torch.uint8, device="cuda")
+        self.maps_ptr = (self.d_maps.data_ptr() + 127) // 128 * 128
+        host = (KvLayerC * self.n)(*[l.struct() for l in layers])
+        check(L.yskn_kv4_ms_prepare(host, self.n, self.hkv, self.hd, self.max_ctx, self.d_layers.data_ptr(), self.maps_ptr, _stream(None)),
+              "yskn_kv4_ms_prepare")
+
+
+def launch_attention_ms(q16, slots: MsSlots, M: int, pos, slot, splits: int, pm, pl, pacc, rope, nh: int, qscale: float, rd: int,
+                        stream=None) -> None:
+    """Partials for M rows of several sequences in one launch (yskn_kv4_attention_ms): pos, slot int32 device tensors [M]."""
+    assert pos.dtype == torch.int32 and slot.dtype == torch.int32 and pos.numel() >= M and slot.numel() >= M
+    a = AttnGArgsC(q16.data_ptr(), KvLayerC(), slots.max_ctx, M, None, splits, pm.data_ptr(), pl.data_ptr(), pacc.data_ptr(),
+                   rope.data_ptr() if rope is not None else None, slots.hkv, nh, qscale)
+    ms = MsRowsC(pos.data_ptr(), slot.data_ptr(), slots.d_layers.data_ptr(), slots.maps_ptr, slots.n)
+    check(_lib.load().yskn_kv4_attention_ms(C.byref(a), C.byref(ms), nh // slots.hkv, slots.hd, rd, _dtype_code(q16), _stream(stream)),
+          "yskn_kv4_attention_ms")
+
+
 def launch_attention_shard(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float,
                            rd: int, shard_start: int, shard_len: int, stream=None, ext: AttnExtC | None = None) -> None:
     """Partials over a cache holding only global tokens [shard_start, shard_start+shard_len); d_pos stays global."""
@@ -183,6 +211,15 @@ def launch_attn_combine_gqa(pm, pl, pacc, splits: int, M: int, o16, nh: int, g: 
     a = AttnGCombineArgsC(pm.data_ptr(), pl.data_ptr(), pacc.data_ptr(), splits, M, bv.data_ptr() if bv is not None else None,
                           o16.data_ptr(), gate.data_ptr() if gate is not None else None, nh, g)
     check(_lib.load().yskn_kv4_combine(C.byref(a), hd, _dtype_code(o16), _stream(stream)), "yskn_kv4_combine")
+
+
+def launch_xform_a8(o16, signs, qx, alpha, stream=None) -> None:
+    """Sign flip, Hadamard-512, int8 codes + fp32 scale per 512 values of the merged rows (yskn_kv4_xform_a8): o16 fp16 [M][nh][hd],
+    signs int8 [nh*hd], qx int8 like o16, alpha fp32 [M][nh*hd/512]."""
+    M = o16.shape[0]
+    n = o16.numel() // M
+    assert o16.dtype == torch.float16 and signs.dtype == torch.int8 and qx.dtype == torch.int8 and alpha.dtype == torch.float32
+    check(_lib.load().yskn_kv4_xform_a8(_ptr(o16), _ptr(signs), _ptr(qx), _ptr(alpha), M, n, _stream(stream)), "yskn_kv4_xform_a8")
 
 
 def launch_attention_prefill(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float,
