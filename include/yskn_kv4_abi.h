@@ -281,6 +281,25 @@ YSKN_KV4_API int yskn_kvx_decode(const int8_t* d_q8, const float* d_scales, void
 YSKN_KV4_API int yskn_kvx_probe(const float* x, int8_t* q, float* scales, float* y, int rows);
 
 /* ---------------------------------------------------------------------------------------------------------------
+ * Family-B row codec, step 2: the trellis ("CDQ") re-quantisation of 256-value rows with 3 / 4 / 5 bits per value and
+ * its packed payload (reference: tb_fakequant, src/kvq_gpu.cuh:54-148; the fast encoder and its packer,
+ * src/kvq_fast.cuh:96-232; launch_tb_fast, :242-255).  The code tables, scale multipliers and per-group records come
+ * from a "KVQP v1" profile blob (fields: src/kvq_gpu.cuh:57-68; loader checks: src/engine35.cpp:50-53), which the
+ * caller uploads to the device as it is.  Bit-exact with the reference on the same blob and rows.
+ *
+ * yskn_tb_blob_info: HOST-side check of a blob with the reference loader's rules; *nm = its number of scale multipliers.
+ * yskn_tb_encode: rows of 256 fp32 values d_x [rows][256]; d_grp[r] = group record of row r ((layer*4 + kv_head)*2 + kind,
+ * kind 0 = K, 1 = V), d_pos[r] = its position (rows below the group's guard position are passed through and not
+ * packed).  Outputs, each optional (NULL): d_y [rows][256] the re-quantised rows; d_pay [rows][pay_stride bytes] the
+ * payload, 8*k 32-bit words per row, the k new bits of every value MSB first (pay_stride >= 160, a multiple of 4);
+ * d_side [rows][2] = the row's scale (fp32 bits) and its two fp16 low-rank coefficients.  d_scratch:
+ * yskn_tb_scratch_bytes(rows, nm) bytes.  Enqueue-only, nothing allocated. */
+YSKN_KV4_API int yskn_tb_blob_info(const uint8_t* h_blob, size_t blob_len, int* nm);
+YSKN_KV4_API size_t yskn_tb_scratch_bytes(int rows, int nm);
+YSKN_KV4_API int yskn_tb_encode(const uint8_t* d_blob, int nm, const float* d_x, const int* d_grp, const int* d_pos, int rows, float* d_y,
+                                uint8_t* d_pay, int pay_stride, uint32_t* d_side, void* d_scratch, size_t scratch_bytes, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
  * Family-B decode attention over the INT8 rows above: the INT8 members of the reference's Q35AttnArgs
  * (src/q35.hpp:126-130), with the head counts the reference fixes at compile time (Q35_NH, Q35_KVH) as fields.
  * head_dim is 256.  q16 [M][nh][256] is bf16 (the reference's dtype) or fp16, already rotated (yskn_kvx_rotate);

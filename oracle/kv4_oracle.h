@@ -75,6 +75,11 @@ void ysko_combine(const float* pm, const float* pl, const float* pacc, int S, in
  * no splits; row r sees keys 0..pos0+r with the own-group-from-shadow rule
  * (src/attention_gqa.cu:24,38-43,55-70).  out: float [M][Hq][HD] (no bias/gate).
  * row_begin/row_end select a subset of rows (others left untouched). */
+/* Family-B step 2: trellis re-quantisation of 256-value rows and its packed payload (tb_oracle.c) */
+int ysko_tb_check_blob(const uint8_t* blob, size_t n);
+void ysko_tb_encode(const uint8_t* blob, const float* x, const int* grp, const int* pos, int rows,
+                    float* y_fq, uint8_t* fields, uint32_t* pay, uint32_t* side, int* kb);
+void ysko_tb_decode_fields(const uint8_t* blob, int g, const uint32_t* pay, float scale, float* xq);
 void ysko_xform_a8(const uint16_t* o16, const int8_t* signs, int8_t* qx, float* alpha, int M, int n);
 void ysko_attention_exact_wk(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,
                              const float* rope, int hkv, int hq, int hd, int rd, float qscale,

@@ -18,7 +18,7 @@ _LIB = None
 def build(force: bool = False) -> str:
     """Compile the oracle (and, if the reference tree is mounted, oracle/_ref)."""
     so = os.path.join(_HERE, "libkv4_oracle.so")
-    srcs = [os.path.join(_HERE, f) for f in ("kv4_oracle.c", "kvx_oracle.c", "kv4_oracle.h")]
+    srcs = [os.path.join(_HERE, f) for f in ("kv4_oracle.c", "kvx_oracle.c", "tb_oracle.c", "kv4_oracle.h")]
     if force or not os.path.exists(so) or os.path.getmtime(so) < max(os.path.getmtime(f) for f in srcs):
         subprocess.run(["make", "-C", _HERE, "libkv4_oracle.so"], check=True, capture_output=True)
     return so
@@ -159,6 +159,31 @@ def merge_triples(parts: np.ndarray) -> np.ndarray:
 
 def max_threads() -> int:
     return int(lib().ysko_max_threads())
+
+
+# ---------------------------------------------------------------- Family-B row codec, step 2: trellis rows (tb_oracle.c)
+def tb_check_blob(blob: bytes) -> int:
+    """0 if the reference's loader would accept the "KVQP v1" blob (src/engine35.cpp:50-53, src/kvq_fast.hpp:52-76)."""
+    a = np.frombuffer(blob, np.uint8)
+    return int(lib().ysko_tb_check_blob(_p(a), C.c_size_t(a.size)))
+
+
+def tb_encode(blob: bytes, x: np.ndarray, grp: np.ndarray, pos: np.ndarray):
+    """x [rows][256] float32; grp, pos int32 [rows] -> dict(y, fields, pay [rows][40] uint32, side [rows][2] uint32, kb [rows])."""
+    a = np.frombuffer(blob, np.uint8)
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, 256); rows = x.shape[0]
+    grp = np.ascontiguousarray(grp, np.int32); pos = np.ascontiguousarray(pos, np.int32)
+    y = np.empty_like(x); fields = np.empty((rows, 256), np.uint8); pay = np.empty((rows, 40), np.uint32)
+    side = np.empty((rows, 2), np.uint32); kb = np.empty(rows, np.int32)
+    lib().ysko_tb_encode(_p(a), _p(x), _p(grp), _p(pos), rows, _p(y), _p(fields), _p(pay), _p(side), _p(kb))
+    return {"y": y, "fields": fields, "pay": pay, "side": side, "kb": kb}
+
+
+def tb_decode_fields(blob: bytes, g: int, pay: np.ndarray, scale: float) -> np.ndarray:
+    a = np.frombuffer(blob, np.uint8)
+    pay = np.ascontiguousarray(pay, np.uint32); xq = np.empty(256, np.float32)
+    lib().ysko_tb_decode_fields(_p(a), int(g), _p(pay), C.c_float(scale), _p(xq))
+    return xq
 
 
 # ---------------------------------------------------------------- Family-B row codec, step 1 (kvx_oracle.c)

@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def declared_symbols():
     text = open(os.path.join(ROOT, "include", "yskn_kv4_abi.h")).read()
-    return sorted(set(re.findall(r"YSKN_KV4_API\s+[\w\s\*]+?\b(yskn_kv[48x]_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"YSKN_KV4_API\s+[\w\s\*]+?\b(yskn_(?:kv[48x]|tb)_\w+)\s*\(", text)))
 
 
 def test_header_and_binding_table_agree():

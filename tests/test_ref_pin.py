@@ -214,3 +214,47 @@ def test_int8_row_decode_agrees_with_the_reference_kernel_and_the_oracle(oracle,
     ours = merged(pm2, pl2, pacc2)
     assert_close(ours, want, "this library's INT8-row kernel vs exact oracle")
     assert_close(ours, theirs, "this library's INT8-row kernel vs the reference kernel")
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Family B, step 2: the trellis ("CDQ") re-quantisation and its payload against the reference's own probes
+# (src/kvx_probe.cu built with YSKN_KVX_MODE=3: yskn_tb_probe = tb_fakequant, yskn_tbp_pack_unpack = the fast encoder
+# with its packer), on the synthetic profile blob.
+REF_TB = os.path.join(os.path.dirname(REF), "libyskn_ref_tb.so")
+
+
+def test_trellis_oracle_and_encoder_equal_the_reference_probes_bit_for_bit(oracle):
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    from make_kvqp_blob import make_blob
+    from yasakani_b200 import kvx
+    if not os.path.exists(REF_TB):
+        pytest.skip("oracle/_ref/libyskn_ref_tb.so not built (reference tree was not mounted at build time)")
+    R = C.CDLL(REF_TB)
+    blob = make_blob(nm=5)
+    rows = 128
+    rng = np.random.default_rng(77)
+    x = (rng.standard_normal((rows, 256)) * np.exp(0.5 * rng.standard_normal((rows, 1)))).astype(np.float32)
+    grp = np.arange(rows, dtype=np.int32)                                  # every group record once
+    pos = rng.integers(0, 300, rows).astype(np.int32); pos[::9] = 2        # some rows below their guard position
+    want = oracle.tb_encode(blob, x, grp, pos)
+    P = lambda a: a.ctypes.data_as(C.c_void_p)
+    bb = np.frombuffer(blob, np.uint8)
+    # (1) tb_fakequant (src/kvq_gpu.cuh:54-148)
+    y1 = np.empty_like(x)
+    assert R.yskn_tb_probe(P(bb), C.c_size_t(bb.size), P(x), P(grp), P(pos), P(y1), rows) == 0
+    assert np.array_equal(y1.view(np.uint32), want["y"].view(np.uint32)), "oracle differs from the reference's tb_fakequant"
+    # (2) the fast encoder, its MSB-first packer and side words (src/kvq_fast.cuh:113-232), and the reference's own unpack
+    stride = 160
+    y2 = np.empty_like(x); ydec = np.empty_like(x)
+    pay = np.zeros((rows, stride), np.uint8); side = np.zeros((rows, 2), np.uint32); ms = np.zeros(2, np.float32)
+    assert R.yskn_tbp_pack_unpack(P(bb), C.c_size_t(bb.size), P(x), P(grp), P(pos), rows, stride, P(y2), P(pay), P(side), P(ydec), P(ms)) == 0
+    packed = want["kb"] > 0
+    assert np.array_equal(y2.view(np.uint32), want["y"].view(np.uint32)), "oracle differs from the reference's fast encoder"
+    assert np.array_equal(pay.view(np.uint32).reshape(rows, 40)[packed], want["pay"][packed]), "payload"
+    assert np.array_equal(side[packed], want["side"][packed]), "side words"
+    # (3) the library's encoder on the same rows
+    y3, pay3, side3 = kvx.tb_encode(kvx.TrellisProfile(blob), torch.from_numpy(x).cuda(), torch.from_numpy(grp).cuda(), torch.from_numpy(pos).cuda(), pay_stride=stride)
+    torch.cuda.synchronize()
+    assert np.array_equal(y3.cpu().numpy().view(np.uint32), y2.view(np.uint32))
+    assert np.array_equal(pay3.cpu().numpy()[packed], pay[packed]) and np.array_equal(side3.cpu().numpy().view(np.uint32)[packed], side[packed])

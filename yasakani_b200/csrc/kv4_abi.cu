@@ -303,6 +303,13 @@ int yskn_kvx_decode(const int8_t* d_q8, const float* d_scales, void* d_y, int y_
   return launch_kvx_decode(d_q8, d_scales, d_y, y_dtype, rows, (cudaStream_t)cuda_stream);
 }
 
+int yskn_tb_blob_info(const uint8_t* h_blob, size_t blob_len, int* nm) { return tb_blob_info(h_blob, blob_len, nm); }
+size_t yskn_tb_scratch_bytes(int rows, int nm) { return tb_scratch_bytes(rows, nm); }
+int yskn_tb_encode(const uint8_t* d_blob, int nm, const float* d_x, const int* d_grp, const int* d_pos, int rows, float* d_y, uint8_t* d_pay,
+                   int pay_stride, uint32_t* d_side, void* d_scratch, size_t scratch_bytes, void* cuda_stream) {
+  return launch_tb_encode(d_blob, nm, d_x, d_grp, d_pos, rows, d_y, d_pay, pay_stride, d_side, d_scratch, scratch_bytes, (cudaStream_t)cuda_stream);
+}
+
 int yskn_kv8_attention(const yskn_kv8_attn_args* a, int act_dtype, void* cuda_stream) {
   if (!a) KV4_REJECT("yskn_kv8_attention: null argument struct");
   return launch_kv8_attention(*a, act_dtype, (cudaStream_t)cuda_stream);

@@ -95,6 +95,12 @@ int launch_kvx_rotate(const float* x, float* y, long long rows, int inverse, cud
 int launch_kvx_encode(const void* x, int x_dtype, int8_t* q8, float* scales, long long rows, cudaStream_t st);
 int launch_kvx_decode(const int8_t* q8, const float* scales, void* y, int y_dtype, long long rows, cudaStream_t st);
 
+// Family-B row codec, step 2: trellis re-quantisation and payload (kvq_trellis.cu)
+size_t tb_scratch_bytes(int rows, int nm);
+int tb_blob_info(const uint8_t* h_blob, size_t n, int* nm);
+int launch_tb_encode(const uint8_t* blob, int nm, const float* x, const int* grp, const int* pos, int rows, float* y, uint8_t* pay, int pay_stride,
+                     uint32_t* side, void* scratch, size_t scratch_bytes, cudaStream_t st);
+
 // Family-B decode attention over INT8 rows (kv8_decode.cu)
 int launch_kv8_attention(const yskn_kv8_attn_args& a, int act_dtype, cudaStream_t st);
 int launch_kv8_combine(const float* pm, const float* pl, const float* pacc, int splits, int M, int nh, const void* gate, void* o16,

@@ -1,0 +1,307 @@
+// Family-B cache codec, step 2 (sm_100a): trellis ("CDQ") re-quantisation of 256-value KV rows and their packed payload.
+//
+// Arithmetic and formats are the reference's, bit for bit: tb_fakequant (src/kvq_gpu.cuh:54-148) = tbf_pre / tbf_chain /
+// tbf_sel (src/kvq_fast.cuh:96-232), blob fields "KVQP v1" (src/kvq_gpu.cuh:57-68, src/engine35.cpp:50-53).
+//   row -> (- mean) -> up to two low-rank projections (fp16 coefficients) -> rms
+//   for each of nm scale multipliers: s = fp16(rms * mult); x_i = clamp(rint(r / s * 256), +-2048); for each of the 4 chains
+//   of 64 values a Viterbi search over 256 states (an 8-bit shift register that takes kk = 3 / 4 / 5 new bits per step;
+//   cost (x_i - code[state])^2); the multiplier with the smallest squared error wins (first on ties)
+//   payload: the kk new bits of every step, MSB first, 8*kk 32-bit words per row; side words: scale, two fp16 coefficients.
+// Sums over a row follow the reference's order (a xor-butterfly over each run of 32 values, then the eight run sums in
+// order), and every product that feeds a rounding decision is an explicit _rn operation, so no FMA contraction moves a bit.
+//
+// Work split (not the reference's): the reference runs one 256-thread block per (row, multiplier, chain) with a block
+// barrier per trellis step.  Here ONE WARP owns a (row, multiplier, chain) search: a lane owns eight consecutive states,
+// which all share one predecessor set, so a step is one vector read of that set (the costs are kept transposed in the
+// warp's own shared memory so that the set is contiguous), one minimum, eight squared differences and eight stores, with
+// a warp-level barrier only.  A second kernel, one block per row, picks the multiplier, rebuilds the row and packs it.
+#include "kv4_common.cuh"
+#include <cstring>
+
+namespace kv4 {
+namespace {
+
+__device__ __forceinline__ unsigned tb_u16(const uint8_t* p) { return (unsigned)p[0] | ((unsigned)p[1] << 8); }
+__device__ __forceinline__ unsigned tb_u32(const uint8_t* p) { return tb_u16(p) | (tb_u16(p + 2) << 16); }
+__device__ __forceinline__ float tb_f32(const uint8_t* p) { return __uint_as_float(tb_u32(p)); }
+__device__ __forceinline__ float tb_f16r(float v) { return __half2float(__float2half_rn(v)); }
+
+struct TbGroup { int ok, mode, kk, tix, guard, m, has_mu; unsigned go, off_m, off_t; };
+__device__ __forceinline__ TbGroup tb_group(const uint8_t* b, int g) {
+  TbGroup P;
+  P.off_m = tb_u32(b + 32); P.off_t = tb_u32(b + 36);
+  const unsigned off_g = tb_u32(b + 40), ngrp = tb_u32(b + 28);
+  P.ok = (unsigned)g < ngrp;
+  P.go = P.ok ? tb_u32(b + off_g + 4u * (unsigned)g) : 0u;
+  P.mode = P.ok ? b[P.go] : 0; P.kk = P.ok ? b[P.go + 1] : 4; P.tix = P.ok ? b[P.go + 2] : 0; P.guard = P.ok ? b[P.go + 3] : 0;
+  P.m = P.ok ? b[P.go + 4] : 0; P.has_mu = P.ok ? b[P.go + 5] : 0;
+  return P;
+}
+
+// ---- a warp's view of a row: lane holds elements 32*w + lane, w = 0..7 (one per run of the reference's reduction)
+__device__ __forceinline__ float warp_rowsum(const float (&v)[8]) {
+  float t = 0.f;
+  #pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    float a = v[w];
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+    t = __fadd_rn(t, a);
+  }
+  return t;
+}
+struct RowPre { float r[8], mud[8], u0[8], u1[8], c0, c1, rms; };
+__device__ __forceinline__ void warp_pre(const uint8_t* b, const TbGroup& P, const float* y, int lane, RowPre& Q) {
+  const uint8_t* mup = b + P.go + 8;
+  const uint8_t* Up = mup + (P.has_mu ? 512 : 0);
+  float tmp[8];
+  Q.c0 = Q.c1 = 0.f;
+  #pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    const int d = 32 * w + lane;
+    Q.mud[w] = P.has_mu ? __half2float(__ushort_as_half((unsigned short)tb_u16(mup + 2 * d))) : 0.f;
+    Q.r[w] = P.has_mu ? __fsub_rn(y[d], Q.mud[w]) : y[d];
+    Q.u0[w] = P.m > 0 ? __half2float(__ushort_as_half((unsigned short)tb_u16(Up + 2 * d))) : 0.f;
+    Q.u1[w] = P.m > 1 ? __half2float(__ushort_as_half((unsigned short)tb_u16(Up + 2 * (256 + d)))) : 0.f;
+  }
+  if (P.m > 0) {
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) tmp[w] = __fmul_rn(Q.r[w], Q.u0[w]);
+    Q.c0 = tb_f16r(warp_rowsum(tmp));
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) Q.r[w] = __fsub_rn(Q.r[w], __fmul_rn(Q.c0, Q.u0[w]));
+  }
+  if (P.m > 1) {
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) tmp[w] = __fmul_rn(Q.r[w], Q.u1[w]);
+    Q.c1 = tb_f16r(warp_rowsum(tmp));
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) Q.r[w] = __fsub_rn(Q.r[w], __fmul_rn(Q.c1, Q.u1[w]));
+  }
+  #pragma unroll
+  for (int w = 0; w < 8; ++w) tmp[w] = __fmul_rn(Q.r[w], Q.r[w]);
+  Q.rms = __fsqrt_rn(__fdiv_rn(warp_rowsum(tmp), 256.f));
+  if (Q.rms == 0.f) Q.rms = 1.f;
+}
+
+constexpr int TB_WARPS = 8;                              // searches per block
+struct alignas(16) TbWarpSmem { int cost[2][256]; uint8_t bp[64][32]; uint8_t st[64]; };
+
+struct TbP {
+  const uint8_t* blob; int nm; const float* x; const int* grp; const int* pos; int rows;
+  float* y; uint8_t* pay; int pay_stride; uint32_t* side; uint8_t* scr_states; float* scr_err;
+};
+
+// One warp per (row, multiplier, chain).  States of the best path -> scr_states[row][mi][64*c ..], the two half-chain error
+// sums -> scr_err[row][mi][2c], [2c+1] (the runs of the reference's error sum, src/kvq_fast.cuh:140-147).
+template <int KK>
+__device__ __forceinline__ void tb_search(TbWarpSmem& S, const uint8_t* b, const TbGroup& P, const RowPre& Q, float s, int c, int lane,
+                                          uint8_t* so, float* wo) {
+  constexpr int KQ = 1 << KK, UU = 256 >> KK, SH = 8 - KK;
+  const unsigned to = tb_u32(b + P.off_t + 4u * (unsigned)P.tix);
+  const float gain = tb_f32(b + to + 4);
+  int ci[8];                                             // codes of this lane's states d = 8*lane + e
+  #pragma unroll
+  for (int e = 0; e < 8; ++e) ci[e] = (int)(short)tb_u16(b + to + 12 + 2 * (8 * lane + e));
+  // this chain's 64 scaled values: lane holds steps lane and lane + 32
+  const float ra = Q.r[2 * c], rb = Q.r[2 * c + 1];
+  const int xa = (int)fminf(fmaxf(rintf(__fmul_rn(__fdiv_rn(ra, s), 256.f)), -2048.f), 2048.f);
+  const int xb = (int)fminf(fmaxf(rintf(__fmul_rn(__fdiv_rn(rb, s), 256.f)), -2048.f), 2048.f);
+  // transposed cost layout: state p sits at (p % UU) * KQ + p / UU, so the predecessors {j*UU + u} of group u are contiguous
+  const int u = (8 * lane) >> KK;                        // the predecessor group of all eight states of this lane
+  int widx[8];
+  #pragma unroll
+  for (int e = 0; e < 8; ++e) { const int d = 8 * lane + e; widx[e] = (d & (UU - 1)) * KQ + (d >> SH); }
+  #pragma unroll
+  for (int e = 0; e < 8; ++e) S.cost[0][widx[e]] = (8 * lane + e == 0) ? 0 : 0x40000000;
+  __syncwarp();
+  #pragma unroll 1
+  for (int t = 0; t < 64; ++t) {
+    const int4* cp = reinterpret_cast<const int4*>(&S.cost[t & 1][u * KQ]);
+    int mn = 0x7fffffff, jb = 0;
+    #pragma unroll
+    for (int q = 0; q < KQ / 4; ++q) {                   // first minimum in predecessor order (src/kvq_gpu.cuh:101-102)
+      const int4 v = cp[q];
+      if (v.x < mn) { mn = v.x; jb = 4 * q; }
+      if (v.y < mn) { mn = v.y; jb = 4 * q + 1; }
+      if (v.z < mn) { mn = v.z; jb = 4 * q + 2; }
+      if (v.w < mn) { mn = v.w; jb = 4 * q + 3; }
+    }
+    const int xt = __shfl_sync(0xffffffffu, t < 32 ? xa : xb, t & 31);
+    int* cn = S.cost[(t + 1) & 1];
+    #pragma unroll
+    for (int e = 0; e < 8; ++e) { const int dx = xt - ci[e]; cn[widx[e]] = dx * dx + mn; }
+    if (((8 * lane) & (KQ - 1)) == 0) S.bp[t][u] = (uint8_t)jb;
+    __syncwarp();
+  }
+  // best final state: smallest (cost, state)
+  unsigned long long key = ~0ull;
+  #pragma unroll
+  for (int e = 0; e < 8; ++e) { const unsigned long long k = ((unsigned long long)(unsigned)S.cost[0][widx[e]] << 8) | (unsigned long long)(8 * lane + e); key = k < key ? k : key; }
+  #pragma unroll
+  for (int o = 16; o; o >>= 1) { const unsigned long long k2 = __shfl_xor_sync(0xffffffffu, key, o); key = k2 < key ? k2 : key; }
+  if (lane == 0) {
+    int st = (int)(key & 255ull);
+    for (int t = 63; t >= 0; --t) { S.st[t] = (uint8_t)st; const int j = S.bp[t][st >> KK]; st = (j << SH) | (st >> KK); }
+  }
+  __syncwarp();
+  #pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int stt = S.st[lane + 32 * h];
+    const int cs = (int)(short)tb_u16(b + to + 12 + 2 * stt);
+    const float rec = __fmul_rn(__fmul_rn(__fmul_rn((float)cs, 0.00390625f), gain), s);
+    const float dd = __fsub_rn(h ? rb : ra, rec);
+    float v = __fmul_rn(dd, dd);
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) wo[h] = v;
+    so[lane + 32 * h] = (uint8_t)stt;
+  }
+  __syncwarp();
+}
+
+__global__ void __launch_bounds__(TB_WARPS * 32) tb_search_kernel(TbP A) {
+  __shared__ TbWarpSmem S[TB_WARPS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long job = (long long)blockIdx.x * TB_WARPS + warp;
+  if (job >= (long long)A.rows * A.nm * 4) return;
+  const int row = (int)(job / (A.nm * 4)), rem = (int)(job - (long long)row * (A.nm * 4)), mi = rem >> 2, c = rem & 3;
+  const TbGroup P = tb_group(A.blob, A.grp[row]);
+  if (!P.ok || A.pos[row] < P.guard || P.mode != 0) return;           // stored as is, or flat codes: no search
+  RowPre Q;
+  warp_pre(A.blob, P, A.x + (size_t)row * 256, lane, Q);
+  float s = tb_f16r(__fmul_rn(Q.rms, tb_f32(A.blob + P.off_m + 4u * (unsigned)mi)));
+  if (s == 0.f) s = 1.f;
+  uint8_t* so = A.scr_states + ((size_t)row * A.nm + mi) * 256 + 64 * c;
+  float* wo = A.scr_err + ((size_t)row * A.nm + mi) * 8 + 2 * c;
+  if (P.kk == 3) tb_search<3>(S[warp], A.blob, P, Q, s, c, lane, so, wo);
+  else if (P.kk == 4) tb_search<4>(S[warp], A.blob, P, Q, s, c, lane, so, wo);
+  else if (P.kk == 5) tb_search<5>(S[warp], A.blob, P, Q, s, c, lane, so, wo);
+  else { so[lane] = 0; so[lane + 32] = 0; if (lane == 0) { wo[0] = 3.0e38f; wo[1] = 3.0e38f; } }   // a step width the code does not have: never the best
+}
+
+// One block per row: pick the multiplier, rebuild the row, pack fields and side words.
+__global__ void __launch_bounds__(256) tb_select_kernel(TbP A) {
+  __shared__ uint8_t fld[256];
+  __shared__ float red[8];
+  const int row = blockIdx.x, d = threadIdx.x, warp = d >> 5, lane = d & 31;
+  const uint8_t* b = A.blob;
+  const TbGroup P = tb_group(b, A.grp[row]);
+  const float yv = A.x[(size_t)row * 256 + d];
+  if (!P.ok || A.pos[row] < P.guard) { if (A.y) A.y[(size_t)row * 256 + d] = yv; return; }
+  auto bsum = [&](float v) -> float {                    // the reference's block sum (src/kvq_fast.cuh:33-43)
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) t = __fadd_rn(t, red[w]);
+    __syncthreads();
+    return t;
+  };
+  const uint8_t* mup = b + P.go + 8;
+  const uint8_t* Up = mup + (P.has_mu ? 512 : 0);
+  float r = yv, mud = 0.f, u0 = 0.f, u1 = 0.f, c0 = 0.f, c1 = 0.f;
+  if (P.has_mu) { mud = __half2float(__ushort_as_half((unsigned short)tb_u16(mup + 2 * d))); r = __fsub_rn(yv, mud); }
+  if (P.m > 0) { u0 = __half2float(__ushort_as_half((unsigned short)tb_u16(Up + 2 * d))); c0 = tb_f16r(bsum(__fmul_rn(r, u0))); r = __fsub_rn(r, __fmul_rn(c0, u0)); }
+  if (P.m > 1) { u1 = __half2float(__ushort_as_half((unsigned short)tb_u16(Up + 2 * (256 + d)))); c1 = tb_f16r(bsum(__fmul_rn(r, u1))); r = __fsub_rn(r, __fmul_rn(c1, u1)); }
+  float rms = __fsqrt_rn(__fdiv_rn(bsum(__fmul_rn(r, r)), 256.f)); if (rms == 0.f) rms = 1.f;
+  float xq, psc; int field, kb;
+  if (P.mode == 1) {                                     // flat 4-bit codes (src/kvq_fast.cuh:193-198)
+    float am = fabsf(r);
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    if (lane == 0) red[warp] = am;
+    __syncthreads();
+    am = 0.f;
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) am = fmaxf(am, red[w]);
+    __syncthreads();
+    float s7 = __fdiv_rn(am, 7.f); if (s7 == 0.f) s7 = 1.f;
+    float q = rintf(__fdiv_rn(r, s7)); q = fminf(fmaxf(q, -7.f), 7.f);
+    xq = __fmul_rn(q, s7); field = (int)q + 8; psc = s7; kb = 4;
+  } else {
+    const float* W = A.scr_err + (size_t)row * A.nm * 8;
+    float best_e = 0.f; int best = 0; bool have = false;
+    for (int mi = 0; mi < A.nm; ++mi) {
+      float e = 0.f;
+      #pragma unroll
+      for (int w = 0; w < 8; ++w) e = __fadd_rn(e, W[mi * 8 + w]);
+      if (!have || e < best_e) { have = true; best_e = e; best = mi; }
+    }
+    float s = tb_f16r(__fmul_rn(rms, tb_f32(b + P.off_m + 4u * (unsigned)best))); if (s == 0.f) s = 1.f;
+    const unsigned to = tb_u32(b + P.off_t + 4u * (unsigned)P.tix);
+    const float gain = tb_f32(b + to + 4);
+    const int st = A.scr_states[((size_t)row * A.nm + best) * 256 + d];
+    const int cs = (int)(short)tb_u16(b + to + 12 + 2 * st);
+    xq = __fmul_rn(__fmul_rn(__fmul_rn((float)cs, 0.00390625f), gain), s);
+    field = st & ((1 << P.kk) - 1); psc = s; kb = P.kk;
+  }
+  float x = xq;
+  if (P.m > 0) x = __fadd_rn(x, __fmul_rn(c0, u0));
+  if (P.m > 1) x = __fadd_rn(x, __fmul_rn(c1, u1));
+  if (P.has_mu) x = __fadd_rn(x, mud);
+  if (A.y) A.y[(size_t)row * 256 + d] = x;
+  if (A.pay) {
+    fld[d] = (uint8_t)field;
+    __syncthreads();
+    if (d < 8 * kb) {                                    // MSB-first bit stream, 32 bits per word (src/kvq_fast.cuh:228-232)
+      unsigned w = 0u;
+      for (int i = 0; i < 32; ++i) { const int gbit = 32 * d + i, e = gbit / kb, jb = gbit - e * kb; w |= (((unsigned)fld[e] >> (kb - 1 - jb)) & 1u) << (31 - i); }
+      reinterpret_cast<unsigned*>(A.pay + (size_t)row * A.pay_stride)[d] = w;
+    }
+    if (d == 0 && A.side) {
+      A.side[2 * row] = __float_as_uint(psc);
+      A.side[2 * row + 1] = (unsigned)__half_as_ushort(__float2half_rn(c0)) | ((unsigned)__half_as_ushort(__float2half_rn(c1)) << 16);
+    }
+  }
+}
+
+}  // namespace
+
+size_t tb_scratch_bytes(int rows, int nm) { return rows > 0 && nm > 0 ? (size_t)rows * nm * (256 + 8 * sizeof(float)) : 0; }
+
+// Host-side check of a "KVQP v1" blob, the reference loader's (src/engine35.cpp:50-53) plus its table checks
+// (src/kvq_fast.hpp:66-69); *nm = number of scale multipliers.
+int tb_blob_info(const uint8_t* b, size_t n, int* nm) {
+  auto u16 = [&](size_t o) { return (unsigned)b[o] | ((unsigned)b[o + 1] << 8); };
+  auto u32 = [&](size_t o) { return u16(o) | (u16(o + 2) << 16); };
+  if (!b || n < 100 || memcmp(b, "KVQP", 4) != 0 || u16(4) != 1 || u16(6) != 96 || u32(8) != n) KV4_REJECT("yskn_tb_blob_info: not a KVQP v1 blob");
+  if (u16(16) != 256 || u16(18) != 16 || u16(20) != 4 || u32(28) != 128u) KV4_REJECT("yskn_tb_blob_info: needs D 256, 16 layers, 4 kv heads");
+  const unsigned nt = u16(22), off_t = u32(36), off_g = u32(40), ngrp = u32(28);
+  if ((size_t)off_t + 4 * (size_t)nt > n || (size_t)off_g + 4 * (size_t)ngrp > n || (size_t)u32(32) + 4 * (size_t)u16(24) > n) KV4_REJECT("yskn_tb_blob_info: offsets beyond the blob");
+  for (unsigned t = 0; t < nt; ++t) {
+    const size_t o = u32(off_t + 4 * t);
+    if (o + 12 + 512 > n || b[o] != 8 || b[o + 2] != 64 || b[o + 3] != 8) KV4_REJECT("yskn_tb_blob_info: code tables must have L 8, chain 64, F 8");
+  }
+  for (unsigned g = 0; g < ngrp; ++g) {
+    const size_t go = u32(off_g + 4 * g);
+    if (go + 8 > n) KV4_REJECT("yskn_tb_blob_info: group record %u beyond the blob", g);
+    const int mode = b[go], kk = b[go + 1], tix = b[go + 2], m = b[go + 4], mu = b[go + 5];
+    if (mode > 1 || (mode == 0 && (kk < 3 || kk > 5 || (unsigned)tix >= nt)) || m > 2 || go + 8 + (mu ? 512 : 0) + 512 * (size_t)m > n)
+      KV4_REJECT("yskn_tb_blob_info: group record %u has fields this codec does not have", g);
+  }
+  const int k = (int)u16(24);
+  if (k < 1 || k > 16) KV4_REJECT("yskn_tb_blob_info: %d scale multipliers (1..16)", k);
+  if (nm) *nm = k;
+  return 0;
+}
+
+int launch_tb_encode(const uint8_t* blob, int nm, const float* x, const int* grp, const int* pos, int rows, float* y, uint8_t* pay, int pay_stride,
+                     uint32_t* side, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  if (!blob || !x || !grp || !pos || !scratch) KV4_REJECT("yskn_tb_encode: null buffer");
+  if (rows <= 0 || nm < 1 || nm > 16) KV4_REJECT("yskn_tb_encode: bad shape (rows %d, multipliers %d)", rows, nm);
+  if (pay && (pay_stride < 160 || pay_stride % 4 || ((uintptr_t)pay & 3))) KV4_REJECT("yskn_tb_encode: payload rows need a stride of at least 160 bytes, a multiple of 4");
+  if (scratch_bytes < tb_scratch_bytes(rows, nm) || ((uintptr_t)scratch & 3)) KV4_REJECT("yskn_tb_encode: scratch of %zu bytes needed", tb_scratch_bytes(rows, nm));
+  TbP A{blob, nm, x, grp, pos, rows, y, pay, pay_stride, side, nullptr, nullptr};
+  A.scr_err = static_cast<float*>(scratch);
+  A.scr_states = static_cast<uint8_t*>(scratch) + (size_t)rows * nm * 8 * sizeof(float);
+  const long long jobs = (long long)rows * nm * 4;
+  tb_search_kernel<<<(unsigned)((jobs + TB_WARPS - 1) / TB_WARPS), TB_WARPS * 32, 0, st>>>(A);
+  if (int rc = launch_status("tb_search_kernel")) return rc;
+  tb_select_kernel<<<rows, 256, 0, st>>>(A);
+  return launch_status("tb_select_kernel");
+}
+
+}  // namespace kv4

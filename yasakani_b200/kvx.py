@@ -78,3 +78,30 @@ def launch_kv8_combine(pm, pl, pacc, splits: int, M: int, nh: int, o16: torch.Te
     """Split merge, inverse rotation, rounding, optional sigmoid gate (src/q35_kernels.cu:1400-1424)."""
     check(_lib.load().yskn_kv8_combine(_ptr(pm), _ptr(pl), _ptr(pacc), splits, M, nh, _ptr(gate), _ptr(o16), _dtype_code(o16),
                                        1 if inverse_rotate else 0, _stream(stream)), "yskn_kv8_combine")
+
+
+# ---------------------------------------------------------------- step 2: trellis rows (src/kvq_gpu.cuh, src/kvq_fast.cuh)
+class TrellisProfile:
+    """A "KVQP v1" profile blob checked with the reference loader's rules and uploaded to the current device."""
+
+    def __init__(self, blob: bytes):
+        host = np.frombuffer(blob, np.uint8)
+        nm = C.c_int(0)
+        check(_lib.load().yskn_tb_blob_info(host.ctypes.data, host.size, C.byref(nm)), "yskn_tb_blob_info")
+        self.nm = nm.value
+        self.dev = torch.from_numpy(host.copy()).cuda()
+
+
+def tb_encode(profile: TrellisProfile, x: torch.Tensor, grp: torch.Tensor, pos: torch.Tensor, pay_stride: int = 160, stream=None):
+    """launch_tb_fast (src/kvq_fast.cuh:242-255) over fp32 rows x [rows][256]: returns (y, pay uint8 [rows][pay_stride],
+    side int32-bits [rows][2]); grp, pos int32 device tensors [rows]."""
+    rows = _rows(x)
+    assert x.dtype == torch.float32 and grp.dtype == torch.int32 and pos.dtype == torch.int32
+    L = _lib.load()
+    y = torch.empty_like(x)
+    pay = torch.zeros((rows, pay_stride), dtype=torch.uint8, device=x.device)
+    side = torch.zeros((rows, 2), dtype=torch.int32, device=x.device)
+    scratch = torch.empty(int(L.yskn_tb_scratch_bytes(rows, profile.nm)), dtype=torch.uint8, device=x.device)
+    check(L.yskn_tb_encode(_ptr(profile.dev), profile.nm, _ptr(x), _ptr(grp), _ptr(pos), rows, _ptr(y), _ptr(pay), pay_stride, _ptr(side),
+                           _ptr(scratch), scratch.numel(), _stream(stream)), "yskn_tb_encode")
+    return y, pay, side
