@@ -294,6 +294,11 @@ YSKN_KV4_API int yskn_kvx_probe(const float* x, int8_t* q, float* scales, float*
  * payload, 8*k 32-bit words per row, the k new bits of every value MSB first (pay_stride >= 160, a multiple of 4);
  * d_side [rows][2] = the row's scale (fp32 bits) and its two fp16 low-rank coefficients.  d_scratch:
  * yskn_tb_scratch_bytes(rows, nm) bytes.  Enqueue-only, nothing allocated. */
+/* yskn_tb_decode: the packed rows back to fp32 values (tba_unpack_kernel, src/kvq_attn.cuh:39-72): every value's state is
+ * the 8-bit window of the row's bit stream that ends with its field, so rows decode without the search; rows that were
+ * not packed take d_yin (may be NULL: zeros).  Same d_grp / d_pos / pay_stride as the encoder's. */
+YSKN_KV4_API int yskn_tb_decode(const uint8_t* d_blob, const int* d_grp, const int* d_pos, const uint8_t* d_pay, int pay_stride,
+                                const uint32_t* d_side, const float* d_yin, float* d_y, int rows, void* cuda_stream);
 YSKN_KV4_API int yskn_tb_blob_info(const uint8_t* h_blob, size_t blob_len, int* nm);
 YSKN_KV4_API size_t yskn_tb_scratch_bytes(int rows, int nm);
 YSKN_KV4_API int yskn_tb_encode(const uint8_t* d_blob, int nm, const float* d_x, const int* d_grp, const int* d_pos, int rows, float* d_y,

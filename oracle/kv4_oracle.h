@@ -79,6 +79,8 @@ void ysko_combine(const float* pm, const float* pl, const float* pacc, int S, in
 int ysko_tb_check_blob(const uint8_t* blob, size_t n);
 void ysko_tb_encode(const uint8_t* blob, const float* x, const int* grp, const int* pos, int rows,
                     float* y_fq, uint8_t* fields, uint32_t* pay, uint32_t* side, int* kb);
+void ysko_tb_unpack(const uint8_t* blob, const int* grp, const int* pos, const uint32_t* pay, int stride_words, const uint32_t* side,
+                    const float* yin, float* y, int rows);
 void ysko_tb_decode_fields(const uint8_t* blob, int g, const uint32_t* pay, float scale, float* xq);
 void ysko_xform_a8(const uint16_t* o16, const int8_t* signs, int8_t* qx, float* alpha, int M, int n);
 void ysko_attention_exact_wk(const uint16_t* q16, const ysko_kv_layer* kv, int max_ctx, int M, int pos0,

@@ -179,6 +179,16 @@ def tb_encode(blob: bytes, x: np.ndarray, grp: np.ndarray, pos: np.ndarray):
     return {"y": y, "fields": fields, "pay": pay, "side": side, "kb": kb}
 
 
+def tb_unpack(blob: bytes, grp, pos, pay: np.ndarray, side: np.ndarray, yin: np.ndarray) -> np.ndarray:
+    """Packed rows back to values (tba_unpack_kernel, src/kvq_attn.cuh:39-72); pay uint32 [rows][stride_words]."""
+    a = np.frombuffer(blob, np.uint8)
+    grp = np.ascontiguousarray(grp, np.int32); pos = np.ascontiguousarray(pos, np.int32)
+    pay = np.ascontiguousarray(pay, np.uint32); side = np.ascontiguousarray(side, np.uint32)
+    yin = np.ascontiguousarray(yin, np.float32).reshape(-1, 256); y = np.empty_like(yin)
+    lib().ysko_tb_unpack(_p(a), _p(grp), _p(pos), _p(pay), pay.shape[1], _p(side), _p(yin), _p(y), yin.shape[0])
+    return y
+
+
 def tb_decode_fields(blob: bytes, g: int, pay: np.ndarray, scale: float) -> np.ndarray:
     a = np.frombuffer(blob, np.uint8)
     pay = np.ascontiguousarray(pay, np.uint32); xq = np.empty(256, np.float32)

@@ -168,3 +168,39 @@ void ysko_tb_decode_fields(const uint8_t* blob, int g, const uint32_t* pay, floa
     xq[e] = (((float)ci * 0.00390625f) * gain) * scale;
   }
 }
+
+/* Packed rows back to values (tba_unpack_kernel, src/kvq_attn.cuh:39-72): a value's state is the 8-bit window of the row's
+ * bit stream that ends with its field (shorter at the start of a chain of 64), the code of that state times gain/256 times
+ * the row's scale, then the low-rank part (fp16 coefficients from the side word) and the mean are added back.  Rows that
+ * were not packed (below the group's guard position, or a group the blob does not have) keep yin. */
+void ysko_tb_unpack(const uint8_t* blob, const int* grp, const int* pos, const uint32_t* pay, int stride_words, const uint32_t* side,
+                    const float* yin, float* y, int rows) {
+  const unsigned ngrp = u32(blob + 28), off_t = u32(blob + 36), off_g = u32(blob + 40);
+  for (int r = 0; r < rows; ++r) {
+    memcpy(y + (size_t)r * 256, yin + (size_t)r * 256, 256 * sizeof(float));
+    const int g = grp[r];
+    if ((unsigned)g >= ngrp) continue;
+    const unsigned go = u32(blob + off_g + 4u * (unsigned)g);
+    const int mode = blob[go], kk = blob[go + 1], tix = blob[go + 2], guard = blob[go + 3], m = blob[go + 4], has_mu = blob[go + 5];
+    if (pos[r] < guard || mode > 1) continue;
+    const uint32_t* wp = pay + (size_t)r * stride_words;
+    float s; memcpy(&s, &side[2 * r], 4);
+    const unsigned pc = side[2 * r + 1];
+    const int kb = mode == 1 ? 4 : kk;
+    const unsigned to = u32(blob + off_t + 4u * (unsigned)tix);
+    const uint8_t* mup = blob + go + 8; const uint8_t* Up = mup + (has_mu ? 512 : 0);
+    for (int d = 0; d < 256; ++d) {
+      const int endb = kb * (d + 1), first = kb * (d & ~63), lo = mode == 1 ? endb - 4 : (endb - 8 > first ? endb - 8 : first);
+      unsigned v = 0;
+      for (int bit = lo; bit < endb; ++bit) v = (v << 1) | ((wp[bit >> 5] >> (31 - (bit & 31))) & 1u);
+      float xq;
+      if (mode == 1) xq = (float)((int)v - 8) * s;
+      else { const int ci = (int)(int16_t)u16(blob + to + 12 + 2 * v); xq = (((float)ci * 0.00390625f) * f32(blob + to + 4)) * s; }
+      float x = xq;
+      if (m > 0) x = x + h2f(pc & 0xffffu) * h2f(u16(Up + 2 * d));
+      if (m > 1) x = x + h2f(pc >> 16) * h2f(u16(Up + 2 * (256 + d)));
+      if (has_mu) x = x + h2f(u16(mup + 2 * d));
+      y[(size_t)r * 256 + d] = x;
+    }
+  }
+}

@@ -41,6 +41,12 @@ def test_encoder_is_bit_exact_with_the_oracle(oracle, nm):
     assert np.array_equal(got_pay[packed], want["pay"][packed]), "payload differs"
     assert not got_pay[~packed].any()                            # rows below the guard position are not packed
     assert np.array_equal(side.cpu().numpy().view(np.uint32)[packed], want["side"][packed]), "side words differ"
+    # and back: the packed rows decode, without the search, to the re-quantised rows (rows that were not packed keep the input)
+    back = kvx.tb_decode(prof, pay, side, torch.from_numpy(grp).cuda(), torch.from_numpy(pos).cuda(), yin=torch.from_numpy(x).cuda())
+    torch.cuda.synchronize()
+    want_back = oracle.tb_unpack(blob, grp, pos, want["pay"], want["side"], x)
+    assert np.array_equal(back.cpu().numpy().view(np.uint32), want_back.view(np.uint32)), "decode differs from the oracle"
+    assert np.array_equal(back.cpu().numpy(), want["y"])         # by value: a flat code of -0 decodes to +0
 
 
 def test_blob_check_rejects_what_the_reference_loader_rejects():

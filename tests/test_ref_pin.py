@@ -253,8 +253,12 @@ def test_trellis_oracle_and_encoder_equal_the_reference_probes_bit_for_bit(oracl
     assert np.array_equal(y2.view(np.uint32), want["y"].view(np.uint32)), "oracle differs from the reference's fast encoder"
     assert np.array_equal(pay.view(np.uint32).reshape(rows, 40)[packed], want["pay"][packed]), "payload"
     assert np.array_equal(side[packed], want["side"][packed]), "side words"
+    assert np.array_equal(oracle.tb_unpack(blob, grp, pos, want["pay"], want["side"], x).view(np.uint32), ydec.view(np.uint32)), "oracle unpack differs from the reference's"
     # (3) the library's encoder on the same rows
     y3, pay3, side3 = kvx.tb_encode(kvx.TrellisProfile(blob), torch.from_numpy(x).cuda(), torch.from_numpy(grp).cuda(), torch.from_numpy(pos).cuda(), pay_stride=stride)
     torch.cuda.synchronize()
     assert np.array_equal(y3.cpu().numpy().view(np.uint32), y2.view(np.uint32))
     assert np.array_equal(pay3.cpu().numpy()[packed], pay[packed]) and np.array_equal(side3.cpu().numpy().view(np.uint32)[packed], side[packed])
+    back = kvx.tb_decode(kvx.TrellisProfile(blob), pay3, side3, torch.from_numpy(grp).cuda(), torch.from_numpy(pos).cuda(), yin=torch.from_numpy(x).cuda())
+    torch.cuda.synchronize()
+    assert np.array_equal(back.cpu().numpy().view(np.uint32), ydec.view(np.uint32)), "library unpack differs from the reference's tba_unpack_kernel"

@@ -75,3 +75,11 @@ def test_more_bits_per_value_give_a_smaller_error(oracle):
         r = oracle.tb_encode(blob, x, np.full(60, g, np.int32), np.full(60, 50, np.int32))
         err[kk] = float(np.sqrt(((r["y"] - x) ** 2).mean()))
     assert err[5] < err[4] < err[3] < 0.25, err
+
+
+def test_unpack_restores_the_quantised_rows(oracle):
+    blob = make_blob()
+    x, grp, pos = _rows(96, 11)
+    r = oracle.tb_encode(blob, x, grp, pos)
+    back = oracle.tb_unpack(blob, grp, pos, r["pay"], r["side"], x)
+    assert np.array_equal(back, r["y"])                          # by value: a flat code of -0 decodes to +0

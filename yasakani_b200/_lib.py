@@ -98,6 +98,7 @@ PROTOTYPES = {
     "yskn_kvx_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_void_p]),
     "yskn_kvx_probe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
     "yskn_tb_blob_info": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_int)]),
+    "yskn_tb_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "yskn_tb_scratch_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "yskn_tb_encode": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
                                  C.c_void_p, C.c_size_t, C.c_void_p]),

@@ -310,6 +310,11 @@ int yskn_tb_encode(const uint8_t* d_blob, int nm, const float* d_x, const int* d
   return launch_tb_encode(d_blob, nm, d_x, d_grp, d_pos, rows, d_y, d_pay, pay_stride, d_side, d_scratch, scratch_bytes, (cudaStream_t)cuda_stream);
 }
 
+int yskn_tb_decode(const uint8_t* d_blob, const int* d_grp, const int* d_pos, const uint8_t* d_pay, int pay_stride, const uint32_t* d_side,
+                   const float* d_yin, float* d_y, int rows, void* cuda_stream) {
+  return launch_tb_decode(d_blob, d_grp, d_pos, d_pay, pay_stride, d_side, d_yin, d_y, rows, (cudaStream_t)cuda_stream);
+}
+
 int yskn_kv8_attention(const yskn_kv8_attn_args* a, int act_dtype, void* cuda_stream) {
   if (!a) KV4_REJECT("yskn_kv8_attention: null argument struct");
   return launch_kv8_attention(*a, act_dtype, (cudaStream_t)cuda_stream);

@@ -101,6 +101,9 @@ int tb_blob_info(const uint8_t* h_blob, size_t n, int* nm);
 int launch_tb_encode(const uint8_t* blob, int nm, const float* x, const int* grp, const int* pos, int rows, float* y, uint8_t* pay, int pay_stride,
                      uint32_t* side, void* scratch, size_t scratch_bytes, cudaStream_t st);
 
+int launch_tb_decode(const uint8_t* blob, const int* grp, const int* pos, const uint8_t* pay, int pay_stride, const uint32_t* side, const float* yin,
+                     float* y, int rows, cudaStream_t st);
+
 // Family-B decode attention over INT8 rows (kv8_decode.cu)
 int launch_kv8_attention(const yskn_kv8_attn_args& a, int act_dtype, cudaStream_t st);
 int launch_kv8_combine(const float* pm, const float* pl, const float* pacc, int splits, int M, int nh, const void* gate, void* o16,

@@ -258,7 +258,61 @@ __global__ void __launch_bounds__(256) tb_select_kernel(TbP A) {
   }
 }
 
+// Packed rows back to values (the reference's tba_unpack_kernel, src/kvq_attn.cuh:39-72): one warp per row.  The state of a
+// value is the 8-bit window of the row's bit stream that ends with its field (shorter at the start of a chain of 64), so
+// every value decodes on its own: two payload words from the warp's shared-memory copy of the row, one funnel shift, one
+// code lookup.  Lane owns values 32*w + lane, so the stores of a warp are contiguous.
+struct TbDecP { const uint8_t* blob; const int* grp; const int* pos; const uint8_t* pay; int pay_stride; const uint32_t* side; const float* yin; float* y; int rows; };
+__global__ void __launch_bounds__(256) tb_unpack_kernel(TbDecP A) {
+  __shared__ unsigned s_w[8][44];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = blockIdx.x * 8 + warp;
+  if (row >= A.rows) return;
+  const uint8_t* b = A.blob;
+  const TbGroup P = tb_group(b, A.grp[row]);
+  const bool packed = P.ok && A.pos[row] >= P.guard && P.mode <= 1;
+  if (!packed) {
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) A.y[(size_t)row * 256 + 32 * w + lane] = A.yin ? A.yin[(size_t)row * 256 + 32 * w + lane] : 0.f;
+    return;
+  }
+  const int kb = P.mode == 1 ? 4 : P.kk, nw = 8 * kb;
+  const unsigned* wp = reinterpret_cast<const unsigned*>(A.pay + (size_t)row * A.pay_stride);
+  for (int i = lane; i < 44; i += 32) s_w[warp][i] = i < nw ? wp[i] : 0u;
+  __syncwarp();
+  const float s = __uint_as_float(A.side[2 * (size_t)row]);
+  const unsigned pc = A.side[2 * (size_t)row + 1];
+  const unsigned to = tb_u32(b + P.off_t + 4u * (unsigned)P.tix);
+  const float gain = P.mode == 0 ? tb_f32(b + to + 4) : 1.f;
+  const uint8_t* mup = b + P.go + 8;
+  const uint8_t* Up = mup + (P.has_mu ? 512 : 0);
+  const float c0 = __half2float(__ushort_as_half((unsigned short)(pc & 0xffffu))), c1 = __half2float(__ushort_as_half((unsigned short)(pc >> 16)));
+  #pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    const int d = 32 * w + lane, endb = kb * (d + 1), first = kb * (d & ~63);
+    const int lo = P.mode == 1 ? endb - 4 : max(endb - 8, first), len = endb - lo;
+    const unsigned hiw = s_w[warp][lo >> 5], low = s_w[warp][(lo >> 5) + 1];
+    const unsigned v = __funnelshift_l(low, hiw, lo & 31) >> (32 - len);     // bits [lo, lo + len) of the MSB-first stream
+    float xq;
+    if (P.mode == 1) xq = __fmul_rn((float)((int)v - 8), s);
+    else xq = __fmul_rn(__fmul_rn(__fmul_rn((float)(int)(short)tb_u16(b + to + 12 + 2 * v), 0.00390625f), gain), s);
+    float x = xq;
+    if (P.m > 0) x = __fadd_rn(x, __fmul_rn(c0, __half2float(__ushort_as_half((unsigned short)tb_u16(Up + 2 * d)))));
+    if (P.m > 1) x = __fadd_rn(x, __fmul_rn(c1, __half2float(__ushort_as_half((unsigned short)tb_u16(Up + 2 * (256 + d))))));
+    if (P.has_mu) x = __fadd_rn(x, __half2float(__ushort_as_half((unsigned short)tb_u16(mup + 2 * d))));
+    A.y[(size_t)row * 256 + d] = x;
+  }
+}
+
 }  // namespace
+
+int launch_tb_decode(const uint8_t* blob, const int* grp, const int* pos, const uint8_t* pay, int pay_stride, const uint32_t* side, const float* yin,
+                     float* y, int rows, cudaStream_t st) {
+  if (!blob || !grp || !pos || !pay || !side || !y) KV4_REJECT("yskn_tb_decode: null buffer");
+  if (rows <= 0 || pay_stride < 160 || pay_stride % 4 || ((uintptr_t)pay & 3)) KV4_REJECT("yskn_tb_decode: bad shape (rows %d, payload stride %d)", rows, pay_stride);
+  TbDecP A{blob, grp, pos, pay, pay_stride, side, yin, y, rows};
+  tb_unpack_kernel<<<(rows + 7) / 8, 256, 0, st>>>(A);
+  return launch_status("tb_unpack_kernel");
+}
 
 size_t tb_scratch_bytes(int rows, int nm) { return rows > 0 && nm > 0 ? (size_t)rows * nm * (256 + 8 * sizeof(float)) : 0; }
 

@@ -105,3 +105,13 @@ def tb_encode(profile: TrellisProfile, x: torch.Tensor, grp: torch.Tensor, pos: 
     check(L.yskn_tb_encode(_ptr(profile.dev), profile.nm, _ptr(x), _ptr(grp), _ptr(pos), rows, _ptr(y), _ptr(pay), pay_stride, _ptr(side),
                            _ptr(scratch), scratch.numel(), _stream(stream)), "yskn_tb_encode")
     return y, pay, side
+
+
+def tb_decode(profile: TrellisProfile, pay: torch.Tensor, side: torch.Tensor, grp: torch.Tensor, pos: torch.Tensor, yin: torch.Tensor | None = None,
+              stream=None) -> torch.Tensor:
+    """tba_unpack_kernel (src/kvq_attn.cuh:39-72): payload rows [rows][stride] + side words -> fp32 rows [rows][256]."""
+    rows = pay.shape[0]
+    y = torch.empty((rows, 256), dtype=torch.float32, device=pay.device)
+    check(_lib.load().yskn_tb_decode(_ptr(profile.dev), _ptr(grp), _ptr(pos), _ptr(pay), pay.shape[1], _ptr(side),
+                                    _ptr(yin) if yin is not None else None, _ptr(y), rows, _stream(stream)), "yskn_tb_decode")
+    return y
