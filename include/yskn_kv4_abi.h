@@ -183,6 +183,13 @@ YSKN_KV4_API int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int 
  * stores).  Semantics, partial layout and `splits` are those of yskn_kv4_attention; yskn_kv4_prefill_tc also merges to
  * o16 (+ optional bias). */
 YSKN_KV4_API size_t yskn_kv4_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M);
+/* Lends the library a workspace on the CURRENT device (NULL takes it back) so that the plain entries -- yskn_kv4_attention,
+ * yskn_kv4_decode, yskn_kv4_prefill, the reference's launcher set unchanged -- run passes of more than 8 rows on the
+ * tcgen05 kernel instead of the CUDA-core kernel, whenever the shape is covered (fp16 activations, head_dim 128 / 256) and
+ * the workspace holds yskn_kv4_tc_workspace_bytes(...) for the call.  Through this route the whole workspace is rewritten
+ * on every call (as with valid_tokens = 0); callers that keep it across passes use the _tc entries.  The library only
+ * stores the pointer: the caller owns the memory and must not run two such passes on one device at the same time. */
+YSKN_KV4_API int yskn_kv4_set_tc_workspace(void* d_workspace, size_t bytes);
 YSKN_KV4_API int yskn_kv4_attention_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, void* d_workspace,
                                        size_t workspace_bytes, int valid_tokens, void* cuda_stream);
 YSKN_KV4_API int yskn_kv4_prefill_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, const uint16_t* bv,

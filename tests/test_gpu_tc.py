@@ -140,3 +140,46 @@ def test_tc_workspace_kept_across_passes_gives_the_same_bits(oracle):
     oracle.append(okv, 0, f16_bits(k), f16_bits(v))
     want = oracle.attention_exact(f16_bits(q2), okv, ctx + M1, rope_np, shape.hq, shape.rd, shape.qscale)
     assert_close(kept.float().cpu().numpy(), want, "second pass on a kept workspace")
+
+
+def test_plain_entries_take_the_tensor_core_kernel_once_a_workspace_is_lent(oracle):
+    """yskn_kv4_attention with 32 rows: on the CUDA-core kernel by default, on the tcgen05 kernel (bit-identical with
+    yskn_kv4_attention_tc at valid_tokens = 0) after yskn_kv4_set_tc_workspace, and back after the workspace is taken back."""
+    from yasakani_b200 import kv4
+    shape, ctx, M, S = synth.C2, 1500, 32, 5
+    k, v = synth.make_kv(shape, ctx + M, seed=71)
+    q = synth.make_q(shape, M, seed=71).cuda()
+    max_ctx = ((ctx + M + 127) // 64) * 64
+    layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
+    okv = oracle.KvCache(shape.hkv, shape.hd, max_ctx)
+    gpu_append_all(kv4, layer, k, v, [ctx, M])
+    oracle.append(okv, 0, f16_bits(k[:ctx]), f16_bits(v[:ctx])); oracle.append(okv, ctx, f16_bits(k[ctx:]), f16_bits(v[ctx:]))
+    rope_np = oracle.rope_table(max_ctx, shape.theta, shape.rd); rope = torch.from_numpy(rope_np).cuda()
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+
+    def run(fn):
+        pm, pl, pacc = kv4.attn_scratch(M, S, shape.hq, shape.hd)
+        fn(pm, pl, pacc)
+        o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+        kv4.launch_attn_combine_gqa(pm, pl, pacc, S, M, o16, shape.hq, shape.g)
+        torch.cuda.synchronize()
+        return pacc.clone(), o16
+
+    plain = lambda pm, pl, pacc: kv4.launch_attention_gqa(q, layer, M, d_pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd)
+    ws = kv4.tc_workspace(layer, M)
+    tc = lambda pm, pl, pacc: kv4.launch_attention_tc(q, layer, M, d_pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, ws)
+    pacc_scalar, o_scalar = run(plain)
+    pacc_tc, o_tc = run(tc)
+    assert not torch.equal(pacc_scalar, pacc_tc)                  # two different kernels
+    lent = kv4.tc_workspace(layer, M)
+    kv4.set_tc_workspace(lent)
+    try:
+        pacc_lent, o_lent = run(plain)
+    finally:
+        kv4.set_tc_workspace(None)
+    assert torch.equal(pacc_lent.view(torch.int32), pacc_tc.view(torch.int32)) and torch.equal(o_lent, o_tc)
+    pacc_back, _ = run(plain)
+    assert torch.equal(pacc_back.view(torch.int32), pacc_scalar.view(torch.int32))
+    assert kv4.device_status() == 0
+    want = oracle.attention_exact(f16_bits(q.cpu()), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    assert_close(o_lent.float().cpu().numpy(), want, "wide pass through the plain entry")

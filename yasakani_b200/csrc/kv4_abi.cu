@@ -12,6 +12,9 @@ namespace kv4 {
 
 static thread_local char g_err[512] = "";
 static std::atomic<int> g_algo{ALGO_AUTO};
+// Per-device workspace that lets the plain entries take the tcgen05 kernel for wide passes (yskn_kv4_set_tc_workspace).
+static std::atomic<void*> g_tc_ws[64];
+static std::atomic<size_t> g_tc_ws_bytes[64];
 int current_algo() { return g_algo.load(std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
@@ -46,6 +49,16 @@ static int attention_dispatch(const yskn_attn_g_args* a, int g, int hd, int rd, 
   if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_attention: rotary width %d needs a rope table", rd);
   const bool mma_ok = decode_mma_supports(g, hd, rd, a->M);
   const int algo = current_algo();
+  // Wide passes (more rows than the warp-level decode kernel takes) go to the tcgen05 kernel when the caller has lent a
+  // workspace for the dequantised rows; the whole workspace is brought up to date on every call (valid_tokens = 0).
+  if (a->M > 8 && algo != ALGO_SCALAR && sh.start == 0 && sh.len == a->max_ctx && attention_tc_supports(g, hd, rd, act_dtype)) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+      void* ws = g_tc_ws[dev].load(); const size_t have = g_tc_ws_bytes[dev].load();
+      if (ws && have >= attention_tc_workspace_bytes(a->kvh, hd, a->max_ctx, a->M) && !(((uintptr_t)a->q16 | (uintptr_t)a->pacc) & 15))
+        return launch_attention_tc(*a, g, hd, rd, act_dtype, ws, have, 0, nullptr, nullptr, st);
+    }
+  }
   if (algo == ALGO_MMA && !mma_ok) KV4_REJECT("yskn_kv4_attention: tensor-core path does not cover (g %d, hd %d, rd %d, M %d)", g, hd, rd, a->M);
   if (mma_ok && algo != ALGO_SCALAR) return launch_decode_mma(*a, g, hd, rd, act_dtype, sh, early, st);
   return launch_attention_scalar(*a, g, hd, rd, act_dtype, sh, st);
@@ -66,6 +79,15 @@ const char* yskn_kv4_build_info(void) {
 int yskn_kv4_set_algo(int algo) {
   if (algo < ALGO_AUTO || algo > ALGO_MMA) KV4_REJECT("yskn_kv4_set_algo: unknown algorithm %d", algo);
   g_algo.store(algo, std::memory_order_relaxed); return 0;
+}
+
+int yskn_kv4_set_tc_workspace(void* d_workspace, size_t bytes) {
+  int dev = 0;
+  KV4_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) KV4_REJECT("yskn_kv4_set_tc_workspace: device ordinal %d out of range", dev);
+  if (d_workspace && ((uintptr_t)d_workspace & 15)) KV4_REJECT("yskn_kv4_set_tc_workspace: the workspace must be 16-byte aligned");
+  g_tc_ws_bytes[dev].store(d_workspace ? bytes : 0); g_tc_ws[dev].store(d_workspace);
+  return 0;
 }
 
 int yskn_kv4_device_status(int* status) {

@@ -230,6 +230,13 @@ def launch_attention_prefill(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, p
                                       _ptr(o16), _stream(stream)), "yskn_kv4_prefill")
 
 
+def set_tc_workspace(ws: torch.Tensor | None) -> None:
+    """Lend (or, with None, take back) a workspace so that the plain attention entries use the tcgen05 kernel for passes of
+    more than 8 rows on the current device (yskn_kv4_set_tc_workspace).  Keep the tensor alive while it is lent."""
+    check(_lib.load().yskn_kv4_set_tc_workspace(ws.data_ptr() if ws is not None else None, ws.numel() * ws.element_size() if ws is not None else 0),
+          "yskn_kv4_set_tc_workspace")
+
+
 def tc_workspace(kv: KvLayer, M: int) -> torch.Tensor:
     """Caller-owned fp16 workspace of the tensor-core multi-row path (the reference's KvF32 arrays, src/args.hpp:37)."""
     n = _lib.load().yskn_kv4_tc_workspace_bytes(kv.hkv, kv.hd, kv.max_ctx, M)
