@@ -562,6 +562,10 @@ def secondary_lines(shape, splits, dev):
                                                                   valid_tokens=ctx), 10, 3)
             res["us_per_pass_kept_workspace"] = tk * 1e6
             res["frac_of_bf16_burst_peak_kept_workspace"] = flops / tk / 1e12 / tf
+        # no workspace: the attention kernel converts the packed cache itself (what the plain entries run for passes of 9..128 rows)
+        tfu = _timed(lambda i: kv4.launch_attention_prefill_tc(qm, layer, M, pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, None), 10, 3)
+        res["us_per_pass_fused"] = tfu * 1e6
+        res["frac_of_bf16_burst_peak_fused"] = flops / tfu / 1e12 / tf
         return res
 
     out["prefill_8192_rows"] = tc_case(0, 8192, 1)
@@ -595,15 +599,19 @@ def run_secondary(args):
         d_pos.fill_(ctx)
         pm, pl, pacc = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
         o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
-        ws = kv4.tc_workspace(layer, M)
-        t = _timed(lambda i: kv4.launch_attention_prefill_tc(q, layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws), K, W)
         flops = shape.attn_flops(sum(ctx + r + 1 for r in range(M)))
-        line = dict(base, metric="kv4_multirow_attn_tflops", value=flops / t / 1e12, unit="TFLOP/s", ms_per_step=t * 1e3, dtype="f16",
-                    config={"workload": name, "rows": M, "cached_tokens": ctx, "splits": splits, "l2": "K/V workspace is L2-resident by design; tensor-bound"},
-                    gpu_launches=(2 if splits == 1 else 3) * K,
-                    roofline={"bound": "tensor", "achieved": flops / t / 1e12, "peak": tf, "unit": "TFLOP/s", "frac": flops / t / 1e12 / tf, "traffic": None,
-                              "kernel": "dequant prep + tcgen05 attention" + ("" if splits == 1 else " + merge"), "peak_kind": f"of {kind}"})
-        print(json.dumps(line), flush=True)
+        for form in ("workspace", "fused"):                        # fused: no workspace, the attention kernel converts the packed cache itself
+            ws = kv4.tc_workspace(layer, M) if form == "workspace" else None
+            t = _timed(lambda i: kv4.launch_attention_prefill_tc(q, layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws), K, W)
+            nl = (2 if form == "workspace" else 1) + (0 if splits == 1 else 1)
+            line = dict(base, metric="kv4_multirow_attn_tflops", value=flops / t / 1e12, unit="TFLOP/s", ms_per_step=t * 1e3, dtype="f16",
+                        config={"workload": name, "form": form, "rows": M, "cached_tokens": ctx, "splits": splits,
+                                "l2": "K/V workspace is L2-resident by design; tensor-bound" if form == "workspace" else "packed cache read once per CTA pair"},
+                        gpu_launches=nl * K,
+                        roofline={"bound": "tensor", "achieved": flops / t / 1e12, "peak": tf, "unit": "TFLOP/s", "frac": flops / t / 1e12 / tf, "traffic": None,
+                                  "kernel": ("dequant prep + tcgen05 attention" if form == "workspace" else "tcgen05 attention with in-kernel conversion") +
+                                            ("" if splits == 1 else " + merge"), "peak_kind": f"of {kind}"})
+            print(json.dumps(line), flush=True)
 
     if args.workload == "prefill":
         tc_case(0, 8192, 1, "C5 causal prefill: 8192 rows from an empty cache, Hq24/Hkv4/hd256")

@@ -181,14 +181,21 @@ YSKN_KV4_API int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int 
  * dequantised tokens [0, valid_tokens) of this cache from an earlier call (valid_tokens <= *d_pos; nothing below the
  * 128-token tile of valid_tokens is touched).  q16 must be fp16; q16, pacc and o16 must be 16-byte aligned (vector
  * stores).  Semantics, partial layout and `splits` are those of yskn_kv4_attention; yskn_kv4_prefill_tc also merges to
- * o16 (+ optional bias). */
+ * o16 (+ optional bias).
+ * d_workspace = NULL with workspace_bytes = 0 selects the form that needs no workspace: converter warps inside the attention
+ * kernel read the packed rows of each key tile (int4 words, scale / zero rows, rope rows, shadow rows of the open groups)
+ * and write the fp16 operand tiles themselves.  One launch, nothing dequantised to memory; valid_tokens is ignored.  This
+ * form also takes bf16 activations (q16, bv and o16 bf16: the queries are staged as fp16 operands) and needs the rotary
+ * width to be a multiple of 16 channels. */
 YSKN_KV4_API size_t yskn_kv4_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M);
-/* Lends the library a workspace on the CURRENT device (NULL takes it back) so that the plain entries -- yskn_kv4_attention,
- * yskn_kv4_decode, yskn_kv4_prefill, the reference's launcher set unchanged -- run passes of more than 8 rows on the
- * tcgen05 kernel instead of the CUDA-core kernel, whenever the shape is covered (fp16 activations, head_dim 128 / 256) and
- * the workspace holds yskn_kv4_tc_workspace_bytes(...) for the call.  Through this route the whole workspace is rewritten
- * on every call (as with valid_tokens = 0); callers that keep it across passes use the _tc entries.  The library only
- * stores the pointer: the caller owns the memory and must not run two such passes on one device at the same time. */
+/* The plain entries -- yskn_kv4_attention, yskn_kv4_decode, yskn_kv4_prefill, the reference's launcher set unchanged -- run
+ * passes of more than 8 rows on the tcgen05 kernel whenever the shape is covered (head_dim 128 / 256, full cache, 16-byte
+ * aligned arrays): without a workspace (the converting form above) by default.  This call lends the library a workspace on
+ * the CURRENT device (NULL takes it back); passes of more than 32 rows with fp16 activations then use the workspace form
+ * when it holds yskn_kv4_tc_workspace_bytes(...) for the call, which is faster for long passes (a prefill converts each
+ * tile once instead of once per query tile).  Through this route the whole workspace is rewritten on every call (as with
+ * valid_tokens = 0); callers that keep it across passes use the _tc entries.  The library only stores the pointer: the
+ * caller owns the memory and must not run two such passes on one device at the same time. */
 YSKN_KV4_API int yskn_kv4_set_tc_workspace(void* d_workspace, size_t bytes);
 YSKN_KV4_API int yskn_kv4_attention_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int act_dtype, void* d_workspace,
                                        size_t workspace_bytes, int valid_tokens, void* cuda_stream);

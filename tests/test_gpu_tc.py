@@ -9,8 +9,9 @@ from yasakani_b200 import synth
 pytestmark = pytest.mark.gpu
 
 
-def _run_tc(kv4, oracle, shape, ctx, M, splits, seed, prefill=False):
-    """Cache of ctx tokens, then one pass appends M rows and attends with them. Returns (got, want)."""
+def _run_tc(kv4, oracle, shape, ctx, M, splits, seed, prefill=False, fused=False):
+    """Cache of ctx tokens, then one pass appends M rows and attends with them. Returns (got, want).
+    fused: no workspace, the kernel converts the packed cache itself."""
     k, v = synth.make_kv(shape, ctx + M, seed=seed)
     q = synth.make_q(shape, M, seed=seed)
     max_ctx = ((ctx + M + 127) // 64) * 64
@@ -27,7 +28,7 @@ def _run_tc(kv4, oracle, shape, ctx, M, splits, seed, prefill=False):
     d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
     pm, pl, pacc = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
     pm.fill_(float("nan")); pl.fill_(float("nan")); pacc.fill_(float("nan"))
-    ws = kv4.tc_workspace(layer, M)
+    ws = None if fused else kv4.tc_workspace(layer, M)
     o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
     if prefill:
         kv4.launch_attention_prefill_tc(q.cuda(), layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws)
@@ -55,20 +56,23 @@ TC_CASES = [
 ]
 
 
+@pytest.mark.parametrize("fused", [False, True], ids=["workspace", "fused"])
 @pytest.mark.parametrize("shape,ctx,M,splits", TC_CASES)
-def test_tc_attention_matches_exact_oracle(oracle, shape, ctx, M, splits):
+def test_tc_attention_matches_exact_oracle(oracle, shape, ctx, M, splits, fused):
     from yasakani_b200 import kv4
-    got, want = _run_tc(kv4, oracle, shape, ctx, M, splits, seed=51)
-    assert_close(got, want, f"tc attention {shape} ctx {ctx} M {M}")
+    got, want = _run_tc(kv4, oracle, shape, ctx, M, splits, seed=51, fused=fused)
+    assert_close(got, want, f"tc attention {shape} ctx {ctx} M {M} fused {fused}")
 
 
-def test_tc_prefill_merges_in_one_call(oracle):
+@pytest.mark.parametrize("fused", [False, True], ids=["workspace", "fused"])
+def test_tc_prefill_merges_in_one_call(oracle, fused):
     from yasakani_b200 import kv4
-    got, want = _run_tc(kv4, oracle, synth.C2, 0, 700, 1, seed=52, prefill=True)
+    got, want = _run_tc(kv4, oracle, synth.C2, 0, 700, 1, seed=52, prefill=True, fused=fused)
     assert_close(got, want, "tc prefill 700 rows")
 
 
-def test_tc_rows_do_not_depend_on_pass_width(oracle):
+@pytest.mark.parametrize("fused", [False, True], ids=["workspace", "fused"])
+def test_tc_rows_do_not_depend_on_pass_width(oracle, fused):
     """16-, 32- and 64-row passes over the same base give bitwise identical shared rows (config 3, scaled down)."""
     from yasakani_b200 import kv4
     shape, ctx = synth.C2, 2048
@@ -85,11 +89,38 @@ def test_tc_rows_do_not_depend_on_pass_width(oracle):
         d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
         pm, pl, pacc = kv4.attn_scratch(M, 7, shape.hq, shape.hd)
         o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
-        kv4.launch_attention_tc(q[:M].cuda(), layer, M, d_pos, 7, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, kv4.tc_workspace(layer, M))
+        kv4.launch_attention_tc(q[:M].cuda(), layer, M, d_pos, 7, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd,
+                                None if fused else kv4.tc_workspace(layer, M))
         kv4.launch_attn_combine_gqa(pm, pl, pacc, 7, M, o16, shape.hq, shape.g)
         torch.cuda.synchronize()
         outs[M] = o16.cpu().view(torch.int16).numpy()
     assert np.array_equal(outs[16], outs[32][:16]) and np.array_equal(outs[32], outs[64][:32])
+
+
+@pytest.mark.parametrize("splits", [1, 4])
+def test_tc_fused_takes_bf16_activations(oracle, splits):
+    """The form without a workspace stages bf16 queries as fp16 operand rows itself and writes bf16 rows (what the 27B
+    engine passes); compared with the exact oracle on the same (bf16-representable) queries."""
+    from yasakani_b200 import kv4
+    shape, ctx, M = synth.C2, 900, 24
+    k, v = synth.make_kv(shape, ctx + M, seed=81)
+    q = synth.make_q(shape, M, seed=81).bfloat16()
+    max_ctx = ((ctx + M + 127) // 64) * 64
+    layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
+    okv = oracle.KvCache(shape.hkv, shape.hd, max_ctx)
+    gpu_append_all(kv4, layer, k, v, [ctx, M])
+    oracle.append(okv, 0, f16_bits(k[:ctx]), f16_bits(v[:ctx])); oracle.append(okv, ctx, f16_bits(k[ctx:]), f16_bits(v[ctx:]))
+    rope_np = oracle.rope_table(max_ctx, shape.theta, shape.rd); rope = torch.from_numpy(rope_np).cuda()
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    pm, pl, pacc = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
+    o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.bfloat16, device="cuda")
+    kv4.launch_attention_prefill_tc(q.cuda(), layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, None)
+    torch.cuda.synchronize()
+    assert kv4.device_status() == 0
+    want = oracle.attention_exact(f16_bits(q.float().half()), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+    got = o16.float().cpu().numpy()
+    err = np.abs(got - want)
+    assert (err <= 2e-3 + 1e-2 * np.abs(want)).all(), f"bf16 fused pass: max err {err.max():.3e}"
 
 
 def test_tc_rejects_what_it_does_not_cover():
@@ -142,44 +173,47 @@ def test_tc_workspace_kept_across_passes_gives_the_same_bits(oracle):
     assert_close(kept.float().cpu().numpy(), want, "second pass on a kept workspace")
 
 
-def test_plain_entries_take_the_tensor_core_kernel_once_a_workspace_is_lent(oracle):
-    """yskn_kv4_attention with 32 rows: on the CUDA-core kernel by default, on the tcgen05 kernel (bit-identical with
-    yskn_kv4_attention_tc at valid_tokens = 0) after yskn_kv4_set_tc_workspace, and back after the workspace is taken back."""
+def test_plain_entries_take_the_tensor_core_kernel_for_wide_passes(oracle):
+    """yskn_kv4_attention with more than 8 rows runs the tcgen05 kernel: the form that converts the packed cache itself
+    (bit-identical with yskn_kv4_attention_tc without a workspace), and for passes of more than 32 rows the workspace form
+    (bit-identical with yskn_kv4_attention_tc at valid_tokens = 0) while a workspace is lent."""
     from yasakani_b200 import kv4
-    shape, ctx, M, S = synth.C2, 1500, 32, 5
-    k, v = synth.make_kv(shape, ctx + M, seed=71)
-    q = synth.make_q(shape, M, seed=71).cuda()
-    max_ctx = ((ctx + M + 127) // 64) * 64
-    layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
-    okv = oracle.KvCache(shape.hkv, shape.hd, max_ctx)
-    gpu_append_all(kv4, layer, k, v, [ctx, M])
-    oracle.append(okv, 0, f16_bits(k[:ctx]), f16_bits(v[:ctx])); oracle.append(okv, ctx, f16_bits(k[ctx:]), f16_bits(v[ctx:]))
-    rope_np = oracle.rope_table(max_ctx, shape.theta, shape.rd); rope = torch.from_numpy(rope_np).cuda()
-    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    shape, ctx, S = synth.C2, 1500, 5
+    for M in (32, 48):
+        k, v = synth.make_kv(shape, ctx + M, seed=71)
+        q = synth.make_q(shape, M, seed=71).cuda()
+        max_ctx = ((ctx + M + 127) // 64) * 64
+        layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
+        okv = oracle.KvCache(shape.hkv, shape.hd, max_ctx)
+        gpu_append_all(kv4, layer, k, v, [ctx, M])
+        oracle.append(okv, 0, f16_bits(k[:ctx]), f16_bits(v[:ctx])); oracle.append(okv, ctx, f16_bits(k[ctx:]), f16_bits(v[ctx:]))
+        rope_np = oracle.rope_table(max_ctx, shape.theta, shape.rd); rope = torch.from_numpy(rope_np).cuda()
+        d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
 
-    def run(fn):
-        pm, pl, pacc = kv4.attn_scratch(M, S, shape.hq, shape.hd)
-        fn(pm, pl, pacc)
-        o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
-        kv4.launch_attn_combine_gqa(pm, pl, pacc, S, M, o16, shape.hq, shape.g)
-        torch.cuda.synchronize()
-        return pacc.clone(), o16
+        def run(fn):
+            pm, pl, pacc = kv4.attn_scratch(M, S, shape.hq, shape.hd)
+            fn(pm, pl, pacc)
+            o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+            kv4.launch_attn_combine_gqa(pm, pl, pacc, S, M, o16, shape.hq, shape.g)
+            torch.cuda.synchronize()
+            return pacc.clone(), o16
 
-    plain = lambda pm, pl, pacc: kv4.launch_attention_gqa(q, layer, M, d_pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd)
-    ws = kv4.tc_workspace(layer, M)
-    tc = lambda pm, pl, pacc: kv4.launch_attention_tc(q, layer, M, d_pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, ws)
-    pacc_scalar, o_scalar = run(plain)
-    pacc_tc, o_tc = run(tc)
-    assert not torch.equal(pacc_scalar, pacc_tc)                  # two different kernels
-    lent = kv4.tc_workspace(layer, M)
-    kv4.set_tc_workspace(lent)
-    try:
-        pacc_lent, o_lent = run(plain)
-    finally:
-        kv4.set_tc_workspace(None)
-    assert torch.equal(pacc_lent.view(torch.int32), pacc_tc.view(torch.int32)) and torch.equal(o_lent, o_tc)
-    pacc_back, _ = run(plain)
-    assert torch.equal(pacc_back.view(torch.int32), pacc_scalar.view(torch.int32))
-    assert kv4.device_status() == 0
-    want = oracle.attention_exact(f16_bits(q.cpu()), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
-    assert_close(o_lent.float().cpu().numpy(), want, "wide pass through the plain entry")
+        plain = lambda pm, pl, pacc: kv4.launch_attention_gqa(q, layer, M, d_pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd)
+        ws = kv4.tc_workspace(layer, M)
+        with_ws = lambda pm, pl, pacc: kv4.launch_attention_tc(q, layer, M, d_pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, ws)
+        fused = lambda pm, pl, pacc: kv4.launch_attention_tc(q, layer, M, d_pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, None)
+        pacc_plain, o_plain = run(plain)
+        pacc_fused, _ = run(fused)
+        pacc_ws, o_ws = run(with_ws)
+        assert torch.equal(pacc_plain.view(torch.int32), pacc_fused.view(torch.int32))
+        lent = kv4.tc_workspace(layer, M)
+        kv4.set_tc_workspace(lent)
+        try:
+            pacc_lent, o_lent = run(plain)
+        finally:
+            kv4.set_tc_workspace(None)
+        assert torch.equal(pacc_lent.view(torch.int32), (pacc_ws if M > 32 else pacc_fused).view(torch.int32))
+        assert kv4.device_status() == 0
+        want = oracle.attention_exact(f16_bits(q.cpu()), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
+        assert_close(o_plain.float().cpu().numpy(), want, f"wide pass ({M} rows) through the plain entry")
+        assert_close(o_lent.float().cpu().numpy(), want, f"wide pass ({M} rows) through the plain entry, workspace lent")

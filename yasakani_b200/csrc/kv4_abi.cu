@@ -49,15 +49,21 @@ static int attention_dispatch(const yskn_attn_g_args* a, int g, int hd, int rd, 
   if (rd > 0 && !a->rope) KV4_REJECT("yskn_kv4_attention: rotary width %d needs a rope table", rd);
   const bool mma_ok = decode_mma_supports(g, hd, rd, a->M);
   const int algo = current_algo();
-  // Wide passes (more rows than the warp-level decode kernel takes) go to the tcgen05 kernel when the caller has lent a
-  // workspace for the dequantised rows; the whole workspace is brought up to date on every call (valid_tokens = 0).
-  if (a->M > 8 && algo != ALGO_SCALAR && sh.start == 0 && sh.len == a->max_ctx && attention_tc_supports(g, hd, rd, act_dtype)) {
+  // Wide passes (more rows than the warp-level decode kernel takes) go to the tcgen05 kernel.  Up to TC_FUSED_MAX_ROWS rows it
+  // converts the packed cache inside the kernel (every CTA pair converts the tiles it reads; measured at 32,768 tokens: 89 / 93 us
+  // for 16 / 32 rows against 111 / 116 us with a full dequantisation in front, but 173 against 141 us for 64 rows); longer
+  // passes dequantise once into a workspace, if the caller has lent one (valid_tokens = 0: the whole workspace is brought
+  // up to date on every call), and take the converting form otherwise.
+  if (a->M > 8 && algo != ALGO_SCALAR && sh.start == 0 && sh.len == a->max_ctx && !(((uintptr_t)a->q16 | (uintptr_t)a->pacc) & 15)) {
+    constexpr int TC_FUSED_MAX_ROWS = 32;
     int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+    if (a->M > TC_FUSED_MAX_ROWS && attention_tc_supports(g, hd, rd, act_dtype) && cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
       void* ws = g_tc_ws[dev].load(); const size_t have = g_tc_ws_bytes[dev].load();
-      if (ws && have >= attention_tc_workspace_bytes(a->kvh, hd, a->max_ctx, a->M) && !(((uintptr_t)a->q16 | (uintptr_t)a->pacc) & 15))
+      if (ws && have >= attention_tc_workspace_bytes(a->kvh, hd, a->max_ctx, a->M))
         return launch_attention_tc(*a, g, hd, rd, act_dtype, ws, have, 0, nullptr, nullptr, st);
     }
+    const uintptr_t al = (uintptr_t)a->kv.kq | (uintptr_t)a->kv.vq | (uintptr_t)a->kv.kscale | (uintptr_t)a->kv.kzero | (uintptr_t)a->kv.kshadow | (uintptr_t)a->rope;
+    if (attention_tc_fused_supports(g, hd, rd, act_dtype) && !(al & 15)) return launch_attention_tc_fused(*a, g, hd, rd, act_dtype, nullptr, nullptr, st);
   }
   if (algo == ALGO_MMA && !mma_ok) KV4_REJECT("yskn_kv4_attention: tensor-core path does not cover (g %d, hd %d, rd %d, M %d)", g, hd, rd, a->M);
   if (mma_ok && algo != ALGO_SCALAR) return launch_decode_mma(*a, g, hd, rd, act_dtype, sh, early, st);

@@ -70,6 +70,8 @@ int decode_status_fetch(int* out);
 int tc_status_fetch(int* out);       // same for the tcgen05 multi-row kernel
 bool attention_tc_supports(int g, int hd, int rd, int act_dtype);
 size_t attention_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M);
+bool attention_tc_fused_supports(int g, int hd, int rd, int act_dtype);
+int launch_attention_tc_fused(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, uint16_t* o16_direct, const uint16_t* bv, cudaStream_t st);
 // o16_direct != nullptr and splits == 1: rows are finished in the kernel (o/l, + bv) and no partials are written
 int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, void* workspace, size_t workspace_bytes,
                         int valid_tokens, uint16_t* o16_direct, const uint16_t* bv, cudaStream_t st);   // reads and clears the device status word of the tensor-core decode kernel

@@ -34,6 +34,7 @@
 // frees its TMEM and returns.
 #include "kv4_common.cuh"
 #include <cuda.h>
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -184,6 +185,10 @@ __device__ __forceinline__ uint32_t leader_addr(uint32_t local) { uint32_t r; as
 __device__ __forceinline__ void bar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// Data that a CTA's converter warps wrote into its own shared memory with ordinary stores is read by the tensor core of the
+// same SM: each writer orders its stores for the async proxy (fence.proxy.async), the warp then arrives on the leader's
+// barrier and the issuing thread waits on it, both with the default release / acquire; no other SM ever reads these bytes
+// with ordinary loads.
 __device__ __forceinline__ void cluster_sync_all() {                 // every thread of both CTAs
   asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -270,9 +275,42 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ float tc_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ uint32_t tc_pack(float lo, float hi) { uint32_t d; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo)); return d; }
 
+// ------------------------------------------------------------------------------------------------ int4 -> fp16 operand rows
+// A packed 32-bit word holds the nibbles of eight consecutive channels.  One logic op reads nibbles (x, x + 4) in place as
+// the fp16 pair (off + n_x, off + n_{x+4}) (off = 1024 under exponent 2^10 for bits 0..3 of a half, 64 under 2^6 for bits
+// 4..7); the offset is removed by an exact fp16 subtraction, so n[x] holds the two nibbles as exact small integers.
+__device__ __forceinline__ uint32_t tc_hadd2(uint32_t a, uint32_t b) { uint32_t d; asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ uint32_t tc_hfma2(uint32_t a, uint32_t b, uint32_t c) { uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
+__device__ __forceinline__ uint32_t tc_hmul2(uint32_t a, uint32_t b) { uint32_t d; asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ void tc_nibs(uint32_t w, uint32_t (&n)[4]) {
+  const uint32_t w8 = w >> 8;
+  n[0] = tc_hadd2((w & 0x000F000Fu) | 0x64006400u, 0xE400E400u); n[1] = tc_hadd2((w & 0x00F000F0u) | 0x54005400u, 0xD400D400u);
+  n[2] = tc_hadd2((w8 & 0x000F000Fu) | 0x64006400u, 0xE400E400u); n[3] = tc_hadd2((w8 & 0x00F000F0u) | 0x54005400u, 0xD400D400u);
+}
+// eight consecutive fp16 (v.x = (e0, e1) .. v.w = (e6, e7)) <-> registers o[x] = (e_x, e_{x+4})
+__device__ __forceinline__ void tc_row_to_pairs(const uint4& v, uint32_t (&o)[4]) {
+  o[0] = __byte_perm(v.x, v.z, 0x5410); o[1] = __byte_perm(v.x, v.z, 0x7632); o[2] = __byte_perm(v.y, v.w, 0x5410); o[3] = __byte_perm(v.y, v.w, 0x7632);
+}
+__device__ __forceinline__ uint4 tc_pairs_to_row(const uint32_t (&r)[4]) {
+  return make_uint4(__byte_perm(r[0], r[1], 0x5410), __byte_perm(r[2], r[3], 0x5410), __byte_perm(r[0], r[1], 0x7632), __byte_perm(r[2], r[3], 0x7632));
+}
+// Global loads as ordered asm statements: the compiler keeps them where they are written, ahead of the arithmetic.
+__device__ __forceinline__ uint32_t tc_ldg32(const void* p) { uint32_t v; asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p)); return v; }
+__device__ __forceinline__ uint32_t tc_ldg16(const void* p) { unsigned short v; asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p)); return v; }
+__device__ __forceinline__ uint4 tc_ldg128(const void* p) {
+  uint4 v; asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)); return v;
+}
+__device__ __forceinline__ void tc_sts128(uint32_t a, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 // ------------------------------------------------------------------------------------------------ attention kernel
 constexpr int TC_SW = 8;                                   // softmax warps: warp w owns rows 32*(w%4).., key columns 64*(w/4)..
-constexpr int TC_THREADS = (TC_SW + 2) * 32;               // + producer warp, + MMA issuer warp
+constexpr int TC_KW = 3, TC_VW = 3, TC_CW = TC_KW + TC_VW;  // converter warps of the fused form: K half tiles, V half tiles
+// + producer warp, + MMA issuer warp; the fused form adds the converter warps and fills up to four warpgroups (16 warps x 128
+// registers at launch), so that setmaxnreg can move registers from the softmax warps (120 each) to the converters (136 each)
+constexpr int tc_threads(bool fused) { return fused ? 512 : (TC_SW + 2) * 32; }
+static_assert(TC_SW == 8 && TC_SW + 2 + TC_CW <= 16, "warpgroups 0-1 = softmax warps, warpgroups 2-3 = producer, MMA issuer, converters");
+constexpr int TC_THREADS = tc_threads(false);
 
 // A pair of CTAs (a cluster of two, tcgen05 cta_group::2) works on 256 query rows with MMAs of M = 256: each CTA keeps
 // its 128 rows of S, P and O in its own tensor memory, its Q rows in shared memory, and stages HALF of every K tile
@@ -306,10 +344,18 @@ struct TcP {
   const int* d_pos; int M, splits, G, nh, max_ctx, ks_rows; float qscale;
   float* pm; float* pl; float* pacc;
   uint16_t* o16; const uint16_t* bv;                       // splits == 1 and o16 set: store the finished rows, no partials
+  yskn_kv_layer kv; const float* rope; int rd;             // the fused form reads the packed cache itself
+  const uint16_t* q16; int bf16;                           // fused form with bf16 activations: the converter warps also stage Q (as fp16)
 };
 
-template <int HD>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+// FUSED = false: K and V tiles come by TMA from the fp16 workspace that kv4_tc_prep_kernel wrote.
+// FUSED = true: no workspace.  Four more warps per CTA read the packed cache rows of each tile straight from global memory
+// (the int4 words, their scale and zero rows, the rope table rows of the rotary channels; for edge tiles also the fp16
+// shadow rows), convert them and store the fp16 operand rows into the same 128-byte-swizzled stages the TMA would have
+// filled; "full" then counts the converter warps of both CTAs instead of bytes.  A pass reads 1/4 of the bytes of the
+// workspace form and needs no launch in front.
+template <int HD, bool FUSED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc_threads(FUSED), 1)
 kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapKd,
                    const __grid_constant__ CUtensorMap mapVd, const __grid_constant__ CUtensorMap mapKs, const TcP P) {
   using L = TcLay<HD>;
@@ -343,10 +389,10 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 
   if (sb & 1023u) { if (threadIdx.x == 0) atomicExch(&g_tc_status, 3); return; }   // same in both CTAs: nobody is left waiting
   if (threadIdx.x == 0) {
-    for (int i = 0; i < L::NK; ++i) { bar_init(b_kfull + 8 * i, 1); bar_init(b_kempty + 8 * i, 1); }
-    for (int i = 0; i < L::NV; ++i) { bar_init(b_vfull + 8 * i, 1); bar_init(b_vempty + 8 * i, 1); }
+    for (int i = 0; i < L::NK; ++i) { bar_init(b_kfull + 8 * i, FUSED ? 2 * TC_KW : 1); bar_init(b_kempty + 8 * i, 1); }
+    for (int i = 0; i < L::NV; ++i) { bar_init(b_vfull + 8 * i, FUSED ? 2 * TC_VW : 1); bar_init(b_vempty + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) { bar_init(b_sready + 8 * i, 1); bar_init(b_pready + 8 * i, 2 * TC_SW); bar_init(b_pvdone + 8 * i, 1); }
-    bar_init(b_q, 1);
+    bar_init(b_q, FUSED && P.bf16 ? 2 * TC_KW : 1);
     *s_abort = 0;
     for (int i = 0; i < 128; ++i) reinterpret_cast<volatile uint32_t*>(smem + L::OFF_XCH + 2 * 2 * 128 * 4)[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -360,16 +406,20 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   cluster_sync_all();                                                // both CTAs' barriers exist before anyone signals the other
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (FUSED) {                                                       // whole warpgroups: 0-1 (softmax) shrink, 2-3 (converters) grow
+    if (warp < TC_SW) asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 136;");
+  }
 
   if (warp == TC_SW) {
     // ======================================================================= TMA producer (one per CTA)
     // Q once, then two rings: K halves are free again as soon as their S MMAs are done, V halves only after P.V.
     // Every copy reports to the leader's "full" barrier; the leader posts the byte count of both CTAs' parts.
-    if (lane == 0 && n > 0) {
+    if (lane == 0 && n > 0 && !(FUSED && P.bf16)) {
       if (rank == 0) bar_expect_tx(b_q, 2 * L::KBLK * G * TOK * 128);
       for (int kb = 0; kb < L::KBLK; ++kb) tma_load_4d_pair(sb + L::OFF_Q + kb * L::Q_BLOCK, &mapQ, 64 * kb, 0, kvh, tok0, lead_q);
       int kit = 0; bool ok = true;
-      for (int i = 0; i < n && ok; ++i) {
+      for (int i = 0; i < n && ok && !FUSED; ++i) {
         const int j = j0 + i;
         for (int half = 0; half < (i >= nbulk ? 2 : 1) && ok; ++half, ++kit) {      // Kd; edge tiles: then Ks
           const int st = kit % L::NK;
@@ -439,7 +489,246 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         issue_pv(i, 0);
       }
     }
-  } else {
+  } else if (FUSED && warp >= TC_SW + 2 && warp < TC_SW + 2 + TC_CW) {
+    // ======================================================================= converter warps (fused form)
+    // Three warps convert the K half tiles, three the V half tiles, each role with its own ring, so neither waits for the
+    // other.  Every global load of a phase is issued before the first dependent instruction (ordered asm statements) and
+    // the loads of the next tile are in flight while the current one is converted: a thread pays the memory latency once.
+    constexpr int NKT = TC_KW * 32, NVT = TC_VW * 32, NWD = HD / 8, NWV = HD / 16;   // threads per role; packed words per K row; per V row in this CTA's channel half
+    const int ct = (int)threadIdx.x - (TC_SW + 2) * 32;
+    const int end = pos0 + P.M;                                      // tokens [0, end) exist
+    const size_t row0 = (size_t)kvh * P.max_ctx, grp0 = (size_t)kvh * (P.max_ctx / 32);
+    bool ok = true;
+    auto publish = [&](uint32_t lead_bar) {                          // this warp's part of the stage is written
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) bar_arrive_cluster(lead_bar);
+    };
+    auto stage_wait = [&](uint32_t bar_empty, int item, int depth) { // the stage's previous contents have been consumed
+      if (item >= depth && !bar_wait(bar_empty, (item / depth - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; }
+      if (*s_abort) ok = false;
+    };
+    if (n > 0 && ct < NKT) {
+      // ------------------------------------------------------------------- K role
+      const int nrw = P.rd / 8, nrp = nrw / 2, half = P.rd / 2;      // rotary words; word pairs (w, w + nrp), a power of two; frequencies
+      const int lp = nrp > 0 ? __ffs(nrp) - 1 : 0, nrot = (TC_BN / 2) * nrp;
+      const int npl = NWD - nrw, nplain = npl * 8;                   // plain word columns; plain items = (column, octet of keys), 8 octets per half tile
+      const uint32_t* kq32 = reinterpret_cast<const uint32_t*>(P.kv.kq);
+      auto k_addr = [&](uint32_t sk, int w, int k) { return sk + (w >> 3) * L::K_BLOCK + k * 128 + (((w & 7) ^ (k & 7)) << 4); };
+      // this thread's plain items (at most three): word column and first key; consecutive lanes take consecutive columns of one octet
+      constexpr int NPI = (NWD * 8 + NKT - 1) / NKT;
+      int pcol[NPI], pkey[NPI];
+      #pragma unroll
+      for (int u = 0; u < NPI; ++u) {
+        const int it = ct + NKT * u;
+        pcol[u] = it < nplain ? nrw + it % (npl > 0 ? npl : 1) : -1; pkey[u] = it < nplain ? 8 * (it / (npl > 0 ? npl : 1)) : 0;
+      }
+      struct PlainIn { uint32_t w[8]; uint4 s, z; };
+      auto plain_load = [&](int u, int tk0, PlainIn& I) {
+        const uint32_t* src = kq32 + (row0 + tk0 + pkey[u]) * (HD / 8) + pcol[u];
+        #pragma unroll
+        for (int e = 0; e < 8; ++e) I.w[e] = tc_ldg32(src + e * (HD / 8));
+        const size_t gb = (grp0 + (tk0 + pkey[u]) / 32) * HD + 8 * pcol[u];
+        I.s = tc_ldg128(P.kv.kscale + gb); I.z = tc_ldg128(P.kv.kzero + gb);
+      };
+      auto plain_store = [&](int u, uint32_t sk, const PlainIn& I) {
+        uint32_t sc[4], zz[4];
+        tc_row_to_pairs(I.s, sc); tc_row_to_pairs(I.z, zz);
+        const uint32_t base = sk + (pcol[u] >> 3) * L::K_BLOCK + pkey[u] * 128;      // pkey is a multiple of 8: key & 7 = e
+        #pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          uint32_t nb[4], r[4];
+          tc_nibs(I.w[e], nb);
+          #pragma unroll
+          for (int x = 0; x < 4; ++x) r[x] = tc_hfma2(nb[x], sc[x], zz[x]);
+          tc_sts128(base + e * 128 + (((pcol[u] & 7) ^ e) << 4), tc_pairs_to_row(r));
+        }
+      };
+      struct RotIn { uint32_t wa, wb; uint4 sa, za, sb, zb; uint4 r[4]; };   // shadow items keep their two fp16 rows in sa, za
+      // one rotary item = key k, word pair (p, p + nrp): 8 + 8 channels (c, c + rd/2) and their 8 (cos, sin) pairs
+      auto rot_load = [&](int it, int tk0, bool shadow, RotIn& R) {
+        const int k = it >> lp, p = it & (nrp - 1), q = p + nrp, t = tk0 + k;
+        if (shadow) {
+          R.sa = tc_ldg128(P.kv.kshadow + (row0 + t) * HD + 8 * p); R.za = tc_ldg128(P.kv.kshadow + (row0 + t) * HD + 8 * q);
+        } else {
+          const uint32_t* rowp = kq32 + (row0 + t) * (HD / 8);
+          R.wa = tc_ldg32(rowp + p); R.wb = tc_ldg32(rowp + q);
+          const size_t gb = (grp0 + t / 32) * HD;
+          R.sa = tc_ldg128(P.kv.kscale + gb + 8 * p); R.za = tc_ldg128(P.kv.kzero + gb + 8 * p);
+          R.sb = tc_ldg128(P.kv.kscale + gb + 8 * q); R.zb = tc_ldg128(P.kv.kzero + gb + 8 * q);
+        }
+        const float* rp = P.rope + ((size_t)t * half + 8 * p) * 2;
+        #pragma unroll
+        for (int e = 0; e < 4; ++e) R.r[e] = tc_ldg128(rp + 4 * e);
+      };
+      // fp16 pairs throughout: registers x hold channels (x, x + 4) of the word, like the nibble reads
+      auto rot_store = [&](int it, int tk0, bool shadow, uint32_t sk, const RotIn& R) {
+        const int k = it >> lp, p = it & (nrp - 1), q = p + nrp, t = tk0 + k;
+        uint32_t a[4], b[4];
+        if (shadow) {
+          tc_row_to_pairs(R.sa, a); tc_row_to_pairs(R.za, b);
+          if (t >= end) { a[0] = a[1] = a[2] = a[3] = 0u; b[0] = b[1] = b[2] = b[3] = 0u; }
+        } else {
+          uint32_t na[4], nb[4], sa[4], za[4], sb4[4], zb[4];
+          tc_nibs(R.wa, na); tc_nibs(R.wb, nb);
+          tc_row_to_pairs(R.sa, sa); tc_row_to_pairs(R.za, za); tc_row_to_pairs(R.sb, sb4); tc_row_to_pairs(R.zb, zb);
+          #pragma unroll
+          for (int x = 0; x < 4; ++x) { a[x] = tc_hfma2(na[x], sa[x], za[x]); b[x] = tc_hfma2(nb[x], sb4[x], zb[x]); }
+        }
+        // R.r[e/2] = (cos e, sin e, cos e+1, sin e+1) as fp32 bits; C[x] = (cos x, cos x+4), S[x] = (sin x, sin x+4)
+        const uint32_t C[4] = {tc_pack(__uint_as_float(R.r[0].x), __uint_as_float(R.r[2].x)), tc_pack(__uint_as_float(R.r[0].z), __uint_as_float(R.r[2].z)),
+                               tc_pack(__uint_as_float(R.r[1].x), __uint_as_float(R.r[3].x)), tc_pack(__uint_as_float(R.r[1].z), __uint_as_float(R.r[3].z))};
+        const uint32_t S[4] = {tc_pack(__uint_as_float(R.r[0].y), __uint_as_float(R.r[2].y)), tc_pack(__uint_as_float(R.r[0].w), __uint_as_float(R.r[2].w)),
+                               tc_pack(__uint_as_float(R.r[1].y), __uint_as_float(R.r[3].y)), tc_pack(__uint_as_float(R.r[1].w), __uint_as_float(R.r[3].w))};
+        uint32_t lo[4], hi[4];
+        #pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          lo[x] = tc_hfma2(a[x], C[x], tc_hmul2(b[x], S[x]) ^ 0x80008000u);      // a cos - b sin
+          hi[x] = tc_hfma2(a[x], S[x], tc_hmul2(b[x], C[x]));                    // a sin + b cos
+        }
+        tc_sts128(k_addr(sk, p, k), tc_pairs_to_row(lo));
+        tc_sts128(k_addr(sk, q, k), tc_pairs_to_row(hi));
+      };
+      auto zero_k = [&](uint32_t sk) {                               // a half tile past max_ctx: nothing to read
+        for (int it = ct; it < (TC_BN / 2) * NWD; it += NKT) tc_sts128(k_addr(sk, it % NWD, it / NWD), make_uint4(0u, 0u, 0u, 0u));
+      };
+      if (P.bf16) {
+        // bf16 activations: this CTA's query rows (token, head) as fp16 operand rows; rows without a query are zero
+        for (int it = ct; it < 128 * NWD; it += NKT) {
+          const int row = it / NWD, w = it % NWD, tk = tok0 + row / G, hq = row % G;
+          uint4 out = make_uint4(0u, 0u, 0u, 0u);
+          if (row < TOK * G && tk < P.M) {
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(P.q16 + ((size_t)tk * P.nh + kvh * G + hq) * HD + 8 * w));
+            const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+            uint32_t o4[4];
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) o4[e] = tc_pack(bf2f((uint16_t)uu[e]), bf2f((uint16_t)(uu[e] >> 16)));
+            out = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+          }
+          tc_sts128(sb + L::OFF_Q + (w >> 3) * L::Q_BLOCK + row * 128 + (((w & 7) ^ (row & 7)) << 4), out);
+        }
+        publish(lead_q);
+      }
+      PlainIn I0, I1;                                                // the coming int4 item's first two plain items (the usual case has two)
+      RotIn R0;                                                      // and its first rotary item
+      bool have = false;
+      int kit = 0;
+      for (int i = 0; i < n && ok; ++i) {
+        const int j = j0 + i;
+        const int tk0 = j * TC_BN + (TC_BN / 2) * (int)rank;         // first key of this CTA's half of the K tile
+        const bool kin = tk0 < P.max_ctx;                            // max_ctx is a multiple of 64: the half tile is inside or outside as a whole
+        // ---- item 1: the int4 keys
+        {
+          const int st = kit % L::NK;
+          const uint32_t sk = sb + L::OFF_K + st * L::K_HALF;
+          const bool h0 = kin && ct < nrot;
+          if (kin && !have) {
+            if (pcol[0] >= 0) plain_load(0, tk0, I0);
+            if (NPI > 1 && pcol[NPI > 1 ? 1 : 0] >= 0) plain_load(1, tk0, I1);
+            if (h0) rot_load(ct, tk0, false, R0);
+          }
+          have = false;
+          stage_wait(b_kempty + 8 * st, kit, L::NK);
+          if (!ok) break;
+          if (!kin) zero_k(sk);
+          else {
+            if (pcol[0] >= 0) plain_store(0, sk, I0);
+            if (NPI > 1 && pcol[NPI > 1 ? 1 : 0] >= 0) plain_store(1, sk, I1);
+            #pragma unroll
+            for (int u = 2; u < NPI; ++u)
+              if (pcol[u] >= 0) { plain_load(u, tk0, I0); plain_store(u, sk, I0); }
+            if (h0) rot_store(ct, tk0, false, sk, R0);
+            {
+              RotIn R1;
+              for (int it = ct + NKT; it < nrot; it += NKT) { rot_load(it, tk0, false, R1); rot_store(it, tk0, false, sk, R1); }   // words and tables already on chip
+            }
+            if (i + 1 < n && tk0 + TC_BN < P.max_ctx) {              // the next tile's words travel while this tile is consumed
+              if (pcol[0] >= 0) plain_load(0, tk0 + TC_BN, I0);
+              if (NPI > 1 && pcol[NPI > 1 ? 1 : 0] >= 0) plain_load(1, tk0 + TC_BN, I1);
+              if (ct < nrot) rot_load(ct, tk0 + TC_BN, false, R0);
+              have = true;
+            }
+          }
+          publish(lead_kfull + 8 * st);
+          ++kit;
+        }
+        // ---- item 2 (edge tiles): the fp16 shadow keys
+        if (i >= nbulk) {
+          const int st = kit % L::NK;
+          const uint32_t sk = sb + L::OFF_K + st * L::K_HALF;
+          stage_wait(b_kempty + 8 * st, kit, L::NK);
+          if (!ok) break;
+          if (!kin) zero_k(sk);
+          else {
+            #pragma unroll
+            for (int u = 0; u < NPI; ++u)
+              if (pcol[u] >= 0) {
+                uint4 x8[8];
+                #pragma unroll
+                for (int e = 0; e < 8; ++e) x8[e] = tc_ldg128(P.kv.kshadow + (row0 + tk0 + pkey[u] + e) * HD + 8 * pcol[u]);
+                #pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  tc_sts128(sk + (pcol[u] >> 3) * L::K_BLOCK + (pkey[u] + e) * 128 + (((pcol[u] & 7) ^ e) << 4), tk0 + pkey[u] + e < end ? x8[e] : make_uint4(0u, 0u, 0u, 0u));
+              }
+            RotIn R1;
+            for (int it = ct; it < nrot; it += NKT) { rot_load(it, tk0, true, R1); rot_store(it, tk0, true, sk, R1); }
+          }
+          publish(lead_kfull + 8 * st);
+          ++kit;
+        }
+      }
+    } else if (n > 0 && ct < NKT + NVT) {
+      // ------------------------------------------------------------------- V role: this CTA's HD/2 channels of all 128 keys of a tile.
+      // Item = (key, 16-byte part of the key's half row = 32 channels); tokens that do not exist yet read as zero.
+      constexpr int PARTS = NWV / 4, NVI = (TC_BN * PARTS + NVT - 1) / NVT;
+      const int vt = ct - NKT;
+      struct VIn { uint4 w; uint32_t s, z; };
+      VIn cur[NVI], nxt[NVI];
+      auto v_load = [&](int j, VIn (&I)[NVI]) {
+        #pragma unroll
+        for (int u = 0; u < NVI; ++u) {
+          const int it = vt + NVT * u, t = j * TC_BN + it / PARTS;
+          if (it < TC_BN * PARTS && t < end) {
+            I[u].w = tc_ldg128(P.kv.vq + (row0 + t) * (HD / 2) + (HD / 4) * (int)rank + 16 * (it % PARTS));
+            I[u].s = tc_ldg16(P.kv.vscale + row0 + t); I[u].z = tc_ldg16(P.kv.vzero + row0 + t);
+          }
+        }
+      };
+      v_load(j0, cur);
+      for (int i = 0; i < n && ok; ++i) {
+        const int j = j0 + i, st = i % L::NV;
+        const uint32_t sv = sb + L::OFF_V + st * L::V_HALF;
+        if (i + 1 < n) v_load(j + 1, nxt);                           // the next tile's rows travel while this one is converted
+        stage_wait(b_vempty + 8 * st, i, L::NV);
+        if (!ok) break;
+        #pragma unroll
+        for (int u = 0; u < NVI; ++u) {
+          const int it = vt + NVT * u, k = it / PARTS, part = it % PARTS;
+          if (it < TC_BN * PARTS) {
+            const bool live = j * TC_BN + k < end;
+            const uint32_t s2 = cur[u].s | (cur[u].s << 16), z2 = cur[u].z | (cur[u].z << 16);
+            const uint32_t ww[4] = {cur[u].w.x, cur[u].w.y, cur[u].w.z, cur[u].w.w};
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              uint4 out = make_uint4(0u, 0u, 0u, 0u);
+              if (live) {
+                uint32_t nb[4], r[4];
+                tc_nibs(ww[e], nb);
+                #pragma unroll
+                for (int x = 0; x < 4; ++x) r[x] = tc_hfma2(nb[x], s2, z2);
+                out = tc_pairs_to_row(r);
+              }
+              const int c = 4 * part + e;                            // 16-byte chunk (8 channels) of the half row
+              tc_sts128(sv + (c >> 3) * L::V_BLOCK + k * 128 + (((c & 7) ^ (k & 7)) << 4), out);
+            }
+          }
+        }
+        publish(lead_vfull + 8 * st);
+        #pragma unroll
+        for (int u = 0; u < NVI; ++u) cur[u] = nxt[u];
+      }
+    }
+  } else if (warp < TC_SW) {
     // ======================================================================= softmax warps: two threads per query row
     const int quad = warp & 3, hf = warp >> 2;                       // TMEM lane quadrant; which 64 of the tile's 128 key columns
     const int rho = quad * 32 + lane;                                // row of the tile = TMEM lane
@@ -555,6 +844,11 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           #pragma unroll
           for (int k = 0; k < 32; k += 2) {
             float y0 = round_f16(o[k] / l), y1 = round_f16(o[k + 1] / l);
+            if (FUSED && P.bf16) {
+              if (P.bv) { y0 = __fadd_rn(y0, bf2f(P.bv[kvh * HD + 32 * c + k])); y1 = __fadd_rn(y1, bf2f(P.bv[kvh * HD + 32 * c + k + 1])); }
+              w[k / 2] = (uint32_t)f2bf(y0) | ((uint32_t)f2bf(y1) << 16);
+              continue;
+            }
             if (P.bv) { y0 = __fadd_rn(y0, h2f(P.bv[kvh * HD + 32 * c + k])); y1 = __fadd_rn(y1, h2f(P.bv[kvh * HD + 32 * c + k + 1])); }
             w[k / 2] = (uint32_t)f2h(y0) | ((uint32_t)f2h(y1) << 16);
           }
@@ -665,13 +959,29 @@ int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int va
   if (!tc_map_q(&mq, a.q16, a.M, a.kvh, g, HD) || !tc_map_rows(&mkd, w.kd, rows, HD, TC_BN / 2, L::KBLK) ||
       !tc_map_rows(&mvd, w.vd, rows, HD, TC_BN, L::KBLK / 2) || !tc_map_rows(&mks, w.ks, (uint64_t)a.kvh * w.ks_rows, HD, TC_BN / 2, L::KBLK))
     KV4_REJECT("yskn_kv4_attention_tc: cuTensorMapEncodeTiled failed or is unavailable");
-  auto kern = kv4_tc_attn_kernel<HD>;
+  auto kern = kv4_tc_attn_kernel<HD, false>;
   static std::atomic<unsigned long long> attr{0};
   if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;        // CTA pairs: an even number of query tiles
-  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv};
+  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv, a.kv, a.rope, rd, nullptr, 0};
   kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mq, mkd, mvd, mks, P);
   return launch_status("kv4_tc_attn_kernel");
+}
+
+// The fused form: one launch, no workspace.
+template <int HD>
+int launch_tc_fused_hd(const yskn_attn_g_args& a, int g, int rd, int bf16, uint16_t* o16, const uint16_t* bv, cudaStream_t st) {
+  using L = TcLay<HD>;
+  CUtensorMap mq;
+  if (bf16) memset(&mq, 0, sizeof(mq));                               // the converter warps stage Q
+  else if (!tc_map_q(&mq, a.q16, a.M, a.kvh, g, HD)) KV4_REJECT("yskn_kv4_attention: cuTensorMapEncodeTiled failed or is unavailable");
+  auto kern = kv4_tc_attn_kernel<HD, true>;
+  static std::atomic<unsigned long long> attr{0};
+  if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+  const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;
+  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, 0, a.qscale, a.pm, a.pl, a.pacc, o16, bv, a.kv, a.rope, rd, static_cast<const uint16_t*>(a.q16), bf16};
+  kern<<<dim3(qtiles, a.splits, a.kvh), tc_threads(true), L::TOTAL, st>>>(mq, mq, mq, mq, P);
+  return launch_status("kv4_tc_attn_kernel (fused)");
 }
 
 }  // namespace
@@ -685,6 +995,7 @@ size_t attention_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M) { retur
 
 int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, void* workspace, size_t workspace_bytes,
                         int valid_tokens, uint16_t* o16_direct, const uint16_t* bv, cudaStream_t st) {
+  if (!workspace && workspace_bytes == 0) return launch_attention_tc_fused(a, g, hd, rd, act_dtype, o16_direct, bv, st);   // no workspace: convert inside the kernel
   if (!attention_tc_supports(g, hd, rd, act_dtype))
     KV4_REJECT("yskn_kv4_attention_tc: unsupported (g %d, hd %d, rd %d, act_dtype %d): fp16 activations, hd 128/256", g, hd, rd, act_dtype);
   const TcWs w = carve(workspace, a.kvh, hd, a.max_ctx, a.M);
@@ -694,6 +1005,22 @@ int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int ac
   if (o16_direct && ((uintptr_t)o16_direct & 15)) KV4_REJECT("yskn_kv4_prefill_tc: o16 must be 16-byte aligned");
   if (!o16_direct && ((uintptr_t)a.pacc & 15)) KV4_REJECT("yskn_kv4_attention_tc: pacc must be 16-byte aligned");
   return hd == 256 ? launch_tc_hd<256>(a, g, rd, w, valid_tokens, o16_direct, bv, st) : launch_tc_hd<128>(a, g, rd, w, valid_tokens, o16_direct, bv, st);
+}
+
+// Many-row attention straight from the packed cache (no workspace, one launch).  Same shapes as the workspace form, and the
+// rotary width must be a whole number of 16-channel word pairs.
+bool attention_tc_fused_supports(int g, int hd, int rd, int act_dtype) {
+  return (act_dtype == YSKN_KV4_F16 || act_dtype == YSKN_KV4_BF16) && attention_tc_supports(g, hd, rd, YSKN_KV4_F16) && rd % 16 == 0;
+}
+
+int launch_attention_tc_fused(const yskn_attn_g_args& a, int g, int hd, int rd, int act_dtype, uint16_t* o16_direct, const uint16_t* bv, cudaStream_t st) {
+  if (!attention_tc_fused_supports(g, hd, rd, act_dtype))
+    KV4_REJECT("yskn_kv4_attention: fused tensor-core form does not cover (g %d, hd %d, rd %d, act_dtype %d)", g, hd, rd, act_dtype);
+  const uintptr_t al = (uintptr_t)a.q16 | (uintptr_t)a.kv.kq | (uintptr_t)a.kv.vq | (uintptr_t)a.kv.kscale | (uintptr_t)a.kv.kzero | (uintptr_t)a.kv.kshadow |
+                       (uintptr_t)a.rope | (o16_direct ? (uintptr_t)o16_direct : (uintptr_t)a.pacc);
+  if (al & 15) KV4_REJECT("yskn_kv4_attention: q16, cache arrays, rope table and pacc / o16 must be 16-byte aligned");
+  const int bf16 = act_dtype == YSKN_KV4_BF16;
+  return hd == 256 ? launch_tc_fused_hd<256>(a, g, rd, bf16, o16_direct, bv, st) : launch_tc_fused_hd<128>(a, g, rd, bf16, o16_direct, bv, st);
 }
 
 int tc_status_fetch(int* out) {

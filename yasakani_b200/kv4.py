@@ -246,19 +246,22 @@ def tc_workspace(kv: KvLayer, M: int) -> torch.Tensor:
 
 
 def launch_attention_tc(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float, rd: int,
-                        workspace: torch.Tensor, valid_tokens: int = 0, stream=None) -> None:
-    """launch_kv_dequant + launch_attention_f32 (src/attention_kv4q.cu:198-285) on tcgen05: partials for M rows."""
+                        workspace: torch.Tensor | None, valid_tokens: int = 0, stream=None) -> None:
+    """launch_kv_dequant + launch_attention_f32 (src/attention_kv4q.cu:198-285) on tcgen05: partials for M rows.
+    workspace None: the kernel converts the packed cache itself (no dequantised copy, one launch)."""
     a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
-    check(_lib.load().yskn_kv4_attention_tc(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), _ptr(workspace),
-                                           workspace.numel(), valid_tokens, _stream(stream)), "yskn_kv4_attention_tc")
+    check(_lib.load().yskn_kv4_attention_tc(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), _ptr(workspace) if workspace is not None else None,
+                                           workspace.numel() if workspace is not None else 0, valid_tokens, _stream(stream)), "yskn_kv4_attention_tc")
 
 
 def launch_attention_prefill_tc(q16, kv: KvLayer, M: int, d_pos, splits: int, pm, pl, pacc, rope, nh: int, qscale: float, rd: int,
-                                o16, workspace: torch.Tensor, bv=None, valid_tokens: int = 0, stream=None) -> None:
-    """launch_attention_prefill_f32 (src/attention_kv4q.cu:287-323) on tcgen05: M appended rows, merged to o16."""
+                                o16, workspace: torch.Tensor | None, bv=None, valid_tokens: int = 0, stream=None) -> None:
+    """launch_attention_prefill_f32 (src/attention_kv4q.cu:287-323) on tcgen05: M appended rows, merged to o16.
+    workspace None: the kernel converts the packed cache itself."""
     a = _attn_args(q16, kv, M, d_pos, splits, pm, pl, pacc, rope, nh, qscale)
     check(_lib.load().yskn_kv4_prefill_tc(C.byref(a), nh // kv.hkv, kv.hd, rd, _dtype_code(q16), bv.data_ptr() if bv is not None else None,
-                                         _ptr(o16), _ptr(workspace), workspace.numel(), valid_tokens, _stream(stream)), "yskn_kv4_prefill_tc")
+                                         _ptr(o16), _ptr(workspace) if workspace is not None else None,
+                                         workspace.numel() if workspace is not None else 0, valid_tokens, _stream(stream)), "yskn_kv4_prefill_tc")
 
 
 def launch_local_triple(pm, pl, pacc, splits: int, M: int, nh: int, hd: int, triple, stream=None) -> None:
