@@ -639,6 +639,29 @@ def run_secondary(args):
                                   "kernel": "kv8 decode attention (split-K partials)", "bytes_per_launch": byt, "peak_kind": f"of {kind}"})
             print(json.dumps(line), flush=True)
             del caches
+        # verify passes over INT8 rows on the tcgen05 kernel (converter warps inside the kernel): 16 / 32 / 64 rows against 32,768 tokens
+        ctx = 32768
+        for M, Sv in ((64, 9), (32, 18), (16, 18)):
+            mc = ((ctx + M + 127) // 64) * 64
+            k8 = torch.randint(-127, 128, (kvh, mc, 256), dtype=torch.int8, device="cuda", generator=g)
+            v8 = torch.randint(-127, 128, (kvh, mc, 256), dtype=torch.int8, device="cuda", generator=g)
+            ks = torch.rand((kvh, mc), device="cuda", generator=g) * 0.03; vs = torch.rand((kvh, mc), device="cuda", generator=g) * 0.03
+            q = torch.randn((M, nh, 256), device="cuda", generator=g).to(torch.bfloat16)
+            d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+            pm = torch.empty((M, Sv, nh), device="cuda"); pl = torch.empty_like(pm); pacc = torch.empty((M, Sv, nh, 256), device="cuda")
+            o16 = torch.empty((M, nh, 256), dtype=torch.bfloat16, device="cuda")
+            def one(i):
+                kvx.launch_kv8_attention_tc(q, k8, v8, ks, vs, M, d_pos, Sv, pm, pl, pacc, nh)
+                kvx.launch_kv8_combine(pm, pl, pacc, Sv, M, nh, o16)
+            t = _timed(one, K, W)
+            flops = shape.attn_flops(sum(ctx + r + 1 for r in range(M)))
+            line = dict(base, metric="kv8_multirow_attn_tflops", value=flops / t / 1e12, unit="TFLOP/s", ms_per_step=t * 1e3, dtype="f16",
+                        config={"workload": f"Family-B verify over INT8 rows: {M} rows against {ctx} cached tokens, Hq{nh}/Hkv{kvh}/hd256", "rows": M, "cached_tokens": ctx,
+                                "splits": Sv, "l2": "INT8 rows read once per CTA pair (68 MB)"},
+                        gpu_launches=2 * K,
+                        roofline={"bound": "tensor", "achieved": flops / t / 1e12, "peak": tf, "unit": "TFLOP/s", "frac": flops / t / 1e12 / tf, "traffic": None,
+                                  "kernel": "tcgen05 attention with in-kernel INT8 conversion + merge", "peak_kind": f"of {kind}"})
+            print(json.dumps(line), flush=True)
     elif args.workload == "kvx":
         rows = 1 << 20
         x = torch.randn((rows, 256), device="cuda", generator=g)

@@ -335,6 +335,12 @@ typedef struct yskn_kv8_attn_args {
 /* launch_q35_attention, INT8 branch (q35_attention_kernel<true>, src/q35_kernels.cu:1176-1281).  nh / kvh <= 8,
  * max_ctx a multiple of 64, k8/v8 16-byte aligned.  Split boundaries are multiples of 16 keys (the merge does not depend on them). */
 YSKN_KV4_API int yskn_kv8_attention(const yskn_kv8_attn_args* a, int act_dtype, void* cuda_stream);
+/* The same partials for many rows (verify passes, prefill) on the tcgen05 kernel: the counterpart of the reference's
+ * tensor-core verify kernels over INT8 rows (launch_q35_atx / q35_fa8_kernel, src/q35_atx.cu:92-793, src/q35_fa.cu:48-303;
+ * same row semantics as q35_attention_kernel<KV8>, row by row).  Converter warps read the INT8 rows and scales and write
+ * fp16 operand tiles (byte times scale, rounded once to fp16); q16 fp16 or bf16; q16 and pacc 16-byte aligned; `splits`
+ * partitions the 128-key tiles below *d_pos.  yskn_kv8_attention takes this route by itself for M > 8. */
+YSKN_KV4_API int yskn_kv8_attention_tc(const yskn_kv8_attn_args* a, int act_dtype, void* cuda_stream);
 
 /* Merge of the splits as launch_q35_combine does up to the gated row (src/q35_kernels.cu:1400-1424): y = o / L, inverse
  * rotation if inverse_rotate != 0, rounding to the activation dtype, then y * sigmoid(gate) with the reference's roundings

@@ -49,6 +49,54 @@ def test_decode_matches_exact_attention_fp16(oracle, ctx, M, splits):
     assert_close(got_r, oracle.kvx_rotate(want.reshape(-1, 256), inverse=True).reshape(want.shape), "after the inverse rotation")
 
 
+def _run_tc(kvx, k8, v8, ks, vs, q, ctx, M, splits, dtype, nh=NH, plain_entry=False):
+    dq = torch.from_numpy(q).to(dtype).cuda()
+    d = [torch.from_numpy(a).cuda() for a in (k8, v8, ks, vs)]
+    d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    pm = torch.full((M, splits, nh), float("nan"), device="cuda"); pl = torch.full_like(pm, float("nan"))
+    pacc = torch.full((M, splits, nh, 256), float("nan"), device="cuda")
+    (kvx.launch_kv8_attention if plain_entry else kvx.launch_kv8_attention_tc)(dq, *d, M, d_pos, splits, pm, pl, pacc, nh)
+    o = torch.empty((M, nh, 256), dtype=dtype, device="cuda")
+    kvx.launch_kv8_combine(pm, pl, pacc, splits, M, nh, o, inverse_rotate=False)
+    torch.cuda.synchronize()
+    from yasakani_b200 import kv4
+    assert kv4.device_status() == 0
+    assert torch.isfinite(pm).all() and torch.isfinite(pl).all() and torch.isfinite(pacc).all(), "a partial slot was not written"
+    return o.float().cpu().numpy(), dq.float().cpu().numpy(), pacc
+
+
+@pytest.mark.parametrize("ctx,M,splits,nh,dtype", [
+    (0, 16, 1, 24, torch.float16),          # first rows of a sequence: causal inside the first tile
+    (0, 100, 1, 24, torch.float16),         # several query tiles
+    (200, 16, 3, 24, torch.float16),
+    (1024, 64, 5, 24, torch.float16),       # verify shape, scaled down
+    (4000, 32, 13, 24, torch.bfloat16),     # the reference's activation dtype
+    (300, 40, 4, 32, torch.float16),        # 8 query heads per kv-head
+    (500, 30, 2, 28, torch.bfloat16),       # 7 heads per kv-head: idle rows in the tile
+])
+def test_many_rows_on_the_tensor_core_kernel_match_exact_attention(oracle, ctx, M, splits, nh, dtype):
+    from yasakani_b200 import kvx
+    k8, v8, ks, vs, q, _ = _case(oracle, ctx, M, seed=100 + ctx + M, nh=nh)
+    got, q16, _ = _run_tc(kvx, k8, v8, ks, vs, q, ctx, M, splits, dtype, nh=nh)
+    want = oracle.kv8_attention_exact(q16, k8, v8, ks, vs, ctx)
+    tol = dict(atol=ATOL + 2 ** -8, rtol=RTOL) if dtype == torch.bfloat16 else {}
+    assert_close(got, want, f"kv8 rows on tcgen05 ctx {ctx} M {M} S {splits} nh {nh}", **tol)
+
+
+def test_many_rows_agree_with_the_decode_kernel_and_the_plain_entry_takes_them(oracle):
+    """Rows of a 12-row pass against twelve one-row decodes (the kernel pinned against the reference's own), and
+    yskn_kv8_attention with more than 8 rows bit-identical with yskn_kv8_attention_tc."""
+    from yasakani_b200 import kvx
+    ctx, M, S = 1500, 12, 6
+    k8, v8, ks, vs, q, _ = _case(oracle, ctx, M, seed=77)
+    got, _, pacc_tc = _run_tc(kvx, k8, v8, ks, vs, q, ctx, M, S, torch.float16)
+    _, _, pacc_plain = _run_tc(kvx, k8, v8, ks, vs, q, ctx, M, S, torch.float16, plain_entry=True)
+    assert torch.equal(pacc_tc.view(torch.int32), pacc_plain.view(torch.int32))
+    for r in range(M):
+        one, _, _ = _run(kvx, k8, v8, ks, vs, q[r:r + 1], ctx + r, 1, S, torch.float16, inverse=False)
+        assert_close(got[r:r + 1], one, f"row {r} against its own decode")
+
+
 def test_bf16_queries_gate_and_roundings(oracle):
     # the reference's dtypes: bf16 q16, bf16 output, sigmoid gate with its three roundings (src/q35_kernels.cu:1421-1424)
     from yasakani_b200 import kvx

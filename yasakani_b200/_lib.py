@@ -104,6 +104,7 @@ PROTOTYPES = {
     "yskn_tb_encode": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
                                  C.c_void_p, C.c_size_t, C.c_void_p]),
     "yskn_kv8_attention": (C.c_int, [C.POINTER(Kv8AttnArgsC), C.c_int, C.c_void_p]),
+    "yskn_kv8_attention_tc": (C.c_int, [C.POINTER(Kv8AttnArgsC), C.c_int, C.c_void_p]),
     "yskn_kv8_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_attention_host": (C.c_int, [C.c_void_p, C.POINTER(KvLayerC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                           C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_int,

@@ -345,7 +345,14 @@ int yskn_tb_decode(const uint8_t* d_blob, const int* d_grp, const int* d_pos, co
 
 int yskn_kv8_attention(const yskn_kv8_attn_args* a, int act_dtype, void* cuda_stream) {
   if (!a) KV4_REJECT("yskn_kv8_attention: null argument struct");
+  // passes of more than 8 rows: the tcgen05 kernel over the INT8 rows, when the arrays are aligned for it
+  if (a->M > 8 && current_algo() != ALGO_SCALAR && a->q16 && a->pacc && !(((uintptr_t)a->q16 | (uintptr_t)a->pacc) & 15))
+    return launch_kv8_attention_tc(*a, act_dtype, (cudaStream_t)cuda_stream);
   return launch_kv8_attention(*a, act_dtype, (cudaStream_t)cuda_stream);
+}
+int yskn_kv8_attention_tc(const yskn_kv8_attn_args* a, int act_dtype, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_kv8_attention_tc: null argument struct");
+  return launch_kv8_attention_tc(*a, act_dtype, (cudaStream_t)cuda_stream);
 }
 int yskn_kv8_combine(const float* d_pm, const float* d_pl, const float* d_pacc, int splits, int M, int nh, const void* d_gate,
                      void* d_o16, int act_dtype, int inverse_rotate, void* cuda_stream) {

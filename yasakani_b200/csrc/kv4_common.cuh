@@ -108,6 +108,7 @@ int launch_tb_decode(const uint8_t* blob, const int* grp, const int* pos, const 
 
 // Family-B decode attention over INT8 rows (kv8_decode.cu)
 int launch_kv8_attention(const yskn_kv8_attn_args& a, int act_dtype, cudaStream_t st);
+int launch_kv8_attention_tc(const yskn_kv8_attn_args& a, int act_dtype, cudaStream_t st);   // kv4_tc.cu, many rows
 int launch_kv8_combine(const float* pm, const float* pl, const float* pacc, int splits, int M, int nh, const void* gate, void* o16,
                        int act_dtype, int inverse_rotate, cudaStream_t st);
 

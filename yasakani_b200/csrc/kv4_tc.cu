@@ -346,6 +346,7 @@ struct TcP {
   uint16_t* o16; const uint16_t* bv;                       // splits == 1 and o16 set: store the finished rows, no partials
   yskn_kv_layer kv; const float* rope; int rd;             // the fused form reads the packed cache itself
   const uint16_t* q16; int bf16;                           // fused form with bf16 activations: the converter warps also stage Q (as fp16)
+  const int8_t* k8; const int8_t* v8; const float* ks8; const float* vs8;     // FORM 2: INT8 rows and their scales
 };
 
 // FUSED = false: K and V tiles come by TMA from the fp16 workspace that kv4_tc_prep_kernel wrote.
@@ -354,11 +355,18 @@ struct TcP {
 // shadow rows), convert them and store the fp16 operand rows into the same 128-byte-swizzled stages the TMA would have
 // filled; "full" then counts the converter warps of both CTAs instead of bytes.  A pass reads 1/4 of the bytes of the
 // workspace form and needs no launch in front.
-template <int HD, bool FUSED>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc_threads(FUSED), 1)
+// FORM 2: the converting form over Family-B INT8 rows (k8, v8 [Hkv][max_ctx][256] with one fp32 scale per row; the
+// reference's q35_attention_kernel<KV8> semantics, src/q35_kernels.cu:1176-1281, for many rows): every key is an INT8 row,
+// nothing is rotated at read time and there is no shadow, so every tile has one K item and the tiles that hold the new
+// rows are masked causally.  A byte is read as the fp16 number 1152 + b by one byte permute, the offset leaves by an exact
+// subtraction, and the row's scale (rounded to fp16) is multiplied in.
+template <int HD, int FORM>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc_threads(FORM != 0), 1)
 kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapKd,
                    const __grid_constant__ CUtensorMap mapVd, const __grid_constant__ CUtensorMap mapKs, const TcP P) {
   using L = TcLay<HD>;
+  constexpr bool FUSED = FORM != 0, I8 = FORM == 2;
+  static_assert(!I8 || HD == 256, "INT8 rows have 256 channels");
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = s_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -385,6 +393,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   const int n = j1 - j0;
   const int jb = (pos0 + tokA) / TC_BN;                              // tiles below jb hold only groups before every row's own group
   const int nbulk = max(0, min(n, jb - j0));
+  const int npipe = I8 ? n : nbulk;                                  // tiles with a single K item, run through the two S buffers in turn
   const int ks0 = (pos0 / TC_BN) * TC_BN;
 
   if (sb & 1023u) { if (threadIdx.x == 0) atomicExch(&g_tc_status, 3); return; }   // same in both CTAs: nobody is left waiting
@@ -476,14 +485,14 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       if (!bar_wait(b_q, 0)) fail();
       tc_fence_after();
       // bulk tiles: S of the next two tiles is done or in flight while the softmax warps work on this one
-      if (ok && nbulk > 0) issue_s(0, 0);
-      if (ok && nbulk > 1) issue_s(1, 1);
-      for (int i = 0; i < nbulk && ok; ++i) {
+      if (ok && npipe > 0) issue_s(0, 0);
+      if (ok && npipe > 1) issue_s(1, 1);
+      for (int i = 0; i < npipe && ok; ++i) {
         issue_pv(i, i & 1);
-        if (ok && i + 2 < nbulk) issue_s(i + 2, i & 1);
+        if (ok && i + 2 < npipe) issue_s(i + 2, i & 1);
       }
       // edge tiles: S from the int4 keys and from the shadow keys, one after the other
-      for (int i = nbulk, kit = nbulk; i < n && ok; ++i, kit += 2) {
+      for (int i = npipe, kit = npipe; i < n && ok; ++i, kit += 2) {
         issue_s(kit, 0); if (!ok) break;
         issue_s(kit + 1, 1); if (!ok) break;
         issue_pv(i, 0);
@@ -508,8 +517,81 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       if (item >= depth && !bar_wait(bar_empty, (item / depth - 1) & 1)) { atomicExch(&g_tc_status, 6); *s_abort = 1; ok = false; }
       if (*s_abort) ok = false;
     };
+
+    // INT8 rows: item = (key, 16-byte chunk = 16 channels) -> two 16-byte chunks of fp16; cur holds this tile's items, each
+    // next-tile item is requested right before the same item of this tile is converted
+    struct I8In { uint4 w; uint32_t s; };
+    auto i8_convert = [&](const I8In& I, bool live, uint4& lo, uint4& hi) {      // channels 0-7 and 8-15 of the chunk
+      // the row's scale as a sum of two fp16 numbers: b * scale = fma(b, hi, b * lo) is then rounded once, without the
+      // per-row relative error of up to 2^-11 that a scale rounded to fp16 alone would put on all 256 channels of the row
+      const float sf = __uint_as_float(I.s), sh = __half2float(__float2half_rn(sf));
+      const uint32_t s_hi = tc_pack(sh, sh), s_lo = tc_pack(sf - sh, sf - sh);
+      const uint32_t ww[4] = {I.w.x ^ 0x80808080u, I.w.y ^ 0x80808080u, I.w.z ^ 0x80808080u, I.w.w ^ 0x80808080u};
+      uint32_t r[8];
+      #pragma unroll
+      for (int e = 0; e < 4; ++e) {                                  // byte b -> 0x64bb = 1152 + b (b two's complement, top bit flipped)
+        const uint32_t n0 = tc_hadd2(__byte_perm(ww[e], 0x64646464u, 0x4140), 0xE480E480u), n1 = tc_hadd2(__byte_perm(ww[e], 0x64646464u, 0x4342), 0xE480E480u);
+        r[2 * e] = tc_hfma2(n0, s_hi, tc_hmul2(n0, s_lo));
+        r[2 * e + 1] = tc_hfma2(n1, s_hi, tc_hmul2(n1, s_lo));
+      }
+      lo = live ? make_uint4(r[0], r[1], r[2], r[3]) : make_uint4(0u, 0u, 0u, 0u);
+      hi = live ? make_uint4(r[4], r[5], r[6], r[7]) : make_uint4(0u, 0u, 0u, 0u);
+    };
     if (n > 0 && ct < NKT) {
       // ------------------------------------------------------------------- K role
+      if constexpr (I8) {
+        constexpr int NKI = ((TC_BN / 2) * 16 + NKT - 1) / NKT;      // 64 keys x 16 chunks over the K threads
+        if (P.bf16) {
+          constexpr int NWD8 = HD / 8;
+          for (int it = ct; it < 128 * NWD8; it += NKT) {            // bf16 queries as fp16 operand rows (see the int4 branch)
+            const int row = it / NWD8, w = it % NWD8, tk = tok0 + row / G, hq = row % G;
+            uint4 out = make_uint4(0u, 0u, 0u, 0u);
+            if (row < TOK * G && tk < P.M) {
+              const uint4 u = __ldg(reinterpret_cast<const uint4*>(P.q16 + ((size_t)tk * P.nh + kvh * G + hq) * HD + 8 * w));
+              const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+              uint32_t o4[4];
+              #pragma unroll
+              for (int e = 0; e < 4; ++e) o4[e] = tc_pack(bf2f((uint16_t)uu[e]), bf2f((uint16_t)(uu[e] >> 16)));
+              out = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            }
+            tc_sts128(sb + L::OFF_Q + (w >> 3) * L::Q_BLOCK + row * 128 + (((w & 7) ^ (row & 7)) << 4), out);
+          }
+          publish(lead_q);
+        }
+        I8In cur[NKI];
+        auto k8_load = [&](int u, int tk0, I8In& I) {
+          const int it = ct + NKT * u, t = tk0 + (it >> 4);
+          if (it < (TC_BN / 2) * 16 && t < P.max_ctx) {
+            I.w = tc_ldg128(P.k8 + (row0 + t) * HD + 16 * (it & 15));
+            I.s = tc_ldg32(P.ks8 + row0 + t);
+          }
+        };
+        {
+          const int tk0 = j0 * TC_BN + (TC_BN / 2) * (int)rank;
+          #pragma unroll
+          for (int u = 0; u < NKI; ++u) k8_load(u, tk0, cur[u]);
+        }
+        for (int i = 0; i < n && ok; ++i) {
+          const int tk0 = (j0 + i) * TC_BN + (TC_BN / 2) * (int)rank, st = i % L::NK;
+          const uint32_t sk = sb + L::OFF_K + st * L::K_HALF;
+          stage_wait(b_kempty + 8 * st, i, L::NK);
+          if (!ok) break;
+          #pragma unroll
+          for (int u = 0; u < NKI; ++u) {
+            const int it = ct + NKT * u, k = it >> 4, c = it & 15;
+            I8In N;
+            if (i + 1 < n) k8_load(u, tk0 + TC_BN, N);
+            if (it < (TC_BN / 2) * 16) {
+              uint4 lo, hi;
+              i8_convert(cur[u], tk0 + k < P.max_ctx, lo, hi);
+              tc_sts128(sk + (c >> 2) * L::K_BLOCK + k * 128 + ((((2 * c) & 7) ^ (k & 7)) << 4), lo);
+              tc_sts128(sk + (c >> 2) * L::K_BLOCK + k * 128 + ((((2 * c + 1) & 7) ^ (k & 7)) << 4), hi);
+            }
+            cur[u] = N;
+          }
+          publish(lead_kfull + 8 * st);
+        }
+      } else {
       const int nrw = P.rd / 8, nrp = nrw / 2, half = P.rd / 2;      // rotary words; word pairs (w, w + nrp), a power of two; frequencies
       const int lp = nrp > 0 ? __ffs(nrp) - 1 : 0, nrot = (TC_BN / 2) * nrp;
       const int npl = NWD - nrw, nplain = npl * 8;                   // plain word columns; plain items = (column, octet of keys), 8 octets per half tile
@@ -677,8 +759,43 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           ++kit;
         }
       }
+      }
     } else if (n > 0 && ct < NKT + NVT) {
       // ------------------------------------------------------------------- V role: this CTA's HD/2 channels of all 128 keys of a tile.
+      if constexpr (I8) {
+        constexpr int NVI8 = (TC_BN * 8 + NVT - 1) / NVT;            // 128 keys x 8 chunks (this CTA's 128 channels) over the V threads
+        const int vt = ct - NKT;
+        I8In cur[NVI8];
+        auto v8_load = [&](int u, int j, I8In& I) {
+          const int it = vt + NVT * u, t = j * TC_BN + (it >> 3);
+          if (it < TC_BN * 8 && t < end) {
+            I.w = tc_ldg128(P.v8 + (row0 + t) * HD + 128 * (int)rank + 16 * (it & 7));
+            I.s = tc_ldg32(P.vs8 + row0 + t);
+          }
+        };
+        #pragma unroll
+        for (int u = 0; u < NVI8; ++u) v8_load(u, j0, cur[u]);
+        for (int i = 0; i < n && ok; ++i) {
+          const int j = j0 + i, st = i % L::NV;
+          const uint32_t sv = sb + L::OFF_V + st * L::V_HALF;
+          stage_wait(b_vempty + 8 * st, i, L::NV);
+          if (!ok) break;
+          #pragma unroll
+          for (int u = 0; u < NVI8; ++u) {
+            const int it = vt + NVT * u, k = it >> 3, c = it & 7;
+            I8In N;
+            if (i + 1 < n) v8_load(u, j + 1, N);
+            if (it < TC_BN * 8) {
+              uint4 lo, hi;
+              i8_convert(cur[u], j * TC_BN + k < end, lo, hi);       // tokens that do not exist yet read as zero
+              tc_sts128(sv + (c >> 2) * L::V_BLOCK + k * 128 + ((((2 * c) & 7) ^ (k & 7)) << 4), lo);
+              tc_sts128(sv + (c >> 2) * L::V_BLOCK + k * 128 + ((((2 * c + 1) & 7) ^ (k & 7)) << 4), hi);
+            }
+            cur[u] = N;
+          }
+          publish(lead_vfull + 8 * st);
+        }
+      } else {
       // Item = (key, 16-byte part of the key's half row = 32 channels); tokens that do not exist yet read as zero.
       constexpr int PARTS = NWV / 4, NVI = (TC_BN * PARTS + NVT - 1) / NVT;
       const int vt = ct - NKT;
@@ -727,6 +844,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         #pragma unroll
         for (int u = 0; u < NVI; ++u) cur[u] = nxt[u];
       }
+      }
     }
   } else if (warp < TC_SW) {
     // ======================================================================= softmax warps: two threads per query row
@@ -756,7 +874,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     bool ok = true;
     for (int i = 0; i < n && ok; ++i) {
       const int j = j0 + i;
-      const bool edge = i >= nbulk;
+      const bool edge = i >= npipe;
       const int buf = edge ? 0 : (i & 1);
       const uint32_t scol = trow + (buf ? L::TM_S1 : L::TM_S0) + 64 * hf;   // this thread's 64 S columns; P goes over the first 32
       float x[64];                                                   // raw scores of this thread's 64 keys
@@ -777,6 +895,11 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           #pragma unroll
           for (int k = 0; k < 32; ++k) x[32 * h2 + k] = gk < cr ? x[32 * h2 + k] : (gk == cr && tb + k <= pr) ? a[k] : -INFINITY;
         }
+      }
+      if (I8 && i >= nbulk) {                                        // INT8 rows: the tiles that hold the new rows are masked causally
+        const int tb = j * TC_BN + 64 * hf;
+        #pragma unroll
+        for (int k = 0; k < 64; ++k) x[k] = tb + k <= pr ? x[k] : -INFINITY;
       }
       // ---- online softmax in the log2 domain on p = 2^(x*cs - m); lazy rescale (the running max may lag by up to 2^8)
       float tmax = fmaxf(x[0], x[1]);
@@ -959,11 +1082,12 @@ int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int va
   if (!tc_map_q(&mq, a.q16, a.M, a.kvh, g, HD) || !tc_map_rows(&mkd, w.kd, rows, HD, TC_BN / 2, L::KBLK) ||
       !tc_map_rows(&mvd, w.vd, rows, HD, TC_BN, L::KBLK / 2) || !tc_map_rows(&mks, w.ks, (uint64_t)a.kvh * w.ks_rows, HD, TC_BN / 2, L::KBLK))
     KV4_REJECT("yskn_kv4_attention_tc: cuTensorMapEncodeTiled failed or is unavailable");
-  auto kern = kv4_tc_attn_kernel<HD, false>;
+  auto kern = kv4_tc_attn_kernel<HD, 0>;
   static std::atomic<unsigned long long> attr{0};
   if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;        // CTA pairs: an even number of query tiles
-  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv, a.kv, a.rope, rd, nullptr, 0};
+  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv, a.kv, a.rope, rd, nullptr, 0,
+        nullptr, nullptr, nullptr, nullptr};
   kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mq, mkd, mvd, mks, P);
   return launch_status("kv4_tc_attn_kernel");
 }
@@ -975,11 +1099,12 @@ int launch_tc_fused_hd(const yskn_attn_g_args& a, int g, int rd, int bf16, uint1
   CUtensorMap mq;
   if (bf16) memset(&mq, 0, sizeof(mq));                               // the converter warps stage Q
   else if (!tc_map_q(&mq, a.q16, a.M, a.kvh, g, HD)) KV4_REJECT("yskn_kv4_attention: cuTensorMapEncodeTiled failed or is unavailable");
-  auto kern = kv4_tc_attn_kernel<HD, true>;
+  auto kern = kv4_tc_attn_kernel<HD, 1>;
   static std::atomic<unsigned long long> attr{0};
   if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;
-  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, 0, a.qscale, a.pm, a.pl, a.pacc, o16, bv, a.kv, a.rope, rd, static_cast<const uint16_t*>(a.q16), bf16};
+  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, 0, a.qscale, a.pm, a.pl, a.pacc, o16, bv, a.kv, a.rope, rd, static_cast<const uint16_t*>(a.q16), bf16,
+        nullptr, nullptr, nullptr, nullptr};
   kern<<<dim3(qtiles, a.splits, a.kvh), tc_threads(true), L::TOTAL, st>>>(mq, mq, mq, mq, P);
   return launch_status("kv4_tc_attn_kernel (fused)");
 }
@@ -1021,6 +1146,29 @@ int launch_attention_tc_fused(const yskn_attn_g_args& a, int g, int hd, int rd, 
   if (al & 15) KV4_REJECT("yskn_kv4_attention: q16, cache arrays, rope table and pacc / o16 must be 16-byte aligned");
   const int bf16 = act_dtype == YSKN_KV4_BF16;
   return hd == 256 ? launch_tc_fused_hd<256>(a, g, rd, bf16, o16_direct, bv, st) : launch_tc_fused_hd<128>(a, g, rd, bf16, o16_direct, bv, st);
+}
+
+// Many-row attention over Family-B INT8 rows on the tcgen05 kernel (FORM 2): partials in the layout of yskn_kv8_attention.
+int launch_kv8_attention_tc(const yskn_kv8_attn_args& a, int act_dtype, cudaStream_t st) {
+  if (!a.q16 || !a.k8 || !a.v8 || !a.ks || !a.vs || !a.d_pos || !a.pm || !a.pl || !a.pacc) KV4_REJECT("yskn_kv8_attention_tc: null buffer");
+  if (a.kvh <= 0 || a.nh <= 0 || a.nh % a.kvh || a.nh / a.kvh > 8 || a.M <= 0 || a.M > 65535 || a.kvh > 65535 || a.splits <= 0 || a.splits > 65535 ||
+      a.max_ctx <= 0 || a.max_ctx % 64)
+    KV4_REJECT("yskn_kv8_attention_tc: bad shape (kvh %d, nh %d, M %d, splits %d, max_ctx %d)", a.kvh, a.nh, a.M, a.splits, a.max_ctx);
+  if (act_dtype != YSKN_KV4_F16 && act_dtype != YSKN_KV4_BF16) KV4_REJECT("yskn_kv8_attention_tc: q16 is fp16 or bf16 (act_dtype %d)", act_dtype);
+  if (((uintptr_t)a.k8 | (uintptr_t)a.v8 | (uintptr_t)a.q16 | (uintptr_t)a.pacc) & 15) KV4_REJECT("yskn_kv8_attention_tc: k8, v8, q16 and pacc must be 16-byte aligned");
+  using L = TcLay<256>;
+  const int g = a.nh / a.kvh, bf16 = act_dtype == YSKN_KV4_BF16;
+  CUtensorMap mq;
+  if (bf16) memset(&mq, 0, sizeof(mq));
+  else if (!tc_map_q(&mq, a.q16, a.M, a.kvh, g, 256)) KV4_REJECT("yskn_kv8_attention_tc: cuTensorMapEncodeTiled failed or is unavailable");
+  auto kern = kv4_tc_attn_kernel<256, 2>;
+  static std::atomic<unsigned long long> attr{0};
+  if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+  const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;
+  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, 0, a.qscale, a.pm, a.pl, a.pacc, nullptr, nullptr, yskn_kv_layer{}, nullptr, 0,
+        a.q16, bf16, a.k8, a.v8, a.ks, a.vs};
+  kern<<<dim3(qtiles, a.splits, a.kvh), tc_threads(true), L::TOTAL, st>>>(mq, mq, mq, mq, P);
+  return launch_status("kv4_tc_attn_kernel (INT8 rows)");
 }
 
 int tc_status_fetch(int* out) {

@@ -73,6 +73,17 @@ def launch_kv8_attention(q16: torch.Tensor, k8: torch.Tensor, v8: torch.Tensor, 
     check(_lib.load().yskn_kv8_attention(C.byref(a), _dtype_code(q16), _stream(stream)), "yskn_kv8_attention")
 
 
+def launch_kv8_attention_tc(q16: torch.Tensor, k8: torch.Tensor, v8: torch.Tensor, ks: torch.Tensor, vs: torch.Tensor, M: int,
+                            d_pos: torch.Tensor, splits: int, pm: torch.Tensor, pl: torch.Tensor, pacc: torch.Tensor, nh: int,
+                            qscale: float = 0.0625, stream=None) -> None:
+    """Many rows over INT8 rows on the tcgen05 kernel (launch_q35_atx, src/q35_atx.cu:92-793): same arguments and partials."""
+    kvh, max_ctx = k8.shape[0], k8.shape[1]
+    for t in (q16, k8, v8, ks, vs, d_pos, pm, pl, pacc):
+        assert t.is_cuda and t.is_contiguous()
+    a = Kv8AttnArgsC(_dp(q16), _dp(k8), _dp(v8), _dp(ks), _dp(vs), max_ctx, M, _dp(d_pos), splits, _dp(pm), _dp(pl), _dp(pacc), kvh, nh, qscale)
+    check(_lib.load().yskn_kv8_attention_tc(C.byref(a), _dtype_code(q16), _stream(stream)), "yskn_kv8_attention_tc")
+
+
 def launch_kv8_combine(pm, pl, pacc, splits: int, M: int, nh: int, o16: torch.Tensor, gate: torch.Tensor | None = None,
                        inverse_rotate: bool = True, stream=None) -> None:
     """Split merge, inverse rotation, rounding, optional sigmoid gate (src/q35_kernels.cu:1400-1424)."""
