@@ -305,11 +305,11 @@ __device__ __forceinline__ void tc_sts128(uint32_t a, const uint4& v) {
 }
 // ------------------------------------------------------------------------------------------------ attention kernel
 constexpr int TC_SW = 8;                                   // softmax warps: warp w owns rows 32*(w%4).., key columns 64*(w/4)..
-constexpr int TC_KW = 3, TC_VW = 3, TC_CW = TC_KW + TC_VW;  // converter warps of the fused form: K half tiles, V half tiles
+constexpr int TC_KW = 4, TC_VW = 3, TC_CW = TC_KW + TC_VW;  // converter warps of the fused forms: K half tiles, V half tiles
 // + producer warp, + MMA issuer warp; the fused form adds the converter warps and fills up to four warpgroups (16 warps x 128
-// registers at launch), so that setmaxnreg can move registers from the softmax warps (120 each) to the converters (136 each)
+// registers at launch), so that setmaxnreg can move registers from the softmax warps (120 each) and the V converters (112) to the K converters (160)
 constexpr int tc_threads(bool fused) { return fused ? 512 : (TC_SW + 2) * 32; }
-static_assert(TC_SW == 8 && TC_SW + 2 + TC_CW <= 16, "warpgroups 0-1 = softmax warps, warpgroups 2-3 = producer, MMA issuer, converters");
+static_assert(TC_SW == 8 && TC_SW + 1 + TC_CW <= 16, "warpgroups 0-1 = softmax warps, warpgroups 2-3 = Q copy + MMA issuer (one warp), converters");
 constexpr int TC_THREADS = tc_threads(false);
 
 // A pair of CTAs (a cluster of two, tcgen05 cta_group::2) works on 256 query rows with MMAs of M = 256: each CTA keeps
@@ -415,12 +415,8 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   cluster_sync_all();                                                // both CTAs' barriers exist before anyone signals the other
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  if (FUSED) {                                                       // whole warpgroups: 0-1 (softmax) shrink, 2-3 (converters) grow
-    if (warp < TC_SW) asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");
-    else asm volatile("setmaxnreg.inc.sync.aligned.u32 136;");
-  }
 
-  if (warp == TC_SW) {
+  auto role_producer = [&]() {
     // ======================================================================= TMA producer (one per CTA)
     // Q once, then two rings: K halves are free again as soon as their S MMAs are done, V halves only after P.V.
     // Every copy reports to the leader's "full" barrier; the leader posts the byte count of both CTAs' parts.
@@ -445,7 +441,10 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         tma_load_3d_pair(sb + L::OFF_V + st * L::V_HALF, &mapVd, 0, kvh * P.max_ctx + j * TC_BN, (L::KBLK / 2) * (int)rank, lead_vfull + 8 * st);
       }
     }
-  } else if (warp == TC_SW + 1) {
+  };
+  // the converting forms have no K / V copies to issue: the warp that requested Q goes on to issue the MMAs
+  constexpr int CONV0 = TC_SW + 1;
+  auto role_mma = [&]() {
     // ======================================================================= MMA issuer (one thread of the leader CTA)
     // The tensor pipe runs this thread's MMAs in issue order, so S of tile i+2, issued after P.V of tile i, may
     // overwrite the TMEM buffer that P.V reads P from without a barrier in between.
@@ -498,13 +497,15 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         issue_pv(i, 0);
       }
     }
-  } else if (FUSED && warp >= TC_SW + 2 && warp < TC_SW + 2 + TC_CW) {
+  };
+  auto role_conv = [&](const bool is_k) {
     // ======================================================================= converter warps (fused form)
-    // Three warps convert the K half tiles, three the V half tiles, each role with its own ring, so neither waits for the
+    // Four warps convert the K half tiles, three the V half tiles, each role with its own ring, so neither waits for the
     // other.  Every global load of a phase is issued before the first dependent instruction (ordered asm statements) and
     // the loads of the next tile are in flight while the current one is converted: a thread pays the memory latency once.
     constexpr int NKT = TC_KW * 32, NVT = TC_VW * 32, NWD = HD / 8, NWV = HD / 16;   // threads per role; packed words per K row; per V row in this CTA's channel half
-    const int ct = (int)threadIdx.x - (TC_SW + 2) * 32;
+    // warps 9-11 (warpgroup 2) convert V, warps 12-15 (warpgroup 3) convert K: ct = 0 .. NKT-1 for K, NKT .. NKT+NVT-1 for V
+    const int ct = is_k ? (int)threadIdx.x - (TC_SW + 4) * 32 : (int)threadIdx.x - CONV0 * 32 + TC_KW * 32;
     const int end = pos0 + P.M;                                      // tokens [0, end) exist
     const size_t row0 = (size_t)kvh * P.max_ctx, grp0 = (size_t)kvh * (P.max_ctx / 32);
     bool ok = true;
@@ -537,7 +538,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       lo = live ? make_uint4(r[0], r[1], r[2], r[3]) : make_uint4(0u, 0u, 0u, 0u);
       hi = live ? make_uint4(r[4], r[5], r[6], r[7]) : make_uint4(0u, 0u, 0u, 0u);
     };
-    if (n > 0 && ct < NKT) {
+    if (n > 0 && is_k) {
       // ------------------------------------------------------------------- K role
       if constexpr (I8) {
         constexpr int NKI = ((TC_BN / 2) * 16 + NKT - 1) / NKT;      // 64 keys x 16 chunks over the K threads
@@ -617,13 +618,20 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         uint32_t sc[4], zz[4];
         tc_row_to_pairs(I.s, sc); tc_row_to_pairs(I.z, zz);
         const uint32_t base = sk + (pcol[u] >> 3) * L::K_BLOCK + pkey[u] * 128;      // pkey is a multiple of 8: key & 7 = e
+        const uint32_t cx = (uint32_t)(pcol[u] & 7);
         #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          uint32_t nb[4], r[4];
-          tc_nibs(I.w[e], nb);
+        for (int h = 0; h < 8; h += 4) {                               // four words converted, then four stores: independent chains interleave
+          uint4 out[4];
           #pragma unroll
-          for (int x = 0; x < 4; ++x) r[x] = tc_hfma2(nb[x], sc[x], zz[x]);
-          tc_sts128(base + e * 128 + (((pcol[u] & 7) ^ e) << 4), tc_pairs_to_row(r));
+          for (int e = 0; e < 4; ++e) {
+            uint32_t nb[4], r[4];
+            tc_nibs(I.w[h + e], nb);
+            #pragma unroll
+            for (int x = 0; x < 4; ++x) r[x] = tc_hfma2(nb[x], sc[x], zz[x]);
+            out[e] = tc_pairs_to_row(r);
+          }
+          #pragma unroll
+          for (int e = 0; e < 4; ++e) tc_sts128(base + (h + e) * 128 + ((cx ^ (uint32_t)(h + e)) << 4), out[e]);
         }
       };
       struct RotIn { uint32_t wa, wb; uint4 sa, za, sb, zb; uint4 r[4]; };   // shadow items keep their two fp16 rows in sa, za
@@ -691,25 +699,80 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         }
         publish(lead_q);
       }
+      // Rotary items of a thread in the compact mapping (rotary width of at most 64 channels): one word pair (p, p + nrp) of
+      // one 32-key group, up to two keys -> the group's scale / zero chunks are loaded once, and all of a tile's rotary
+      // items are in flight together.  Wider rotary parts take the items one after the other (rot_load / rot_store).
+      const bool compact = nrp >= 1 && nrp <= 4;
+      const int tpc = compact ? NKT / (2 * nrp) : 1;                 // threads per (pair, group); keys c and c + tpc of the group
+      const int cp = ct & (nrp - 1), cg = compact ? (ct >> lp) & 1 : 0, cc = compact ? ct / (2 * nrp) : 0;
+      constexpr int RCI = 2;                                         // keys per thread: 32 / tpc <= 2 with 128 K threads
+      struct RotC { uint4 sa, za, sb, zb; uint32_t wa[RCI], wb[RCI]; uint4 r[RCI][4]; };
+      auto rotc_load = [&](int tk0, RotC& R) {
+        const int p = cp, q = cp + nrp;
+        const size_t gb = (grp0 + tk0 / 32 + cg) * HD;
+        R.sa = tc_ldg128(P.kv.kscale + gb + 8 * p); R.za = tc_ldg128(P.kv.kzero + gb + 8 * p);
+        R.sb = tc_ldg128(P.kv.kscale + gb + 8 * q); R.zb = tc_ldg128(P.kv.kzero + gb + 8 * q);
+        #pragma unroll
+        for (int u = 0; u < RCI; ++u) {
+          const int kk = cc + tpc * u;
+          if (kk < 32) {
+            const int t = tk0 + 32 * cg + kk;
+            const uint32_t* rowp = kq32 + (row0 + t) * (HD / 8);
+            R.wa[u] = tc_ldg32(rowp + p); R.wb[u] = tc_ldg32(rowp + q);
+            const float* rp = P.rope + ((size_t)t * half + 8 * p) * 2;
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) R.r[u][e] = tc_ldg128(rp + 4 * e);
+          }
+        }
+      };
+      auto rotc_store = [&](uint32_t sk, const RotC& R, int u0, int u1) {     // items u0 .. u1-1
+        const int p = cp, q = cp + nrp;
+        uint32_t sa[4], za[4], sb4[4], zb[4];
+        tc_row_to_pairs(R.sa, sa); tc_row_to_pairs(R.za, za); tc_row_to_pairs(R.sb, sb4); tc_row_to_pairs(R.zb, zb);
+        #pragma unroll
+        for (int u = 0; u < RCI; ++u) {
+          const int kk = cc + tpc * u;
+          if (u >= u0 && u < u1 && kk < 32) {
+            const int k = 32 * cg + kk;
+            uint32_t na[4], nb[4], a[4], b[4], lo[4], hi[4];
+            tc_nibs(R.wa[u], na); tc_nibs(R.wb[u], nb);
+            #pragma unroll
+            for (int x = 0; x < 4; ++x) { a[x] = tc_hfma2(na[x], sa[x], za[x]); b[x] = tc_hfma2(nb[x], sb4[x], zb[x]); }
+            const uint4* r = R.r[u];                                 // r[e/2] = (cos e, sin e, cos e+1, sin e+1) as fp32 bits
+            const uint32_t C[4] = {tc_pack(__uint_as_float(r[0].x), __uint_as_float(r[2].x)), tc_pack(__uint_as_float(r[0].z), __uint_as_float(r[2].z)),
+                                   tc_pack(__uint_as_float(r[1].x), __uint_as_float(r[3].x)), tc_pack(__uint_as_float(r[1].z), __uint_as_float(r[3].z))};
+            const uint32_t S[4] = {tc_pack(__uint_as_float(r[0].y), __uint_as_float(r[2].y)), tc_pack(__uint_as_float(r[0].w), __uint_as_float(r[2].w)),
+                                   tc_pack(__uint_as_float(r[1].y), __uint_as_float(r[3].y)), tc_pack(__uint_as_float(r[1].w), __uint_as_float(r[3].w))};
+            #pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              lo[x] = tc_hfma2(a[x], C[x], tc_hmul2(b[x], S[x]) ^ 0x80008000u);      // a cos - b sin
+              hi[x] = tc_hfma2(a[x], S[x], tc_hmul2(b[x], C[x]));                    // a sin + b cos
+            }
+            tc_sts128(k_addr(sk, p, k), tc_pairs_to_row(lo));
+            tc_sts128(k_addr(sk, q, k), tc_pairs_to_row(hi));
+          }
+        }
+      };
       PlainIn I0, I1;                                                // the coming int4 item's first two plain items (the usual case has two)
-      RotIn R0;                                                      // and its first rotary item
       bool have = false;
       int kit = 0;
       for (int i = 0; i < n && ok; ++i) {
         const int j = j0 + i;
         const int tk0 = j * TC_BN + (TC_BN / 2) * (int)rank;         // first key of this CTA's half of the K tile
         const bool kin = tk0 < P.max_ctx;                            // max_ctx is a multiple of 64: the half tile is inside or outside as a whole
-        // ---- item 1: the int4 keys
+        // ---- item 1: the int4 keys.  The converters never idle, so a request must be made a whole phase before its data
+        //      is used: the tile's rotary items are requested before its plain words (requested during the previous tile's
+        //      rotary phase) are converted, and the next tile's plain words before the rotary items are converted.
         {
           const int st = kit % L::NK;
           const uint32_t sk = sb + L::OFF_K + st * L::K_HALF;
-          const bool h0 = kin && ct < nrot;
           if (kin && !have) {
             if (pcol[0] >= 0) plain_load(0, tk0, I0);
             if (NPI > 1 && pcol[NPI > 1 ? 1 : 0] >= 0) plain_load(1, tk0, I1);
-            if (h0) rot_load(ct, tk0, false, R0);
           }
           have = false;
+          RotC RC;
+          if (kin && compact) rotc_load(tk0, RC);
           stage_wait(b_kempty + 8 * st, kit, L::NK);
           if (!ok) break;
           if (!kin) zero_k(sk);
@@ -719,16 +782,16 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             #pragma unroll
             for (int u = 2; u < NPI; ++u)
               if (pcol[u] >= 0) { plain_load(u, tk0, I0); plain_store(u, sk, I0); }
-            if (h0) rot_store(ct, tk0, false, sk, R0);
-            {
-              RotIn R1;
-              for (int it = ct + NKT; it < nrot; it += NKT) { rot_load(it, tk0, false, R1); rot_store(it, tk0, false, sk, R1); }   // words and tables already on chip
-            }
-            if (i + 1 < n && tk0 + TC_BN < P.max_ctx) {              // the next tile's words travel while this tile is consumed
+            if (compact) rotc_store(sk, RC, 0, 1);
+            if (i + 1 < n && tk0 + TC_BN < P.max_ctx) {
               if (pcol[0] >= 0) plain_load(0, tk0 + TC_BN, I0);
               if (NPI > 1 && pcol[NPI > 1 ? 1 : 0] >= 0) plain_load(1, tk0 + TC_BN, I1);
-              if (ct < nrot) rot_load(ct, tk0 + TC_BN, false, R0);
               have = true;
+            }
+            if (compact) rotc_store(sk, RC, 1, RCI);
+            else {
+              RotIn R1;
+              for (int it = ct; it < nrot; it += NKT) { rot_load(it, tk0, false, R1); rot_store(it, tk0, false, sk, R1); }
             }
           }
           publish(lead_kfull + 8 * st);
@@ -760,7 +823,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         }
       }
       }
-    } else if (n > 0 && ct < NKT + NVT) {
+    } else if (n > 0) {
       // ------------------------------------------------------------------- V role: this CTA's HD/2 channels of all 128 keys of a tile.
       if constexpr (I8) {
         constexpr int NVI8 = (TC_BN * 8 + NVT - 1) / NVT;            // 128 keys x 8 chunks (this CTA's 128 channels) over the V threads
@@ -822,22 +885,23 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         for (int u = 0; u < NVI; ++u) {
           const int it = vt + NVT * u, k = it / PARTS, part = it % PARTS;
           if (it < TC_BN * PARTS) {
+            // no branches inside an item: a token that does not exist yet gets scale = zero = 0 (nibbles are finite whatever
+            // the word holds), and the four words are converted before the four stores, so their chains interleave
             const bool live = j * TC_BN + k < end;
-            const uint32_t s2 = cur[u].s | (cur[u].s << 16), z2 = cur[u].z | (cur[u].z << 16);
+            const uint32_t s2 = live ? cur[u].s | (cur[u].s << 16) : 0u, z2 = live ? cur[u].z | (cur[u].z << 16) : 0u;
             const uint32_t ww[4] = {cur[u].w.x, cur[u].w.y, cur[u].w.z, cur[u].w.w};
+            uint4 out[4];
             #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              uint4 out = make_uint4(0u, 0u, 0u, 0u);
-              if (live) {
-                uint32_t nb[4], r[4];
-                tc_nibs(ww[e], nb);
-                #pragma unroll
-                for (int x = 0; x < 4; ++x) r[x] = tc_hfma2(nb[x], s2, z2);
-                out = tc_pairs_to_row(r);
-              }
-              const int c = 4 * part + e;                            // 16-byte chunk (8 channels) of the half row
-              tc_sts128(sv + (c >> 3) * L::V_BLOCK + k * 128 + (((c & 7) ^ (k & 7)) << 4), out);
+              uint32_t nb[4], r[4];
+              tc_nibs(ww[e], nb);
+              #pragma unroll
+              for (int x = 0; x < 4; ++x) r[x] = tc_hfma2(nb[x], s2, z2);
+              out[e] = tc_pairs_to_row(r);
             }
+            const uint32_t base = sv + (part >> 1) * L::V_BLOCK + k * 128, kx = (uint32_t)(k & 7), c0 = 4 * (part & 1);   // chunk 4*part + e of the half row
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) tc_sts128(base + (((c0 + e) ^ kx) << 4), out[e]);
           }
         }
         publish(lead_vfull + 8 * st);
@@ -846,7 +910,8 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       }
       }
     }
-  } else if (warp < TC_SW) {
+  };
+  auto role_softmax = [&]() {
     // ======================================================================= softmax warps: two threads per query row
     const int quad = warp & 3, hf = warp >> 2;                       // TMEM lane quadrant; which 64 of the tile's 128 key columns
     const int rho = quad * 32 + lane;                                // row of the tile = TMEM lane
@@ -985,6 +1050,19 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         }
       }
     }
+  };
+  // ---- roles.  In the converting forms each warpgroup first sets its register budget (120 / 120 / 112 / 160 per thread: 512
+  //      per scheduler lane) and the role code sits under that branch, so that each role is compiled for its own budget.
+  if constexpr (FUSED) {
+    if (warp < TC_SW) { asm volatile("setmaxnreg.dec.sync.aligned.u32 120;"); role_softmax(); }
+    else if (warp < TC_SW + 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 112;");
+      if (warp == TC_SW) { role_producer(); role_mma(); } else role_conv(false);
+    } else { asm volatile("setmaxnreg.inc.sync.aligned.u32 160;"); role_conv(true); }
+  } else {
+    if (warp == TC_SW) role_producer();
+    else if (warp == TC_SW + 1) role_mma();
+    else role_softmax();
   }
   tc_fence_before();
   __syncthreads();
