@@ -300,6 +300,7 @@ __device__ __forceinline__ uint32_t tc_ldg16(const void* p) { unsigned short v; 
 __device__ __forceinline__ uint4 tc_ldg128(const void* p) {
   uint4 v; asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)); return v;
 }
+__device__ __forceinline__ void tc_prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void tc_sts128(uint32_t a, const uint4& v) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -756,10 +757,22 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       PlainIn I0, I1;                                                // the coming int4 item's first two plain items (the usual case has two)
       bool have = false;
       int kit = 0;
+      // L2 prefetch of a half tile two tiles ahead (64 packed rows, the scale and zero rows of its two groups; one line per
+      // thread), so that the register loads one phase ahead find their lines in L2
+      auto k_prefetch = [&](int tk) {
+        if (tk >= P.max_ctx) return;
+        if (ct < TC_BN / 2) tc_prefetch_l2(P.kv.kq + (row0 + tk + ct) * (HD / 2));
+        else if (ct < TC_BN / 2 + 4 * (HD / 64)) {
+          const int x = ct - TC_BN / 2, arr = x & 1, grp = (x >> 1) & 1, line = x >> 2;      // line < HD/64 (128-byte lines of an HD x fp16 row)
+          tc_prefetch_l2((arr ? P.kv.kzero : P.kv.kscale) + (grp0 + tk / 32 + grp) * HD + 64 * line);
+        }
+      };
+      if (n > 1) k_prefetch(j0 * TC_BN + TC_BN + (TC_BN / 2) * (int)rank);
       for (int i = 0; i < n && ok; ++i) {
         const int j = j0 + i;
         const int tk0 = j * TC_BN + (TC_BN / 2) * (int)rank;         // first key of this CTA's half of the K tile
         const bool kin = tk0 < P.max_ctx;                            // max_ctx is a multiple of 64: the half tile is inside or outside as a whole
+        if (i + 2 < n) k_prefetch(tk0 + 2 * TC_BN);
         // ---- item 1: the int4 keys.  The converters never idle, so a request must be made a whole phase before its data
         //      is used: the tile's rotary items are requested before its plain words (requested during the previous tile's
         //      rotary phase) are converted, and the next tile's plain words before the rotary items are converted.
