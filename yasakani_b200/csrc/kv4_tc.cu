@@ -26,6 +26,10 @@
 //     Tiles that contain a row's own group ("edge" tiles) get S twice, from Kd and from Ks, and each row picks per
 //     32-key group: int4 keys for groups before its own, shadow keys (causally masked) for its own.
 //
+//  The attention kernel has three forms (template FORM): 0 = operand tiles by TMA from the workspace, as above; 1 = no
+//  workspace and no prep launch, converter warps build the tiles from the packed KV4 cache inside the kernel; 2 = the same over
+//  Family-B INT8 rows.  The converting forms run 16 warps: 0-7 softmax, 8 Q copy + MMA issue, 9-11 V tiles, 12-15 K tiles.
+//
 // Rows are independent of one another inside every step (an MMA output row depends on its own A row only, the lazy
 // rescale multiplies other rows by exactly 1), tiles start at multiples of 128 keys and split boundaries depend on
 // *d_pos and `splits` only, so a row's result does not depend on how many rows the pass holds.
@@ -350,8 +354,8 @@ struct TcP {
   const int8_t* k8; const int8_t* v8; const float* ks8; const float* vs8;     // FORM 2: INT8 rows and their scales
 };
 
-// FUSED = false: K and V tiles come by TMA from the fp16 workspace that kv4_tc_prep_kernel wrote.
-// FUSED = true: no workspace.  Four more warps per CTA read the packed cache rows of each tile straight from global memory
+// FORM 0: K and V tiles come by TMA from the fp16 workspace that kv4_tc_prep_kernel wrote.
+// FORM 1: no workspace.  Seven converter warps per CTA read the packed cache rows of each tile straight from global memory
 // (the int4 words, their scale and zero rows, the rope table rows of the rotary channels; for edge tiles also the fp16
 // shadow rows), convert them and store the fp16 operand rows into the same 128-byte-swizzled stages the TMA would have
 // filled; "full" then counts the converter warps of both CTAs instead of bytes.  A pass reads 1/4 of the bytes of the
