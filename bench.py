@@ -461,6 +461,30 @@ def _timed(fn, steps, warmup):
     return e0.elapsed_time(e1) / steps * 1e-3
 
 
+def _timed_graph(fn, steps, warmup, per_graph=8):
+    """Like _timed, but the calls are captured into a CUDA graph of `per_graph` passes and replayed, so that passes shorter
+    than the host's launch rate through ctypes are timed as the device runs them (every entry is enqueue-only)."""
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(max(1, warmup)):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(per_graph):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        reps = max(1, (steps + per_graph - 1) // per_graph)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * per_graph) * 1e-3
+
+
 def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -553,17 +577,17 @@ def secondary_lines(shape, splits, dev):
         pm, pl, pacc = kv4.attn_scratch(M, S, shape.hq, shape.hd)
         o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device=dev)
         ws = kv4.tc_workspace(layer, M)
-        t = _timed(lambda i: kv4.launch_attention_prefill_tc(qm, layer, M, pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws), 10, 3)
+        t = _timed_graph(lambda i: kv4.launch_attention_prefill_tc(qm, layer, M, pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws), 16, 3)
         flops = shape.attn_flops(sum(ctx + r + 1 for r in range(M)))
         res = {"us_per_pass": t * 1e6, "tflops": flops / t / 1e12, "frac_of_bf16_burst_peak": flops / t / 1e12 / tf,
                "frac_of_bf16_sustained_peak": flops / t / 1e12 / tf_sus, "splits": S, "includes": "dequant prep + attention" + ("" if S == 1 else " + merge")}
         if ctx > 0:        # a verify loop keeps the workspace: only the pass's own rows are dequantised again
-            tk = _timed(lambda i: kv4.launch_attention_prefill_tc(qm, layer, M, pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws,
-                                                                  valid_tokens=ctx), 10, 3)
+            tk = _timed_graph(lambda i: kv4.launch_attention_prefill_tc(qm, layer, M, pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws,
+                                                                        valid_tokens=ctx), 16, 3)
             res["us_per_pass_kept_workspace"] = tk * 1e6
             res["frac_of_bf16_burst_peak_kept_workspace"] = flops / tk / 1e12 / tf
         # no workspace: the attention kernel converts the packed cache itself (what the plain entries run for passes of 9..128 rows)
-        tfu = _timed(lambda i: kv4.launch_attention_prefill_tc(qm, layer, M, pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, None), 10, 3)
+        tfu = _timed_graph(lambda i: kv4.launch_attention_prefill_tc(qm, layer, M, pos, S, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, None), 16, 3)
         res["us_per_pass_fused"] = tfu * 1e6
         res["frac_of_bf16_burst_peak_fused"] = flops / tfu / 1e12 / tf
         return res
@@ -602,7 +626,7 @@ def run_secondary(args):
         flops = shape.attn_flops(sum(ctx + r + 1 for r in range(M)))
         for form in ("workspace", "fused"):                        # fused: no workspace, the attention kernel converts the packed cache itself
             ws = kv4.tc_workspace(layer, M) if form == "workspace" else None
-            t = _timed(lambda i: kv4.launch_attention_prefill_tc(q, layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws), K, W)
+            t = _timed_graph(lambda i: kv4.launch_attention_prefill_tc(q, layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws), K, W)
             nl = (2 if form == "workspace" else 1) + (0 if splits == 1 else 1)
             line = dict(base, metric="kv4_multirow_attn_tflops", value=flops / t / 1e12, unit="TFLOP/s", ms_per_step=t * 1e3, dtype="f16",
                         config={"workload": name, "form": form, "rows": M, "cached_tokens": ctx, "splits": splits,
@@ -653,7 +677,7 @@ def run_secondary(args):
             def one(i):
                 kvx.launch_kv8_attention_tc(q, k8, v8, ks, vs, M, d_pos, Sv, pm, pl, pacc, nh)
                 kvx.launch_kv8_combine(pm, pl, pacc, Sv, M, nh, o16)
-            t = _timed(one, K, W)
+            t = _timed_graph(one, K, W)
             flops = shape.attn_flops(sum(ctx + r + 1 for r in range(M)))
             line = dict(base, metric="kv8_multirow_attn_tflops", value=flops / t / 1e12, unit="TFLOP/s", ms_per_step=t * 1e3, dtype="f16",
                         config={"workload": f"Family-B verify over INT8 rows: {M} rows against {ctx} cached tokens, Hq{nh}/Hkv{kvh}/hd256", "rows": M, "cached_tokens": ctx,

@@ -385,22 +385,6 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::OFF_BAR + 188);
   const uint32_t lead_kfull = leader_addr(b_kfull), lead_vfull = leader_addr(b_vfull), lead_pready = leader_addr(b_pready), lead_q = leader_addr(b_q);
 
-  // ---- geometry: uniform over the pair except tok0
-  const int G = P.G, TOK = 128 / G, kvh = blockIdx.z, S = P.splits, split = blockIdx.y;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;               // heaviest query tiles first; gridDim.x is even
-  const int tok0 = qt * TOK;                                         // this CTA's first token
-  const int tokA = (qt & ~1) * TOK;                                  // the pair's first token (always < M)
-  const int pos0 = *P.d_pos;
-  const int pmax = pos0 + min(tokA + 2 * TOK, P.M) - 1;              // last key any row of the pair sees
-  const int nt_all = pmax / TC_BN + 1;
-  const int per = (pos0 / TC_BN + 1 + S - 1) / S;                    // split width in tiles: a function of *d_pos and S only
-  const int j0 = min(split * per, nt_all), j1 = split == S - 1 ? nt_all : min((split + 1) * per, nt_all);
-  const int n = j1 - j0;
-  const int jb = (pos0 + tokA) / TC_BN;                              // tiles below jb hold only groups before every row's own group
-  const int nbulk = max(0, min(n, jb - j0));
-  const int npipe = I8 ? n : nbulk;                                  // tiles with a single K item, run through the two S buffers in turn
-  const int ks0 = (pos0 / TC_BN) * TC_BN;
-
   if (sb & 1023u) { if (threadIdx.x == 0) atomicExch(&g_tc_status, 3); return; }   // same in both CTAs: nobody is left waiting
   if (threadIdx.x == 0) {
     for (int i = 0; i < L::NK; ++i) { bar_init(b_kfull + 8 * i, FUSED ? 2 * TC_KW : 1); bar_init(b_kempty + 8 * i, 1); }
@@ -420,6 +404,29 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   cluster_sync_all();                                                // both CTAs' barriers exist before anyone signals the other
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // Programmatic dependent launch: the grid may be scheduled while its predecessor in the stream drains, and everything above
+  // (barriers, tensor memory, the cluster handshake) touches nothing the predecessor wrote.  From here on the position, the
+  // queries and the cache (or the workspace the prep kernel fills) are read; the merge kernel that follows may be scheduled
+  // early in turn and waits for this grid before it reads the partials.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  // ---- geometry: uniform over the pair except tok0
+  const int G = P.G, TOK = 128 / G, kvh = blockIdx.z, S = P.splits, split = blockIdx.y;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;               // heaviest query tiles first; gridDim.x is even
+  const int tok0 = qt * TOK;                                         // this CTA's first token
+  const int tokA = (qt & ~1) * TOK;                                  // the pair's first token (always < M)
+  const int pos0 = *P.d_pos;
+  const int pmax = pos0 + min(tokA + 2 * TOK, P.M) - 1;              // last key any row of the pair sees
+  const int nt_all = pmax / TC_BN + 1;
+  const int per = (pos0 / TC_BN + 1 + S - 1) / S;                    // split width in tiles: a function of *d_pos and S only
+  const int j0 = min(split * per, nt_all), j1 = split == S - 1 ? nt_all : min((split + 1) * per, nt_all);
+  const int n = j1 - j0;
+  const int jb = (pos0 + tokA) / TC_BN;                              // tiles below jb hold only groups before every row's own group
+  const int nbulk = max(0, min(n, jb - j0));
+  const int npipe = I8 ? n : nbulk;                                  // tiles with a single K item, run through the two S buffers in turn
+  const int ks0 = (pos0 / TC_BN) * TC_BN;
+
 
   auto role_producer = [&]() {
     // ======================================================================= TMA producer (one per CTA)
@@ -1150,6 +1157,19 @@ bool tc_map_q(CUtensorMap* out, const void* q16, int M, int kvh, int G, int hd) 
   });
 }
 
+// Launch with programmatic stream serialization allowed (the kernel waits in griddepcontrol.wait after its set-up).
+template <class K>
+int tc_launch_pdl(K kern, dim3 grid, int threads, int smem_bytes, cudaStream_t st, const CUtensorMap& m0, const CUtensorMap& m1, const CUtensorMap& m2,
+                  const CUtensorMap& m3, const TcP& P) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = dim3(threads); cfg.dynamicSmemBytes = smem_bytes; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  KV4_CUDA(cudaLaunchKernelEx(&cfg, kern, m0, m1, m2, m3, P));
+  return 0;
+}
+
 struct TcWs { uint16_t* kd; uint16_t* vd; uint16_t* ks; int ks_rows; size_t bytes; };
 TcWs carve(void* ws, int kvh, int hd, int max_ctx, int M) {
   TcWs w; const size_t plane = (size_t)kvh * max_ctx * hd * 2;
@@ -1183,7 +1203,7 @@ int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int va
   const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;        // CTA pairs: an even number of query tiles
   TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv, a.kv, a.rope, rd, nullptr, 0,
         nullptr, nullptr, nullptr, nullptr};
-  kern<<<dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st>>>(mq, mkd, mvd, mks, P);
+  if (int rc = tc_launch_pdl(kern, dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st, mq, mkd, mvd, mks, P)) return rc;
   return launch_status("kv4_tc_attn_kernel");
 }
 
@@ -1200,7 +1220,7 @@ int launch_tc_fused_hd(const yskn_attn_g_args& a, int g, int rd, int bf16, uint1
   const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;
   TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, 0, a.qscale, a.pm, a.pl, a.pacc, o16, bv, a.kv, a.rope, rd, static_cast<const uint16_t*>(a.q16), bf16,
         nullptr, nullptr, nullptr, nullptr};
-  kern<<<dim3(qtiles, a.splits, a.kvh), tc_threads(true), L::TOTAL, st>>>(mq, mq, mq, mq, P);
+  if (int rc = tc_launch_pdl(kern, dim3(qtiles, a.splits, a.kvh), tc_threads(true), L::TOTAL, st, mq, mq, mq, mq, P)) return rc;
   return launch_status("kv4_tc_attn_kernel (fused)");
 }
 
@@ -1262,7 +1282,7 @@ int launch_kv8_attention_tc(const yskn_kv8_attn_args& a, int act_dtype, cudaStre
   const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;
   TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, 0, a.qscale, a.pm, a.pl, a.pacc, nullptr, nullptr, yskn_kv_layer{}, nullptr, 0,
         a.q16, bf16, a.k8, a.v8, a.ks, a.vs};
-  kern<<<dim3(qtiles, a.splits, a.kvh), tc_threads(true), L::TOTAL, st>>>(mq, mq, mq, mq, P);
+  if (int rc = tc_launch_pdl(kern, dim3(qtiles, a.splits, a.kvh), tc_threads(true), L::TOTAL, st, mq, mq, mq, mq, P)) return rc;
   return launch_status("kv4_tc_attn_kernel (INT8 rows)");
 }
 
