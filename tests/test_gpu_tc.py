@@ -53,6 +53,9 @@ TC_CASES = [
     (synth.C1, 300, 40, 4),               # hd 128, G = 8: 16 tokens per tile
     (synth.Shape(28, 4, 128, 128, 1e6), 500, 30, 2),     # G = 7: 18 tokens per tile, 2 idle rows
     (synth.Shape(24, 4, 256, 0, 1.0), 333, 20, 2),       # no rotary channels
+    (synth.Shape(24, 4, 256, 32, 1e4), 700, 20, 3),      # narrow rotary parts: two and one word pairs per key
+    (synth.Shape(24, 4, 256, 16, 1e4), 260, 12, 2),
+    (synth.Shape(24, 4, 256, 128, 1e4), 450, 24, 2),     # a wide rotary part: its items are converted one after the other
 ]
 
 
