@@ -144,8 +144,10 @@ def test_config5_eight_decodes_as_one_launch(oracle):
             assert_close(o16[r:r + 1].float().cpu().numpy(), want, f"ctx {ctx} vs oracle")
 
 
-def test_config3_verify_widths_over_32768_tokens(oracle):
-    """16-, 32- and 64-row verify passes over a 32,768-token cache: shared rows bitwise identical; sampled rows vs oracle."""
+@pytest.mark.parametrize("form", ["workspace", "converting"])
+def test_config3_verify_widths_over_32768_tokens(oracle, form):
+    """16-, 32- and 64-row verify passes over a 32,768-token cache: shared rows bitwise identical; every row vs the oracle.
+    Both forms of the tcgen05 kernel: over the dequantised workspace, and converting the packed cache inside the kernel."""
     from yasakani_b200 import kv4
     shape, ctx = synth.C2, 32768
     base, okv, max_ctx = _build(kv4, oracle, shape, ctx, seed=90)
@@ -162,7 +164,8 @@ def test_config3_verify_widths_over_32768_tokens(oracle):
         kv4.launch_kv_append(layer, k_new[:M].cuda(), v_new[:M].cuda(), d_pos, M)
         pm, pl, pacc = kv4.attn_scratch(M, 7, shape.hq, shape.hd)          # same split count for every width
         o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
-        kv4.launch_attention_tc(q[:M].cuda(), layer, M, d_pos, 7, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, kv4.tc_workspace(layer, M))
+        kv4.launch_attention_tc(q[:M].cuda(), layer, M, d_pos, 7, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd,
+                                kv4.tc_workspace(layer, M) if form == "workspace" else None)
         kv4.launch_attn_combine_gqa(pm, pl, pacc, 7, M, o16, shape.hq, shape.g)
         torch.cuda.synchronize()
         assert kv4.device_status() == 0
@@ -178,6 +181,6 @@ def test_config3_verify_widths_over_32768_tokens(oracle):
     assert_close(got, want, "verify, all 64 rows")
     err = np.abs(got - want)
     ratio = err / (2e-3 + 1e-2 * np.abs(want))
-    print(f"verify 64 rows vs 32768 tokens: max abs err {err.max():.3e}, p99 {np.percentile(err, 99):.3e}, "
+    print(f"verify ({form} form) 64 rows vs 32768 tokens: max abs err {err.max():.3e}, p99 {np.percentile(err, 99):.3e}, "
           f"largest fraction of the bar {ratio.max():.3f}, p99 {np.percentile(ratio, 99):.3f}")
     assert np.percentile(ratio, 99) <= 0.5, "the bulk of the verify error should sit well inside the bar"

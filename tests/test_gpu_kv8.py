@@ -83,6 +83,21 @@ def test_many_rows_on_the_tensor_core_kernel_match_exact_attention(oracle, ctx, 
     assert_close(got, want, f"kv8 rows on tcgen05 ctx {ctx} M {M} S {splits} nh {nh}", **tol)
 
 
+def test_verify_widths_over_32768_int8_rows(oracle):
+    """Configuration 3 on Family-B rows: 16-, 32- and 64-row passes over 32,768 cached tokens; shared rows bitwise identical
+    across the widths (same split count), every row of the widest pass against the exact oracle."""
+    from yasakani_b200 import kvx
+    ctx, S = 32768, 9
+    k8, v8, ks, vs, q, _ = _case(oracle, ctx, 64, seed=321)
+    outs = {}
+    for M in (16, 32, 64):
+        got, q16, _ = _run_tc(kvx, k8, v8, ks, vs, q[:M], ctx, M, S, torch.bfloat16)
+        outs[M] = got
+    assert np.array_equal(outs[16], outs[32][:16]) and np.array_equal(outs[32], outs[64][:32])
+    want = oracle.kv8_attention_exact(q16, k8, v8, ks, vs, ctx)
+    assert_close(outs[64], want, "kv8 verify, all 64 rows vs 32768 tokens", atol=ATOL + 2 ** -8, rtol=RTOL)
+
+
 def test_many_rows_agree_with_the_decode_kernel_and_the_plain_entry_takes_them(oracle):
     """Rows of a 12-row pass against twelve one-row decodes (the kernel pinned against the reference's own), and
     yskn_kv8_attention with more than 8 rows bit-identical with yskn_kv8_attention_tc."""
