@@ -191,7 +191,7 @@ YSKN_KV4_API size_t yskn_kv4_tc_workspace_bytes(int kvh, int hd, int max_ctx, in
 /* The plain entries -- yskn_kv4_attention, yskn_kv4_decode, yskn_kv4_prefill, the reference's launcher set unchanged -- run
  * passes of more than 8 rows on the tcgen05 kernel whenever the shape is covered (head_dim 128 / 256, full cache, 16-byte
  * aligned arrays): without a workspace (the converting form above) by default.  This call lends the library a workspace on
- * the CURRENT device (NULL takes it back); passes of more than 32 rows with fp16 activations then use the workspace form
+ * the CURRENT device (NULL takes it back); passes of more than 64 rows with fp16 activations then use the workspace form
  * when it holds yskn_kv4_tc_workspace_bytes(...) for the call, which is faster for long passes (a prefill converts each
  * tile once instead of once per query tile).  Through this route the whole workspace is rewritten on every call (as with
  * valid_tokens = 0); callers that keep it across passes use the _tc entries.  The library only stores the pointer: the

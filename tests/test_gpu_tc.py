@@ -178,11 +178,11 @@ def test_tc_workspace_kept_across_passes_gives_the_same_bits(oracle):
 
 def test_plain_entries_take_the_tensor_core_kernel_for_wide_passes(oracle):
     """yskn_kv4_attention with more than 8 rows runs the tcgen05 kernel: the form that converts the packed cache itself
-    (bit-identical with yskn_kv4_attention_tc without a workspace), and for passes of more than 32 rows the workspace form
+    (bit-identical with yskn_kv4_attention_tc without a workspace), and for passes of more than 64 rows the workspace form
     (bit-identical with yskn_kv4_attention_tc at valid_tokens = 0) while a workspace is lent."""
     from yasakani_b200 import kv4
     shape, ctx, S = synth.C2, 1500, 5
-    for M in (32, 48):
+    for M in (32, 80):
         k, v = synth.make_kv(shape, ctx + M, seed=71)
         q = synth.make_q(shape, M, seed=71).cuda()
         max_ctx = ((ctx + M + 127) // 64) * 64
@@ -215,7 +215,7 @@ def test_plain_entries_take_the_tensor_core_kernel_for_wide_passes(oracle):
             pacc_lent, o_lent = run(plain)
         finally:
             kv4.set_tc_workspace(None)
-        assert torch.equal(pacc_lent.view(torch.int32), (pacc_ws if M > 32 else pacc_fused).view(torch.int32))
+        assert torch.equal(pacc_lent.view(torch.int32), (pacc_ws if M > 64 else pacc_fused).view(torch.int32))
         assert kv4.device_status() == 0
         want = oracle.attention_exact(f16_bits(q.cpu()), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
         assert_close(o_plain.float().cpu().numpy(), want, f"wide pass ({M} rows) through the plain entry")

@@ -471,9 +471,11 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         if (!bar_wait(b_kfull + 8 * st, (item / L::NK) & 1)) { fail(); return; }
         tc_fence_after();
         const uint64_t kd = kdesc0 + (uint64_t)((st * L::K_HALF) >> 4);
-        #pragma unroll
+        // The workspace form (prefill) lives on this thread's issue rate: everything unrolled.  The converting forms are paced
+        // by their converter warps and their code has to stay inside the instruction cache: loops, one expansion per lambda.
+        #pragma unroll (FUSED ? 1 : L::KBLK)
         for (int kb = 0; kb < L::KBLK; ++kb)
-          #pragma unroll
+          #pragma unroll (FUSED ? 1 : 4)
           for (int ks = 0; ks < 4; ++ks)
             umma2_ss(tmem + (buf ? L::TM_S1 : L::TM_S0), qdesc0 + (uint64_t)((kb * L::Q_BLOCK + ks * 32) >> 4),
                      kd + (uint64_t)((kb * L::K_BLOCK + ks * 32) >> 4), ID_S, (kb | ks) ? 1u : 0u);
@@ -487,7 +489,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         tc_fence_after();
         const uint64_t vd = vdesc0 + (uint64_t)((st * L::V_HALF) >> 4);
         const uint32_t pcol = tmem + (buf ? L::TM_S1 : L::TM_S0);
-        #pragma unroll
+        #pragma unroll (FUSED ? 1 : TC_BN / 16)
         for (int ks = 0; ks < TC_BN / 16; ++ks)                      // P columns: keys 0-63 at +0.., keys 64-127 at +64..
           umma2_ts(tmem + L::TM_O, pcol + 64 * (ks >> 2) + 8 * (ks & 3), vd + (uint64_t)((ks * 2048) >> 4), ID_PV, (tile_i | ks) ? 1u : 0u);
         umma2_commit(b_pvdone + 8 * (tile_i & 1));                   // O may be rescaled
@@ -495,18 +497,30 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       };
       if (!bar_wait(b_q, 0)) fail();
       tc_fence_after();
-      // bulk tiles: S of the next two tiles is done or in flight while the softmax warps work on this one
-      if (ok && npipe > 0) issue_s(0, 0);
-      if (ok && npipe > 1) issue_s(1, 1);
-      for (int i = 0; i < npipe && ok; ++i) {
-        issue_pv(i, i & 1);
-        if (ok && i + 2 < npipe) issue_s(i + 2, i & 1);
-      }
-      // edge tiles: S from the int4 keys and from the shadow keys, one after the other
-      for (int i = npipe, kit = npipe; i < n && ok; ++i, kit += 2) {
-        issue_s(kit, 0); if (!ok) break;
-        issue_s(kit + 1, 1); if (!ok) break;
-        issue_pv(i, 0);
+      // Bulk tiles: S(0), S(1), then P.V(i), S(i+2), ...: S of the next two tiles is done or in flight while the softmax
+      // warps work on this one.  Edge tiles: S from the int4 keys, S from the shadow keys, then P.V.
+      if constexpr (FUSED) {                                         // the same order as one loop with a single expansion of each lambda
+        int s_next = 0, pv_next = 0;
+        const int s_total = npipe + 2 * (n - npipe);
+        while (ok && pv_next < n) {
+          bool do_s = false; int buf = 0;
+          if (s_next < npipe) { do_s = s_next < pv_next + 2; buf = s_next & 1; }
+          else if (pv_next >= npipe) { const int e = s_next - (npipe + 2 * (pv_next - npipe)); do_s = s_next < s_total && e < 2; buf = e; }
+          if (do_s) { issue_s(s_next, buf); ++s_next; }
+          else { issue_pv(pv_next, pv_next < npipe ? (pv_next & 1) : 0); ++pv_next; }
+        }
+      } else {
+        if (ok && npipe > 0) issue_s(0, 0);
+        if (ok && npipe > 1) issue_s(1, 1);
+        for (int i = 0; i < npipe && ok; ++i) {
+          issue_pv(i, i & 1);
+          if (ok && i + 2 < npipe) issue_s(i + 2, i & 1);
+        }
+        for (int i = npipe, kit = npipe; i < n && ok; ++i, kit += 2) {
+          issue_s(kit, 0); if (!ok) break;
+          issue_s(kit + 1, 1); if (!ok) break;
+          issue_pv(i, 0);
+        }
       }
     }
   };
@@ -829,17 +843,18 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           if (!ok) break;
           if (!kin) zero_k(sk);
           else {
-            #pragma unroll
-            for (int u = 0; u < NPI; ++u)
-              if (pcol[u] >= 0) {
-                uint4 x8[8];
-                #pragma unroll
-                for (int e = 0; e < 8; ++e) x8[e] = tc_ldg128(P.kv.kshadow + (row0 + tk0 + pkey[u] + e) * HD + 8 * pcol[u]);
-                #pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  tc_sts128(sk + (pcol[u] >> 3) * L::K_BLOCK + (pkey[u] + e) * 128 + (((pcol[u] & 7) ^ e) << 4), tk0 + pkey[u] + e < end ? x8[e] : make_uint4(0u, 0u, 0u, 0u));
-              }
+            // plain channels: a copy, kept as a small loop (edge tiles are few; the kernel's code must stay inside the
+            // instruction cache)
+            #pragma unroll 1
+            for (int it = ct; it < (TC_BN / 2) * NWD; it += NKT) {
+              const int k = it / NWD, w = it % NWD;
+              if (w < nrw) continue;
+              uint4 x = make_uint4(0u, 0u, 0u, 0u);
+              if (tk0 + k < end) x = tc_ldg128(P.kv.kshadow + (row0 + tk0 + k) * HD + 8 * w);
+              tc_sts128(k_addr(sk, w, k), x);
+            }
             RotIn R1;
+            #pragma unroll 1
             for (int it = ct; it < nrot; it += NKT) { rot_load(it, tk0, true, R1); rot_store(it, tk0, true, sk, R1); }
           }
           publish(lead_kfull + 8 * st);
