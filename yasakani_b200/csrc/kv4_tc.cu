@@ -585,36 +585,41 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           }
           publish(lead_q);
         }
-        I8In cur[NKI];
-        auto k8_load = [&](int u, int tk0, I8In& I) {
-          const int it = ct + NKT * u, t = tk0 + (it >> 4);
-          if (it < (TC_BN / 2) * 16 && t < P.max_ctx) {
+        // The items of all tiles form one stream (NKI per tile); two are in flight ahead of the one being converted.  Rolled
+        // loops: the kernel's code has to stay inside the instruction cache.
+        auto k8_load = [&](int q, I8In& I) {                         // q-th item of this thread's stream
+          const int it = ct + NKT * (q % NKI), t = (j0 + q / NKI) * TC_BN + (TC_BN / 2) * (int)rank + (it >> 4);
+          if (q < n * NKI && it < (TC_BN / 2) * 16 && t < P.max_ctx) {
             I.w = tc_ldg128(P.k8 + (row0 + t) * HD + 16 * (it & 15));
             I.s = tc_ldg32(P.ks8 + row0 + t);
           }
         };
-        {
-          const int tk0 = j0 * TC_BN + (TC_BN / 2) * (int)rank;
-          #pragma unroll
-          for (int u = 0; u < NKI; ++u) k8_load(u, tk0, cur[u]);
-        }
+        auto k8_prefetch = [&](int tk) {                             // L2 prefetch of a half tile: 64 rows of 256 bytes, two lines each
+          if (tk >= P.max_ctx) return;
+          tc_prefetch_l2(P.k8 + (row0 + tk + (ct >> 1)) * HD + 128 * (ct & 1));
+          if (ct < 2) tc_prefetch_l2(P.ks8 + row0 + tk + 32 * ct);
+        };
+        I8In cur, n1, n2;
+        k8_load(0, cur); k8_load(1, n1);
+        if (n > 1) k8_prefetch((j0 + 1) * TC_BN + (TC_BN / 2) * (int)rank);
+        int q = 0;
         for (int i = 0; i < n && ok; ++i) {
           const int tk0 = (j0 + i) * TC_BN + (TC_BN / 2) * (int)rank, st = i % L::NK;
           const uint32_t sk = sb + L::OFF_K + st * L::K_HALF;
+          if (i + 2 < n) k8_prefetch(tk0 + 2 * TC_BN);
           stage_wait(b_kempty + 8 * st, i, L::NK);
           if (!ok) break;
-          #pragma unroll
-          for (int u = 0; u < NKI; ++u) {
+          #pragma unroll 1
+          for (int u = 0; u < NKI; ++u, ++q) {
+            k8_load(q + 2, n2);
             const int it = ct + NKT * u, k = it >> 4, c = it & 15;
-            I8In N;
-            if (i + 1 < n) k8_load(u, tk0 + TC_BN, N);
             if (it < (TC_BN / 2) * 16) {
               uint4 lo, hi;
-              i8_convert(cur[u], tk0 + k < P.max_ctx, lo, hi);
+              i8_convert(cur, tk0 + k < P.max_ctx, lo, hi);
               tc_sts128(sk + (c >> 2) * L::K_BLOCK + k * 128 + ((((2 * c) & 7) ^ (k & 7)) << 4), lo);
               tc_sts128(sk + (c >> 2) * L::K_BLOCK + k * 128 + ((((2 * c + 1) & 7) ^ (k & 7)) << 4), hi);
             }
-            cur[u] = N;
+            cur = n1; n1 = n2;
           }
           publish(lead_kfull + 8 * st);
         }
@@ -867,33 +872,38 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       if constexpr (I8) {
         constexpr int NVI8 = (TC_BN * 8 + NVT - 1) / NVT;            // 128 keys x 8 chunks (this CTA's 128 channels) over the V threads
         const int vt = ct - NKT;
-        I8In cur[NVI8];
-        auto v8_load = [&](int u, int j, I8In& I) {
-          const int it = vt + NVT * u, t = j * TC_BN + (it >> 3);
-          if (it < TC_BN * 8 && t < end) {
+        auto v8_load = [&](int q, I8In& I) {                         // q-th item of this thread's stream (NVI8 per tile)
+          const int it = vt + NVT * (q % NVI8), t = (j0 + q / NVI8) * TC_BN + (it >> 3);
+          if (q < n * NVI8 && it < TC_BN * 8 && t < end) {
             I.w = tc_ldg128(P.v8 + (row0 + t) * HD + 128 * (int)rank + 16 * (it & 7));
             I.s = tc_ldg32(P.vs8 + row0 + t);
           }
         };
-        #pragma unroll
-        for (int u = 0; u < NVI8; ++u) v8_load(u, j0, cur[u]);
+        auto v8_prefetch = [&](int j) {                              // L2 prefetch of a tile's 128 half rows (one line each) and scales
+          for (int x = vt; x < TC_BN; x += NVT) if (j * TC_BN + x < end) tc_prefetch_l2(P.v8 + (row0 + j * TC_BN + x) * HD + 128 * (int)rank);
+          if (vt < 4 && j * TC_BN + 32 * vt < end) tc_prefetch_l2(P.vs8 + row0 + j * TC_BN + 32 * vt);
+        };
+        I8In cur, n1, n2;
+        v8_load(0, cur); v8_load(1, n1);
+        if (n > 1) v8_prefetch(j0 + 1);
+        int q = 0;
         for (int i = 0; i < n && ok; ++i) {
           const int j = j0 + i, st = i % L::NV;
           const uint32_t sv = sb + L::OFF_V + st * L::V_HALF;
+          if (i + 2 < n) v8_prefetch(j + 2);
           stage_wait(b_vempty + 8 * st, i, L::NV);
           if (!ok) break;
-          #pragma unroll
-          for (int u = 0; u < NVI8; ++u) {
+          #pragma unroll 1
+          for (int u = 0; u < NVI8; ++u, ++q) {
+            v8_load(q + 2, n2);
             const int it = vt + NVT * u, k = it >> 3, c = it & 7;
-            I8In N;
-            if (i + 1 < n) v8_load(u, j + 1, N);
             if (it < TC_BN * 8) {
               uint4 lo, hi;
-              i8_convert(cur[u], j * TC_BN + k < end, lo, hi);       // tokens that do not exist yet read as zero
+              i8_convert(cur, j * TC_BN + k < end, lo, hi);          // tokens that do not exist yet read as zero
               tc_sts128(sv + (c >> 2) * L::V_BLOCK + k * 128 + ((((2 * c) & 7) ^ (k & 7)) << 4), lo);
               tc_sts128(sv + (c >> 2) * L::V_BLOCK + k * 128 + ((((2 * c + 1) & 7) ^ (k & 7)) << 4), hi);
             }
-            cur[u] = N;
+            cur = n1; n1 = n2;
           }
           publish(lead_vfull + 8 * st);
         }
@@ -902,33 +912,40 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       constexpr int PARTS = NWV / 4, NVI = (TC_BN * PARTS + NVT - 1) / NVT;
       const int vt = ct - NKT;
       struct VIn { uint4 w; uint32_t s, z; };
-      VIn cur[NVI], nxt[NVI];
-      auto v_load = [&](int j, VIn (&I)[NVI]) {
-        #pragma unroll
-        for (int u = 0; u < NVI; ++u) {
-          const int it = vt + NVT * u, t = j * TC_BN + it / PARTS;
-          if (it < TC_BN * PARTS && t < end) {
-            I[u].w = tc_ldg128(P.kv.vq + (row0 + t) * (HD / 2) + (HD / 4) * (int)rank + 16 * (it % PARTS));
-            I[u].s = tc_ldg16(P.kv.vscale + row0 + t); I[u].z = tc_ldg16(P.kv.vzero + row0 + t);
-          }
+      // The items of all tiles form one stream (tile by tile, NVI items each); two items are in flight ahead of the one being
+      // converted.  A rolled loop: the lines are in L2 already (prefetched two tiles ahead), and small code matters more
+      // here than the last cycles of latency.
+      auto v_item_load = [&](int q, VIn& I) {                        // q-th item of this thread's stream
+        const int j = j0 + q / NVI, it = vt + NVT * (q % NVI), t = j * TC_BN + it / PARTS;
+        if (q < n * NVI && it < TC_BN * PARTS && t < end) {
+          I.w = tc_ldg128(P.kv.vq + (row0 + t) * (HD / 2) + (HD / 4) * (int)rank + 16 * (it % PARTS));
+          I.s = tc_ldg16(P.kv.vscale + row0 + t); I.z = tc_ldg16(P.kv.vzero + row0 + t);
         }
       };
-      v_load(j0, cur);
+      auto v_prefetch = [&](int j) {                                 // L2 prefetch of a tile's half rows and per-token scales
+        for (int x = vt; x < TC_BN; x += NVT) if (j * TC_BN + x < end) tc_prefetch_l2(P.kv.vq + (row0 + j * TC_BN + x) * (HD / 2) + (HD / 4) * (int)rank);
+        if (vt < 4 && j * TC_BN + 64 * (vt & 1) < end) tc_prefetch_l2((vt & 2 ? P.kv.vzero : P.kv.vscale) + row0 + j * TC_BN + 64 * (vt & 1));
+      };
+      VIn cur, n1, n2;
+      v_item_load(0, cur); v_item_load(1, n1);
+      if (n > 1) v_prefetch(j0 + 1);
+      int q = 0;
       for (int i = 0; i < n && ok; ++i) {
         const int j = j0 + i, st = i % L::NV;
         const uint32_t sv = sb + L::OFF_V + st * L::V_HALF;
-        if (i + 1 < n) v_load(j + 1, nxt);                           // the next tile's rows travel while this one is converted
+        if (i + 2 < n) v_prefetch(j + 2);
         stage_wait(b_vempty + 8 * st, i, L::NV);
         if (!ok) break;
-        #pragma unroll
-        for (int u = 0; u < NVI; ++u) {
+        #pragma unroll 1
+        for (int u = 0; u < NVI; ++u, ++q) {
+          v_item_load(q + 2, n2);
           const int it = vt + NVT * u, k = it / PARTS, part = it % PARTS;
           if (it < TC_BN * PARTS) {
             // no branches inside an item: a token that does not exist yet gets scale = zero = 0 (nibbles are finite whatever
             // the word holds), and the four words are converted before the four stores, so their chains interleave
             const bool live = j * TC_BN + k < end;
-            const uint32_t s2 = live ? cur[u].s | (cur[u].s << 16) : 0u, z2 = live ? cur[u].z | (cur[u].z << 16) : 0u;
-            const uint32_t ww[4] = {cur[u].w.x, cur[u].w.y, cur[u].w.z, cur[u].w.w};
+            const uint32_t s2 = live ? cur.s | (cur.s << 16) : 0u, z2 = live ? cur.z | (cur.z << 16) : 0u;
+            const uint32_t ww[4] = {cur.w.x, cur.w.y, cur.w.z, cur.w.w};
             uint4 out[4];
             #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -942,10 +959,9 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             #pragma unroll
             for (int e = 0; e < 4; ++e) tc_sts128(base + (((c0 + e) ^ kx) << 4), out[e]);
           }
+          cur = n1; n1 = n2;
         }
         publish(lead_vfull + 8 * st);
-        #pragma unroll
-        for (int u = 0; u < NVI; ++u) cur[u] = nxt[u];
       }
       }
     }
