@@ -50,8 +50,8 @@ static int attention_dispatch(const yskn_attn_g_args* a, int g, int hd, int rd, 
   const bool mma_ok = decode_mma_supports(g, hd, rd, a->M);
   const int algo = current_algo();
   // Wide passes (more rows than the warp-level decode kernel takes) go to the tcgen05 kernel.  Up to TC_FUSED_MAX_ROWS rows it
-  // converts the packed cache inside the kernel (every CTA pair converts the tiles it reads; measured at 32,768 tokens: 69 / 72 / 132 us
-  // for 16 / 32 / 64 rows against 105 / 109 / 134 us with a full dequantisation in front); longer
+  // converts the packed cache inside the kernel (every CTA pair converts the tiles it reads; measured at 32,768 tokens: 61 / 65 / 111 us
+  // for 16 / 32 / 64 rows against 105 / 109 / 136 us with a full dequantisation in front); longer
   // passes dequantise once into a workspace, if the caller has lent one (valid_tokens = 0: the whole workspace is brought
   // up to date on every call), and take the converting form otherwise.
   if (a->M > 8 && algo != ALGO_SCALAR && sh.start == 0 && sh.len == a->max_ctx && !(((uintptr_t)a->q16 | (uintptr_t)a->pacc) & 15)) {

@@ -626,30 +626,33 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       } else {
       const int nrw = P.rd / 8, nrp = nrw / 2, half = P.rd / 2;      // rotary words; word pairs (w, w + nrp), a power of two; frequencies
       const int lp = nrp > 0 ? __ffs(nrp) - 1 : 0, nrot = (TC_BN / 2) * nrp;
-      const int npl = NWD - nrw, nplain = npl * 8;                   // plain word columns; plain items = (column, octet of keys), 8 octets per half tile
+      const int npl = NWD - nrw;                                     // plain word columns
       const uint32_t* kq32 = reinterpret_cast<const uint32_t*>(P.kv.kq);
       auto k_addr = [&](uint32_t sk, int w, int k) { return sk + (w >> 3) * L::K_BLOCK + k * 128 + (((w & 7) ^ (k & 7)) << 4); };
-      // this thread's plain items (at most three): word column and first key; consecutive lanes take consecutive columns of one octet
+      // Plain items: (word column, octet of keys); item x of a tile = column nrw + x % npl, keys 8 (x / npl) .. +7, so that
+      // consecutive lanes take consecutive columns of one octet.  A thread's items of all tiles form one stream (NPI per tile).
       constexpr int NPI = (NWD * 8 + NKT - 1) / NKT;
-      int pcol[NPI], pkey[NPI];
-      #pragma unroll
-      for (int u = 0; u < NPI; ++u) {
-        const int it = ct + NKT * u;
-        pcol[u] = it < nplain ? nrw + it % (npl > 0 ? npl : 1) : -1; pkey[u] = it < nplain ? 8 * (it / (npl > 0 ? npl : 1)) : 0;
-      }
+      const int np1 = npl > 0 ? npl : 1, nplain = npl * 8;
       struct PlainIn { uint32_t w[8]; uint4 s, z; };
-      auto plain_load = [&](int u, int tk0, PlainIn& I) {
-        const uint32_t* src = kq32 + (row0 + tk0 + pkey[u]) * (HD / 8) + pcol[u];
-        #pragma unroll
-        for (int e = 0; e < 8; ++e) I.w[e] = tc_ldg32(src + e * (HD / 8));
-        const size_t gb = (grp0 + (tk0 + pkey[u]) / 32) * HD + 8 * pcol[u];
-        I.s = tc_ldg128(P.kv.kscale + gb); I.z = tc_ldg128(P.kv.kzero + gb);
+      auto plain_load = [&](int q, PlainIn& I) {                     // q-th item of the stream
+        const int x = ct + NKT * (q % NPI), tk = (j0 + q / NPI) * TC_BN + (TC_BN / 2) * (int)rank;
+        if (q < n * NPI && x < nplain && tk < P.max_ctx) {
+          const int col = nrw + x % np1, key = 8 * (x / np1);
+          const uint32_t* src = kq32 + (row0 + tk + key) * (HD / 8) + col;
+          #pragma unroll
+          for (int e = 0; e < 8; ++e) I.w[e] = tc_ldg32(src + e * (HD / 8));
+          const size_t gb = (grp0 + (tk + key) / 32) * HD + 8 * col;
+          I.s = tc_ldg128(P.kv.kscale + gb); I.z = tc_ldg128(P.kv.kzero + gb);
+        }
       };
       auto plain_store = [&](int u, uint32_t sk, const PlainIn& I) {
+        const int x = ct + NKT * u;
+        if (x >= nplain) return;
+        const int col = nrw + x % np1, key = 8 * (x / np1);
         uint32_t sc[4], zz[4];
         tc_row_to_pairs(I.s, sc); tc_row_to_pairs(I.z, zz);
-        const uint32_t base = sk + (pcol[u] >> 3) * L::K_BLOCK + pkey[u] * 128;      // pkey is a multiple of 8: key & 7 = e
-        const uint32_t cx = (uint32_t)(pcol[u] & 7);
+        const uint32_t base = sk + (col >> 3) * L::K_BLOCK + key * 128;      // key is a multiple of 8: (key + e) & 7 = e
+        const uint32_t cx = (uint32_t)(col & 7);
         #pragma unroll
         for (int h = 0; h < 8; h += 4) {                               // four words converted, then four stores: independent chains interleave
           uint4 out[4];
@@ -658,7 +661,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             uint32_t nb[4], r[4];
             tc_nibs(I.w[h + e], nb);
             #pragma unroll
-            for (int x = 0; x < 4; ++x) r[x] = tc_hfma2(nb[x], sc[x], zz[x]);
+            for (int x2 = 0; x2 < 4; ++x2) r[x2] = tc_hfma2(nb[x2], sc[x2], zz[x2]);
             out[e] = tc_pairs_to_row(r);
           }
           #pragma unroll
@@ -730,65 +733,60 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         }
         publish(lead_q);
       }
-      // Rotary items of a thread in the compact mapping (rotary width of at most 64 channels): one word pair (p, p + nrp) of
-      // one 32-key group, up to two keys -> the group's scale / zero chunks are loaded once, and all of a tile's rotary
-      // items are in flight together.  Wider rotary parts take the items one after the other (rot_load / rot_store).
+      // Rotary items in the compact mapping (rotary width of at most 64 channels): a thread owns one word pair (p, p + nrp) of
+      // one 32-key group and up to two keys of it, so the group's scale / zero chunks are loaded once per tile; its items of
+      // all tiles form one stream (RCI per tile).  Wider rotary parts take the items one after the other (rot_load / rot_store).
       const bool compact = nrp >= 1 && nrp <= 4;
+      constexpr int RCI = 2;                                         // keys per thread: 32 / tpc <= 2 with 128 K threads
       const int tpc = compact ? NKT / (2 * nrp) : 1;                 // threads per (pair, group); keys c and c + tpc of the group
       const int cp = ct & (nrp - 1), cg = compact ? (ct >> lp) & 1 : 0, cc = compact ? ct / (2 * nrp) : 0;
-      constexpr int RCI = 2;                                         // keys per thread: 32 / tpc <= 2 with 128 K threads
-      struct RotC { uint4 sa, za, sb, zb; uint32_t wa[RCI], wb[RCI]; uint4 r[RCI][4]; };
-      auto rotc_load = [&](int tk0, RotC& R) {
-        const int p = cp, q = cp + nrp;
+      struct RotS { uint4 sa, za, sb, zb; };                         // the group's scale / zero chunks of the two words
+      struct RotI { uint32_t wa, wb; uint4 r[4]; };                  // one key: the two words and the 8 (cos, sin) pairs
+      auto rots_load = [&](int tk0, RotS& R) {
         const size_t gb = (grp0 + tk0 / 32 + cg) * HD;
-        R.sa = tc_ldg128(P.kv.kscale + gb + 8 * p); R.za = tc_ldg128(P.kv.kzero + gb + 8 * p);
-        R.sb = tc_ldg128(P.kv.kscale + gb + 8 * q); R.zb = tc_ldg128(P.kv.kzero + gb + 8 * q);
-        #pragma unroll
-        for (int u = 0; u < RCI; ++u) {
-          const int kk = cc + tpc * u;
-          if (kk < 32) {
-            const int t = tk0 + 32 * cg + kk;
-            const uint32_t* rowp = kq32 + (row0 + t) * (HD / 8);
-            R.wa[u] = tc_ldg32(rowp + p); R.wb[u] = tc_ldg32(rowp + q);
-            const float* rp = P.rope + ((size_t)t * half + 8 * p) * 2;
-            #pragma unroll
-            for (int e = 0; e < 4; ++e) R.r[u][e] = tc_ldg128(rp + 4 * e);
-          }
+        R.sa = tc_ldg128(P.kv.kscale + gb + 8 * cp); R.za = tc_ldg128(P.kv.kzero + gb + 8 * cp);
+        R.sb = tc_ldg128(P.kv.kscale + gb + 8 * (cp + nrp)); R.zb = tc_ldg128(P.kv.kzero + gb + 8 * (cp + nrp));
+      };
+      auto roti_load = [&](int q, RotI& R) {                         // q-th item of the stream
+        const int kk = cc + tpc * (q % RCI), tk = (j0 + q / RCI) * TC_BN + (TC_BN / 2) * (int)rank;
+        if (q < n * RCI && kk < 32 && tk < P.max_ctx) {
+          const int t = tk + 32 * cg + kk;
+          const uint32_t* rowp = kq32 + (row0 + t) * (HD / 8);
+          R.wa = tc_ldg32(rowp + cp); R.wb = tc_ldg32(rowp + cp + nrp);
+          const float* rp = P.rope + ((size_t)t * half + 8 * cp) * 2;
+          #pragma unroll
+          for (int e = 0; e < 4; ++e) R.r[e] = tc_ldg128(rp + 4 * e);
         }
       };
-      auto rotc_store = [&](uint32_t sk, const RotC& R, int u0, int u1) {     // items u0 .. u1-1
-        const int p = cp, q = cp + nrp;
-        uint32_t sa[4], za[4], sb4[4], zb[4];
-        tc_row_to_pairs(R.sa, sa); tc_row_to_pairs(R.za, za); tc_row_to_pairs(R.sb, sb4); tc_row_to_pairs(R.zb, zb);
+      auto roti_store = [&](int u, uint32_t sk, const RotS& Sc, const RotI& R) {
+        const int kk = cc + tpc * u;
+        if (kk >= 32) return;
+        const int p = cp, q = cp + nrp, k = 32 * cg + kk;
+        uint32_t sa[4], za[4], sb4[4], zb[4], na[4], nb[4], a[4], b[4], lo[4], hi[4];
+        tc_row_to_pairs(Sc.sa, sa); tc_row_to_pairs(Sc.za, za); tc_row_to_pairs(Sc.sb, sb4); tc_row_to_pairs(Sc.zb, zb);
+        tc_nibs(R.wa, na); tc_nibs(R.wb, nb);
         #pragma unroll
-        for (int u = 0; u < RCI; ++u) {
-          const int kk = cc + tpc * u;
-          if (u >= u0 && u < u1 && kk < 32) {
-            const int k = 32 * cg + kk;
-            uint32_t na[4], nb[4], a[4], b[4], lo[4], hi[4];
-            tc_nibs(R.wa[u], na); tc_nibs(R.wb[u], nb);
-            #pragma unroll
-            for (int x = 0; x < 4; ++x) { a[x] = tc_hfma2(na[x], sa[x], za[x]); b[x] = tc_hfma2(nb[x], sb4[x], zb[x]); }
-            const uint4* r = R.r[u];                                 // r[e/2] = (cos e, sin e, cos e+1, sin e+1) as fp32 bits
-            const uint32_t C[4] = {tc_pack(__uint_as_float(r[0].x), __uint_as_float(r[2].x)), tc_pack(__uint_as_float(r[0].z), __uint_as_float(r[2].z)),
-                                   tc_pack(__uint_as_float(r[1].x), __uint_as_float(r[3].x)), tc_pack(__uint_as_float(r[1].z), __uint_as_float(r[3].z))};
-            const uint32_t S[4] = {tc_pack(__uint_as_float(r[0].y), __uint_as_float(r[2].y)), tc_pack(__uint_as_float(r[0].w), __uint_as_float(r[2].w)),
-                                   tc_pack(__uint_as_float(r[1].y), __uint_as_float(r[3].y)), tc_pack(__uint_as_float(r[1].w), __uint_as_float(r[3].w))};
-            #pragma unroll
-            for (int x = 0; x < 4; ++x) {
-              lo[x] = tc_hfma2(a[x], C[x], tc_hmul2(b[x], S[x]) ^ 0x80008000u);      // a cos - b sin
-              hi[x] = tc_hfma2(a[x], S[x], tc_hmul2(b[x], C[x]));                    // a sin + b cos
-            }
-            tc_sts128(k_addr(sk, p, k), tc_pairs_to_row(lo));
-            tc_sts128(k_addr(sk, q, k), tc_pairs_to_row(hi));
-          }
+        for (int x = 0; x < 4; ++x) { a[x] = tc_hfma2(na[x], sa[x], za[x]); b[x] = tc_hfma2(nb[x], sb4[x], zb[x]); }
+        const uint4* r = R.r;                                        // r[e/2] = (cos e, sin e, cos e+1, sin e+1) as fp32 bits
+        const uint32_t C[4] = {tc_pack(__uint_as_float(r[0].x), __uint_as_float(r[2].x)), tc_pack(__uint_as_float(r[0].z), __uint_as_float(r[2].z)),
+                               tc_pack(__uint_as_float(r[1].x), __uint_as_float(r[3].x)), tc_pack(__uint_as_float(r[1].z), __uint_as_float(r[3].z))};
+        const uint32_t S[4] = {tc_pack(__uint_as_float(r[0].y), __uint_as_float(r[2].y)), tc_pack(__uint_as_float(r[0].w), __uint_as_float(r[2].w)),
+                               tc_pack(__uint_as_float(r[1].y), __uint_as_float(r[3].y)), tc_pack(__uint_as_float(r[1].w), __uint_as_float(r[3].w))};
+        #pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          lo[x] = tc_hfma2(a[x], C[x], tc_hmul2(b[x], S[x]) ^ 0x80008000u);      // a cos - b sin
+          hi[x] = tc_hfma2(a[x], S[x], tc_hmul2(b[x], C[x]));                    // a sin + b cos
         }
+        tc_sts128(k_addr(sk, p, k), tc_pairs_to_row(lo));
+        tc_sts128(k_addr(sk, q, k), tc_pairs_to_row(hi));
       };
-      PlainIn I0, I1;                                                // the coming int4 item's first two plain items (the usual case has two)
-      bool have = false;
-      int kit = 0;
+      PlainIn pc, pn;                                                // plain stream: current item, next item
+      RotI rc, rn;                                                   // rotary stream (compact mapping)
+      plain_load(0, pc);
+      if (compact) roti_load(0, rc);
+      int pq = 0, rq = 0, kit = 0;
       // L2 prefetch of a half tile two tiles ahead (64 packed rows, the scale and zero rows of its two groups; one line per
-      // thread), so that the register loads one phase ahead find their lines in L2
+      // thread), so that the register loads a phase ahead find their lines in L2
       auto k_prefetch = [&](int tk) {
         if (tk >= P.max_ctx) return;
         if (ct < TC_BN / 2) tc_prefetch_l2(P.kv.kq + (row0 + tk + ct) * (HD / 2));
@@ -804,36 +802,35 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         const bool kin = tk0 < P.max_ctx;                            // max_ctx is a multiple of 64: the half tile is inside or outside as a whole
         if (i + 2 < n) k_prefetch(tk0 + 2 * TC_BN);
         // ---- item 1: the int4 keys.  The converters never idle, so a request must be made a whole phase before its data
-        //      is used: the tile's rotary items are requested before its plain words (requested during the previous tile's
-        //      rotary phase) are converted, and the next tile's plain words before the rotary items are converted.
+        //      is used: each plain item is requested while the one before it is converted (the first of a tile during the
+        //      previous tile's last plain item, i.e. a whole rotary phase ahead), each rotary item likewise (the first of a
+        //      tile a whole plain phase ahead), the tile's rotary scales before its plain phase.  Rolled loops, one expansion
+        //      of each conversion: the kernel's code has to stay inside the instruction cache.
         {
           const int st = kit % L::NK;
           const uint32_t sk = sb + L::OFF_K + st * L::K_HALF;
-          if (kin && !have) {
-            if (pcol[0] >= 0) plain_load(0, tk0, I0);
-            if (NPI > 1 && pcol[NPI > 1 ? 1 : 0] >= 0) plain_load(1, tk0, I1);
-          }
-          have = false;
-          RotC RC;
-          if (kin && compact) rotc_load(tk0, RC);
+          RotS RS;
+          if (kin && compact) rots_load(tk0, RS);
           stage_wait(b_kempty + 8 * st, kit, L::NK);
           if (!ok) break;
-          if (!kin) zero_k(sk);
+          if (!kin) { zero_k(sk); pq += NPI; rq += RCI; plain_load(pq, pc); if (compact) roti_load(rq, rc); }
           else {
-            if (pcol[0] >= 0) plain_store(0, sk, I0);
-            if (NPI > 1 && pcol[NPI > 1 ? 1 : 0] >= 0) plain_store(1, sk, I1);
-            #pragma unroll
-            for (int u = 2; u < NPI; ++u)
-              if (pcol[u] >= 0) { plain_load(u, tk0, I0); plain_store(u, sk, I0); }
-            if (compact) rotc_store(sk, RC, 0, 1);
-            if (i + 1 < n && tk0 + TC_BN < P.max_ctx) {
-              if (pcol[0] >= 0) plain_load(0, tk0 + TC_BN, I0);
-              if (NPI > 1 && pcol[NPI > 1 ? 1 : 0] >= 0) plain_load(1, tk0 + TC_BN, I1);
-              have = true;
+            #pragma unroll 1
+            for (int u = 0; u < NPI; ++u, ++pq) {
+              plain_load(pq + 1, pn);
+              plain_store(u, sk, pc);
+              pc = pn;
             }
-            if (compact) rotc_store(sk, RC, 1, RCI);
-            else {
+            if (compact) {
+              #pragma unroll 1
+              for (int u = 0; u < RCI; ++u, ++rq) {
+                roti_load(rq + 1, rn);
+                roti_store(u, sk, RS, rc);
+                rc = rn;
+              }
+            } else {
               RotIn R1;
+              #pragma unroll 1
               for (int it = ct; it < nrot; it += NKT) { rot_load(it, tk0, false, R1); rot_store(it, tk0, false, sk, R1); }
             }
           }
