@@ -471,14 +471,28 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         if (!bar_wait(b_kfull + 8 * st, (item / L::NK) & 1)) { fail(); return; }
         tc_fence_after();
         const uint64_t kd = kdesc0 + (uint64_t)((st * L::K_HALF) >> 4);
-        // The workspace form (prefill) lives on this thread's issue rate: everything unrolled.  The converting forms are paced
-        // by their converter warps and their code has to stay inside the instruction cache: loops, one expansion per lambda.
-        #pragma unroll (FUSED ? 1 : L::KBLK)
+        // The workspace form (prefill) lives on this thread's issue rate: everything unrolled.  The converting forms keep
+        // their code inside the instruction cache: one expansion per lambda and a rolled loop, whose iteration is kept to a
+        // handful of instructions by stepping the two descriptors (an MMA cost this thread ~220 cycles with the
+        // descriptors recomputed in every iteration, and the thread then paced the whole kernel).
+        if constexpr (FUSED) {
+          const uint32_t dcol = tmem + (buf ? L::TM_S1 : L::TM_S0);
+          uint64_t qd = qdesc0, kdd = kd;
+          #pragma unroll 1
+          for (int t = 0; t < 4 * L::KBLK; ++t) {
+            umma2_ss(dcol, qd, kdd, ID_S, t ? 1u : 0u);
+            const bool last = (t & 3) == 3;                          // next 64-channel block: the next operand block of Q and of K
+            qd += last ? (uint64_t)((L::Q_BLOCK - 96) >> 4) : 2ull;
+            kdd += last ? (uint64_t)((L::K_BLOCK - 96) >> 4) : 2ull;
+          }
+        } else {
+        #pragma unroll
         for (int kb = 0; kb < L::KBLK; ++kb)
-          #pragma unroll (FUSED ? 1 : 4)
+          #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
             umma2_ss(tmem + (buf ? L::TM_S1 : L::TM_S0), qdesc0 + (uint64_t)((kb * L::Q_BLOCK + ks * 32) >> 4),
                      kd + (uint64_t)((kb * L::K_BLOCK + ks * 32) >> 4), ID_S, (kb | ks) ? 1u : 0u);
+        }
         umma2_commit(b_sready + 8 * buf);
         umma2_commit(b_kempty + 8 * st);                             // the K halves may be overwritten once these MMAs are done
       };
@@ -489,9 +503,18 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         tc_fence_after();
         const uint64_t vd = vdesc0 + (uint64_t)((st * L::V_HALF) >> 4);
         const uint32_t pcol = tmem + (buf ? L::TM_S1 : L::TM_S0);
-        #pragma unroll (FUSED ? 1 : TC_BN / 16)
+        if constexpr (FUSED) {
+          uint32_t pa = pcol; uint64_t vdd = vd;
+          #pragma unroll 1
+          for (int ks = 0; ks < TC_BN / 16; ++ks) {                  // P columns: keys 0-63 at +0.., keys 64-127 at +64..
+            umma2_ts(tmem + L::TM_O, pa, vdd, ID_PV, (tile_i | ks) ? 1u : 0u);
+            pa += ks == 3 ? 64u - 24u : 8u; vdd += 128ull;
+          }
+        } else {
+        #pragma unroll
         for (int ks = 0; ks < TC_BN / 16; ++ks)                      // P columns: keys 0-63 at +0.., keys 64-127 at +64..
           umma2_ts(tmem + L::TM_O, pcol + 64 * (ks >> 2) + 8 * (ks & 3), vd + (uint64_t)((ks * 2048) >> 4), ID_PV, (tile_i | ks) ? 1u : 0u);
+        }
         umma2_commit(b_pvdone + 8 * (tile_i & 1));                   // O may be rescaled
         umma2_commit(b_vempty + 8 * st);                             // the V halves may be overwritten
       };
