@@ -607,7 +607,7 @@ def run_secondary(args):
     g = torch.Generator(device="cuda").manual_seed(1234)
     base = {"n_gpus": 1, "steps": K, "warmup": W, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic"}
 
-    def tc_case(ctx, M, splits, name):
+    def tc_case(ctx, M, splits, name, act=torch.float16):
         max_ctx = ((ctx + M + 127) // 64) * 64
         layer = kv4.KvLayer(shape.hkv, shape.hd, max_ctx)
         d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -619,17 +619,17 @@ def run_secondary(args):
             kv4.launch_kv_append(layer, k, v, d_pos, n)
         rope = torch.empty((max_ctx, shape.rd // 2, 2), dtype=torch.float32, device="cuda")
         kv4.launch_rope_table_g(rope, max_ctx, shape.theta, shape.rd)
-        q = torch.randn((M, shape.hq, shape.hd), generator=g, device="cuda", dtype=torch.float16)
+        q = torch.randn((M, shape.hq, shape.hd), generator=g, device="cuda", dtype=torch.float16).to(act)
         d_pos.fill_(ctx)
         pm, pl, pacc = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
-        o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.float16, device="cuda")
+        o16 = torch.empty((M, shape.hq, shape.hd), dtype=act, device="cuda")
         flops = shape.attn_flops(sum(ctx + r + 1 for r in range(M)))
         for form in ("workspace", "fused"):                        # fused: no workspace, the attention kernel converts the packed cache itself
             ws = kv4.tc_workspace(layer, M) if form == "workspace" else None
             t = _timed_graph(lambda i: kv4.launch_attention_prefill_tc(q, layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, ws), K, W)
             nl = (2 if form == "workspace" else 1) + (0 if splits == 1 else 1)
             line = dict(base, metric="kv4_multirow_attn_tflops", value=flops / t / 1e12, unit="TFLOP/s", ms_per_step=t * 1e3, dtype="f16",
-                        config={"workload": name, "form": form, "rows": M, "cached_tokens": ctx, "splits": splits,
+                        config={"workload": name, "form": form, "activations": "bf16" if act == torch.bfloat16 else "f16", "rows": M, "cached_tokens": ctx, "splits": splits,
                                 "l2": "K/V workspace is L2-resident by design; tensor-bound" if form == "workspace" else "packed cache read once per CTA pair"},
                         gpu_launches=nl * K,
                         roofline={"bound": "tensor", "achieved": flops / t / 1e12, "peak": tf, "unit": "TFLOP/s", "frac": flops / t / 1e12 / tf, "traffic": None,
@@ -639,9 +639,11 @@ def run_secondary(args):
 
     if args.workload == "prefill":
         tc_case(0, 8192, 1, "C5 causal prefill: 8192 rows from an empty cache, Hq24/Hkv4/hd256")
+        tc_case(0, 8192, 1, "C5 causal prefill: 8192 rows from an empty cache, Hq24/Hkv4/hd256", act=torch.bfloat16)
     elif args.workload == "verify":
         for M, S in ((64, 9), (32, 18), (16, 18)):                 # splits: one wave of CTA pairs (74) over 4 kv-heads
             tc_case(32768, M, S, f"C3 verify: {M} rows against 32768 cached tokens, Hq24/Hkv4/hd256")
+        tc_case(32768, 16, 18, "C3 verify: 16 rows against 32768 cached tokens, Hq24/Hkv4/hd256", act=torch.bfloat16)
     elif args.workload == "kv8":
         kvh, nh, S = shape.hkv, shape.hq, args.splits
         for ctx in (262144, 32768):

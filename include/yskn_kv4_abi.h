@@ -179,19 +179,19 @@ YSKN_KV4_API int yskn_kv4_prefill(const yskn_attn_g_args* a, int g, int hd, int 
  * workspace of yskn_kv4_tc_workspace_bytes(kvh, hd, max_ctx, M) bytes (16-byte aligned).  Each call first brings the
  * workspace up to date for tokens [valid_tokens, *d_pos + M): pass 0 unless the same workspace already holds the
  * dequantised tokens [0, valid_tokens) of this cache from an earlier call (valid_tokens <= *d_pos; nothing below the
- * 128-token tile of valid_tokens is touched).  q16 must be fp16; q16, pacc and o16 must be 16-byte aligned (vector
- * stores).  Semantics, partial layout and `splits` are those of yskn_kv4_attention; yskn_kv4_prefill_tc also merges to
+ * 128-token tile of valid_tokens is touched).  q16 is fp16 or bf16 (act_dtype; bv and o16 have the same type: bf16
+ * queries are converted to fp16 operand rows inside the kernel, which is exact for values within the fp16 range); q16,
+ * pacc and o16 must be 16-byte aligned (vector stores).  Semantics, partial layout and `splits` are those of yskn_kv4_attention; yskn_kv4_prefill_tc also merges to
  * o16 (+ optional bias).
  * d_workspace = NULL with workspace_bytes = 0 selects the form that needs no workspace: converter warps inside the attention
  * kernel read the packed rows of each key tile (int4 words, scale / zero rows, rope rows, shadow rows of the open groups)
  * and write the fp16 operand tiles themselves.  One launch, nothing dequantised to memory; valid_tokens is ignored.  This
- * form also takes bf16 activations (q16, bv and o16 bf16: the queries are staged as fp16 operands) and needs the rotary
- * width to be a multiple of 16 channels. */
+ * form needs the rotary width to be a multiple of 16 channels. */
 YSKN_KV4_API size_t yskn_kv4_tc_workspace_bytes(int kvh, int hd, int max_ctx, int M);
 /* The plain entries -- yskn_kv4_attention, yskn_kv4_decode, yskn_kv4_prefill, the reference's launcher set unchanged -- run
  * passes of more than 8 rows on the tcgen05 kernel whenever the shape is covered (head_dim 128 / 256, full cache, 16-byte
  * aligned arrays): without a workspace (the converting form above) by default.  This call lends the library a workspace on
- * the CURRENT device (NULL takes it back); passes of more than 64 rows with fp16 activations then use the workspace form
+ * the CURRENT device (NULL takes it back); passes of more than 64 rows then use the workspace form
  * when it holds yskn_kv4_tc_workspace_bytes(...) for the call, which is faster for long passes (a prefill converts each
  * tile once instead of once per query tile).  Through this route the whole workspace is rewritten on every call (as with
  * valid_tokens = 0); callers that keep it across passes use the _tc entries.  The library only stores the pointer: the

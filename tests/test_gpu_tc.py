@@ -100,12 +100,14 @@ def test_tc_rows_do_not_depend_on_pass_width(oracle, fused):
     assert np.array_equal(outs[16], outs[32][:16]) and np.array_equal(outs[32], outs[64][:32])
 
 
-@pytest.mark.parametrize("splits", [1, 4])
-def test_tc_fused_takes_bf16_activations(oracle, splits):
-    """The form without a workspace stages bf16 queries as fp16 operand rows itself and writes bf16 rows (what the 27B
-    engine passes); compared with the exact oracle on the same (bf16-representable) queries."""
+@pytest.mark.parametrize("form", ["workspace", "fused"])
+@pytest.mark.parametrize("splits,M", [(1, 24), (4, 24), (1, 150), (3, 150)])
+def test_tc_takes_bf16_activations(oracle, splits, M, form):
+    """Both forms stage bf16 queries as fp16 operand rows themselves (the converter warps, or the softmax warps in the
+    workspace form) and write bf16 rows (what the 27B engine passes); compared with the exact oracle on the same
+    (bf16-representable) queries.  150 rows: several query tiles per head, the last one ragged."""
     from yasakani_b200 import kv4
-    shape, ctx, M = synth.C2, 900, 24
+    shape, ctx = synth.C2, 900
     k, v = synth.make_kv(shape, ctx + M, seed=81)
     q = synth.make_q(shape, M, seed=81).bfloat16()
     max_ctx = ((ctx + M + 127) // 64) * 64
@@ -117,25 +119,36 @@ def test_tc_fused_takes_bf16_activations(oracle, splits):
     d_pos = torch.tensor([ctx], dtype=torch.int32, device="cuda")
     pm, pl, pacc = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
     o16 = torch.empty((M, shape.hq, shape.hd), dtype=torch.bfloat16, device="cuda")
-    kv4.launch_attention_prefill_tc(q.cuda(), layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16, None)
+    kv4.launch_attention_prefill_tc(q.cuda(), layer, M, d_pos, splits, pm, pl, pacc, rope, shape.hq, shape.qscale, shape.rd, o16,
+                                    kv4.tc_workspace(layer, M) if form == "workspace" else None)
     torch.cuda.synchronize()
     assert kv4.device_status() == 0
     want = oracle.attention_exact(f16_bits(q.float().half()), okv, ctx, rope_np, shape.hq, shape.rd, shape.qscale)
     got = o16.float().cpu().numpy()
     err = np.abs(got - want)
-    assert (err <= 2e-3 + 1e-2 * np.abs(want)).all(), f"bf16 fused pass: max err {err.max():.3e}"
+    assert (err <= 2e-3 + 1e-2 * np.abs(want)).all(), f"bf16 pass ({form} form): max err {err.max():.3e}"
+    if form == "workspace" and M > 64 and splits > 1:            # the plain entry takes a lent workspace for bf16 rows too
+        pm2, pl2, pacc2 = kv4.attn_scratch(M, splits, shape.hq, shape.hd)
+        lent = kv4.tc_workspace(layer, M)
+        kv4.set_tc_workspace(lent)
+        try:
+            kv4.launch_attention_gqa(q.cuda(), layer, M, d_pos, splits, pm2, pl2, pacc2, rope, shape.hq, shape.qscale, shape.rd)
+            torch.cuda.synchronize()
+        finally:
+            kv4.set_tc_workspace(None)
+        assert torch.equal(pacc2.view(torch.int32), pacc.view(torch.int32))
 
 
 def test_tc_rejects_what_it_does_not_cover():
     from yasakani_b200 import kv4, Kv4Error
     layer = kv4.KvLayer(4, 256, 128)
-    q = torch.zeros((16, 24, 256), dtype=torch.bfloat16, device="cuda")
+    q = torch.zeros((16, 24, 256), dtype=torch.float16, device="cuda")
     d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
     pm, pl, pacc = kv4.attn_scratch(16, 1, 24, 256)
-    with pytest.raises(Kv4Error, match="fp16 activations"):
-        kv4.launch_attention_tc(q, layer, 16, d_pos, 1, pm, pl, pacc, None, 24, 0.0625, 0, kv4.tc_workspace(layer, 16))
+    with pytest.raises(Kv4Error, match="hd 128/256"):          # a rotary width that is not a whole number of 8-channel words per half
+        kv4.launch_attention_tc(q, layer, 16, d_pos, 1, pm, pl, pacc, torch.zeros((128, 24), device="cuda"), 24, 0.0625, 24, kv4.tc_workspace(layer, 16))
     with pytest.raises(Kv4Error, match="workspace of"):
-        kv4.launch_attention_tc(q.half(), layer, 16, d_pos, 1, pm, pl, pacc, None, 24, 0.0625, 0, torch.empty(1024, dtype=torch.uint8, device="cuda"))
+        kv4.launch_attention_tc(q, layer, 16, d_pos, 1, pm, pl, pacc, None, 24, 0.0625, 0, torch.empty(1024, dtype=torch.uint8, device="cuda"))
 
 
 def test_tc_workspace_kept_across_passes_gives_the_same_bits(oracle):

@@ -26,7 +26,8 @@
 //     Tiles that contain a row's own group ("edge" tiles) get S twice, from Kd and from Ks, and each row picks per
 //     32-key group: int4 keys for groups before its own, shadow keys (causally masked) for its own.
 //
-//  The attention kernel has three forms (template FORM): 0 = operand tiles by TMA from the workspace, as above; 1 = no
+//  The attention kernel has four forms (template FORM): 0 = operand tiles by TMA from the workspace, as above (3 = the same
+//  with bf16 queries and output rows: the softmax warps convert the queries, there is no Q copy); 1 = no
 //  workspace and no prep launch, converter warps build the tiles from the packed KV4 cache inside the kernel; 2 = the same over
 //  Family-B INT8 rows.  The converting forms run 16 warps: 0-7 softmax, 8 Q copy + MMA issue, 9-11 V tiles, 12-15 K tiles.
 //
@@ -308,6 +309,32 @@ __device__ __forceinline__ void tc_prefetch_l2(const void* p) { asm volatile("pr
 __device__ __forceinline__ void tc_sts128(uint32_t a, const uint4& v) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+// bf16 queries of one CTA (128 operand rows = (token, head) pairs) as fp16 rows in the swizzled Q blocks; rows without a
+// query are zero.  Thread t of nt; eight 16-byte loads are in flight per thread before the first one is converted.
+template <int HD>
+__device__ __forceinline__ void tc_stage_q_bf16(uint32_t sq, int q_block, const uint16_t* q16, int tok0, int G, int TOK, int M, int nh, int head0,
+                                                int t, int nt) {
+  constexpr int NW = HD / 8, B = 8;
+  for (int base = t; base < 128 * NW; base += B * nt) {
+    uint4 u[B];
+    #pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const int it = base + b * nt, row = it / NW, w = it % NW, tk = tok0 + row / G;
+      u[b] = make_uint4(0u, 0u, 0u, 0u);
+      if (it < 128 * NW && row < TOK * G && tk < M) u[b] = tc_ldg128(q16 + ((size_t)tk * nh + head0 + row % G) * HD + 8 * w);
+    }
+    #pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const int it = base + b * nt, row = it / NW, w = it % NW;
+      if (it >= 128 * NW) break;
+      const uint32_t uu[4] = {u[b].x, u[b].y, u[b].z, u[b].w};
+      uint32_t o4[4];
+      #pragma unroll
+      for (int e = 0; e < 4; ++e) o4[e] = tc_pack(__uint_as_float(uu[e] << 16), __uint_as_float(uu[e] & 0xffff0000u));
+      tc_sts128(sq + (w >> 3) * q_block + row * 128 + (((w & 7) ^ (row & 7)) << 4), make_uint4(o4[0], o4[1], o4[2], o4[3]));
+    }
+  }
+}
 // ------------------------------------------------------------------------------------------------ attention kernel
 constexpr int TC_SW = 8;                                   // softmax warps: warp w owns rows 32*(w%4).., key columns 64*(w/4)..
 constexpr int TC_KW = 4, TC_VW = 3, TC_CW = TC_KW + TC_VW;  // converter warps of the fused forms: K half tiles, V half tiles
@@ -355,6 +382,7 @@ struct TcP {
 };
 
 // FORM 0: K and V tiles come by TMA from the fp16 workspace that kv4_tc_prep_kernel wrote.
+// FORM 3: FORM 0 for bf16 activations, a form of its own so that the fp16 kernel carries none of its code.
 // FORM 1: no workspace.  Seven converter warps per CTA read the packed cache rows of each tile straight from global memory
 // (the int4 words, their scale and zero rows, the rope table rows of the rotary channels; for edge tiles also the fp16
 // shadow rows), convert them and store the fp16 operand rows into the same 128-byte-swizzled stages the TMA would have
@@ -366,11 +394,12 @@ struct TcP {
 // rows are masked causally.  A byte is read as the fp16 number 1152 + b by one byte permute, the offset leaves by an exact
 // subtraction, and the row's scale (rounded to fp16) is multiplied in.
 template <int HD, int FORM>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc_threads(FORM != 0), 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc_threads(FORM == 1 || FORM == 2), 1)
 kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapKd,
                    const __grid_constant__ CUtensorMap mapVd, const __grid_constant__ CUtensorMap mapKs, const TcP P) {
   using L = TcLay<HD>;
-  constexpr bool FUSED = FORM != 0, I8 = FORM == 2;
+  constexpr bool FUSED = FORM == 1 || FORM == 2, I8 = FORM == 2;
+  const bool act_bf16 = FUSED ? P.bf16 != 0 : FORM == 3;              // a compile-time constant in the workspace forms
   static_assert(!I8 || HD == 256, "INT8 rows have 256 channels");
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = s_u32(smem);
@@ -390,7 +419,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     for (int i = 0; i < L::NK; ++i) { bar_init(b_kfull + 8 * i, FUSED ? 2 * TC_KW : 1); bar_init(b_kempty + 8 * i, 1); }
     for (int i = 0; i < L::NV; ++i) { bar_init(b_vfull + 8 * i, FUSED ? 2 * TC_VW : 1); bar_init(b_vempty + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) { bar_init(b_sready + 8 * i, 1); bar_init(b_pready + 8 * i, 2 * TC_SW); bar_init(b_pvdone + 8 * i, 1); }
-    bar_init(b_q, FUSED && P.bf16 ? 2 * TC_KW : 1);
+    bar_init(b_q, act_bf16 ? (FUSED ? 2 * TC_KW : 2 * TC_SW) : 1);   // bf16 queries are staged by warps, not by TMA
     *s_abort = 0;
     for (int i = 0; i < 128; ++i) reinterpret_cast<volatile uint32_t*>(smem + L::OFF_XCH + 2 * 2 * 128 * 4)[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -432,9 +461,11 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     // ======================================================================= TMA producer (one per CTA)
     // Q once, then two rings: K halves are free again as soon as their S MMAs are done, V halves only after P.V.
     // Every copy reports to the leader's "full" barrier; the leader posts the byte count of both CTAs' parts.
-    if (lane == 0 && n > 0 && !(FUSED && P.bf16)) {
-      if (rank == 0) bar_expect_tx(b_q, 2 * L::KBLK * G * TOK * 128);
-      for (int kb = 0; kb < L::KBLK; ++kb) tma_load_4d_pair(sb + L::OFF_Q + kb * L::Q_BLOCK, &mapQ, 64 * kb, 0, kvh, tok0, lead_q);
+    if (lane == 0 && n > 0 && !(FUSED && act_bf16)) {
+      if (!act_bf16) {                                                 // bf16 queries are converted and written by warps instead
+        if (rank == 0) bar_expect_tx(b_q, 2 * L::KBLK * G * TOK * 128);
+        for (int kb = 0; kb < L::KBLK; ++kb) tma_load_4d_pair(sb + L::OFF_Q + kb * L::Q_BLOCK, &mapQ, 64 * kb, 0, kvh, tok0, lead_q);
+      }
       int kit = 0; bool ok = true;
       for (int i = 0; i < n && ok && !FUSED; ++i) {
         const int j = j0 + i;
@@ -592,20 +623,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       if constexpr (I8) {
         constexpr int NKI = ((TC_BN / 2) * 16 + NKT - 1) / NKT;      // 64 keys x 16 chunks over the K threads
         if (P.bf16) {
-          constexpr int NWD8 = HD / 8;
-          for (int it = ct; it < 128 * NWD8; it += NKT) {            // bf16 queries as fp16 operand rows (see the int4 branch)
-            const int row = it / NWD8, w = it % NWD8, tk = tok0 + row / G, hq = row % G;
-            uint4 out = make_uint4(0u, 0u, 0u, 0u);
-            if (row < TOK * G && tk < P.M) {
-              const uint4 u = __ldg(reinterpret_cast<const uint4*>(P.q16 + ((size_t)tk * P.nh + kvh * G + hq) * HD + 8 * w));
-              const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
-              uint32_t o4[4];
-              #pragma unroll
-              for (int e = 0; e < 4; ++e) o4[e] = tc_pack(bf2f((uint16_t)uu[e]), bf2f((uint16_t)(uu[e] >> 16)));
-              out = make_uint4(o4[0], o4[1], o4[2], o4[3]);
-            }
-            tc_sts128(sb + L::OFF_Q + (w >> 3) * L::Q_BLOCK + row * 128 + (((w & 7) ^ (row & 7)) << 4), out);
-          }
+          tc_stage_q_bf16<HD>(sb + L::OFF_Q, L::Q_BLOCK, P.q16, tok0, G, TOK, P.M, P.nh, kvh * G, ct, NKT);
           publish(lead_q);
         }
         // The items of all tiles form one stream (NKI per tile); two are in flight ahead of the one being converted.  Rolled
@@ -741,19 +759,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       };
       if (P.bf16) {
         // bf16 activations: this CTA's query rows (token, head) as fp16 operand rows; rows without a query are zero
-        for (int it = ct; it < 128 * NWD; it += NKT) {
-          const int row = it / NWD, w = it % NWD, tk = tok0 + row / G, hq = row % G;
-          uint4 out = make_uint4(0u, 0u, 0u, 0u);
-          if (row < TOK * G && tk < P.M) {
-            const uint4 u = __ldg(reinterpret_cast<const uint4*>(P.q16 + ((size_t)tk * P.nh + kvh * G + hq) * HD + 8 * w));
-            const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
-            uint32_t o4[4];
-            #pragma unroll
-            for (int e = 0; e < 4; ++e) o4[e] = tc_pack(bf2f((uint16_t)uu[e]), bf2f((uint16_t)(uu[e] >> 16)));
-            out = make_uint4(o4[0], o4[1], o4[2], o4[3]);
-          }
-          tc_sts128(sb + L::OFF_Q + (w >> 3) * L::Q_BLOCK + row * 128 + (((w & 7) ^ (row & 7)) << 4), out);
-        }
+        tc_stage_q_bf16<HD>(sb + L::OFF_Q, L::Q_BLOCK, P.q16, tok0, G, TOK, P.M, P.nh, kvh * G, ct, NKT);
         publish(lead_q);
       }
       // Rotary items in the compact mapping (rotary width of at most 64 channels): a thread owns one word pair (p, p + nrp) of
@@ -995,6 +1001,16 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     const int pr = pos0 + tok, cr = pr / 32;                         // row position and its own group
     const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
     const float cs = P.qscale * TC_LOG2E;
+    if constexpr (FORM == 3) {
+      if (n > 0) {
+        // bf16 activations in the workspace form: these eight warps write this CTA's query rows as fp16 operand rows
+        // (the converting forms leave that to their K converters); rows without a query are zero
+        tc_stage_q_bf16<HD>(sb + L::OFF_Q, L::Q_BLOCK, P.q16, tok0, G, TOK, P.M, P.nh, kvh * G, threadIdx.x, 32 * TC_SW);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) bar_arrive_cluster(lead_q);
+      }
+    }
     // The row's two threads swap one float per tile through shared memory: value first, then a sequence number the
     // partner polls (bounded, like every wait here; a named barrier could not give up).
     volatile float* xval = reinterpret_cast<volatile float*>(smem + L::OFF_XCH);
@@ -1107,7 +1123,7 @@ kv4_tc_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           #pragma unroll
           for (int k = 0; k < 32; k += 2) {
             float y0 = round_f16(o[k] / l), y1 = round_f16(o[k + 1] / l);
-            if (FUSED && P.bf16) {
+            if (act_bf16) {
               if (P.bv) { y0 = __fadd_rn(y0, bf2f(P.bv[kvh * HD + 32 * c + k])); y1 = __fadd_rn(y1, bf2f(P.bv[kvh * HD + 32 * c + k + 1])); }
               w[k / 2] = (uint32_t)f2bf(y0) | ((uint32_t)f2bf(y1) << 16);
               continue;
@@ -1233,7 +1249,7 @@ TcWs carve(void* ws, int kvh, int hd, int max_ctx, int M) {
 }
 
 template <int HD>
-int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int valid_tokens, uint16_t* o16, const uint16_t* bv, cudaStream_t st) {
+int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, int bf16, const TcWs& w, int valid_tokens, uint16_t* o16, const uint16_t* bv, cudaStream_t st) {
   using L = TcLay<HD>;
   // Tokens below valid_tokens are in the workspace already (the caller guarantees valid_tokens <= *d_pos); the group that
   // holds valid_tokens may have been completed since, and the shadow rows start at the 128-token tile of *d_pos.
@@ -1245,15 +1261,16 @@ int launch_tc_hd(const yskn_attn_g_args& a, int g, int rd, const TcWs& w, int va
   if (int rc = launch_status("kv4_tc_prep_kernel")) return rc;
   CUtensorMap mq, mkd, mvd, mks;
   const uint64_t rows = (uint64_t)a.kvh * a.max_ctx;
-  if (!tc_map_q(&mq, a.q16, a.M, a.kvh, g, HD) || !tc_map_rows(&mkd, w.kd, rows, HD, TC_BN / 2, L::KBLK) ||
+  if (bf16) memset(&mq, 0, sizeof(mq));                               // the softmax warps stage Q
+  if ((!bf16 && !tc_map_q(&mq, a.q16, a.M, a.kvh, g, HD)) || !tc_map_rows(&mkd, w.kd, rows, HD, TC_BN / 2, L::KBLK) ||
       !tc_map_rows(&mvd, w.vd, rows, HD, TC_BN, L::KBLK / 2) || !tc_map_rows(&mks, w.ks, (uint64_t)a.kvh * w.ks_rows, HD, TC_BN / 2, L::KBLK))
     KV4_REJECT("yskn_kv4_attention_tc: cuTensorMapEncodeTiled failed or is unavailable");
-  auto kern = kv4_tc_attn_kernel<HD, 0>;
-  static std::atomic<unsigned long long> attr{0};
-  if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+  auto kern = bf16 ? kv4_tc_attn_kernel<HD, 3> : kv4_tc_attn_kernel<HD, 0>;
+  static std::atomic<unsigned long long> attr[2] = {{0}, {0}};
+  if (first_use_on_device(attr[bf16 != 0])) KV4_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   const int tok = 128 / g, qtiles = ((a.M + tok - 1) / tok + 1) & ~1;        // CTA pairs: an even number of query tiles
-  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv, a.kv, a.rope, rd, nullptr, 0,
-        nullptr, nullptr, nullptr, nullptr};
+  TcP P{a.d_pos, a.M, a.splits, g, a.nh, a.max_ctx, w.ks_rows, a.qscale, a.pm, a.pl, a.pacc, o16, bv, a.kv, a.rope, rd,
+        static_cast<const uint16_t*>(a.q16), bf16, nullptr, nullptr, nullptr, nullptr};
   if (int rc = tc_launch_pdl(kern, dim3(qtiles, a.splits, a.kvh), TC_THREADS, L::TOTAL, st, mq, mkd, mvd, mks, P)) return rc;
   return launch_status("kv4_tc_attn_kernel");
 }
@@ -1278,7 +1295,7 @@ int launch_tc_fused_hd(const yskn_attn_g_args& a, int g, int rd, int bf16, uint1
 }  // namespace
 
 bool attention_tc_supports(int g, int hd, int rd, int act_dtype) {
-  return g >= 1 && g <= 8 && (hd == 256 || hd == 128) && rd >= 0 && rd <= hd && rd % 2 == 0 && act_dtype == YSKN_KV4_F16 &&
+  return g >= 1 && g <= 8 && (hd == 256 || hd == 128) && rd >= 0 && rd <= hd && rd % 2 == 0 && (act_dtype == YSKN_KV4_F16 || act_dtype == YSKN_KV4_BF16) &&
          (rd == 0 || ((rd / 2) % (hd / 32) == 0 && (((rd / 2) / (hd / 32)) & ((rd / 2) / (hd / 32) - 1)) == 0));
 }
 
@@ -1288,14 +1305,15 @@ int launch_attention_tc(const yskn_attn_g_args& a, int g, int hd, int rd, int ac
                         int valid_tokens, uint16_t* o16_direct, const uint16_t* bv, cudaStream_t st) {
   if (!workspace && workspace_bytes == 0) return launch_attention_tc_fused(a, g, hd, rd, act_dtype, o16_direct, bv, st);   // no workspace: convert inside the kernel
   if (!attention_tc_supports(g, hd, rd, act_dtype))
-    KV4_REJECT("yskn_kv4_attention_tc: unsupported (g %d, hd %d, rd %d, act_dtype %d): fp16 activations, hd 128/256", g, hd, rd, act_dtype);
+    KV4_REJECT("yskn_kv4_attention_tc: unsupported (g %d, hd %d, rd %d, act_dtype %d): fp16 or bf16 activations, hd 128/256", g, hd, rd, act_dtype);
   const TcWs w = carve(workspace, a.kvh, hd, a.max_ctx, a.M);
   if (!workspace || workspace_bytes < w.bytes) KV4_REJECT("yskn_kv4_attention_tc: workspace of %zu bytes needed, %zu given", w.bytes, workspace_bytes);
   if (((uintptr_t)workspace | (uintptr_t)a.q16) & 15) KV4_REJECT("yskn_kv4_attention_tc: workspace and q16 must be 16-byte aligned");
   if (valid_tokens < 0) valid_tokens = 0;
   if (o16_direct && ((uintptr_t)o16_direct & 15)) KV4_REJECT("yskn_kv4_prefill_tc: o16 must be 16-byte aligned");
   if (!o16_direct && ((uintptr_t)a.pacc & 15)) KV4_REJECT("yskn_kv4_attention_tc: pacc must be 16-byte aligned");
-  return hd == 256 ? launch_tc_hd<256>(a, g, rd, w, valid_tokens, o16_direct, bv, st) : launch_tc_hd<128>(a, g, rd, w, valid_tokens, o16_direct, bv, st);
+  const int bf16 = act_dtype == YSKN_KV4_BF16;
+  return hd == 256 ? launch_tc_hd<256>(a, g, rd, bf16, w, valid_tokens, o16_direct, bv, st) : launch_tc_hd<128>(a, g, rd, bf16, w, valid_tokens, o16_direct, bv, st);
 }
 
 // Many-row attention straight from the packed cache (no workspace, one launch).  Same shapes as the workspace form, and the
