@@ -701,6 +701,25 @@ def run_secondary(args):
                         roofline={"bound": "hbm", "achieved": byt / t / 1e9, "peak": hbm, "unit": "GB/s", "frac": byt / t / 1e9 / hbm, "traffic": None,
                                   "kernel": f"kvx_{name}_kernel", "bytes_per_launch": byt, "peak_kind": f"of {kind}"})
             print(json.dumps(line), flush=True)
+        # the attention block's row epilogue: M tokens of the 27B shape (24 query heads of 512 projection values, 4 + 4 KV rows)
+        M, nh, kvh, rd, max_ctx = 8192, 24, 4, 64, 2 * 8192
+        mk = lambda *shape: torch.randn(shape, device="cuda", generator=g).to(torch.bfloat16)
+        sets = [(mk(M, nh, 512), mk(M, kvh, 256), mk(M, kvh, 256)) for _ in range(2)]            # 2 x 218 MB in: larger than L2
+        qn_w, kn_w = mk(256) * 0.2, mk(256) * 0.2
+        rope = torch.empty((max_ctx, rd // 2, 2), device="cuda"); kv4.launch_rope_table_g(rope, max_ctx, 1e7, rd)
+        q16 = torch.empty((M, nh, 256), dtype=torch.bfloat16, device="cuda"); gate16 = torch.empty_like(q16)
+        k8 = torch.empty((kvh, max_ctx, 256), dtype=torch.int8, device="cuda"); v8 = torch.empty_like(k8)
+        ks = torch.empty((kvh, max_ctx), device="cuda"); vs = torch.empty_like(ks)
+        d_pos = torch.tensor([4096], dtype=torch.int32, device="cuda")
+        t = _timed(lambda i: kvx.launch_attn_post(*sets[i & 1], qn_w, kn_w, 1e-6, d_pos, rope, rd, q16, gate16, k8, ks, v8, vs), K, W)
+        byt = M * (nh * 512 * 2 + 2 * kvh * 256 * 2 + 2 * nh * 256 * 2 + 2 * kvh * 260 + rd * 4)
+        line = dict(base, metric="kvx_attn_post_tokens_per_s", value=M / t, unit="tokens/s", ms_per_step=t * 1e3, dtype="f32",
+                    config={"workload": f"Family-B attention row epilogue: {M} tokens, Hq{nh}/Hkv{kvh}/hd256, rotary 64 (norm + RoPE + rotation + INT8 append)",
+                            "l2": f"2 input sets cycled; {byt / 1e6:.0f} MB per launch (L2 is 126 MB)"},
+                    gpu_launches=K,
+                    roofline={"bound": "hbm", "achieved": byt / t / 1e9, "peak": hbm, "unit": "GB/s", "frac": byt / t / 1e9 / hbm, "traffic": None,
+                              "kernel": "kvx_attn_post_kernel", "bytes_per_launch": byt, "peak_kind": f"of {kind}"})
+        print(json.dumps(line), flush=True)
 
 
 def main():

@@ -289,6 +289,30 @@ YSKN_KV4_API int yskn_kvx_encode(const void* d_x, int x_dtype, int8_t* d_q8, flo
 /* (float)q * scale, then the inverse rotation (src/kvx_probe.cu:15-19); y_dtype F16/BF16 rounds the fp32 result once. */
 YSKN_KV4_API int yskn_kvx_decode(const int8_t* d_q8, const float* d_scales, void* d_y, int y_dtype, long long rows, void* cuda_stream);
 
+/* The attention block's row epilogue for INT8 rows: the reference's launch_q35_attn_post / q35_attn_post_kernel
+ * (src/q35_kernels.cu:1013-1069, argument struct Q35AttnPostArgs, src/q35.hpp:97-104) from the point where a thread holds
+ * its bf16-rounded projection value (:1029).  What precedes that point in the reference's kernel -- the combine of the
+ * GEMV's partial sums, tau, and the inverse Hadamard-512 (part_*, tau_*, nw_*, sg_*, xsm) -- belongs to the weight path
+ * and stays with the caller, which hands over the rows instead:
+ *   q_rows bf16 [M][nh][512]   per head 256 query channels, then the 256 gate channels (the projection's output order)
+ *   k_rows, v_rows bf16 [M][kvh][256]
+ * Per query / key head: RMS norm over the 256 channels with weight (1 + w), partial RoPE (rotate-half over the first rd
+ * channels, table row of *d_pos + token), sign-Hadamard-256 rotation; q16 bf16 [M][nh][256]; keys and (rotated) values go
+ * to the INT8 row caches k8 / v8 [kvh][max_ctx][256] with ks / vs [kvh][max_ctx] at the token's position; gate16 bf16
+ * [M][nh][256] is the gate half as it is.  Bit-exact with the reference's kernel: pm != 0 computes 1 / sqrt with IEEE
+ * operations (its portable-math mode, src/pm_math.cuh:16, q35_set_pm), pm = 0 uses rsqrtf like its default.  rd is a
+ * multiple of 64 up to 256 (the reference: 64); rope is the float2 table [max_ctx][rd/2] (yskn_kv4_rope_table), 16-byte
+ * aligned; row arrays 8-byte aligned.  A token whose position lies outside [0, max_ctx) stores no cache row. */
+typedef struct {
+  const uint16_t* q_rows; const uint16_t* k_rows; const uint16_t* v_rows;
+  const uint16_t* qn_w; const uint16_t* kn_w;   /* bf16 [256] each */
+  float eps; int M; const int* d_pos; const float* rope; int rd;
+  uint16_t* q16; uint16_t* gate16;
+  int8_t* k8; int8_t* v8; float* ks; float* vs;
+  int max_ctx; int nh; int kvh; int pm;
+} yskn_kvx_attn_post_args;
+YSKN_KV4_API int yskn_kvx_attn_post(const yskn_kvx_attn_post_args* a, void* cuda_stream);
+
 /* Host-pointer probe with the contract of the reference's yskn_kvx_probe (src/kvx_probe.cu:22-36): rows even and > 0,
  * x[rows*256] in; q[rows*256], scales[rows], y[rows*256] (decoded) out.  Returns 0, -1 (bad rows) or a cudaError_t.
  * Allocates and frees its own device memory. */

@@ -216,6 +216,24 @@ def kvx_encode(x: np.ndarray):
     return q, sc
 
 
+def kvx_attn_post(q_rows, k_rows, v_rows, qn_w, kn_w, eps: float, pos0: int, rope, rd: int, max_ctx: int, k8, ks, v8, vs):
+    """ysko_kvx_attn_post: rows as bf16 bit patterns (uint16) -- q_rows [M][nh][512], k_rows / v_rows [M][kvh][256]; the
+    INT8 row caches k8 / v8 [kvh][max_ctx][256] and ks / vs [kvh][max_ctx] are updated in place at pos0 .. pos0 + M - 1.
+    Returns (q16, gate16) as bf16 bit patterns [M][nh][256]."""
+    q_rows = np.ascontiguousarray(q_rows, dtype=np.uint16); k_rows = np.ascontiguousarray(k_rows, dtype=np.uint16)
+    v_rows = np.ascontiguousarray(v_rows, dtype=np.uint16)
+    qn_w = np.ascontiguousarray(qn_w, dtype=np.uint16); kn_w = np.ascontiguousarray(kn_w, dtype=np.uint16)
+    rope = np.ascontiguousarray(rope, dtype=np.float32)
+    M, nh = q_rows.shape[0], q_rows.shape[1]; kvh = k_rows.shape[1]
+    assert q_rows.shape == (M, nh, 512) and k_rows.shape == (M, kvh, 256) and v_rows.shape == (M, kvh, 256)
+    assert k8.dtype == np.int8 and v8.dtype == np.int8 and ks.dtype == np.float32 and vs.dtype == np.float32
+    assert k8.shape == (kvh, max_ctx, 256) and k8.flags.c_contiguous and v8.flags.c_contiguous and pos0 + M <= max_ctx
+    q16 = np.empty((M, nh, 256), dtype=np.uint16); gate16 = np.empty((M, nh, 256), dtype=np.uint16)
+    lib().ysko_kvx_attn_post(_p(q_rows), _p(k_rows), _p(v_rows), _p(qn_w), _p(kn_w), C.c_float(eps), int(M), int(pos0), _p(rope), int(rd),
+                             int(nh), int(kvh), int(max_ctx), _p(q16), _p(gate16), _p(k8), _p(ks), _p(v8), _p(vs))
+    return q16, gate16
+
+
 def kvx_decode(q: np.ndarray, sc: np.ndarray) -> np.ndarray:
     q = np.ascontiguousarray(q, dtype=np.int8).reshape(-1, 256); sc = np.ascontiguousarray(sc, dtype=np.float32)
     y = np.empty(q.shape, dtype=np.float32)

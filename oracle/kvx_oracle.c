@@ -100,3 +100,69 @@ void ysko_kv8_attention_exact(const float* q, const int8_t* k8, const int8_t* v8
       for (int d = 0; d < 256; ++d) out[((size_t)r * nh + h) * 256 + d] = (float)(o[d] / l);
     }
 }
+
+/* ---- The attention block's row epilogue for INT8 rows, restated from q35_attn_post_kernel (src/q35_kernels.cu:1013-1065)
+ * from the point where a thread holds its bf16-rounded projection value y (:1029): the weight path's combine and inverse
+ * Hadamard-512 in front of it (:1025-1028) are not part of this path.
+ *   V head:  rotate (sign-Hadamard-256) -> INT8 row at position pos                                            (:1030-1038)
+ *   Q, K:    ss = y*y summed per warp of 32 channels by an xor-shuffle tree (strides 16, 8, 4, 2, 1), the 8 warp sums
+ *            added in order; r = 1/sqrt(tot/256 + eps) with IEEE sqrt and division (the reference's portable-math mode,
+ *            src/pm_math.cuh:16; its default rsqrtf is an approximation with no CPU restatement);
+ *            xn = bf16(y*r*(1 + w[d])); rotate-half over the first rd channels with the table row of pos, every product
+ *            and the sum rounded to bf16; rotate; Q -> bf16, K -> INT8 row                                      (:1043-1064)
+ *   gate:    the second 256 outputs of a query head, copied as bf16                                            (:1042)
+ * Rows are bf16 bit patterns.  q_rows [M][nh][512], k_rows / v_rows [M][kvh][256]; rope float2 [max_ctx][rd/2]. */
+static float bf_bits_to_f(uint16_t b) { union { uint32_t u; float f; } v; v.u = (uint32_t)b << 16; return v.f; }
+static uint16_t f_to_bf_bits(float f) {                       /* __float2bfloat16_rn: round to nearest even, NaN kept quiet */
+  union { uint32_t u; float f; } v; v.f = f;
+  if ((v.u & 0x7fffffffu) > 0x7f800000u) return 0x7fffu;
+  return (uint16_t)((v.u + 0x7fffu + ((v.u >> 16) & 1u)) >> 16);
+}
+static float rbf(float f) { return bf_bits_to_f(f_to_bf_bits(f)); }
+
+static void post_norm_rope(const uint16_t* y16, const uint16_t* w16, float eps, const float* rope_row, int rd, float* out) {
+  float y[256], xn[256], s[8];
+  for (int d = 0; d < 256; ++d) y[d] = bf_bits_to_f(y16[d]);
+  for (int w = 0; w < 8; ++w) {
+    float t[32];
+    for (int j = 0; j < 32; ++j) t[j] = y[32 * w + j] * y[32 * w + j];
+    for (int o = 16; o; o >>= 1) { float n[32]; for (int j = 0; j < 32; ++j) n[j] = t[j] + t[j ^ o]; memcpy(t, n, sizeof t); }
+    s[w] = t[0];
+  }
+  float tot = 0.f;
+  for (int w = 0; w < 8; ++w) tot = tot + s[w];
+  const float r = 1.f / sqrtf(tot / 256.f + eps);
+  for (int d = 0; d < 256; ++d) xn[d] = rbf((y[d] * r) * (1.f + bf_bits_to_f(w16[d])));
+  for (int d = 0; d < 256; ++d) {
+    float o = xn[d];
+    if (d < rd / 2) { const float c = rope_row[2 * d], sn = rope_row[2 * d + 1]; o = rbf(rbf(xn[d] * c) + rbf(-xn[d + rd / 2] * sn)); }
+    else if (d < rd) { const float c = rope_row[2 * (d - rd / 2)], sn = rope_row[2 * (d - rd / 2) + 1]; o = rbf(rbf(xn[d] * c) + rbf(xn[d - rd / 2] * sn)); }
+    out[d] = o;
+  }
+}
+
+void ysko_kvx_attn_post(const uint16_t* q_rows, const uint16_t* k_rows, const uint16_t* v_rows, const uint16_t* qn_w, const uint16_t* kn_w,
+                        float eps, int M, int pos0, const float* rope, int rd, int nh, int kvh, int max_ctx,
+                        uint16_t* q16, uint16_t* gate16, int8_t* k8, float* ks, int8_t* v8, float* vs) {
+  float x[256], rot[256];
+  for (int t = 0; t < M; ++t) {
+    const int pos = pos0 + t;
+    const float* rr = rope + (size_t)pos * (rd / 2) * 2;
+    for (int h = 0; h < nh; ++h) {
+      const uint16_t* row = q_rows + ((size_t)t * nh + h) * 512;
+      post_norm_rope(row, qn_w, eps, rr, rd, x);
+      rotate_row(x, rot, 0);
+      for (int d = 0; d < 256; ++d) {
+        q16[((size_t)t * nh + h) * 256 + d] = f_to_bf_bits(rot[d]);
+        gate16[((size_t)t * nh + h) * 256 + d] = row[256 + d];
+      }
+    }
+    for (int h = 0; h < kvh; ++h) {
+      const size_t dst = (size_t)h * max_ctx + pos;
+      post_norm_rope(k_rows + ((size_t)t * kvh + h) * 256, kn_w, eps, rr, rd, x);
+      ysko_kvx_encode(x, k8 + dst * 256, ks + dst, 1);
+      for (int d = 0; d < 256; ++d) x[d] = bf_bits_to_f(v_rows[((size_t)t * kvh + h) * 256 + d]);
+      ysko_kvx_encode(x, v8 + dst * 256, vs + dst, 1);
+    }
+  }
+}

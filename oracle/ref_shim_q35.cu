@@ -22,3 +22,19 @@ extern "C" int yref_q35_attention_kv8(const uint16_t* q16, const int8_t* k8, con
   try { yskn::launch_q35_attention(A, (cudaStream_t)st); } catch (const std::exception&) { return -1; }
   return (int)cudaGetLastError();
 }
+
+// src/q35_kernels.cu:1013-1069 (launch_q35_attn_post, the plain kernel: no xsm, no prefetch, INT8 row caches).  One GEMV
+// slice (nw = 1) and tau = 1 (`ones`, at least 24 * 512 floats), signs all +1 (`signs`, at least 24 * 512 bytes), so that a
+// block's 512 projection values are bf16(H512(part) / sqrt(512)).  part_q [M][24 * 512], part_k / part_v [M][4 * 256].
+// pm selects the kernel's portable-math mode (q35_set_pm, src/q35_kernels.cu:1139).
+extern "C" int yref_q35_attn_post(const float* part_q, const float* part_k, const float* part_v, const float* ones, const int8_t* signs,
+                                  const uint16_t* qn_w, const uint16_t* kn_w, float eps, int M, const int* d_pos, const float* rope,
+                                  uint16_t* q16, uint16_t* gate16, int8_t* k8, int8_t* v8, float* ks, float* vs, int max_ctx, int pm, void* st) {
+  yskn::Q35AttnPostArgs A{};
+  A.part_q = part_q; A.part_k = part_k; A.part_v = part_v; A.tau_q = ones; A.tau_k = ones; A.tau_v = ones;
+  A.nw_q = 1; A.nw_k = 1; A.nw_v = 1; A.sg_q = signs; A.sg_k = signs; A.sg_v = signs; A.qn_w = qn_w; A.kn_w = kn_w;
+  A.eps = eps; A.M = M; A.d_pos = d_pos; A.rope = reinterpret_cast<const float2*>(rope); A.q16 = q16; A.gate16 = gate16;
+  A.kc = nullptr; A.vc = nullptr; A.max_ctx = max_ctx; A.k8 = k8; A.v8 = v8; A.ks = ks; A.vs = vs;
+  try { yskn::q35_set_pm(pm, (cudaStream_t)st); yskn::launch_q35_attn_post(A, (cudaStream_t)st); } catch (const std::exception&) { return -1; }
+  return (int)cudaGetLastError();
+}

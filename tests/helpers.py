@@ -64,3 +64,30 @@ def gpu_attention(kv4, layer, q: torch.Tensor, pos0: int, splits: int, rope, sha
     kv4.launch_attn_combine_gqa(pm, pl, pacc, splits, M, o16, shape.hq, shape.g, bv=bv, gate=gate)
     torch.cuda.synchronize()
     return o16.float().cpu().numpy(), (pm.cpu().numpy(), pl.cpu().numpy(), pacc.cpu().numpy())
+
+
+# ---------------------------------------------------------------- inputs of the attention block's row epilogue (kvx attn_post)
+def _oracle():
+    from oracle import kv4_oracle
+    return kv4_oracle
+
+
+def bf16_bits(x: np.ndarray) -> np.ndarray:
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).bfloat16().view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def post_inputs(seed, M, nh, kvh, rd, max_ctx, theta=1e7):
+    """Seeded projection rows (bf16 bits), norm weights, rope table.  Returns a dict of numpy arrays."""
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((M, nh, 512)) * np.exp(rng.uniform(-1.0, 1.5, (1, nh, 1)))
+    k = rng.standard_normal((M, kvh, 256)) * np.exp(rng.uniform(np.log(0.5), np.log(4.0), (1, kvh, 256)))
+    v = rng.standard_normal((M, kvh, 256))
+    if M > 1:
+        q[1, 0, :256] = 0.0                      # an all-zero query head: r = 1 / sqrt(eps)
+        k[1, 0] = 0.0                            # an all-zero key row: scale 0, payload 0
+        v[1, kvh - 1] = 0.0
+        k[0, kvh - 1] *= 3e3                     # large values
+    rope = _oracle().rope_table(max_ctx, theta, rd) if rd else np.zeros((max_ctx, 0, 2), dtype=np.float32)
+    return dict(q_rows=bf16_bits(q), k_rows=bf16_bits(k), v_rows=bf16_bits(v),
+                qn_w=bf16_bits(rng.standard_normal(256) * 0.2), kn_w=bf16_bits(rng.standard_normal(256) * 0.2 + 0.5),
+                rope=np.ascontiguousarray(rope, dtype=np.float32))

@@ -89,3 +89,93 @@ def test_bad_arguments_are_rejected():
         kvx.rotate(torch.zeros(256, device="cuda", dtype=torch.float16))
     q, sc = kvx.encode(torch.zeros((0, 256), device="cuda"))   # zero rows: a no-op
     assert q.shape == (0, 256) and sc.shape == (0,)
+
+
+# ---------------------------------------------------------------- the attention block's row epilogue (yskn_kvx_attn_post)
+POST_GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kvx_post_kat.npz")
+
+
+def _bf_t(bits: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16).cuda()
+
+
+def _bits(t: torch.Tensor) -> np.ndarray:
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _gpu_post(kvx, d, eps, pos0, rd, max_ctx, pm=True, fill=0):
+    M, nh, kvh = d["q_rows"].shape[0], d["q_rows"].shape[1], d["k_rows"].shape[1]
+    k8 = torch.full((kvh, max_ctx, 256), fill, dtype=torch.int8, device="cuda"); v8 = torch.full_like(k8, fill)
+    ks = torch.full((kvh, max_ctx), float(fill), device="cuda"); vs = torch.full_like(ks, float(fill))
+    q16 = torch.empty((M, nh, 256), dtype=torch.bfloat16, device="cuda"); gate16 = torch.empty_like(q16)
+    rope = torch.from_numpy(d["rope"]).cuda() if rd else None
+    kvx.launch_attn_post(_bf_t(d["q_rows"]), _bf_t(d["k_rows"]), _bf_t(d["v_rows"]), _bf_t(d["qn_w"]), _bf_t(d["kn_w"]), eps,
+                         torch.tensor([pos0], dtype=torch.int32, device="cuda"), rope, rd, q16, gate16, k8, ks, v8, vs, pm=pm)
+    torch.cuda.synchronize()
+    return _bits(q16), _bits(gate16), k8.cpu().numpy(), ks.cpu().numpy(), v8.cpu().numpy(), vs.cpu().numpy()
+
+
+def _oracle_post(oracle, d, eps, pos0, rd, max_ctx, fill=0):
+    kvh = d["k_rows"].shape[1]
+    k8 = np.full((kvh, max_ctx, 256), fill, dtype=np.int8); v8 = np.full_like(k8, fill)
+    ks = np.full((kvh, max_ctx), float(fill), dtype=np.float32); vs = np.full_like(ks, float(fill))
+    q16, gate16 = oracle.kvx_attn_post(d["q_rows"], d["k_rows"], d["v_rows"], d["qn_w"], d["kn_w"], eps, pos0, d["rope"], rd, max_ctx, k8, ks, v8, vs)
+    return q16, gate16, k8, ks, v8, vs
+
+
+def _same(got, want, what):
+    for g_, w_, n in zip(got, want, ("q16", "gate16", "k8", "ks", "v8", "vs")):
+        a = g_.view(np.uint32) if g_.dtype == np.float32 else g_
+        b = w_.view(np.uint32) if w_.dtype == np.float32 else w_
+        assert np.array_equal(a, b), f"{what}: {n} differs in {int((a != b).sum())} of {a.size} elements"
+
+
+def test_attn_post_known_answers():
+    from yasakani_b200 import kvx
+    g = np.load(POST_GOLD)
+    for name, c in {"a": dict(rd=64, max_ctx=64, pos0=37, eps=1e-6), "b": dict(rd=128, max_ctx=32, pos0=5, eps=1e-5)}.items():
+        d = {k_: g[f"{name}_{k_}"] for k_ in ("q_rows", "k_rows", "v_rows", "qn_w", "kn_w", "rope")}
+        q16, gate16, k8, ks, v8, vs = _gpu_post(kvx, d, c["eps"], c["pos0"], c["rd"], c["max_ctx"])
+        M = d["q_rows"].shape[0]; sl = slice(c["pos0"], c["pos0"] + M)
+        _same((q16, gate16, k8[:, sl], ks[:, sl], v8[:, sl], vs[:, sl]),
+              tuple(g[f"{name}_{k_}"] for k_ in ("q16", "gate16", "k8", "ks", "v8", "vs")), f"known answers {name}")
+
+
+@pytest.mark.parametrize("M,nh,kvh,rd,pos0", [(1, 24, 4, 64, 0), (5, 24, 4, 64, 1000), (33, 8, 2, 128, 17), (7, 6, 1, 0, 3), (4, 16, 2, 256, 60),
+                                              (3, 5, 3, 192, 9)])
+def test_attn_post_equals_the_oracle_bit_for_bit(oracle, M, nh, kvh, rd, pos0):
+    """Bit-exact in the portable-math mode; rows that are not appended keep their contents (the caches start filled with 7)."""
+    from tests.helpers import post_inputs
+    from yasakani_b200 import kvx
+    max_ctx = pos0 + M + 11
+    d = post_inputs(900 + M, M, nh, kvh, rd, max_ctx)
+    _same(_gpu_post(kvx, d, 1e-6, pos0, rd, max_ctx, fill=7), _oracle_post(oracle, d, 1e-6, pos0, rd, max_ctx, fill=7), f"M {M} nh {nh} kvh {kvh} rd {rd}")
+
+
+def test_attn_post_default_math_mode_is_within_one_bf16_step(oracle):
+    """pm = 0 takes rsqrtf like the reference's default (an approximation: no CPU restatement); against the portable-math
+    oracle the query rows may differ by one bf16 step and the INT8 payload by one count."""
+    from tests.helpers import post_inputs
+    from yasakani_b200 import kvx
+    M, nh, kvh, rd, pos0, max_ctx = 6, 24, 4, 64, 40, 64
+    d = post_inputs(77, M, nh, kvh, rd, max_ctx)
+    got = _gpu_post(kvx, d, 1e-6, pos0, rd, max_ctx, pm=False)
+    want = _oracle_post(oracle, d, 1e-6, pos0, rd, max_ctx)
+    qg = (got[0].astype(np.uint32) << 16).view(np.float32); qw = (want[0].astype(np.uint32) << 16).view(np.float32)
+    assert np.abs(qg - qw).max() <= 2.0 ** -7 * np.abs(qw).max()
+    assert (got[0] == want[0]).mean() > 0.9
+    assert np.abs(got[2].astype(np.int32) - want[2].astype(np.int32)).max() <= 1 and np.array_equal(got[4], want[4])
+
+
+def test_attn_post_outside_the_cache_stores_no_row_and_bad_arguments_are_rejected(oracle):
+    from tests.helpers import post_inputs
+    from yasakani_b200 import kvx, Kv4Error
+    M, nh, kvh, rd, max_ctx = 4, 4, 2, 64, 16
+    d = post_inputs(5, M, nh, kvh, rd, max_ctx + M)
+    d["rope"] = d["rope"][:max_ctx + M]
+    got = _gpu_post(kvx, d, 1e-6, max_ctx - 2, rd, max_ctx, fill=7)             # tokens 2 and 3 fall outside
+    want = _oracle_post(oracle, {**d, **{k_: d[k_][:2] for k_ in ("q_rows", "k_rows", "v_rows")}}, 1e-6, max_ctx - 2, rd, max_ctx, fill=7)
+    _same(got[2:], want[2:], "cache rows")
+    assert np.array_equal(got[0][:2], want[0])
+    with pytest.raises(Kv4Error, match="multiple of 64"):
+        _gpu_post(kvx, d, 1e-6, 0, 32, max_ctx)

@@ -262,3 +262,72 @@ def test_trellis_oracle_and_encoder_equal_the_reference_probes_bit_for_bit(oracl
     back = kvx.tb_decode(kvx.TrellisProfile(blob), pay3, side3, torch.from_numpy(grp).cuda(), torch.from_numpy(pos).cuda(), yin=torch.from_numpy(x).cuda())
     torch.cuda.synchronize()
     assert np.array_equal(back.cpu().numpy().view(np.uint32), ydec.view(np.uint32)), "library unpack differs from the reference's tba_unpack_kernel"
+
+
+@pytest.mark.parametrize("pm", [1, 0], ids=["portable-math", "default-math"])
+def test_attn_post_equals_the_reference_kernel_bit_for_bit(oracle, pm):
+    """The reference's q35_attn_post_kernel (src/q35_kernels.cu:1013-1065, compiled from its source) against this library's
+    yskn_kvx_attn_post and, in the portable-math mode, the CPU oracle.  The reference kernel starts from GEMV partial sums:
+    it is driven with one slice, tau = 1, signs = +1 and partial sums whose upper 256 entries per block are zero, which makes
+    the two halves of a block's 512 projection values equal.  The gate half, which the kernel stores untouched (gate16), is
+    then the witness of the values its query half normalises; key and value blocks get the partial sums of query heads
+    0 / 1, so their two heads see the same witnessed rows."""
+    from yasakani_b200 import kvx
+    path = os.path.join(os.path.dirname(REF), "libyskn_ref_q35.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref not built (reference tree was not mounted at build time)")
+    ref = C.CDLL(path)
+    nh, kvh, hd = C.c_int(), C.c_int(), C.c_int()
+    ref.yref_q35_shape(C.byref(nh), C.byref(kvh), C.byref(hd))
+    nh, kvh = nh.value, kvh.value
+    assert hd.value == 256 and kvh == 4
+    M, rd, max_ctx, pos0, eps = 5, 64, 96, 70, 1e-6
+    g = torch.Generator().manual_seed(4242)
+    part_q = torch.zeros((M, nh, 512))
+    part_q[:, :, :256] = torch.randn((M, nh, 256), generator=g) * torch.exp(torch.rand((1, nh, 1), generator=g) * 3.0 - 1.0) * 16.0
+    part_q[1, 2] = 0.0                                             # an all-zero head
+    part_k = part_q[:, :2].reshape(M, 1024).contiguous()           # key heads (0, 1) <- query head 0, (2, 3) <- query head 1
+    part_v = part_k.clone()
+    rng = np.random.default_rng(3)
+    from tests.helpers import bf16_bits
+    qn_w = bf16_bits(rng.standard_normal(256) * 0.2); kn_w = bf16_bits(rng.standard_normal(256) * 0.2 + 0.5)
+    rope_np = oracle.rope_table(max_ctx, 1e7, rd)
+    dev = "cuda"
+    bf = lambda bits: torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16).to(dev)
+    t = dict(part_q=part_q.reshape(M, nh * 512).to(dev), part_k=part_k.to(dev), part_v=part_v.to(dev), ones=torch.ones(nh * 512, device=dev),
+             signs=torch.ones(nh * 512, dtype=torch.int8, device=dev), qn_w=bf(qn_w), kn_w=bf(kn_w), rope=torch.from_numpy(rope_np).to(dev),
+             d_pos=torch.tensor([pos0], dtype=torch.int32, device=dev))
+
+    def caches():
+        return (torch.zeros((kvh, max_ctx, 256), dtype=torch.int8, device=dev), torch.zeros((kvh, max_ctx, 256), dtype=torch.int8, device=dev),
+                torch.zeros((kvh, max_ctx), device=dev), torch.zeros((kvh, max_ctx), device=dev))
+    P = lambda x: C.c_void_p(x.data_ptr())
+    rq16 = torch.empty((M, nh, 256), dtype=torch.bfloat16, device=dev); rgate = torch.empty_like(rq16)
+    rk8, rv8, rks, rvs = caches()
+    ref.yref_q35_attn_post.argtypes = [C.c_void_p] * 7 + [C.c_float, C.c_int] + [C.c_void_p] * 8 + [C.c_int, C.c_int, C.c_void_p]
+    rc = ref.yref_q35_attn_post(P(t["part_q"]), P(t["part_k"]), P(t["part_v"]), P(t["ones"]), P(t["signs"]), P(t["qn_w"]), P(t["kn_w"]), eps, M,
+                                P(t["d_pos"]), P(t["rope"]), P(rq16), P(rgate), P(rk8), P(rv8), P(rks), P(rvs), max_ctx, pm, None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    # the witnessed projection rows: query head h = [y_h | y_h]; key / value head j = y of query head j // 2
+    y = rgate                                                      # bf16 [M][nh][256]
+    assert float(y.float().abs().max()) > 0.5
+    q_rows = torch.cat([y, y], dim=2).contiguous()
+    kv_rows = y[:, [0, 0, 1, 1]].contiguous()
+    q16 = torch.empty_like(rq16); gate16 = torch.empty_like(rq16)
+    k8, v8, ks, vs = caches()
+    kvx.launch_attn_post(q_rows, kv_rows, kv_rows, t["qn_w"], t["kn_w"], eps, t["d_pos"], t["rope"], rd, q16, gate16, k8, ks, v8, vs, pm=bool(pm))
+    torch.cuda.synchronize()
+    i16 = lambda x: x.view(torch.int16)
+    assert torch.equal(i16(q16), i16(rq16)), f"q16 differs in {(i16(q16) != i16(rq16)).sum().item()} elements"
+    assert torch.equal(i16(gate16), i16(rgate))
+    assert torch.equal(k8, rk8) and torch.equal(v8, rv8)
+    assert torch.equal(ks.view(torch.int32), rks.view(torch.int32)) and torch.equal(vs.view(torch.int32), rvs.view(torch.int32))
+    assert int((rk8[:, pos0:pos0 + M] != 0).sum()) > 1000 and not rk8[:, :pos0].any()
+    if pm:
+        bits = lambda x: x.view(torch.int16).cpu().numpy().view(np.uint16)
+        ok8 = np.zeros((kvh, max_ctx, 256), np.int8); ov8 = np.zeros_like(ok8)
+        oks = np.zeros((kvh, max_ctx), np.float32); ovs = np.zeros_like(oks)
+        oq16, _ = oracle.kvx_attn_post(bits(q_rows), bits(kv_rows), bits(kv_rows), qn_w, kn_w, eps, pos0, rope_np, rd, max_ctx, ok8, oks, ov8, ovs)
+        assert np.array_equal(oq16, bits(rq16)) and np.array_equal(ok8, rk8.cpu().numpy()) and np.array_equal(ov8, rv8.cpu().numpy())
+        assert np.array_equal(oks.view(np.uint32), rks.cpu().numpy().view(np.uint32)) and np.array_equal(ovs.view(np.uint32), rvs.cpu().numpy().view(np.uint32))

@@ -44,6 +44,13 @@ class Kv8AttnArgsC(C.Structure):
                 ("pm", C.c_void_p), ("pl", C.c_void_p), ("pacc", C.c_void_p), ("kvh", C.c_int), ("nh", C.c_int), ("qscale", C.c_float)]
 
 
+class KvxAttnPostArgsC(C.Structure):  # yskn_kvx_attn_post_args
+    _fields_ = [("q_rows", C.c_void_p), ("k_rows", C.c_void_p), ("v_rows", C.c_void_p), ("qn_w", C.c_void_p), ("kn_w", C.c_void_p),
+                ("eps", C.c_float), ("M", C.c_int), ("d_pos", C.c_void_p), ("rope", C.c_void_p), ("rd", C.c_int),
+                ("q16", C.c_void_p), ("gate16", C.c_void_p), ("k8", C.c_void_p), ("v8", C.c_void_p), ("ks", C.c_void_p), ("vs", C.c_void_p),
+                ("max_ctx", C.c_int), ("nh", C.c_int), ("kvh", C.c_int), ("pm", C.c_int)]
+
+
 class AttnExtC(C.Structure):          # yskn_kv4_attn_ext
     _fields_ = [("early", C.c_int), ("splits_short", C.c_int), ("long_len", C.c_int), ("wk", C.c_void_p)]
 
@@ -98,6 +105,7 @@ PROTOTYPES = {
     "yskn_kvx_encode": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]),
     "yskn_kvx_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_void_p]),
     "yskn_kvx_probe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
+    "yskn_kvx_attn_post": (C.c_int, [C.POINTER(KvxAttnPostArgsC), C.c_void_p]),
     "yskn_tb_blob_info": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_int)]),
     "yskn_tb_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "yskn_tb_scratch_bytes": (C.c_size_t, [C.c_int, C.c_int]),

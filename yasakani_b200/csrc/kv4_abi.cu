@@ -330,6 +330,10 @@ int yskn_kvx_encode(const void* d_x, int x_dtype, int8_t* d_q8, float* d_scales,
 int yskn_kvx_decode(const int8_t* d_q8, const float* d_scales, void* d_y, int y_dtype, long long rows, void* cuda_stream) {
   return launch_kvx_decode(d_q8, d_scales, d_y, y_dtype, rows, (cudaStream_t)cuda_stream);
 }
+int yskn_kvx_attn_post(const yskn_kvx_attn_post_args* a, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_kvx_attn_post: null argument struct");
+  return launch_kvx_attn_post(*a, (cudaStream_t)cuda_stream);
+}
 
 int yskn_tb_blob_info(const uint8_t* h_blob, size_t blob_len, int* nm) { return tb_blob_info(h_blob, blob_len, nm); }
 size_t yskn_tb_scratch_bytes(int rows, int nm) { return tb_scratch_bytes(rows, nm); }

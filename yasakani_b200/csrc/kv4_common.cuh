@@ -96,6 +96,7 @@ void set_peer_wait_polls(unsigned polls);
 int launch_kvx_rotate(const float* x, float* y, long long rows, int inverse, cudaStream_t st);
 int launch_kvx_encode(const void* x, int x_dtype, int8_t* q8, float* scales, long long rows, cudaStream_t st);
 int launch_kvx_decode(const int8_t* q8, const float* scales, void* y, int y_dtype, long long rows, cudaStream_t st);
+int launch_kvx_attn_post(const yskn_kvx_attn_post_args& a, cudaStream_t st);
 
 // Family-B row codec, step 2: trellis re-quantisation and payload (kvq_trellis.cu)
 size_t tb_scratch_bytes(int rows, int nm);

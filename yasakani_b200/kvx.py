@@ -45,6 +45,24 @@ def decode(q8: torch.Tensor, scales: torch.Tensor, dtype=torch.float32, out: tor
     return out
 
 
+def launch_attn_post(q_rows, k_rows, v_rows, qn_w, kn_w, eps: float, d_pos, rope, rd: int, q16, gate16, k8, ks, v8, vs,
+                     pm: bool = True, stream=None) -> None:
+    """launch_q35_attn_post (src/q35_kernels.cu:1013-1069) from the bf16 projection rows on: RMS norm, partial RoPE and
+    rotation of the query and key heads, INT8 rows of keys and values appended at *d_pos + token, gate copied.
+    q_rows bf16 [M, nh, 512]; k_rows / v_rows bf16 [M, kvh, 256]; k8 / v8 int8 [kvh, max_ctx, 256]; ks / vs fp32 [kvh, max_ctx]."""
+    M, nh = q_rows.shape[0], q_rows.shape[1]
+    kvh, max_ctx = k8.shape[0], k8.shape[1]
+    for t in (q_rows, k_rows, v_rows, qn_w, kn_w, q16, gate16):
+        if t.dtype != torch.bfloat16:
+            raise TypeError("yskn_kvx_attn_post takes bf16 rows and norm weights")
+    if tuple(q_rows.shape) != (M, nh, 512) or tuple(k_rows.shape) != (M, kvh, 256) or tuple(v_rows.shape) != (M, kvh, 256):
+        raise ValueError("q_rows [M, nh, 512], k_rows / v_rows [M, kvh, 256]")
+    a = _lib.KvxAttnPostArgsC(_ptr(q_rows), _ptr(k_rows), _ptr(v_rows), _ptr(qn_w), _ptr(kn_w), eps, M, _ptr(d_pos),
+                              _ptr(rope) if rope is not None else None, rd, _ptr(q16), _ptr(gate16), _ptr(k8), _ptr(v8), _ptr(ks), _ptr(vs),
+                              max_ctx, nh, kvh, 1 if pm else 0)
+    check(_lib.load().yskn_kvx_attn_post(C.byref(a), _stream(stream)), "yskn_kvx_attn_post")
+
+
 def probe(x: np.ndarray):
     """The reference's yskn_kvx_probe contract over host arrays: (q, scales, y)."""
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, 256)
