@@ -688,6 +688,30 @@ def run_secondary(args):
                         roofline={"bound": "tensor", "achieved": flops / t / 1e12, "peak": tf, "unit": "TFLOP/s", "frac": flops / t / 1e12 / tf, "traffic": None,
                                   "kernel": "tcgen05 attention with in-kernel INT8 conversion + merge", "peak_kind": f"of {kind}"})
             print(json.dumps(line), flush=True)
+        # decode straight over packed trellis rows (synthetic profile; groups of 4-bit trellis records): a first path on CUDA cores
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "tests", "golden"))
+        from make_kvqp_blob import make_blob
+        prof = kvx.TrellisProfile(make_blob())
+        ctx, S = 32768, 37
+        grp = torch.tensor([1, 5, 10, 14], dtype=torch.int32, device="cuda")      # 4-bit trellis records without a guard
+        rows_grp = grp.repeat_interleave(ctx); rows_pos = torch.arange(ctx, dtype=torch.int32, device="cuda").repeat(kvh)
+        packs = []
+        for _ in range(2):
+            _, pk, sk_ = kvx.tb_encode(prof, torch.randn((kvh * ctx, 256), device="cuda", generator=g), rows_grp, rows_pos)
+            _, pv, sv_ = kvx.tb_encode(prof, torch.randn((kvh * ctx, 256), device="cuda", generator=g), rows_grp, rows_pos)
+            packs.append((pk.view(kvh, ctx, -1), sk_.view(kvh, ctx, 2), pv.view(kvh, ctx, -1), sv_.view(kvh, ctx, 2)))
+        q = torch.randn((1, nh, 256), device="cuda", generator=g).to(torch.bfloat16)
+        d_pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda")
+        pm = torch.empty((1, S, nh), device="cuda"); pl = torch.empty_like(pm); pacc = torch.empty((1, S, nh, 256), device="cuda")
+        t = _timed(lambda i: kvx.launch_tb_attention(prof, q, *packs[i & 1], grp, grp, 1, d_pos, S, pm, pl, pacc, nh), K, W)
+        byt = kvh * ctx * 2 * (128 + 8)                                # 4-bit payload (128 B of the 160-B row slot) + side words, K and V
+        line = dict(base, metric="tb_decode_attn_tokens_per_s", value=1.0 / t, unit="tokens/s", ms_per_step=t * 1e3, dtype="f32",
+                    config={"workload": f"Family-B decode over packed trellis rows (4 bits): 1 query token, Hq{nh}/Hkv{kvh}/hd256, {ctx} cached tokens",
+                            "splits": S, "l2": f"2 cache copies cycled; {byt / 1e6:.1f} MB read per launch: L2-resident, the kernel is instruction-bound"},
+                    gpu_launches=K,
+                    roofline={"bound": "hbm", "achieved": byt / t / 1e9, "peak": hbm, "unit": "GB/s", "frac": byt / t / 1e9 / hbm, "traffic": None,
+                              "kernel": "tb_attn_kernel", "bytes_per_launch": byt, "peak_kind": f"of {kind}"})
+        print(json.dumps(line), flush=True)
     elif args.workload == "kvx":
         rows = 1 << 20
         x = torch.randn((rows, 256), device="cuda", generator=g)

@@ -342,6 +342,28 @@ YSKN_KV4_API size_t yskn_tb_scratch_bytes(int rows, int nm);
 YSKN_KV4_API int yskn_tb_encode(const uint8_t* d_blob, int nm, const float* d_x, const int* d_grp, const int* d_pos, int rows, float* d_y,
                                 uint8_t* d_pay, int pay_stride, uint32_t* d_side, void* d_scratch, size_t scratch_bytes, void* cuda_stream);
 
+/* Decode attention straight over packed trellis rows: the counterpart of the reference's attention over packed rows
+ * (launch_q35_atxpk, src/q35_atxpk.hpp:14-24, src/q35_atxpk3.cuh / q35_atxpk4.cuh) for passes of a few rows.  Every key and
+ * value row is unpacked inside the kernel by the rule of yskn_tb_decode (tba_unpack_kernel, src/kvq_attn.cuh:39-72; bit for
+ * bit the same values) and consumed at once, so the result equals attention over the unpacked rows; nothing unpacked is
+ * written to memory.  k_pay / v_pay [kvh][max_ctx][pay_stride] bytes and k_side / v_side [kvh][max_ctx][2] words as
+ * yskn_tb_encode writes them with pos = the token's position; grp_k / grp_v [kvh] (device) name the profile's group record
+ * of each head's rows; rows the profile leaves unpacked (position below the group's guard, or a group that is not a
+ * packed one) are read from k_plain / v_plain fp32 [kvh][max_ctx][256] (NULL: zeros), the `yin` of yskn_tb_decode.
+ * q16 [M][nh][256] bf16 or fp16; row r sits at *d_pos + r and sees keys 0 .. *d_pos + r; partials in the layout of
+ * yskn_kv8_attention (merge with yskn_kv8_combine).  A CUDA-core kernel: a first path, not a tuned one. */
+typedef struct {
+  const uint16_t* q16; const uint8_t* blob;
+  const uint8_t* k_pay; const uint8_t* v_pay; int pay_stride;
+  const uint32_t* k_side; const uint32_t* v_side;
+  const int* grp_k; const int* grp_v;
+  const float* k_plain; const float* v_plain;
+  int max_ctx; int M; const int* d_pos; int splits;
+  float* pm; float* pl; float* pacc;
+  int kvh; int nh; float qscale;
+} yskn_tb_attn_args;
+YSKN_KV4_API int yskn_tb_attention(const yskn_tb_attn_args* a, int act_dtype, void* cuda_stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * Family-B decode attention over the INT8 rows above: the INT8 members of the reference's Q35AttnArgs
  * (src/q35.hpp:126-130), with the head counts the reference fixes at compile time (Q35_NH, Q35_KVH) as fields.

@@ -104,6 +104,8 @@ void ysko_kvx_decode(const int8_t* q8, const float* scales, float* y, long rows)
 void ysko_kvx_attn_post(const uint16_t* q_rows, const uint16_t* k_rows, const uint16_t* v_rows, const uint16_t* qn_w, const uint16_t* kn_w,
                         float eps, int M, int pos0, const float* rope, int rd, int nh, int kvh, int max_ctx,
                         uint16_t* q16, uint16_t* gate16, int8_t* k8, float* ks, int8_t* v8, float* vs);
+void ysko_rows_attention_exact(const float* q, const float* k, const float* v, int max_ctx, int M, int pos0, int kvh, int nh,
+                               float qscale, float* out);
 void ysko_kv8_attention_exact(const float* q, const int8_t* k8, const int8_t* v8, const float* ks, const float* vs, int max_ctx,
                               int M, int pos0, int kvh, int nh, float qscale, float* out);
 #ifdef __cplusplus

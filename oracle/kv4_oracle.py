@@ -250,3 +250,13 @@ def kv8_attention_exact(q: np.ndarray, k8: np.ndarray, v8: np.ndarray, ks: np.nd
     lib().ysko_kv8_attention_exact(_p(q), _p(k8), _p(v8), _p(ks), _p(vs), C.c_int(max_ctx), C.c_int(M), C.c_int(pos0), C.c_int(kvh),
                                    C.c_int(nh), C.c_float(qscale), _p(out))
     return out
+
+
+def rows_attention_exact(q: np.ndarray, k: np.ndarray, v: np.ndarray, pos0: int, qscale: float = 0.0625) -> np.ndarray:
+    """q [M, nh, 256] fp32, k / v [kvh, max_ctx, 256] fp32 rows -> [M, nh, 256] (ysko_rows_attention_exact)."""
+    q = np.ascontiguousarray(q, dtype=np.float32); k = np.ascontiguousarray(k, dtype=np.float32); v = np.ascontiguousarray(v, dtype=np.float32)
+    M, nh = q.shape[0], q.shape[1]; kvh, max_ctx = k.shape[0], k.shape[1]
+    assert q.shape == (M, nh, 256) and k.shape == (kvh, max_ctx, 256) and v.shape == k.shape and pos0 + M <= max_ctx
+    out = np.empty((M, nh, 256), dtype=np.float32)
+    lib().ysko_rows_attention_exact(_p(q), _p(k), _p(v), int(max_ctx), int(M), int(pos0), int(kvh), int(nh), C.c_float(qscale), _p(out))
+    return out

@@ -166,3 +166,31 @@ void ysko_kvx_attn_post(const uint16_t* q_rows, const uint16_t* k_rows, const ui
     }
   }
 }
+
+/* Exact attention over fp32 rows: what the attention over packed trellis rows must equal once every row is unpacked
+ * (ysko_tb_unpack).  Same row semantics as q35_attention_kernel (src/q35_kernels.cu:1176-1281): row r at pos0 + r sees keys
+ * 0 .. pos0 + r; s_t = sum_c (q_c * qscale) * k_tc; softmax; O = sum_t p_t * v_t.  q [M][nh][256], k / v [kvh][max_ctx][256];
+ * out [M][nh][256].  Double accumulation: the oracle for tolerance parity, not a restatement of a summation order. */
+void ysko_rows_attention_exact(const float* q, const float* k, const float* v, int max_ctx, int M, int pos0, int kvh, int nh,
+                               float qscale, float* out) {
+  const int G = nh / kvh;
+  #pragma omp parallel for collapse(2) schedule(dynamic)
+  for (int r = 0; r < M; ++r)
+    for (int h = 0; h < nh; ++h) {
+      const int kv = h / G, len = pos0 + r + 1;
+      const float* qr = q + ((size_t)r * nh + h) * 256;
+      double mx = -1e300, l = 0.0, o[256];
+      for (int d = 0; d < 256; ++d) o[d] = 0.0;
+      for (int t = 0; t < len; ++t) {
+        const float* kr = k + ((size_t)kv * max_ctx + t) * 256;
+        double s = 0.0;
+        for (int d = 0; d < 256; ++d) s += (double)(qr[d] * qscale) * (double)kr[d];
+        if (s > mx) { const double a = exp(mx - s); l *= a; for (int d = 0; d < 256; ++d) o[d] *= a; mx = s; }
+        const double p = exp(s - mx);
+        l += p;
+        const float* vr = v + ((size_t)kv * max_ctx + t) * 256;
+        for (int d = 0; d < 256; ++d) o[d] += p * (double)vr[d];
+      }
+      for (int d = 0; d < 256; ++d) out[((size_t)r * nh + h) * 256 + d] = (float)(o[d] / l);
+    }
+}

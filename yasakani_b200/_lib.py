@@ -51,6 +51,13 @@ class KvxAttnPostArgsC(C.Structure):  # yskn_kvx_attn_post_args
                 ("max_ctx", C.c_int), ("nh", C.c_int), ("kvh", C.c_int), ("pm", C.c_int)]
 
 
+class TbAttnArgsC(C.Structure):       # yskn_tb_attn_args
+    _fields_ = [("q16", C.c_void_p), ("blob", C.c_void_p), ("k_pay", C.c_void_p), ("v_pay", C.c_void_p), ("pay_stride", C.c_int),
+                ("k_side", C.c_void_p), ("v_side", C.c_void_p), ("grp_k", C.c_void_p), ("grp_v", C.c_void_p),
+                ("k_plain", C.c_void_p), ("v_plain", C.c_void_p), ("max_ctx", C.c_int), ("M", C.c_int), ("d_pos", C.c_void_p), ("splits", C.c_int),
+                ("pm", C.c_void_p), ("pl", C.c_void_p), ("pacc", C.c_void_p), ("kvh", C.c_int), ("nh", C.c_int), ("qscale", C.c_float)]
+
+
 class AttnExtC(C.Structure):          # yskn_kv4_attn_ext
     _fields_ = [("early", C.c_int), ("splits_short", C.c_int), ("long_len", C.c_int), ("wk", C.c_void_p)]
 
@@ -106,6 +113,7 @@ PROTOTYPES = {
     "yskn_kvx_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_void_p]),
     "yskn_kvx_probe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
     "yskn_kvx_attn_post": (C.c_int, [C.POINTER(KvxAttnPostArgsC), C.c_void_p]),
+    "yskn_tb_attention": (C.c_int, [C.POINTER(TbAttnArgsC), C.c_int, C.c_void_p]),
     "yskn_tb_blob_info": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_int)]),
     "yskn_tb_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "yskn_tb_scratch_bytes": (C.c_size_t, [C.c_int, C.c_int]),

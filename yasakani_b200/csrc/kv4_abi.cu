@@ -330,6 +330,10 @@ int yskn_kvx_encode(const void* d_x, int x_dtype, int8_t* d_q8, float* d_scales,
 int yskn_kvx_decode(const int8_t* d_q8, const float* d_scales, void* d_y, int y_dtype, long long rows, void* cuda_stream) {
   return launch_kvx_decode(d_q8, d_scales, d_y, y_dtype, rows, (cudaStream_t)cuda_stream);
 }
+int yskn_tb_attention(const yskn_tb_attn_args* a, int act_dtype, void* cuda_stream) {
+  if (!a) KV4_REJECT("yskn_tb_attention: null argument struct");
+  return launch_tb_attention(*a, act_dtype, (cudaStream_t)cuda_stream);
+}
 int yskn_kvx_attn_post(const yskn_kvx_attn_post_args* a, void* cuda_stream) {
   if (!a) KV4_REJECT("yskn_kvx_attn_post: null argument struct");
   return launch_kvx_attn_post(*a, (cudaStream_t)cuda_stream);

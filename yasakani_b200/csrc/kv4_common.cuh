@@ -101,6 +101,7 @@ int launch_kvx_attn_post(const yskn_kvx_attn_post_args& a, cudaStream_t st);
 // Family-B row codec, step 2: trellis re-quantisation and payload (kvq_trellis.cu)
 size_t tb_scratch_bytes(int rows, int nm);
 int tb_blob_info(const uint8_t* h_blob, size_t n, int* nm);
+int launch_tb_attention(const yskn_tb_attn_args& a, int act_dtype, cudaStream_t st);
 int launch_tb_encode(const uint8_t* blob, int nm, const float* x, const int* grp, const int* pos, int rows, float* y, uint8_t* pay, int pay_stride,
                      uint32_t* side, void* scratch, size_t scratch_bytes, cudaStream_t st);
 

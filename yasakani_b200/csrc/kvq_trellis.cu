@@ -303,6 +303,149 @@ __global__ void __launch_bounds__(256) tb_unpack_kernel(TbDecP A) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Decode attention straight over packed rows: every key and value row is unpacked inside the kernel by tb_unpack_kernel's
+// rule (bit for bit the same values) and consumed at once; nothing unpacked is written to memory.  The counterpart of the
+// reference's attention over packed rows (launch_q35_atxpk, src/q35_atxpk3.cuh / q35_atxpk4.cuh) for passes of a few rows,
+// on CUDA cores.  Row r at *d_pos + r sees keys 0 .. *d_pos + r; grid (splits, kvh, M); a warp takes every eighth key of the
+// split: unpack K (lane owns d = 32w + lane), G dot products by shuffle trees, online softmax in the exp2 domain with a lazy
+// rescale, unpack V, accumulate.  Partials in the layout of yskn_kv8_attention.
+constexpr int TBA_WARPS = 8;
+struct TbAttnP { yskn_tb_attn_args a; int G; };
+struct TbTab { float cg[256], mu[256], u0[256], u1[256]; };          // one group's code table (x gain / 256) and row terms
+
+// per-group constants of the unpack rule
+struct TbRule { int packed_ok, mode, kb, guard, m, has_mu; };
+__device__ __forceinline__ TbRule tb_stage_group(const uint8_t* b, int g, TbTab& T) {   // all threads of the CTA
+  const TbGroup P = tb_group(b, g);
+  TbRule R{P.ok && P.mode <= 1, P.mode, P.mode == 1 ? 4 : P.kk, P.guard, P.m, P.has_mu};
+  const unsigned to = tb_u32(b + P.off_t + 4u * (unsigned)P.tix);
+  const float gain = P.mode == 0 ? tb_f32(b + to + 4) : 1.f;
+  const uint8_t* mup = b + P.go + 8;
+  const uint8_t* Up = mup + (P.has_mu ? 512 : 0);
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    T.cg[i] = !R.packed_ok ? 0.f : (P.mode == 1 ? (float)(i - 8) : __fmul_rn(__fmul_rn((float)(int)(short)tb_u16(b + to + 12 + 2 * i), 0.00390625f), gain));
+    T.mu[i] = R.packed_ok && P.has_mu ? __half2float(__ushort_as_half((unsigned short)tb_u16(mup + 2 * i))) : 0.f;
+    T.u0[i] = R.packed_ok && P.m > 0 ? __half2float(__ushort_as_half((unsigned short)tb_u16(Up + 2 * i))) : 0.f;
+    T.u1[i] = R.packed_ok && P.m > 1 ? __half2float(__ushort_as_half((unsigned short)tb_u16(Up + 2 * (256 + i)))) : 0.f;
+  }
+  return R;
+}
+// one row by one warp: x[w] = value d = 32w + lane
+__device__ __forceinline__ void tb_row(const TbRule& R, const TbTab& T, int pos, const uint8_t* pay, const uint32_t* side, const float* plain,
+                                       unsigned* s_w, int lane, float (&x)[8]) {
+  if (!(R.packed_ok && pos >= R.guard)) {                            // a row the profile leaves unpacked
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) x[w] = plain ? __ldg(plain + 32 * w + lane) : 0.f;
+    return;
+  }
+  const int nw = 8 * R.kb;
+  const unsigned* wp = reinterpret_cast<const unsigned*>(pay);
+  __syncwarp();
+  for (int i = lane; i < 44; i += 32) s_w[i] = i < nw ? __ldg(wp + i) : 0u;
+  const float s = __uint_as_float(__ldg(side));
+  const unsigned pc = __ldg(side + 1);
+  const float c0 = __half2float(__ushort_as_half((unsigned short)(pc & 0xffffu))), c1 = __half2float(__ushort_as_half((unsigned short)(pc >> 16)));
+  __syncwarp();
+  #pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    const int d = 32 * w + lane, endb = R.kb * (d + 1), first = R.kb * (d & ~63);
+    const int lo = R.mode == 1 ? endb - 4 : max(endb - 8, first), len = endb - lo;
+    const unsigned hiw = s_w[lo >> 5], low = s_w[(lo >> 5) + 1];
+    const unsigned v = __funnelshift_l(low, hiw, lo & 31) >> (32 - len);
+    float xv = __fmul_rn(T.cg[v], s);
+    if (R.m > 0) xv = __fadd_rn(xv, __fmul_rn(c0, T.u0[d]));
+    if (R.m > 1) xv = __fadd_rn(xv, __fmul_rn(c1, T.u1[d]));
+    if (R.has_mu) xv = __fadd_rn(xv, T.mu[d]);
+    x[w] = xv;
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(TBA_WARPS * 32) tb_attn_kernel(TbAttnP P) {
+  extern __shared__ __align__(16) unsigned char tba_smem[];
+  const yskn_tb_attn_args& A = P.a;
+  const int G = P.G, split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  TbTab* tk = reinterpret_cast<TbTab*>(tba_smem); TbTab* tv = tk + 1;
+  unsigned* s_w = reinterpret_cast<unsigned*>(tv + 1) + 44 * warp;
+  float* mbuf = reinterpret_cast<float*>(reinterpret_cast<unsigned*>(tv + 1) + 44 * TBA_WARPS);    // [warp][8][258]
+  const TbRule rk = tb_stage_group(A.blob, __ldg(A.grp_k + kvh), *tk), rv = tb_stage_group(A.blob, __ldg(A.grp_v + kvh), *tv);
+  __syncthreads();
+  const int pos = __ldg(A.d_pos) + r, len = max(0, min(pos + 1, A.max_ctx));
+  const int per = (len + (int)gridDim.x - 1) / (int)gridDim.x, t0 = min(len, split * per), t1 = min(len, t0 + per);
+  const float qs = A.qscale * 1.4426950408889634f;
+  float q[8][8], acc[8][8], m[8], l[8];
+  #pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    m[g] = -1e30f; l[g] = 0.f;
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      acc[g][w] = 0.f;
+      q[g][w] = g < G ? act_load<DT>(A.q16, ((size_t)r * A.nh + kvh * G + g) * 256 + 32 * w + lane) * qs : 0.f;
+    }
+  }
+  const size_t row0 = (size_t)kvh * A.max_ctx;
+  for (int t = t0 + warp; t < t1; t += TBA_WARPS) {
+    float x[8];
+    tb_row(rk, *tk, t, A.k_pay + (row0 + t) * A.pay_stride, A.k_side + 2 * (row0 + t), A.k_plain ? A.k_plain + (row0 + t) * 256 : nullptr, s_w, lane, x);
+    float sc[8];
+    #pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float d = 0.f;
+      if (g < G) {
+        #pragma unroll
+        for (int w = 0; w < 8; ++w) d = fmaf(q[g][w], x[w], d);
+        #pragma unroll
+        for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      }
+      sc[g] = d;
+    }
+    tb_row(rv, *tv, t, A.v_pay + (row0 + t) * A.pay_stride, A.v_side + 2 * (row0 + t), A.v_plain ? A.v_plain + (row0 + t) * 256 : nullptr, s_w, lane, x);
+    #pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      if (g >= G) continue;
+      if (sc[g] > m[g]) {                                            // warp-uniform: the score is the same in every lane
+        const float a = exp2f(m[g] - sc[g]);
+        l[g] *= a;
+        #pragma unroll
+        for (int w = 0; w < 8; ++w) acc[g][w] *= a;
+        m[g] = sc[g];
+      }
+      const float p = exp2f(sc[g] - m[g]);
+      l[g] += p;
+      #pragma unroll
+      for (int w = 0; w < 8; ++w) acc[g][w] = fmaf(p, x[w], acc[g][w]);
+    }
+  }
+  // ---- merge the warps and store the split's partial (natural-log m, as the merge kernel expects)
+  #pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    if (g >= G) continue;
+    float* wb = mbuf + ((size_t)warp * 8 + g) * 258;
+    if (lane == 0) { wb[0] = m[g]; wb[1] = l[g]; }
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) wb[2 + 32 * w + lane] = acc[g][w];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < G * 256; e += TBA_WARPS * 32) {
+    const int g = e >> 8, d = e & 255;
+    float M2 = -1e30f;
+    #pragma unroll
+    for (int w = 0; w < TBA_WARPS; ++w) M2 = fmaxf(M2, mbuf[((size_t)w * 8 + g) * 258]);
+    float L2 = 0.f, o = 0.f;
+    #pragma unroll
+    for (int w = 0; w < TBA_WARPS; ++w) {
+      const float* wb = mbuf + ((size_t)w * 8 + g) * 258;
+      const float f = wb[0] > -1e29f ? exp2f(wb[0] - M2) : 0.f;
+      L2 += f * wb[1]; o += f * wb[2 + d];
+    }
+    const size_t pidx = ((size_t)r * A.splits + split) * A.nh + kvh * G + g;
+    if (d == 0) { A.pm[pidx] = M2 > -1e29f ? M2 * 0.6931471805599453f : -1e30f; A.pl[pidx] = L2; }
+    A.pacc[pidx * 256 + d] = o;
+  }
+}
+
 }  // namespace
 
 int launch_tb_decode(const uint8_t* blob, const int* grp, const int* pos, const uint8_t* pay, int pay_stride, const uint32_t* side, const float* yin,
@@ -356,6 +499,27 @@ int launch_tb_encode(const uint8_t* blob, int nm, const float* x, const int* grp
   if (int rc = launch_status("tb_search_kernel")) return rc;
   tb_select_kernel<<<rows, 256, 0, st>>>(A);
   return launch_status("tb_select_kernel");
+}
+
+int launch_tb_attention(const yskn_tb_attn_args& a, int act_dtype, cudaStream_t st) {
+  if (!a.q16 || !a.blob || !a.k_pay || !a.v_pay || !a.k_side || !a.v_side || !a.grp_k || !a.grp_v || !a.d_pos || !a.pm || !a.pl || !a.pacc)
+    KV4_REJECT("yskn_tb_attention: null buffer");
+  if (a.kvh <= 0 || a.nh <= 0 || a.nh % a.kvh || a.nh / a.kvh > 8 || a.M <= 0 || a.M > 65535 || a.kvh > 65535 || a.splits <= 0 || a.max_ctx <= 0)
+    KV4_REJECT("yskn_tb_attention: bad shape (kvh %d, nh %d, M %d, splits %d, max_ctx %d): at most 8 query heads per kv-head", a.kvh, a.nh, a.M, a.splits, a.max_ctx);
+  if (a.pay_stride < 160 || a.pay_stride % 4 || (((uintptr_t)a.k_pay | (uintptr_t)a.v_pay) & 3)) KV4_REJECT("yskn_tb_attention: bad payload stride %d or alignment", a.pay_stride);
+  const size_t smem = 2 * sizeof(TbTab) + 44 * TBA_WARPS * 4 + (size_t)TBA_WARPS * 8 * 258 * 4;
+  TbAttnP P{a, a.nh / a.kvh};
+  const dim3 grid(a.splits, a.kvh, a.M);
+  if (act_dtype == YSKN_KV4_BF16) {
+    static std::atomic<unsigned long long> attr{0};
+    if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(tb_attn_kernel<YSKN_KV4_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tb_attn_kernel<YSKN_KV4_BF16><<<grid, TBA_WARPS * 32, smem, st>>>(P);
+  } else if (act_dtype == YSKN_KV4_F16) {
+    static std::atomic<unsigned long long> attr{0};
+    if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(tb_attn_kernel<YSKN_KV4_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tb_attn_kernel<YSKN_KV4_F16><<<grid, TBA_WARPS * 32, smem, st>>>(P);
+  } else KV4_REJECT("yskn_tb_attention: q16 is bf16 or fp16 (act_dtype %d)", act_dtype);
+  return launch_status("tb_attn_kernel");
 }
 
 }  // namespace kv4

@@ -144,3 +144,15 @@ def tb_decode(profile: TrellisProfile, pay: torch.Tensor, side: torch.Tensor, gr
     check(_lib.load().yskn_tb_decode(_ptr(profile.dev), _ptr(grp), _ptr(pos), _ptr(pay), pay.shape[1], _ptr(side),
                                     _ptr(yin) if yin is not None else None, _ptr(y), rows, _stream(stream)), "yskn_tb_decode")
     return y
+
+
+def launch_tb_attention(profile: TrellisProfile, q16, k_pay, k_side, v_pay, v_side, grp_k, grp_v, M: int, d_pos, splits: int, pm, pl, pacc, nh: int,
+                        k_plain=None, v_plain=None, qscale: float = 0.0625, stream=None) -> None:
+    """Decode attention straight over packed trellis rows (the reference's launch_q35_atxpk for a few rows): k_pay / v_pay uint8
+    [kvh, max_ctx, stride], k_side / v_side int32-bits [kvh, max_ctx, 2], grp_k / grp_v int32 [kvh]; rows the profile leaves
+    unpacked come from k_plain / v_plain fp32 [kvh, max_ctx, 256].  Partials as launch_kv8_attention."""
+    kvh, max_ctx, stride = k_pay.shape
+    a = _lib.TbAttnArgsC(_ptr(q16), _ptr(profile.dev), _ptr(k_pay), _ptr(v_pay), stride, _ptr(k_side), _ptr(v_side), _ptr(grp_k), _ptr(grp_v),
+                         _ptr(k_plain) if k_plain is not None else None, _ptr(v_plain) if v_plain is not None else None,
+                         max_ctx, M, _ptr(d_pos), splits, _ptr(pm), _ptr(pl), _ptr(pacc), kvh, nh, qscale)
+    check(_lib.load().yskn_tb_attention(C.byref(a), _dtype_code(q16), _stream(stream)), "yskn_tb_attention")
