@@ -306,11 +306,10 @@ __global__ void __launch_bounds__(256) tb_unpack_kernel(TbDecP A) {
 
 // ---------------------------------------------------------------------------------------------------------------------
 // Decode attention straight over packed rows: every key and value row is unpacked inside the kernel by tb_unpack_kernel's
-// rule (bit for bit the same values) and consumed at once; nothing unpacked is written to memory.  The counterpart of the
-// reference's attention over packed rows (launch_q35_atxpk, src/q35_atxpk3.cuh / q35_atxpk4.cuh) for passes of a few rows,
-// on CUDA cores.  Row r at *d_pos + r sees keys 0 .. *d_pos + r; grid (splits, kvh, M); a warp takes every eighth key of the
-// split: unpack K (lane owns d = 32w + lane), G dot products by shuffle trees, online softmax in the exp2 domain with a lazy
-// rescale, unpack V, accumulate.  Partials in the layout of yskn_kv8_attention.
+// rule and consumed at once; nothing unpacked is written to memory.  The counterpart of the reference's attention over packed
+// rows (launch_q35_atxpk, src/q35_atxpk3.cuh / q35_atxpk4.cuh) for passes of a few rows, on CUDA cores.  Row r at *d_pos + r
+// sees keys 0 .. *d_pos + r; grid (splits, kvh, M); a warp takes every eighth run of 32 keys of the split.  Online softmax in
+// the exp2 domain, one rescale per 32 keys.  Partials in the layout of yskn_kv8_attention.
 constexpr int TBA_WARPS = 8;
 struct TbAttnP { yskn_tb_attn_args a; int G; };
 struct TbTab { float cg[256], mu[256], u0[256], u1[256]; };          // one group's code table (x gain / 256) and row terms
@@ -332,100 +331,192 @@ __device__ __forceinline__ TbRule tb_stage_group(const uint8_t* b, int g, TbTab&
   }
   return R;
 }
-// one row by one warp: x[w] = value d = 32w + lane
-__device__ __forceinline__ void tb_row(const TbRule& R, const TbTab& T, int pos, const uint8_t* pay, const uint32_t* side, const float* plain,
-                                       unsigned* s_w, int lane, float (&x)[8]) {
-  if (!(R.packed_ok && pos >= R.guard)) {                            // a row the profile leaves unpacked
+// ---- 32 keys per warp step.  Scores: a lane takes one key and walks its 256 fields (the window offsets
+// are then the same in every lane and known at compile time per code width); the row terms of the unpack rule leave the inner
+// loop: q.x = s * sum_d q_d cg[v_d] + c0 (q.U0) + c1 (q.U1) + q.mu, with the three dot products formed once per CTA.  Values: a
+// lane takes eight channels of every key, O = sum_t p_t s_t cg[v_td] + (sum p_t c0_t) U0 + (sum p_t c1_t) U1 + (sum p_t) mu.
+// The unpacked values themselves are those of tb_unpack_kernel; only the order of the fp32 sums differs (tolerance parity).
+constexpr int TBA_PW = 41;                                           // staged payload row: 40 words + 1 (conflict-free lane stride)
+struct TbWarpSm { unsigned kp[2][32 * TBA_PW]; unsigned vp[2][32 * TBA_PW]; float pw[32][8]; int vplain[32]; };   // two staging buffers: the next 32 keys arrive while these are used
+__device__ __forceinline__ void tb_cp4(unsigned* dst, const unsigned* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int KB, bool FLAT>
+__device__ __forceinline__ void tb_scores32(const unsigned* row, const float* cg, const float (*q)[8], float (&dot)[8]) {
+  #pragma unroll 1
+  for (int c = 0; c < 4; ++c) {                                      // chains of 64 fields: same bit offsets, 2*KB words further
+    const unsigned* wr = row + 2 * KB * c;
     #pragma unroll
-    for (int w = 0; w < 8; ++w) x[w] = plain ? __ldg(plain + 32 * w + lane) : 0.f;
-    return;
+    for (int i = 0; i < 64; ++i) {
+      constexpr int dummy = 0; (void)dummy;
+      const int endb = KB * (i + 1), lo = FLAT ? endb - 4 : (endb - 8 > 0 ? endb - 8 : 0), len = endb - lo;
+      const unsigned v = __funnelshift_l(wr[(lo >> 5) + 1], wr[lo >> 5], lo & 31) >> (32 - len);
+      const float cv = cg[v];
+      const float4 qa = *reinterpret_cast<const float4*>(&q[64 * c + i][0]), qb = *reinterpret_cast<const float4*>(&q[64 * c + i][4]);
+      dot[0] = fmaf(cv, qa.x, dot[0]); dot[1] = fmaf(cv, qa.y, dot[1]); dot[2] = fmaf(cv, qa.z, dot[2]); dot[3] = fmaf(cv, qa.w, dot[3]);
+      dot[4] = fmaf(cv, qb.x, dot[4]); dot[5] = fmaf(cv, qb.y, dot[5]); dot[6] = fmaf(cv, qb.z, dot[6]); dot[7] = fmaf(cv, qb.w, dot[7]);
+    }
   }
-  const int nw = 8 * R.kb;
-  const unsigned* wp = reinterpret_cast<const unsigned*>(pay);
-  __syncwarp();
-  for (int i = lane; i < 44; i += 32) s_w[i] = i < nw ? __ldg(wp + i) : 0u;
-  const float s = __uint_as_float(__ldg(side));
-  const unsigned pc = __ldg(side + 1);
-  const float c0 = __half2float(__ushort_as_half((unsigned short)(pc & 0xffffu))), c1 = __half2float(__ushort_as_half((unsigned short)(pc >> 16)));
-  __syncwarp();
+}
+
+template <int KB, bool FLAT>
+__device__ __forceinline__ void tb_values32(const TbWarpSm& W, const unsigned* vp, const float* cg, const float* plain, int lane, int nk, float (&acc)[8][8]) {
+  int wi[8], sh[8], ln[8];
   #pragma unroll
   for (int w = 0; w < 8; ++w) {
-    const int d = 32 * w + lane, endb = R.kb * (d + 1), first = R.kb * (d & ~63);
-    const int lo = R.mode == 1 ? endb - 4 : max(endb - 8, first), len = endb - lo;
-    const unsigned hiw = s_w[lo >> 5], low = s_w[(lo >> 5) + 1];
-    const unsigned v = __funnelshift_l(low, hiw, lo & 31) >> (32 - len);
-    float xv = __fmul_rn(T.cg[v], s);
-    if (R.m > 0) xv = __fadd_rn(xv, __fmul_rn(c0, T.u0[d]));
-    if (R.m > 1) xv = __fadd_rn(xv, __fmul_rn(c1, T.u1[d]));
-    if (R.has_mu) xv = __fadd_rn(xv, T.mu[d]);
-    x[w] = xv;
+    const int d = 32 * w + lane, endb = KB * (d + 1), first = KB * (d & ~63), lo = FLAT ? endb - 4 : max(endb - 8, first);
+    wi[w] = lo >> 5; sh[w] = lo & 31; ln[w] = 32 - (endb - lo);
+  }
+  #pragma unroll 2
+  for (int j = 0; j < nk; ++j) {
+    const float4 pa = *reinterpret_cast<const float4*>(&W.pw[j][0]), pb = *reinterpret_cast<const float4*>(&W.pw[j][4]);
+    const float pg[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+    const unsigned* row = vp + j * TBA_PW;
+    const bool pl = W.vplain[j] != 0;                                // warp-uniform: a row the profile leaves unpacked
+    #pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      float x;
+      if (pl) x = plain ? __ldg(plain + (size_t)j * 256 + 32 * w + lane) : 0.f;
+      else x = cg[__funnelshift_l(row[wi[w] + 1], row[wi[w]], sh[w]) >> ln[w]];
+      #pragma unroll
+      for (int g = 0; g < 8; ++g) acc[g][w] = fmaf(pg[g], x, acc[g][w]);
+    }
   }
 }
 
 template <int DT>
-__global__ void __launch_bounds__(TBA_WARPS * 32) tb_attn_kernel(TbAttnP P) {
+__global__ void __launch_bounds__(TBA_WARPS * 32) tb_attn32_kernel(TbAttnP P) {
   extern __shared__ __align__(16) unsigned char tba_smem[];
   const yskn_tb_attn_args& A = P.a;
   const int G = P.G, split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   TbTab* tk = reinterpret_cast<TbTab*>(tba_smem); TbTab* tv = tk + 1;
-  unsigned* s_w = reinterpret_cast<unsigned*>(tv + 1) + 44 * warp;
-  float* mbuf = reinterpret_cast<float*>(reinterpret_cast<unsigned*>(tv + 1) + 44 * TBA_WARPS);    // [warp][8][258]
+  float (*q)[8] = reinterpret_cast<float (*)[8]>(tv + 1);            // [256][8]: q * qscale * log2(e), heads past G are zero
+  float (*kq)[8] = q + 256;                                           // [3][8]: q.U0, q.U1, q.mu of the key group
+  TbWarpSm* Wall = reinterpret_cast<TbWarpSm*>(kq + 4);
+  TbWarpSm& W = Wall[warp];
+  float* mbuf = reinterpret_cast<float*>(Wall);                       // [warp][8][258], takes the staging area's place after the loop
   const TbRule rk = tb_stage_group(A.blob, __ldg(A.grp_k + kvh), *tk), rv = tb_stage_group(A.blob, __ldg(A.grp_v + kvh), *tv);
+  const float qs = A.qscale * 1.4426950408889634f;
+  for (int e = threadIdx.x; e < 256 * 8; e += TBA_WARPS * 32) {
+    const int d = e >> 3, g = e & 7;
+    q[d][g] = g < G ? act_load<DT>(A.q16, ((size_t)r * A.nh + kvh * G + g) * 256 + d) * qs : 0.f;
+  }
+  __syncthreads();
+  if (threadIdx.x < 24) {
+    const int which = threadIdx.x >> 3, g = threadIdx.x & 7;
+    const float* vec = which == 0 ? tk->u0 : (which == 1 ? tk->u1 : tk->mu);
+    float a = 0.f;
+    for (int d = 0; d < 256; ++d) a = fmaf(q[d][g], vec[d], a);
+    kq[which][g] = a;
+  }
   __syncthreads();
   const int pos = __ldg(A.d_pos) + r, len = max(0, min(pos + 1, A.max_ctx));
   const int per = (len + (int)gridDim.x - 1) / (int)gridDim.x, t0 = min(len, split * per), t1 = min(len, t0 + per);
-  const float qs = A.qscale * 1.4426950408889634f;
-  float q[8][8], acc[8][8], m[8], l[8];
+  const size_t row0 = (size_t)kvh * A.max_ctx;
+  const int psw = A.pay_stride / 4, nwk = 8 * rk.kb, nwv = 8 * rv.kb;
+  float acc[8][8], m[8], l[8], a0[8], a1[8], am[8];
   #pragma unroll
   for (int g = 0; g < 8; ++g) {
-    m[g] = -1e30f; l[g] = 0.f;
+    m[g] = -1e30f; l[g] = a0[g] = a1[g] = am[g] = 0.f;
     #pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      acc[g][w] = 0.f;
-      q[g][w] = g < G ? act_load<DT>(A.q16, ((size_t)r * A.nh + kvh * G + g) * 256 + 32 * w + lane) * qs : 0.f;
-    }
+    for (int w = 0; w < 8; ++w) acc[g][w] = 0.f;
   }
-  const size_t row0 = (size_t)kvh * A.max_ctx;
-  for (int t = t0 + warp; t < t1; t += TBA_WARPS) {
-    float x[8];
-    tb_row(rk, *tk, t, A.k_pay + (row0 + t) * A.pay_stride, A.k_side + 2 * (row0 + t), A.k_plain ? A.k_plain + (row0 + t) * 256 : nullptr, s_w, lane, x);
+  // payload rows of 32 keys into staging buffer `b`, asynchronously (4-byte copies: the padded row stride is not a multiple of 16)
+  auto stage = [&](int tc, int b) {
+    const int nk = min(32, t1 - tc);
+    const unsigned* kw = reinterpret_cast<const unsigned*>(A.k_pay) + (row0 + tc) * psw;
+    const unsigned* vw = reinterpret_cast<const unsigned*>(A.v_pay) + (row0 + tc) * psw;
+    for (int idx = lane; idx < nk * 40; idx += 32) {
+      const int rr = idx / 40, i = idx - 40 * rr;
+      if (i < nwk) tb_cp4(&W.kp[b][rr * TBA_PW + i], kw + (size_t)rr * psw + i); else W.kp[b][rr * TBA_PW + i] = 0u;
+      if (i < nwv) tb_cp4(&W.vp[b][rr * TBA_PW + i], vw + (size_t)rr * psw + i); else W.vp[b][rr * TBA_PW + i] = 0u;
+    }
+    if (lane < nk) { W.kp[b][lane * TBA_PW + 40] = 0u; W.vp[b][lane * TBA_PW + 40] = 0u; }
+  };
+  int buf = 0;
+  if (t0 + 32 * warp < t1) stage(t0 + 32 * warp, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int tc = t0 + 32 * warp; tc < t1; tc += 32 * TBA_WARPS, buf ^= 1) {
+    const int nk = min(32, t1 - tc);
+    __syncwarp();                                                    // every lane is done with the other buffer
+    if (tc + 32 * TBA_WARPS < t1) stage(tc + 32 * TBA_WARPS, buf ^ 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");           // this step's rows have landed (this lane's copies)
+    __syncwarp();                                                    // ... and every other lane's
+    const int t = tc + lane;
+    const bool live = lane < nk, kpk = rk.packed_ok && t >= rk.guard, vpk = rv.packed_ok && t >= rv.guard;
+    float sk = 0.f, c0k = 0.f, c1k = 0.f, sv = 1.f, c0v = 0.f, c1v = 0.f;
+    if (live && kpk) {
+      sk = __uint_as_float(__ldg(A.k_side + 2 * (row0 + t))); const unsigned pc = __ldg(A.k_side + 2 * (row0 + t) + 1);
+      c0k = rk.m > 0 ? __half2float(__ushort_as_half((unsigned short)(pc & 0xffffu))) : 0.f;
+      c1k = rk.m > 1 ? __half2float(__ushort_as_half((unsigned short)(pc >> 16))) : 0.f;
+    }
+    if (live && vpk) {
+      sv = __uint_as_float(__ldg(A.v_side + 2 * (row0 + t))); const unsigned pc = __ldg(A.v_side + 2 * (row0 + t) + 1);
+      c0v = rv.m > 0 ? __half2float(__ushort_as_half((unsigned short)(pc & 0xffffu))) : 0.f;
+      c1v = rv.m > 1 ? __half2float(__ushort_as_half((unsigned short)(pc >> 16))) : 0.f;
+    }
+    float dot[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const unsigned* myrow = W.kp[buf] + lane * TBA_PW;
+    if (rk.mode == 1) tb_scores32<4, true>(myrow, tk->cg, q, dot);
+    else if (rk.kb == 3) tb_scores32<3, false>(myrow, tk->cg, q, dot);
+    else if (rk.kb == 4) tb_scores32<4, false>(myrow, tk->cg, q, dot);
+    else tb_scores32<5, false>(myrow, tk->cg, q, dot);
     float sc[8];
     #pragma unroll
-    for (int g = 0; g < 8; ++g) {
-      float d = 0.f;
-      if (g < G) {
-        #pragma unroll
-        for (int w = 0; w < 8; ++w) d = fmaf(q[g][w], x[w], d);
-        #pragma unroll
-        for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    for (int g = 0; g < 8; ++g) sc[g] = fmaf(sk, dot[g], fmaf(c0k, kq[0][g], fmaf(c1k, kq[1][g], kq[2][g])));
+    if (live && !kpk) {                                              // a key row the profile leaves unpacked: the plain row
+      #pragma unroll
+      for (int g = 0; g < 8; ++g) sc[g] = 0.f;
+      if (A.k_plain) {
+        const float* pr = A.k_plain + (row0 + t) * 256;
+        for (int d = 0; d < 256; ++d) {
+          const float x = __ldg(pr + d);
+          #pragma unroll
+          for (int g = 0; g < 8; ++g) sc[g] = fmaf(q[d][g], x, sc[g]);
+        }
       }
-      sc[g] = d;
     }
-    tb_row(rv, *tv, t, A.v_pay + (row0 + t) * A.pay_stride, A.v_side + 2 * (row0 + t), A.v_plain ? A.v_plain + (row0 + t) * 256 : nullptr, s_w, lane, x);
+    W.vplain[lane] = vpk ? 0 : 1;
     #pragma unroll
     for (int g = 0; g < 8; ++g) {
-      if (g >= G) continue;
-      if (sc[g] > m[g]) {                                            // warp-uniform: the score is the same in every lane
-        const float a = exp2f(m[g] - sc[g]);
-        l[g] *= a;
-        #pragma unroll
-        for (int w = 0; w < 8; ++w) acc[g][w] *= a;
-        m[g] = sc[g];
-      }
-      const float p = exp2f(sc[g] - m[g]);
-      l[g] += p;
+      if (g >= G) { W.pw[lane][g] = 0.f; continue; }
+      float mx = live ? sc[g] : -1e30f;
       #pragma unroll
-      for (int w = 0; w < 8; ++w) acc[g][w] = fmaf(p, x[w], acc[g][w]);
+      for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float mn = fmaxf(m[g], mx), al = exp2f(m[g] - mn), p = live ? exp2f(sc[g] - mn) : 0.f;
+      float s0 = p, s1 = p * c0v, s2 = p * c1v, s3 = vpk ? p : 0.f;
+      #pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        s0 += __shfl_xor_sync(0xffffffffu, s0, o); s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o); s3 += __shfl_xor_sync(0xffffffffu, s3, o);
+      }
+      l[g] = fmaf(l[g], al, s0); a0[g] = fmaf(a0[g], al, s1); a1[g] = fmaf(a1[g], al, s2); am[g] = fmaf(am[g], al, s3); m[g] = mn;
+      #pragma unroll
+      for (int w = 0; w < 8; ++w) acc[g][w] *= al;
+      W.pw[lane][g] = p * sv;
     }
+    __syncwarp();
+    const float* vpl = A.v_plain ? A.v_plain + (row0 + tc) * 256 : nullptr;
+    if (rv.mode == 1) tb_values32<4, true>(W, W.vp[buf], tv->cg, vpl, lane, nk, acc);
+    else if (rv.kb == 3) tb_values32<3, false>(W, W.vp[buf], tv->cg, vpl, lane, nk, acc);
+    else if (rv.kb == 4) tb_values32<4, false>(W, W.vp[buf], tv->cg, vpl, lane, nk, acc);
+    else tb_values32<5, false>(W, W.vp[buf], tv->cg, vpl, lane, nk, acc);
   }
-  // ---- merge the warps and store the split's partial (natural-log m, as the merge kernel expects)
+  // ---- the row terms of the value group, then the merge of the warps (natural-log m, as the merge kernel expects)
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();                                                   // the staging area becomes the merge buffer
   #pragma unroll
   for (int g = 0; g < 8; ++g) {
     if (g >= G) continue;
     float* wb = mbuf + ((size_t)warp * 8 + g) * 258;
     if (lane == 0) { wb[0] = m[g]; wb[1] = l[g]; }
     #pragma unroll
-    for (int w = 0; w < 8; ++w) wb[2 + 32 * w + lane] = acc[g][w];
+    for (int w = 0; w < 8; ++w) {
+      const int d = 32 * w + lane;
+      wb[2 + d] = fmaf(a0[g], tv->u0[d], fmaf(a1[g], tv->u1[d], fmaf(am[g], tv->mu[d], acc[g][w])));
+    }
   }
   __syncthreads();
   for (int e = threadIdx.x; e < G * 256; e += TBA_WARPS * 32) {
@@ -507,19 +598,20 @@ int launch_tb_attention(const yskn_tb_attn_args& a, int act_dtype, cudaStream_t 
   if (a.kvh <= 0 || a.nh <= 0 || a.nh % a.kvh || a.nh / a.kvh > 8 || a.M <= 0 || a.M > 65535 || a.kvh > 65535 || a.splits <= 0 || a.max_ctx <= 0)
     KV4_REJECT("yskn_tb_attention: bad shape (kvh %d, nh %d, M %d, splits %d, max_ctx %d): at most 8 query heads per kv-head", a.kvh, a.nh, a.M, a.splits, a.max_ctx);
   if (a.pay_stride < 160 || a.pay_stride % 4 || (((uintptr_t)a.k_pay | (uintptr_t)a.v_pay) & 3)) KV4_REJECT("yskn_tb_attention: bad payload stride %d or alignment", a.pay_stride);
-  const size_t smem = 2 * sizeof(TbTab) + 44 * TBA_WARPS * 4 + (size_t)TBA_WARPS * 8 * 258 * 4;
+  const size_t stage = sizeof(TbWarpSm) * TBA_WARPS, merge = (size_t)TBA_WARPS * 8 * 258 * 4;
+  const size_t smem = 2 * sizeof(TbTab) + (256 + 4) * 8 * 4 + (stage > merge ? stage : merge);
   TbAttnP P{a, a.nh / a.kvh};
   const dim3 grid(a.splits, a.kvh, a.M);
   if (act_dtype == YSKN_KV4_BF16) {
     static std::atomic<unsigned long long> attr{0};
-    if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(tb_attn_kernel<YSKN_KV4_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    tb_attn_kernel<YSKN_KV4_BF16><<<grid, TBA_WARPS * 32, smem, st>>>(P);
+    if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(tb_attn32_kernel<YSKN_KV4_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tb_attn32_kernel<YSKN_KV4_BF16><<<grid, TBA_WARPS * 32, smem, st>>>(P);
   } else if (act_dtype == YSKN_KV4_F16) {
     static std::atomic<unsigned long long> attr{0};
-    if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(tb_attn_kernel<YSKN_KV4_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    tb_attn_kernel<YSKN_KV4_F16><<<grid, TBA_WARPS * 32, smem, st>>>(P);
+    if (first_use_on_device(attr)) KV4_CUDA(cudaFuncSetAttribute(tb_attn32_kernel<YSKN_KV4_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tb_attn32_kernel<YSKN_KV4_F16><<<grid, TBA_WARPS * 32, smem, st>>>(P);
   } else KV4_REJECT("yskn_tb_attention: q16 is bf16 or fp16 (act_dtype %d)", act_dtype);
-  return launch_status("tb_attn_kernel");
+  return launch_status("tb_attn32_kernel");
 }
 
 }  // namespace kv4
