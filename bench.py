@@ -707,7 +707,7 @@ def run_secondary(args):
         byt = kvh * ctx * 2 * (128 + 8)                                # 4-bit payload (128 B of the 160-B row slot) + side words, K and V
         line = dict(base, metric="tb_decode_attn_tokens_per_s", value=1.0 / t, unit="tokens/s", ms_per_step=t * 1e3, dtype="f32",
                     config={"workload": f"Family-B decode over packed trellis rows (4 bits): 1 query token, Hq{nh}/Hkv{kvh}/hd256, {ctx} cached tokens",
-                            "splits": S, "l2": f"2 cache copies cycled; {byt / 1e6:.1f} MB read per launch: L2-resident, the kernel is bound by shared-memory traffic"},
+                            "splits": S, "l2": f"2 cache copies cycled; {byt / 1e6:.1f} MB read per launch: L2-resident, the kernel is latency-bound"},
                     gpu_launches=K,
                     roofline={"bound": "hbm", "achieved": byt / t / 1e9, "peak": hbm, "unit": "GB/s", "frac": byt / t / 1e9 / hbm, "traffic": None,
                               "kernel": "tb_attn32_kernel", "bytes_per_launch": byt, "peak_kind": f"of {kind}"})

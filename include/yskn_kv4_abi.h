@@ -351,7 +351,7 @@ YSKN_KV4_API int yskn_tb_encode(const uint8_t* d_blob, int nm, const float* d_x,
  * of each head's rows; rows the profile leaves unpacked (position below the group's guard, or a group that is not a
  * packed one) are read from k_plain / v_plain fp32 [kvh][max_ctx][256] (NULL: zeros), the `yin` of yskn_tb_decode.
  * q16 [M][nh][256] bf16 or fp16; row r sits at *d_pos + r and sees keys 0 .. *d_pos + r; partials in the layout of
- * yskn_kv8_attention (merge with yskn_kv8_combine).  A CUDA-core kernel (32 keys per warp step, payload rows staged by asynchronous copies): a first path, far from the memory roofline. */
+ * yskn_kv8_attention (merge with yskn_kv8_combine).  A CUDA-core kernel (32 keys per warp step, payload rows staged by asynchronous copies): a first path, far from the memory roofline (latency-bound). */
 typedef struct {
   const uint16_t* q16; const uint8_t* blob;
   const uint8_t* k_pay; const uint8_t* v_pay; int pay_stride;
