@@ -36,6 +36,11 @@ def test_struct_layouts_match_the_reference_structs():
     assert _lib.AttnGCombineArgsC.splits.offset == 24 and _lib.AttnGCombineArgsC.bv.offset == 32
     assert _lib.AttnGCombineArgsC.g.offset == 60 and ctypes.sizeof(_lib.AttnGCombineArgsC) == 64
     assert _lib.KvQuantArgsC.d_pos.offset == 56 and ctypes.sizeof(_lib.KvQuantArgsC) == 72
+    # this library's own structs: the ctypes mirrors against the C compiler's layout of include/yskn_kv4_abi.h
+    assert _lib.KvxAttnPostArgsC.d_pos.offset == 48 and _lib.KvxAttnPostArgsC.q16.offset == 72 and _lib.KvxAttnPostArgsC.pm.offset == 132
+    assert ctypes.sizeof(_lib.KvxAttnPostArgsC) == 136
+    assert _lib.TbAttnArgsC.k_side.offset == 40 and _lib.TbAttnArgsC.d_pos.offset == 96 and _lib.TbAttnArgsC.qscale.offset == 144
+    assert ctypes.sizeof(_lib.TbAttnArgsC) == 152
 
 
 def test_argument_rejection_needs_no_gpu():
@@ -43,3 +48,9 @@ def test_argument_rejection_needs_no_gpu():
     assert L.yskn_kv4_set_algo(99) == -1 and b"unknown algorithm" in L.yskn_kv4_last_error()
     assert L.yskn_kv4_attention(None, 6, 256, 64, 0, None) == -1 and b"null argument" in L.yskn_kv4_last_error()
     assert L.yskn_kv4_rope_table(None, 64, 1e6, 64, None) == -1
+    assert L.yskn_kvx_attn_post(None, None) == -1 and b"null argument" in L.yskn_kv4_last_error()
+    assert L.yskn_tb_attention(None, 0, None) == -1 and b"null argument" in L.yskn_kv4_last_error()
+    bad = _lib.KvxAttnPostArgsC()
+    assert L.yskn_kvx_attn_post(ctypes.byref(bad), None) == 0          # M = 0: nothing to do
+    bad.M = 1
+    assert L.yskn_kvx_attn_post(ctypes.byref(bad), None) == -1 and b"null buffer" in L.yskn_kv4_last_error()
