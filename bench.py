@@ -317,12 +317,19 @@ def run_ours(args, rank, world, local_rank):
             d.d_lpos.fill_(ctx - 1 - plan.start)
 
         def e2e_body(d):                                           # host buffers in, the step, host buffer out
-            in_dev.copy_(in_host, non_blocking=True)
+            # the copies to and from pinned host memory: by the library's copy kernel (yskn_kv4_copy), or as memcpy nodes
+            if args.e2e_copies == "kernel":
+                kv4.copy_small(in_dev, in_host)
+            else:
+                in_dev.copy_(in_host, non_blocking=True)
             if plan.is_last:
                 kv4.launch_kv_append(d.layer, kn_dev, vn_dev, d.d_lpos, 1)
             step(d)
             if rank == 0:
-                o_host.copy_(d.o16, non_blocking=True)
+                if args.e2e_copies == "kernel":
+                    kv4.copy_small(o_host, d.o16)
+                else:
+                    o_host.copy_(d.o16, non_blocking=True)
 
         # the whole step, copies included, is one captured graph per cache copy (the copies become memcpy nodes that run on
         # every replay); the host waits for the result after each step, as a caller that samples the next token would
@@ -363,7 +370,8 @@ def run_ours(args, rank, world, local_rank):
                 "cache_copies": n_copies, "mb_read_per_launch": shard_bytes / 1e6, "kv_tokens_scanned_per_s": ctx * value},
         "clocks": clocks,
         "e2e": {"value": K / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(q_host.numel() * 2 + (kn_host.numel() + vn_host.numel()) * 2),
-                "d2h_bytes_per_step": int(o_host.numel() * 2), "ms_per_step": ms_e2e / K},
+                "d2h_bytes_per_step": int(o_host.numel() * 2), "ms_per_step": ms_e2e / K,
+                "copies": "yskn_kv4_copy kernel nodes from / to pinned host memory" if args.e2e_copies == "kernel" else "cudaMemcpyAsync nodes from / to pinned host memory"},
         "gpu_launches": launches_per_step * K,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                      "kernel": "decode attention (split-K partials)", "us_per_launch": t_attn * 1e6, "bytes_per_launch": shard_bytes,
@@ -759,6 +767,8 @@ def main():
     ap.add_argument("--no-early", action="store_true", help="do not set the `early` flag of yskn_kv4_attn_ext on the decode launches")
     ap.add_argument("--no-secondary", action="store_true", help="skip the device-timed figures of the other contexts and kernels (`secondary`)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="N > 1: how the shards' (m, l, O) triples travel")
+    ap.add_argument("--e2e-copies", default="kernel", choices=["kernel", "memcpy"],
+                    help="end-to-end step: host<->device copies by the library's copy kernel (default) or by cudaMemcpyAsync nodes")
     ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch from an ncu capture, if known")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "verify", "kv8", "kvx"],
                     help="decode = the headline metric (default); the others time the remaining kernels of the path on one GPU")

@@ -93,6 +93,13 @@ YSKN_KV4_API int yskn_kv4_device_status(int* status);
 /* launch_rope_table_g, src/attention_gqa.cu:158-167. */
 YSKN_KV4_API int yskn_kv4_rope_table(float* d_out, int max_ctx, float theta, int rd, void* cuda_stream);
 
+/* No counterpart in the reference (its engine keeps activations on the device).  A copy by a kernel for the few kilobytes a
+ * decode step exchanges with the host -- the query and the new token's K / V rows in, the attention rows out: dst and src
+ * are device pointers or pinned host memory (cudaHostAlloc / cudaHostRegister: device-accessible under unified addressing);
+ * bytes and both addresses multiples of 16, at most 64 MiB.  Enqueue-only and graph-capturable like every launcher; in a
+ * captured pass it replaces a memcpy node of about 6 us by a kernel node of about 2.  Host memory is read past the caches. */
+YSKN_KV4_API int yskn_kv4_copy(void* dst, const void* src, size_t bytes, void* cuda_stream);
+
 /* K shadow store + per-token V int4 (src/post_kernels.cu:48-82) followed by the group quant of every
  * 32-token K group completed by rows [*d_pos, *d_pos+M) (launch_kv_group_quant_g, src/attention_gqa.cu:182-187). */
 YSKN_KV4_API int yskn_kv4_append(const yskn_kv_append_args* a, void* cuda_stream);

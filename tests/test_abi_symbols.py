@@ -48,6 +48,8 @@ def test_argument_rejection_needs_no_gpu():
     assert L.yskn_kv4_set_algo(99) == -1 and b"unknown algorithm" in L.yskn_kv4_last_error()
     assert L.yskn_kv4_attention(None, 6, 256, 64, 0, None) == -1 and b"null argument" in L.yskn_kv4_last_error()
     assert L.yskn_kv4_rope_table(None, 64, 1e6, 64, None) == -1
+    assert L.yskn_kv4_copy(None, None, 0, None) == 0 and L.yskn_kv4_copy(None, None, 16, None) == -1
+    assert L.yskn_kv4_copy(ctypes.c_void_p(16), ctypes.c_void_p(32), 24, None) == -1 and b"multiples of 16" in L.yskn_kv4_last_error()
     assert L.yskn_kvx_attn_post(None, None) == -1 and b"null argument" in L.yskn_kv4_last_error()
     assert L.yskn_tb_attention(None, 0, None) == -1 and b"null argument" in L.yskn_kv4_last_error()
     bad = _lib.KvxAttnPostArgsC()

@@ -138,3 +138,27 @@ def test_projection_input_transform_is_bit_exact(oracle):
     assert np.array_equal(qx.cpu().numpy(), want_q)
     assert np.array_equal(alpha.cpu().numpy().view(np.uint32), want_a.view(np.uint32))
     assert float(alpha[2, 1]) == 0.0 and not qx[2, 512:1024].any()
+
+
+def test_copy_kernel_moves_small_buffers_between_pinned_host_memory_and_the_device():
+    """yskn_kv4_copy: host -> device -> host by kernels, also as nodes of a captured graph that is replayed after the host
+    buffer changed (host memory is read past the caches); misaligned sizes are rejected."""
+    from yasakani_b200 import kv4, Kv4Error
+    h = torch.randn(8192, generator=torch.Generator().manual_seed(9)).half().pin_memory()
+    d = torch.empty(8192, dtype=torch.float16, device="cuda")
+    back = torch.zeros(8192, dtype=torch.float16).pin_memory()
+    kv4.copy_small(d, h); kv4.copy_small(back, d)
+    torch.cuda.synchronize()
+    assert torch.equal(back, h) and torch.equal(d.cpu(), h)
+    g, s = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            kv4.copy_small(d, h); kv4.copy_small(back, d)
+    for i in range(3):
+        h.fill_(float(i + 1))
+        g.replay(); torch.cuda.synchronize()
+        assert float(back[5]) == i + 1 and float(back[-1]) == i + 1
+    with pytest.raises(Kv4Error, match="multiples of 16"):
+        kv4.copy_small(d[:3], h[:3])
+    with pytest.raises(ValueError, match="pinned"):
+        kv4.copy_small(d, torch.zeros(8192, dtype=torch.float16))

@@ -77,6 +77,7 @@ PROTOTYPES = {
     "yskn_kv4_set_algo": (C.c_int, [C.c_int]),
     "yskn_kv4_device_status": (C.c_int, [C.POINTER(C.c_int)]),
     "yskn_kv4_rope_table": (C.c_int, [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "yskn_kv4_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "yskn_kv4_append": (C.c_int, [C.POINTER(KvAppendArgsC), C.c_void_p]),
     "yskn_kv4_group_quant": (C.c_int, [C.POINTER(KvQuantArgsC), C.c_int, C.c_int, C.c_void_p]),
     "yskn_kv4_attention": (C.c_int, [C.POINTER(AttnGArgsC), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),

@@ -153,6 +153,10 @@ int yskn_kv4_prefill_tc(const yskn_attn_g_args* a, int g, int hd, int rd, int ac
   return launch_combine(c, hd, act_dtype, (cudaStream_t)cuda_stream);
 }
 
+int yskn_kv4_copy(void* dst, const void* src, size_t bytes, void* cuda_stream) {
+  return launch_copy16(dst, src, bytes, (cudaStream_t)cuda_stream);
+}
+
 int yskn_kv4_rope_table(float* d_out, int max_ctx, float theta, int rd, void* cuda_stream) {
   return launch_rope_table(d_out, max_ctx, theta, rd, (cudaStream_t)cuda_stream);
 }

@@ -153,7 +153,25 @@ template <int HD, bool FUSE> int append_dt(const yskn_kv_append_args& a, cudaStr
   return launch_status("kv4_append_rows_kernel");
 }
 
+// A copy by a kernel, for the few kilobytes a decode step exchanges with the host: either side may be pinned (mapped) host
+// memory.  Inside a captured pass a kernel node of this size runs in about 2 us where a memcpy node takes about 6.  Host
+// memory is read past the caches (ld.global.cv), so a replayed graph sees what the host wrote since the last replay.
+__global__ void __launch_bounds__(256) kv4_copy16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n16) {
+  const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+  if (i < n16) dst[i] = __ldcv(src + i);
+}
+
 }  // namespace
+
+int launch_copy16(void* dst, const void* src, size_t bytes, cudaStream_t st) {
+  if (bytes == 0) return 0;
+  if (!dst || !src) KV4_REJECT("yskn_kv4_copy: null buffer");
+  if ((bytes & 15) || (((uintptr_t)dst | (uintptr_t)src) & 15)) KV4_REJECT("yskn_kv4_copy: %zu bytes: size and both addresses must be multiples of 16", bytes);
+  if (bytes > ((size_t)1 << 26)) KV4_REJECT("yskn_kv4_copy: %zu bytes: meant for small buffers (at most 64 MiB)", bytes);
+  const size_t n16 = bytes / 16;
+  kv4_copy16_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), n16);
+  return launch_status("kv4_copy16_kernel");
+}
 
 int launch_rope_table(float* d_out, int max_ctx, float theta, int rd, cudaStream_t st) {
   if (!d_out || max_ctx <= 0 || rd <= 0 || (rd & 1)) KV4_REJECT("yskn_kv4_rope_table: bad arguments (max_ctx %d, rd %d)", max_ctx, rd);

@@ -93,6 +93,7 @@ int merge_status_fetch(int* out);
 void set_peer_wait_polls(unsigned polls);
 
 // Family-B row codec, step 1 (kvx_codec.cu)
+int launch_copy16(void* dst, const void* src, size_t bytes, cudaStream_t st);
 int launch_kvx_rotate(const float* x, float* y, long long rows, int inverse, cudaStream_t st);
 int launch_kvx_encode(const void* x, int x_dtype, int8_t* q8, float* scales, long long rows, cudaStream_t st);
 int launch_kvx_decode(const int8_t* q8, const float* scales, void* y, int y_dtype, long long rows, cudaStream_t st);

@@ -326,3 +326,14 @@ def launch_exchange_merge(pm, pl, pacc, splits: int, M: int, nh: int, g: int, hd
 
 def default_qscale(hd: int) -> float:
     return 1.0 / math.sqrt(hd)
+
+
+def copy_small(dst: torch.Tensor, src: torch.Tensor, stream=None) -> None:
+    """yskn_kv4_copy: dst <- src by a kernel; either tensor may live in pinned host memory.  Sizes and addresses multiples of 16."""
+    nbytes = src.numel() * src.element_size()
+    if nbytes != dst.numel() * dst.element_size() or not (src.is_contiguous() and dst.is_contiguous()):
+        raise ValueError("copy_small: contiguous tensors of equal size")
+    for t in (dst, src):
+        if not (t.is_cuda or t.is_pinned()):
+            raise ValueError("copy_small: host tensors must be pinned")
+    check(_lib.load().yskn_kv4_copy(dst.data_ptr(), src.data_ptr(), nbytes, _stream(stream)), "yskn_kv4_copy")
